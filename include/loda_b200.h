@@ -1,0 +1,195 @@
+/*
+ * loda_b200 — C ABI of the B200 (sm_100a) decode hot path of LoDA-SA / NFA
+ * two-level sparse attention: paged KV append with page metadata and packed
+ * 4-bit tail keys, L1 page scoring + top-k, L2 token scoring + top-k + union,
+ * split-K gather attention.
+ *
+ * Conventions (they mirror what the reference's CUDA-graph decode requires of
+ * its operators, sparse_attn/indexer/nfa_layer_batch_selector.py:2769-2783 and
+ * sparse_attn/engine/graph_runner.py:78-133):
+ *   - every pointer is a DEVICE pointer owned by the caller, at a fixed address
+ *     for the lifetime of a captured graph; the library allocates nothing;
+ *   - calls are stream-ordered on `stream` (a cudaStream_t passed as void*),
+ *     never synchronise the host and never copy to the host;
+ *   - lengths, block tables, slot mappings and request ids are read on the
+ *     device at run time, so a captured call can be replayed after they change;
+ *   - functions return 0 on success and a negative code on an argument error
+ *     (loda_last_error() gives the message); kernels never trap: a row that
+ *     cannot be processed produces an empty selection / zero output and sets a
+ *     bit in the optional device status word.
+ */
+#ifndef LODA_B200_H_
+#define LODA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LODA_DTYPE_BF16 0
+#define LODA_DTYPE_FP32 1
+
+#define LODA_OK 0
+#define LODA_ERR_ARGUMENT (-1)
+#define LODA_ERR_UNSUPPORTED (-2)
+#define LODA_ERR_LAUNCH (-3)
+
+/* device status word bits (sparse_attn/ops/eager_decoding.py:7-35 keeps the
+ * same "deferred error flag" convention) */
+#define LODA_STATUS_BAD_SLOT 1u
+#define LODA_STATUS_BAD_PAGE 2u
+#define LODA_STATUS_TRUNCATED 4u
+
+/* Static geometry of one attention layer's cache and selector.
+ * Mirrors GraphReadyPagedRegionCache.__init__ (sparse_attn/cache/
+ * paged_region_cache.py:128-244), RegionGeometry (sparse_attn/policies/
+ * region_geometry.py:5-23) and the NFAIndexer constants
+ * (sparse_attn/indexer/nfa_indexer.py:28-121). */
+typedef struct loda_geometry {
+  int32_t dtype;          /* LODA_DTYPE_*: KV pool, query and output dtype */
+  int32_t num_q_heads;
+  int32_t num_kv_heads;
+  int32_t head_dim;       /* K head dim */
+  int32_t head_dim_v;
+  int32_t sub_dims;       /* d': size of the scoring subspace (multiple of 16) */
+  int32_t sub_lo0;        /* subspace = [sub_lo0, sub_lo0 + d'/2) U          */
+  int32_t sub_lo1;        /*            [sub_lo1, sub_lo1 + d'/2)            */
+  int32_t page;           /* tokens per page == selector block size */
+  int32_t num_pages;      /* physical pages including the trailing PAD page */
+  int32_t max_blocks;     /* block-table row length (logical pages per request) */
+  int32_t max_requests;
+  int32_t max_query_tokens; /* most batch rows / query rows of one call */
+  int32_t max_visible;    /* row length of the gather list */
+  int32_t k_far;          /* far pages kept by L1  (level1_topk - near_pages) */
+  int32_t k_near;         /* near pages kept by L1 */
+  int32_t level2_topk;    /* K2: token budget including sink and window */
+  int32_t sink;
+  int32_t swa;            /* sliding window, a multiple of `page` */
+  int32_t near_len;       /* region geometry `near` */
+  int32_t pool_near_len;  /* near candidate-pool span in tokens */
+} loda_geometry;
+
+/* Per-layer device buffers.
+ *   pool_k / pool_v  [num_pages, num_kv_heads, page, head_dim(_v)]   (the
+ *        reference arena [pages+1, 1, Hkv, PAGE, D], paged_region_cache.py:89-98)
+ *   page_mm   [max_requests, num_kv_heads, max_blocks, 2, d']  per logical page:
+ *        min then max of the subspace keys over the visible tokens
+ *   page_sum  [max_requests, num_kv_heads, max_blocks, d']     sum of the same
+ *        (replace P_MIN / P_MAX / P_SUM, nfa_layer_batch_selector.py:2103-2118)
+ *   tail_code [num_pages, num_kv_heads, page, d'/2] bytes: two 4-bit codes per
+ *        byte, dim 2i in the low nibble
+ *   tail_sz   [num_pages, num_kv_heads, page, 2]: quantisation scale and zero
+ *   block_table [max_requests, max_blocks] int32 logical -> physical page      */
+typedef struct loda_layer {
+  void* pool_k;
+  void* pool_v;
+  void* page_mm;
+  void* page_sum;
+  uint8_t* tail_code;
+  void* tail_sz;
+  const int32_t* block_table;
+} loda_layer;
+
+/* Per-step batch metadata (paged_region_cache.py:214-231). */
+typedef struct loda_batch {
+  int32_t batch;                  /* rows in this step */
+  const int32_t* lengths;         /* [batch] length including the current token */
+  const int64_t* valid_req_ids;   /* [batch] request slot of each row (pad rows: 0) */
+  const int64_t* active_req_ids;  /* [batch] < 0 marks a padding row */
+} loda_batch;
+
+/* Selection outputs (workspace tensors of the reference selector).
+ *   i_far [batch, Hkv, k_far], i_near [batch, Hkv, k_near]: page ids, best first;
+ *   n_far / n_near [batch, Hkv]: how many leading entries carry a finite score
+ *   gather [>=batch, Hkv, max_visible] physical slots in ascending logical order
+ *   visible_lens [>=batch, Hkv]
+ *   middle / middle_counts (optional, may be NULL): the L2 survivors as logical
+ *   token ids [batch, Hkv, level2_topk] before the union                        */
+typedef struct loda_selection {
+  int32_t* i_far;
+  int32_t* n_far;
+  int32_t* i_near;
+  int32_t* n_near;
+  int32_t* gather;
+  int32_t* visible_lens;
+  int32_t* middle;
+  int32_t* middle_counts;
+} loda_selection;
+
+const char* loda_version(void);
+const char* loda_last_error(void);
+
+/* Scratch bytes needed by the calls below (sized by g->max_query_tokens).  The
+ * scratch must be zero-filled once before first use; kernels leave it zeroed
+ * where that matters.  Returns 0 if the geometry is not supported. */
+size_t loda_workspace_bytes(const loda_geometry* g);
+
+/* Append one decode token per row: K/V rows into the pool, packed 4-bit tail
+ * key of the token, and min/max/sum of its logical page.
+ * Replaces paged_write_decode (sparse_attn/ops/paged_region_kernels.py:665-724)
+ * and the fused owner write + page-stats body
+ * (nfa_layer_batch_selector.py:31-131, 1005-1078).
+ *   k_new [batch, Hkv, head_dim], v_new [batch, Hkv, head_dim_v], slots [batch]
+ *   (-1 routes the row to the PAD page and skips the metadata).
+ *   k_new == v_new == NULL: the rows are already in the pool; only the packed
+ *   key of the newest token (position lengths[row] - 1) and the statistics of
+ *   its page are refreshed. */
+int loda_append_decode(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
+                       const void* k_new, const void* v_new, const int32_t* slots,
+                       uint32_t* status, void* stream);
+
+/* Scatter a prefill [Hkv, n_tokens, head_dim] through one block-table row.
+ * Replaces paged_write_prefill (paged_region_kernels.py:610-662). */
+int loda_write_prefill(const loda_geometry* g, const loda_layer* layer,
+                       const void* k, const void* v, const int32_t* block_table_row,
+                       int32_t n_tokens, void* stream);
+
+/* (Re)build page metadata and packed tail keys of logical pages
+ * [first_block, first_block + n_blocks) of request slot `req_id` whose length
+ * is `length`, reading the keys from the pool.  Replaces the full page-stats
+ * rebuild after freeze (nfa_layer_batch_selector.py:2121-2145). */
+int loda_build_index(const loda_geometry* g, const loda_layer* layer, int32_t req_id,
+                     int32_t length, int32_t first_block, int32_t n_blocks, void* stream);
+
+/* L1: page scores from the min/max bound (far pool) and page mean (near pool),
+ * exact top-k per pool with ties toward the lower page id.  Replaces
+ * _l1_scores + the L1 top-k kernels (nfa_layer_batch_selector.py:174-354,
+ * 1473-1863).  q [batch, Hq, head_dim]. */
+int loda_select_l1(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
+                   const void* q, float scale, const loda_selection* out,
+                   void* workspace, void* stream);
+
+/* L2: grouped-query logits on the packed 4-bit tail keys of the surviving
+ * pages, exact top-quota with ties toward the lower token id, hole fill, union
+ * with sink and window tokens, logical -> physical slots.  Replaces candidate
+ * expansion, fine scores, filtered top-k and the final union
+ * (nfa_layer_batch_selector.py:422-848, 1116-1437). */
+int loda_select_l2(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
+                   const void* q, float scale, const loda_selection* sel,
+                   uint32_t* status, void* workspace, void* stream);
+
+/* Gather attention over the selected slots with split-K and a log-sum-exp
+ * merge.  Replaces sparse_paged_attention_gather (paged_region_kernels.py:
+ * 800-1041).  q [n_query, Hq, head_dim], query_to_req [n_query] (<0: output
+ * row of zeros), out [n_query, Hq, head_dim_v]. */
+int loda_gather_attend(const loda_geometry* g, const loda_layer* layer,
+                       const void* q, const int32_t* gather, const int32_t* visible_lens,
+                       const int32_t* query_to_req, int32_t n_query, int32_t n_req_rows,
+                       float scale, void* out, void* workspace, void* stream);
+
+/* The whole decode step of one layer on one stream: append, L1, L2, attend.
+ * Replaces select_topk_for_layer_batched(decode_write=...) followed by
+ * decode_graph_ready (nfa_layer_batch_selector.py:2649-2720,
+ * sparse_attn/ops/paged_region_kernels_nfa.py:122-162).  One query per row
+ * (query_to_req is the identity over the batch rows). */
+int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
+                     const void* q, const void* k_new, const void* v_new, const int32_t* slots,
+                     float scale, const loda_selection* sel, const int32_t* query_to_req,
+                     void* out, uint32_t* status, void* workspace, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LODA_B200_H_ */

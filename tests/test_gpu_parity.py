@@ -1,0 +1,213 @@
+"""GPU parity: the CUDA path, called through the reference-shaped Python API
+(which goes through the C ABI), against the CPU oracle on the same seeded
+inputs.  Integer outputs must be identical; attention within the bf16
+tolerance 2e-2 (absolute + relative)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import loda_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+ATOL = RTOL = 2e-2      # bf16 attention tolerance of the specification
+
+# ragged, tiny, page-aligned and long requests in one batch
+LENGTHS_A = [1, 3, 4, 5, 16, 17, 100, 131]
+LENGTHS_B = [132, 133, 200, 1003, 1280, 1500, 2500, 4400]
+LENGTHS_C = [6000, 12289, 20000, 4229, 4240, 4241]
+
+
+def _run_step(setup, fused_write=True):
+    from helpers import mod
+    sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
+    nfa = mod("sparse_attn.ops.paged_region_kernels_nfa")
+    cache = setup.cache
+    cache.plan_common(setup.req_ids)
+    slots = cache.slot_mapping_for_layer(0)[:len(setup.req_ids)]
+    if fused_write:
+        sel_mod.select_topk_for_layer_batched(
+            cache, 0, setup.req_ids, setup.q, attention=setup.attention,
+            decode_write=(setup.k_new, setup.v_new, slots))
+    else:
+        cache.write_decode(0, setup.k_new, setup.v_new, slots)
+        sel_mod.select_topk_for_layer_batched(cache, 0, setup.req_ids, setup.q, attention=setup.attention)
+    out = nfa.decode_graph_ready(setup.attention, setup.q, cache)
+    torch.cuda.synchronize()
+    assert cache.read_status() == 0
+    return out
+
+
+def _check_against_oracle(setup, out):
+    from helpers import bf16_to_f32_np, oracle_selection, pools_np
+    cache = setup.cache
+    rt = cache._runtime
+    layer = cache.layers[0]
+    page = setup.cfg.block_size
+    table = cache.block_table_buf[0].cpu().numpy()
+    gather = cache.gather_indices_for_layer(0).cpu().numpy()
+    lens = cache.visible_lens_for_layer(0).cpu().numpy()
+    i_far, n_far = rt.i_far.cpu().numpy(), rt.n_far.cpu().numpy()
+    i_near, n_near = rt.i_near.cpu().numpy(), rt.n_near.cpu().numpy()
+    middle, mcount = rt.middle.cpu().numpy(), rt.middle_counts.cpu().numpy()
+    mm = bf16_to_f32_np(layer.page_mm)
+    psum = bf16_to_f32_np(layer.page_sum)
+    code = layer.tail_code.cpu().numpy()
+    sz = bf16_to_f32_np(layer.tail_sz)
+    for b, rid in enumerate(setup.req_ids):
+        case = setup.cases[b]
+        length = case.length
+        k_np = bf16_to_f32_np(case.k)
+        idx = O.build_index(k_np, length, setup.cfg)
+        kt = (length + page - 1) // page
+        # page statistics, bit exact
+        assert np.array_equal(mm[rid, :, :kt, 0].transpose(1, 0, 2), idx.vmin), f"min L={length}"
+        assert np.array_equal(mm[rid, :, :kt, 1].transpose(1, 0, 2), idx.vmax), f"max L={length}"
+        assert np.array_equal(psum[rid, :, :kt].transpose(1, 0, 2), idx.vsum), f"sum L={length}"
+        # packed 4-bit keys, bit exact
+        tok = np.arange(length)
+        phys = table[rid][tok // page]
+        cc = code[phys, :, tok % page]                       # [L, Hkv, d'/2]
+        unpacked = np.stack((cc & 15, cc >> 4), axis=-1).reshape(length, cc.shape[1], -1)
+        assert np.array_equal(unpacked, idx.code), f"codes L={length}"
+        assert np.array_equal(sz[phys, :, tok % page, 0], idx.scale), f"scale L={length}"
+        assert np.array_equal(sz[phys, :, tok % page, 1], idx.zero), f"zero L={length}"
+        sel = oracle_selection(setup, b)
+        assert np.array_equal(n_far[b], sel.n_far), f"n_far L={length}"
+        assert np.array_equal(n_near[b], sel.n_near), f"n_near L={length}"
+        assert np.array_equal(i_far[b], sel.i_far), f"I_F L={length}"
+        assert np.array_equal(i_near[b], sel.i_near), f"I_N L={length}"
+        for kv in range(setup.cfg.num_kv_heads):
+            assert mcount[b, kv] == len(sel.middle[kv]), f"middle count L={length} kv={kv}"
+            assert np.array_equal(middle[b, kv, :mcount[b, kv]], sel.middle[kv]), f"middle L={length} kv={kv}"
+            n = lens[b, kv]
+            assert n == len(sel.logical[kv]), f"vis_len L={length} kv={kv}"
+            assert np.array_equal(gather[b, kv, :n], O.to_slots(sel.logical[kv], table[rid], page))
+    pool_k, pool_v = pools_np(layer)
+    q2r = np.arange(len(setup.req_ids))
+    ref = O.gather_attention(bf16_to_f32_np(setup.q), pool_k, pool_v, gather, lens, q2r,
+                             setup.attention.scaling, "bf16")
+    np.testing.assert_allclose(bf16_to_f32_np(out), ref, atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("lengths", [LENGTHS_A, LENGTHS_B, LENGTHS_C], ids=["tiny", "short", "long"])
+def test_decode_step_matches_oracle(lengths):
+    from helpers import make_setup
+    setup = make_setup(lengths, seed=1)
+    out = _run_step(setup)
+    _check_against_oracle(setup, out)
+
+
+def test_separate_write_then_select_matches_fused_write():
+    from helpers import make_setup
+    a = make_setup([700, 4500, 9000], seed=2)
+    b = make_setup([700, 4500, 9000], seed=2)
+    out_a = _run_step(a, fused_write=True)
+    out_b = _run_step(b, fused_write=False)
+    assert torch.equal(a.cache.gather_indices_for_layer(0), b.cache.gather_indices_for_layer(0))
+    assert torch.equal(a.cache.visible_lens_for_layer(0), b.cache.visible_lens_for_layer(0))
+    assert torch.equal(out_a, out_b)
+    _check_against_oracle(b, out_b)
+
+
+def test_incremental_append_equals_bulk_rebuild_over_many_steps():
+    """Decode 40 tokens (crossing page boundaries) with the append kernel, then
+    compare the index with a bulk rebuild and the selection with the oracle."""
+    from helpers import make_setup, mod
+    sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
+    synth = mod("synth")
+    base = [5000, 777]
+    steps = 40
+    setup = make_setup(base, seed=3, extra_blocks=8)
+    cache = setup.cache
+    full = [synth.make_decode_case(l + steps, seed=3 * 1000 + i, dtype=torch.bfloat16, device="cpu")
+            for i, l in enumerate(base)]
+    for s in range(steps + 1):
+        # token at position base-1+s of the longer synthetic stream
+        k_new = torch.stack([c.k[l - 1 + s] for c, l in zip(full, base)])[:, :, None].to(setup.dev)
+        v_new = torch.stack([c.v[l - 1 + s] for c, l in zip(full, base)])[:, :, None].to(setup.dev)
+        cache.plan_common(setup.req_ids)
+        slots = cache.slot_mapping_for_layer(0)[:2]
+        sel_mod.select_topk_for_layer_batched(cache, 0, setup.req_ids, setup.q, attention=setup.attention,
+                                              decode_write=(k_new, v_new, slots))
+        cache.commit_step()
+    torch.cuda.synchronize()
+    assert cache.read_status() == 0
+    # rebuild the oracle view: prefix of the original case (l-1 tokens) + appended stream
+    for i, l in enumerate(base):
+        case = setup.cases[i]
+        k = torch.cat((case.k[:l - 1], full[i].k[l - 1:l + steps]))
+        v = torch.cat((case.v[:l - 1], full[i].v[l - 1:l + steps]))
+        case.k, case.v, case.length = k, v, l + steps
+    nfa = mod("sparse_attn.ops.paged_region_kernels_nfa")
+    out = nfa.decode_graph_ready(setup.attention, setup.q, cache)
+    torch.cuda.synchronize()
+    _check_against_oracle(setup, out)
+
+
+def test_padding_rows_and_noncontiguous_request_slots():
+    from helpers import make_setup, mod
+    sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
+    nfa = mod("sparse_attn.ops.paged_region_kernels_nfa")
+    setup = make_setup([3000, 640, 5000], seed=4, max_requests=6)
+    cache = setup.cache
+    # drop the middle request: row 1 becomes a padding row (request id -1)
+    cache.remove_request(setup.req_ids[1])
+    req_ids = [setup.req_ids[0], -1, setup.req_ids[2]]
+    cache.plan_common(req_ids)
+    slots = cache.slot_mapping_for_layer(0)[:3]
+    poison = torch.full_like(cache.gather_indices_for_layer(0), 13)
+    cache.gather_indices_for_layer(0).copy_(poison)
+    sel_mod.select_topk_for_layer_batched(cache, 0, req_ids, setup.q, attention=setup.attention,
+                                          decode_write=(setup.k_new, setup.v_new, slots))
+    out = nfa.decode_graph_ready(setup.attention, setup.q, cache)
+    torch.cuda.synchronize()
+    lens = cache.visible_lens_for_layer(0).cpu().numpy()
+    assert (lens[1] == 0).all()
+    assert (out[1] == 0).all()
+    gather = cache.gather_indices_for_layer(0).cpu().numpy()
+    assert (gather[1] == 13).all()                      # untouched row
+    for b in (0, 2):
+        for kv in range(8):
+            assert (gather[b, kv, lens[b, kv]:] == 13).all()   # tails beyond vis_len untouched
+    setup.req_ids = req_ids
+    keep = [0, 2]
+    sub_cases = [setup.cases[i] for i in keep]
+    from helpers import oracle_selection
+    table = cache.block_table_buf[0].cpu().numpy()
+    for b in keep:
+        sel = oracle_selection(setup, b)
+        for kv in range(8):
+            n = lens[b, kv]
+            assert np.array_equal(gather[b, kv, :n], O.to_slots(sel.logical[kv], table[req_ids[b]], 16))
+    assert len(sub_cases) == 2
+
+
+def test_graph_replay_equals_eager():
+    from helpers import make_setup, mod
+    sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
+    nfa = mod("sparse_attn.ops.paged_region_kernels_nfa")
+    setup = make_setup([9000, 2000], seed=5)
+    cache = setup.cache
+    out_eager = _run_step(setup)                      # warm-up: builds the index, allocates scratch
+    g_eager = cache.gather_indices_for_layer(0).clone()
+    l_eager = cache.visible_lens_for_layer(0).clone()
+    slots = cache.slot_mapping_for_layer(0)[:2]
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    static_out = []
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            sel_mod.select_topk_for_layer_batched(cache, 0, setup.req_ids, setup.q, attention=setup.attention,
+                                                  decode_write=(setup.k_new, setup.v_new, slots))
+            static_out.append(nfa.decode_graph_ready(setup.attention, setup.q, cache))
+    cache.gather_indices_for_layer(0).fill_(-7)
+    cache.visible_lens_for_layer(0).zero_()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(cache.gather_indices_for_layer(0)[:, :, :1024] * (torch.arange(1024, device=setup.dev)
+                       < l_eager[..., None]), g_eager * (torch.arange(1024, device=setup.dev) < l_eager[..., None]))
+    assert torch.equal(cache.visible_lens_for_layer(0), l_eager)
+    assert torch.equal(static_out[0], out_eager)

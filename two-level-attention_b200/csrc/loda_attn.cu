@@ -1,0 +1,307 @@
+// Split-K gather attention over the selected tokens of the paged KV cache.
+//
+// Restates sparse_paged_attention_gather (sparse_attn/ops/paged_region_kernels.py:
+// 800-1041; grouped kernel :251-363, split kernel :367-529, combine :578-607):
+// for query row t, kv head h and its GQA group, exact softmax attention over
+// the physical slots gather[req, h, 0:visible_lens[req, h]]; slots < 0 are
+// skipped; an empty list gives zeros; rows with query_to_req < 0 give zeros.
+//
+// Grid = (nsplit, Hkv, n_query).  CTA (s, h, t) owns the balanced chunk
+// [floor(s n / nsplit), floor((s + 1) n / nsplit)) of the list.  K and V rows
+// are staged by physical slot with 16-byte cp.async copies (one 256-byte row per
+// 16 lanes) into padded shared-memory tiles of 64 tokens; each of the 4 warps
+// owns 16 tokens of a tile: S = Q K^T with mma.sync m16n8k16 (M = the GQA group
+// padded to 16 rows, operands bf16, fp32 accumulate), fp32 online softmax in the
+// exp2 domain, O += P V with P rounded to bf16.  Warps, then splits, are merged
+// by log-sum-exp in a fixed order; the last CTA of a (t, h) pair to finish
+// (atomic ticket, no spinning) performs the split merge and writes bf16.
+#include "loda_common.cuh"
+
+namespace loda {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int ATT_TILE = 64;
+constexpr int ATT_WARPS = 4;
+constexpr int ATT_NT = 32 * ATT_WARPS;
+constexpr int ATT_MAX_SPLIT = 16;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_ptr) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_ptr) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *(uint32_t*)&v;
+}
+
+template <int D, int DV>
+__global__ void __launch_bounds__(ATT_NT) attn_kernel(
+    loda_geometry g, loda_layer L, const bf16* __restrict__ q, const int32_t* __restrict__ gather,
+    const int32_t* __restrict__ visible_lens, const int32_t* __restrict__ query_to_req,
+    int n_req_rows, float scale_log2, bf16* __restrict__ out, AttnWorkspace ws, int nsplit) {
+  constexpr int KSTR = D + 8, VSTR = DV + 8;   // padded rows: conflict-free ldmatrix
+  constexpr int KSTEPS = D / 16, NTV = DV / 8;
+  extern __shared__ __align__(16) unsigned char smem[];
+  bf16* Ks = (bf16*)smem;                          // [TILE][KSTR]
+  bf16* Vs = Ks + ATT_TILE * KSTR;                 // [TILE][VSTR]
+  int* slot_s = (int*)(Vs + ATT_TILE * VSTR);      // [TILE]
+  float* wm = (float*)(slot_s + ATT_TILE);         // [WARPS][16]
+  float* wz = wm + ATT_WARPS * 16;                 // [WARPS][16]
+  int* sh = (int*)(wz + ATT_WARPS * 16);           // 4
+  float* wo = (float*)(sh + 4);                    // [WARPS][G][DV]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int split = blockIdx.x, kv = blockIdx.y, t = blockIdx.z;
+  const int G = g.num_q_heads / g.num_kv_heads;
+  const int req = query_to_req[t];
+  int n = 0;
+  if (req >= 0 && req < n_req_rows) n = min(max(visible_lens[(size_t)req * g.num_kv_heads + kv], 0), g.max_visible);
+  const int c0 = (int)(((long long)split * n) / nsplit);
+  const int c1 = (int)(((long long)(split + 1) * n) / nsplit);
+  const int32_t* list = gather + ((size_t)max(req, 0) * g.num_kv_heads + kv) * g.max_visible;
+
+  // Q fragments: A operand, rows = heads of the group (zero beyond G)
+  uint32_t qa[KSTEPS][4];
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8, kc = (lane & 3) * 2;
+    const bf16* q0 = q + ((size_t)t * g.num_q_heads + kv * G + r0) * D;
+    const bf16* q1 = q + ((size_t)t * g.num_q_heads + kv * G + r1) * D;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      qa[ks][0] = r0 < G ? *(const uint32_t*)(q0 + ks * 16 + kc) : 0u;
+      qa[ks][1] = r1 < G ? *(const uint32_t*)(q1 + ks * 16 + kc) : 0u;
+      qa[ks][2] = r0 < G ? *(const uint32_t*)(q0 + ks * 16 + kc + 8) : 0u;
+      qa[ks][3] = r1 < G ? *(const uint32_t*)(q1 + ks * 16 + kc + 8) : 0u;
+    }
+  }
+
+  float oacc[NTV][4];
+#pragma unroll
+  for (int i = 0; i < NTV; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.0f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, z_run[2] = {0.0f, 0.0f};   // rows lane/4 and lane/4 + 8
+
+  for (int base = c0; base < c1; base += ATT_TILE) {
+    const int ntok = min(ATT_TILE, c1 - base);
+    __syncthreads();   // previous tile fully consumed
+    if (tid < ATT_TILE) {
+      int s = tid < ntok ? list[base + tid] : -1;
+      if (s >= g.num_pages * g.page) s = -1;
+      slot_s[tid] = s;
+    }
+    __syncthreads();
+    // stage K and V rows: 16 lanes per 256-byte row
+    constexpr int KCH = D / 8, VCH = DV / 8;
+    for (int c = tid; c < ATT_TILE * KCH; c += ATT_NT) {
+      const int r = c / KCH, cc = c % KCH;
+      const int s = slot_s[r];
+      const size_t rowi = s >= 0 ? ((size_t)(s / g.page) * g.num_kv_heads + kv) * g.page + (s % g.page) : 0;
+      cp_async16(Ks + r * KSTR + cc * 8, (const bf16*)L.pool_k + rowi * D + cc * 8, s >= 0);
+    }
+    for (int c = tid; c < ATT_TILE * VCH; c += ATT_NT) {
+      const int r = c / VCH, cc = c % VCH;
+      const int s = slot_s[r];
+      const size_t rowi = s >= 0 ? ((size_t)(s / g.page) * g.num_kv_heads + kv) * g.page + (s % g.page) : 0;
+      cp_async16(Vs + r * VSTR + cc * 8, (const bf16*)L.pool_v + rowi * DV + cc * 8, s >= 0);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+
+    const int tok0 = warp * 16;
+    if (tok0 < ntok) {
+      // S = Q K^T for this warp's 16 tokens: two n-tiles of 8 tokens
+      float sacc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        uint32_t kb[4];
+        const int mi = lane >> 3, r = lane & 7;
+        ldmatrix_x4(kb, Ks + (tok0 + (mi >> 1) * 8 + r) * KSTR + ks * 16 + (mi & 1) * 8);
+        mma_bf16(sacc[0], qa[ks], kb[0], kb[1]);
+        mma_bf16(sacc[1], qa[ks], kb[2], kb[3]);
+      }
+      // mask, scale (log2 domain), per-row max over this warp's tokens
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tk = tok0 + j * 8 + (lane & 3) * 2 + (e & 1);
+          const bool ok = tk < ntok && slot_s[tk] >= 0;
+          const float v = ok ? sacc[j][e] * scale_log2 : -INFINITY;
+          sacc[j][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      }
+      float alpha[2], msafe[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float m_new = fmaxf(m_run[h], mx[h]);
+        msafe[h] = m_new == -INFINITY ? 0.0f : m_new;
+        alpha[h] = exp2f(m_run[h] - msafe[h]);     // m_run = -inf -> 0
+        m_run[h] = m_new;
+      }
+      uint32_t pa[4];
+      float zs[2] = {0.0f, 0.0f};
+      {
+        float p[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            p[j][e] = exp2f(sacc[j][e] - msafe[e >> 1]);
+            zs[e >> 1] += p[j][e];
+          }
+        pa[0] = pack_bf16(p[0][0], p[0][1]);   // row r,   tokens 0..7
+        pa[1] = pack_bf16(p[0][2], p[0][3]);   // row r+8, tokens 0..7
+        pa[2] = pack_bf16(p[1][0], p[1][1]);   // row r,   tokens 8..15
+        pa[3] = pack_bf16(p[1][2], p[1][3]);   // row r+8, tokens 8..15
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        zs[h] += __shfl_xor_sync(0xffffffffu, zs[h], 1);
+        zs[h] += __shfl_xor_sync(0xffffffffu, zs[h], 2);
+        z_run[h] = z_run[h] * alpha[h] + zs[h];
+      }
+#pragma unroll
+      for (int i = 0; i < NTV; ++i) {
+        oacc[i][0] *= alpha[0]; oacc[i][1] *= alpha[0];
+        oacc[i][2] *= alpha[1]; oacc[i][3] *= alpha[1];
+      }
+      // O += P V: V^T fragments by transposed ldmatrix, two dv n-tiles per load
+#pragma unroll
+      for (int i = 0; i < NTV; i += 2) {
+        uint32_t vb[4];
+        const int mi = lane >> 3, r = lane & 7;
+        ldmatrix_x4_trans(vb, Vs + (tok0 + (mi & 1) * 8 + r) * VSTR + i * 8 + (mi >> 1) * 8);
+        mma_bf16(oacc[i], pa, vb[0], vb[1]);
+        mma_bf16(oacc[i + 1], pa, vb[2], vb[3]);
+      }
+    }
+  }
+
+  // ---- merge the warps of this CTA (fixed order) -------------------------------
+  __syncthreads();
+  {
+    const int r0 = lane >> 2;
+    if ((lane & 3) == 0) {
+      wm[warp * 16 + r0] = m_run[0]; wz[warp * 16 + r0] = z_run[0];
+      wm[warp * 16 + r0 + 8] = m_run[1]; wz[warp * 16 + r0 + 8] = z_run[1];
+    }
+#pragma unroll
+    for (int i = 0; i < NTV; ++i) {
+      const int col = i * 8 + (lane & 3) * 2;
+      if (r0 < G) { wo[(warp * G + r0) * DV + col] = oacc[i][0]; wo[(warp * G + r0) * DV + col + 1] = oacc[i][1]; }
+      if (r0 + 8 < G) { wo[(warp * G + r0 + 8) * DV + col] = oacc[i][2]; wo[(warp * G + r0 + 8) * DV + col + 1] = oacc[i][3]; }
+    }
+  }
+  __syncthreads();
+  const size_t pair = (size_t)t * g.num_kv_heads + kv;
+  for (int e = tid; e < G * DV; e += ATT_NT) {
+    const int gi = e / DV, dv = e % DV;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, wm[w * 16 + gi]);
+    float z = 0.0f, o = 0.0f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < ATT_WARPS; ++w) {
+        const float a = exp2f(wm[w * 16 + gi] - M);
+        z += wz[w * 16 + gi] * a;
+        o += wo[(w * G + gi) * DV + dv] * a;
+      }
+    }
+    if (nsplit == 1) {
+      out[((size_t)t * g.num_q_heads + kv * G + gi) * DV + dv] = __float2bfloat16_rn(z == 0.0f ? 0.0f : o / z);
+    } else {
+      const size_t ps = pair * nsplit + split;
+      ws.part_o[(ps * G + gi) * DV + dv] = o;
+      if (dv == 0) { ws.part_m[ps * G + gi] = M; ws.part_z[ps * G + gi] = z; }
+    }
+  }
+  if (nsplit == 1) return;
+
+  // ---- last CTA of the (t, kv) pair merges the splits in split order -------------
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) sh[0] = (atomicAdd(ws.ticket + pair, 1) == nsplit - 1);
+  __syncthreads();
+  if (!sh[0]) return;
+  __threadfence();
+  for (int e = tid; e < G * DV; e += ATT_NT) {
+    const int gi = e / DV, dv = e % DV;
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, __ldcg(ws.part_m + (pair * nsplit + s) * G + gi));
+    float z = 0.0f, o = 0.0f;
+    if (M != -INFINITY) {
+      for (int s = 0; s < nsplit; ++s) {
+        const size_t ps = pair * nsplit + s;
+        const float a = exp2f(__ldcg(ws.part_m + ps * G + gi) - M);
+        z += __ldcg(ws.part_z + ps * G + gi) * a;
+        o += __ldcg(ws.part_o + (ps * G + gi) * DV + dv) * a;
+      }
+    }
+    out[((size_t)t * g.num_q_heads + kv * G + gi) * DV + dv] = __float2bfloat16_rn(z == 0.0f ? 0.0f : o / z);
+  }
+  if (tid == 0) ws.ticket[pair] = 0;
+}
+
+size_t attn_smem_bytes(const loda_geometry& g) {
+  const int G = g.num_q_heads / g.num_kv_heads;
+  return (size_t)ATT_TILE * (g.head_dim + 8) * 2 + (size_t)ATT_TILE * (g.head_dim_v + 8) * 2 + ATT_TILE * 4 +
+         2 * ATT_WARPS * 16 * 4 + 16 + (size_t)ATT_WARPS * G * g.head_dim_v * 4;
+}
+
+int attn_nsplit(const loda_geometry& g, int n_query) {
+  const int pairs = n_query * g.num_kv_heads;
+  int ns = (2 * 148 + pairs - 1) / pairs;
+  const int by_len = (g.max_visible + ATT_TILE - 1) / ATT_TILE;   // at least one tile per split
+  if (ns > by_len) ns = by_len;
+  if (ns > ATT_MAX_SPLIT) ns = ATT_MAX_SPLIT;
+  if (ns < 1) ns = 1;
+  return ns;
+}
+
+cudaError_t launch_attn(const loda_geometry& g, const loda_layer& L, const void* q, const int32_t* gather,
+                        const int32_t* visible_lens, const int32_t* query_to_req, int n_query,
+                        int n_req_rows, float scale, void* out, const AttnWorkspace& ws, cudaStream_t st) {
+  if (n_query <= 0) return cudaSuccess;
+  const int nsplit = attn_nsplit(g, n_query);
+  const dim3 grid(nsplit, g.num_kv_heads, n_query);
+  const size_t smem = attn_smem_bytes(g);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  cudaError_t e;
+  if (g.head_dim == 128 && g.head_dim_v == 128) {
+    e = cudaFuncSetAttribute(attn_kernel<128, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attn_kernel<128, 128><<<grid, ATT_NT, smem, st>>>(g, L, (const bf16*)q, gather, visible_lens, query_to_req,
+                                                      n_req_rows, scale_log2, (bf16*)out, ws, nsplit);
+  } else if (g.head_dim == 64 && g.head_dim_v == 64) {
+    e = cudaFuncSetAttribute(attn_kernel<64, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attn_kernel<64, 64><<<grid, ATT_NT, smem, st>>>(g, L, (const bf16*)q, gather, visible_lens, query_to_req,
+                                                    n_req_rows, scale_log2, (bf16*)out, ws, nsplit);
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace loda

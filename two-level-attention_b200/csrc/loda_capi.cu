@@ -1,0 +1,246 @@
+// C ABI of loda_b200 (declared in include/loda_b200.h): argument validation,
+// scratch layout and kernel launches.  No allocation, no host synchronisation.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "loda_common.cuh"
+
+namespace loda {
+
+cudaError_t launch_append_decode(const loda_geometry&, const loda_layer&, const loda_batch&, const void*,
+                                 const void*, const int32_t*, uint32_t*, cudaStream_t);
+cudaError_t launch_build_index(const loda_geometry&, const loda_layer&, int, int, int, int, cudaStream_t);
+cudaError_t launch_write_prefill(const loda_geometry&, const loda_layer&, const void*, const void*,
+                                 const int32_t*, int, cudaStream_t);
+cudaError_t launch_l1(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
+                      const loda_selection&, const L1Workspace&, cudaStream_t);
+cudaError_t launch_l2(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
+                      const loda_selection&, uint32_t*, cudaStream_t);
+cudaError_t launch_attn(const loda_geometry&, const loda_layer&, const void*, const int32_t*, const int32_t*,
+                        const int32_t*, int, int, float, void*, const AttnWorkspace&, cudaStream_t);
+int l1_nsplit(const loda_geometry&);
+size_t l1_smem_bytes(const loda_geometry&);
+size_t l2_smem_bytes(const loda_geometry&);
+int attn_nsplit(const loda_geometry&, int);
+
+static thread_local char g_error[512] = "";
+
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return LODA_OK;
+  return fail(LODA_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+}
+
+static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+constexpr int kAttnMaxSplit = 16;
+
+struct WsLayout {
+  size_t l1_ticket, l1_cnt_far, l1_cnt_near, l1_part_far, l1_part_near;
+  size_t at_ticket, at_m, at_z, at_o, total;
+};
+
+static WsLayout ws_layout(const loda_geometry& g) {
+  const int max_batch = g.max_query_tokens, max_query = g.max_query_tokens;
+  WsLayout w;
+  const size_t rows = (size_t)max_batch * g.num_kv_heads;
+  const size_t ns = l1_nsplit(g);
+  const size_t pairs = (size_t)max_query * g.num_kv_heads;
+  const size_t G = g.num_q_heads / g.num_kv_heads;
+  size_t off = 0;
+  w.l1_ticket = off; off = align_up(off + rows * 4, 256);
+  w.at_ticket = off; off = align_up(off + pairs * 4, 256);
+  w.l1_cnt_far = off; off = align_up(off + rows * ns * 4, 256);
+  w.l1_cnt_near = off; off = align_up(off + rows * ns * 4, 256);
+  w.l1_part_far = off; off = align_up(off + rows * ns * g.k_far * 4, 256);
+  w.l1_part_near = off; off = align_up(off + rows * ns * g.k_near * 4, 256);
+  w.at_m = off; off = align_up(off + pairs * kAttnMaxSplit * G * 4, 256);
+  w.at_z = off; off = align_up(off + pairs * kAttnMaxSplit * G * 4, 256);
+  w.at_o = off; off = align_up(off + pairs * kAttnMaxSplit * G * g.head_dim_v * 4, 256);
+  w.total = off;
+  return w;
+}
+
+static int check_geometry(const loda_geometry* g) {
+  if (!g) return fail(LODA_ERR_ARGUMENT, "geometry is NULL");
+  if (g->dtype != LODA_DTYPE_BF16)
+    return fail(LODA_ERR_UNSUPPORTED, "only bf16 KV pools are implemented (dtype=%d)", g->dtype);
+  if (g->num_kv_heads < 1 || g->num_q_heads % g->num_kv_heads)
+    return fail(LODA_ERR_ARGUMENT, "GQA requires num_q_heads %% num_kv_heads == 0");
+  const int G = g->num_q_heads / g->num_kv_heads;
+  if (G > 16) return fail(LODA_ERR_UNSUPPORTED, "GQA group %d > 16", G);
+  if (g->head_dim % 16 || g->head_dim_v % 16) return fail(LODA_ERR_ARGUMENT, "head dims must be multiples of 16");
+  if (g->sub_dims != 16 && g->sub_dims != 32 && g->sub_dims != 64)
+    return fail(LODA_ERR_UNSUPPORTED, "subspace size %d not in {16, 32, 64}", g->sub_dims);
+  const int half = g->sub_dims / 2;
+  if (g->sub_lo0 < 0 || g->sub_lo1 < 0 || g->sub_lo0 + half > g->head_dim || g->sub_lo1 + half > g->head_dim)
+    return fail(LODA_ERR_ARGUMENT, "subspace ranges outside the head");
+  if (g->page < 1 || (g->page & (g->page - 1))) return fail(LODA_ERR_ARGUMENT, "page must be a power of two");
+  if (g->swa < 1 || g->swa % g->page) return fail(LODA_ERR_ARGUMENT, "swa must be a positive multiple of page");
+  if (g->max_blocks < 1 || g->max_blocks > 65536) return fail(LODA_ERR_UNSUPPORTED, "max_blocks must be in [1, 65536]");
+  if (g->max_requests < 1 || g->max_query_tokens < 1)
+    return fail(LODA_ERR_ARGUMENT, "max_requests / max_query_tokens must be >= 1");
+  if (g->num_pages < 2) return fail(LODA_ERR_ARGUMENT, "num_pages must include the PAD page");
+  if (g->k_far < 0 || g->k_near < 0 || g->k_far > 512 || g->k_near > 512)
+    return fail(LODA_ERR_UNSUPPORTED, "k_far / k_near must be in [0, 512]");
+  if (g->k_far > g->max_blocks || g->k_near > g->max_blocks)
+    return fail(LODA_ERR_ARGUMENT, "k_far / k_near exceed max_blocks");
+  if ((size_t)(g->k_far + g->k_near + 2) * g->page > 65535)
+    return fail(LODA_ERR_UNSUPPORTED, "more than 65535 L2 candidates per row");
+  if (g->level2_topk < g->sink + g->swa) return fail(LODA_ERR_ARGUMENT, "level2_topk < sink + swa");
+  if (g->max_visible < g->level2_topk) return fail(LODA_ERR_ARGUMENT, "max_visible < level2_topk");
+  if (g->sink < 0 || g->near_len < 0 || g->pool_near_len < g->page)
+    return fail(LODA_ERR_ARGUMENT, "bad sink / near_len / pool_near_len");
+  if ((size_t)l1_nsplit(*g) * (g->k_far > g->k_near ? g->k_far : g->k_near) * 4 >
+      (size_t)512 * (4 * g->sub_dims + 16))
+    return fail(LODA_ERR_UNSUPPORTED, "L1 merge list does not fit in shared memory");
+  if (l1_smem_bytes(*g) > 200 * 1024 || l2_smem_bytes(*g) > 200 * 1024)
+    return fail(LODA_ERR_UNSUPPORTED, "geometry needs more than 200 KB of shared memory");
+  return LODA_OK;
+}
+
+static int check_layer(const loda_layer* l, bool need_index = true) {
+  if (!l || !l->pool_k || !l->pool_v) return fail(LODA_ERR_ARGUMENT, "layer pools must be non-NULL");
+  if (need_index &&
+      (!l->page_mm || !l->page_sum || !l->tail_code || !l->tail_sz || !l->block_table))
+    return fail(LODA_ERR_ARGUMENT, "layer index buffers and block table must be non-NULL");
+  return LODA_OK;
+}
+
+static int check_batch(const loda_geometry* g, const loda_batch* b) {
+  if (!b || b->batch < 0 || b->batch > g->max_query_tokens)
+    return fail(LODA_ERR_ARGUMENT, "batch must be in [0, max_query_tokens]");
+  if (b->batch > 0 && (!b->lengths || !b->valid_req_ids || !b->active_req_ids))
+    return fail(LODA_ERR_ARGUMENT, "batch metadata pointers must be non-NULL");
+  return LODA_OK;
+}
+
+}  // namespace loda
+
+using namespace loda;
+
+#define LODA_TRY(expr)          \
+  do {                          \
+    int rc_ = (expr);           \
+    if (rc_ != LODA_OK) return rc_; \
+  } while (0)
+
+extern "C" {
+
+const char* loda_version(void) { return "loda_b200 0.1 (sm_100a)"; }
+
+const char* loda_last_error(void) { return g_error; }
+
+size_t loda_workspace_bytes(const loda_geometry* g) {
+  if (check_geometry(g) != LODA_OK) return 0;
+  return ws_layout(*g).total;
+}
+
+int loda_append_decode(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
+                       const void* k_new, const void* v_new, const int32_t* slots, uint32_t* status,
+                       void* stream) {
+  LODA_TRY(check_geometry(g));
+  // a layer without index buffers may only be used for a plain K/V write: the
+  // kernel touches the index only for rows whose active_req_ids entry is >= 0
+  LODA_TRY(check_layer(layer, layer && layer->page_mm != nullptr));
+  LODA_TRY(check_batch(g, b));
+  if (b->batch == 0) return LODA_OK;
+  if ((k_new == nullptr) != (v_new == nullptr) || (k_new && !slots))
+    return fail(LODA_ERR_ARGUMENT, "k_new, v_new and slots go together (all NULL = refresh the index only)");
+  return check_cuda(launch_append_decode(*g, *layer, *b, k_new, v_new, slots, status, (cudaStream_t)stream),
+                    "append_decode");
+}
+
+int loda_write_prefill(const loda_geometry* g, const loda_layer* layer, const void* k, const void* v,
+                       const int32_t* block_table_row, int32_t n_tokens, void* stream) {
+  LODA_TRY(check_geometry(g));
+  LODA_TRY(check_layer(layer, false));
+  if (n_tokens < 0 || n_tokens > g->max_blocks * g->page)
+    return fail(LODA_ERR_ARGUMENT, "prefill length exceeds block-table capacity");
+  if (!k || !v || !block_table_row) return fail(LODA_ERR_ARGUMENT, "k / v / block_table_row must be non-NULL");
+  return check_cuda(launch_write_prefill(*g, *layer, k, v, block_table_row, n_tokens, (cudaStream_t)stream),
+                    "write_prefill");
+}
+
+int loda_build_index(const loda_geometry* g, const loda_layer* layer, int32_t req_id, int32_t length,
+                     int32_t first_block, int32_t n_blocks, void* stream) {
+  LODA_TRY(check_geometry(g));
+  LODA_TRY(check_layer(layer));
+  if (req_id < 0 || req_id >= g->max_requests) return fail(LODA_ERR_ARGUMENT, "req_id out of range");
+  if (length < 0 || first_block < 0 || n_blocks < 0 || first_block + n_blocks > g->max_blocks)
+    return fail(LODA_ERR_ARGUMENT, "block range out of range");
+  return check_cuda(launch_build_index(*g, *layer, req_id, length, first_block, n_blocks, (cudaStream_t)stream),
+                    "build_index");
+}
+
+int loda_select_l1(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
+                   float scale, const loda_selection* out, void* workspace, void* stream) {
+  LODA_TRY(check_geometry(g));
+  LODA_TRY(check_layer(layer));
+  LODA_TRY(check_batch(g, b));
+  if (b->batch == 0) return LODA_OK;
+  if (!q || !out || !out->i_far || !out->i_near || !out->n_far || !out->n_near || !workspace)
+    return fail(LODA_ERR_ARGUMENT, "L1 needs q, i_far, n_far, i_near, n_near and a workspace");
+  const WsLayout w = ws_layout(*g);
+  char* base = (char*)workspace;
+  const L1Workspace ws{(int*)(base + w.l1_ticket), (int*)(base + w.l1_cnt_far), (int*)(base + w.l1_cnt_near),
+                       (uint32_t*)(base + w.l1_part_far), (uint32_t*)(base + w.l1_part_near)};
+  return check_cuda(launch_l1(*g, *layer, *b, q, scale, *out, ws, (cudaStream_t)stream), "select_l1");
+}
+
+int loda_select_l2(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
+                   float scale, const loda_selection* sel, uint32_t* status, void* workspace, void* stream) {
+  (void)workspace;
+  LODA_TRY(check_geometry(g));
+  LODA_TRY(check_layer(layer));
+  LODA_TRY(check_batch(g, b));
+  if (b->batch == 0) return LODA_OK;
+  if (!q || !sel || !sel->i_far || !sel->i_near || !sel->n_far || !sel->n_near || !sel->gather ||
+      !sel->visible_lens)
+    return fail(LODA_ERR_ARGUMENT, "L2 needs q, the L1 outputs, gather and visible_lens");
+  if ((sel->middle == nullptr) != (sel->middle_counts == nullptr))
+    return fail(LODA_ERR_ARGUMENT, "middle and middle_counts must be given together");
+  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, status, (cudaStream_t)stream), "select_l2");
+}
+
+int loda_gather_attend(const loda_geometry* g, const loda_layer* layer, const void* q, const int32_t* gather,
+                       const int32_t* visible_lens, const int32_t* query_to_req, int32_t n_query,
+                       int32_t n_req_rows, float scale, void* out, void* workspace, void* stream) {
+  LODA_TRY(check_geometry(g));
+  LODA_TRY(check_layer(layer, false));
+  if (n_query < 0 || n_query > g->max_query_tokens)
+    return fail(LODA_ERR_ARGUMENT, "n_query must be in [0, max_query_tokens]");
+  if (n_query == 0) return LODA_OK;
+  if (!q || !gather || !visible_lens || !query_to_req || !out || !workspace || n_req_rows < 1)
+    return fail(LODA_ERR_ARGUMENT, "gather attention needs q, gather, visible_lens, query_to_req, out, workspace");
+  if (!((g->head_dim == 128 && g->head_dim_v == 128) || (g->head_dim == 64 && g->head_dim_v == 64)))
+    return fail(LODA_ERR_UNSUPPORTED, "gather attention supports head dims 64 and 128");
+  const WsLayout w = ws_layout(*g);
+  char* base = (char*)workspace;
+  const AttnWorkspace ws{(int*)(base + w.at_ticket), (float*)(base + w.at_m), (float*)(base + w.at_z),
+                         (float*)(base + w.at_o)};
+  return check_cuda(launch_attn(*g, *layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale,
+                                out, ws, (cudaStream_t)stream),
+                    "gather_attend");
+}
+
+int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
+                     const void* k_new, const void* v_new, const int32_t* slots, float scale,
+                     const loda_selection* sel, const int32_t* query_to_req, void* out, uint32_t* status,
+                     void* workspace, void* stream) {
+  LODA_TRY(loda_append_decode(g, layer, b, k_new, v_new, slots, status, stream));
+  LODA_TRY(loda_select_l1(g, layer, b, q, scale, sel, workspace, stream));
+  LODA_TRY(loda_select_l2(g, layer, b, q, scale, sel, status, workspace, stream));
+  return loda_gather_attend(g, layer, q, sel->gather, sel->visible_lens, query_to_req, b->batch,
+                            g->max_requests, scale, out, workspace, stream);
+}
+
+}  // extern "C"
