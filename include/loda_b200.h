@@ -179,6 +179,25 @@ int loda_gather_attend(const loda_geometry* g, const loda_layer* layer,
                        const int32_t* query_to_req, int32_t n_query, int32_t n_req_rows,
                        float scale, void* out, void* workspace, void* stream);
 
+/* Gather attention without a caller-provided workspace and without any
+ * allocation.  (No counterpart in the reference: its Triton operators always
+ * allocate their split buffers through torch.)
+ * Meant for hosts that cannot allocate device memory where they call this
+ * library — a plugin inside another framework's fixed memory plan, a process
+ * whose device memory was handed out at start-up, code under a no-allocation
+ * guard.  The split-K partials and tickets live in a fixed array inside the
+ * library (about 4.1 MiB on every GPU that loads it, held until exit), which
+ * limits the call to n_query * num_kv_heads <= 64, num_q_heads / num_kv_heads
+ * <= 8 and head_dim_v <= 128; larger calls return LODA_ERR_UNSUPPORTED.
+ * The first call on each device looks up the array's device address; make that
+ * first call before any stream capture.  All calls on a device share the one
+ * array: calls that overlap on the GPU (different streams) race on it.
+ * Same arguments and results as loda_gather_attend otherwise. */
+int loda_gather_attend_static(const loda_geometry* g, const loda_layer* layer,
+                              const void* q, const int32_t* gather, const int32_t* visible_lens,
+                              const int32_t* query_to_req, int32_t n_query, int32_t n_req_rows,
+                              float scale, void* out, void* stream);
+
 /* The whole decode step of one layer on one stream: append, L1, L2, attend.
  * Replaces select_topk_for_layer_batched(decode_write=...) followed by
  * decode_graph_ready (nfa_layer_batch_selector.py:2649-2720,

@@ -15,6 +15,8 @@
 // exp2 domain, O += P V with P rounded to bf16.  Warps, then splits, are merged
 // by log-sum-exp in a fixed order; the last CTA of a (t, h) pair to finish
 // (atomic ticket, no spinning) performs the split merge and writes bf16.
+#include <cstdio>
+
 #include "loda_common.cuh"
 
 namespace loda {
@@ -304,4 +306,89 @@ cudaError_t launch_attn(const loda_geometry& g, const loda_layer& L, const void*
   return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------
+// Gather attention for callers that cannot hand the library any scratch memory
+// ---------------------------------------------------------------------------
+// Some hosts of this library cannot call cudaMalloc (or any allocating routine)
+// at the point where they need attention: a plugin running inside another
+// framework's memory plan, a process whose device memory was carved up at start,
+// code running under a "no allocation" guard.  For them the split-K partials and
+// the tickets live in the fixed array below, which every GPU that loads the
+// library carries until the process exits (about 4.1 MiB).
+constexpr int ATT_STATIC_MAX_PAIRS = 64;   // n_query * num_kv_heads
+constexpr int ATT_STATIC_MAX_G = 8;        // query heads per kv head
+constexpr int ATT_STATIC_MAX_DV = 128;
+constexpr size_t ATT_STATIC_TICKET_BYTES = 256;                                     // 64 ints
+constexpr size_t ATT_STATIC_MZ_BYTES = (size_t)ATT_STATIC_MAX_PAIRS * ATT_MAX_SPLIT * ATT_STATIC_MAX_G * 4;
+constexpr size_t ATT_STATIC_O_BYTES = ATT_STATIC_MZ_BYTES * ATT_STATIC_MAX_DV;
+constexpr size_t ATT_STATIC_BYTES = ATT_STATIC_TICKET_BYTES + 2 * ATT_STATIC_MZ_BYTES + ATT_STATIC_O_BYTES;
+
+static __device__ __align__(256) unsigned char g_attn_static_scratch[ATT_STATIC_BYTES];
+
+int report_error(int code, const char* message);
+int check_gather_attend_args(const loda_geometry*, const loda_layer*, const void*, const int32_t*,
+                             const int32_t*, const int32_t*, int32_t, int32_t, const void*);
+
+// Device address of the static scratch on the current device.  The array's name
+// is only a host-side handle; the address a kernel can use comes from
+// cudaGetSymbolAddress, looked up once per device with that device current.
+static int static_scratch_address(unsigned char** out) {
+  constexpr int kMaxDevices = 64;
+  static unsigned char* address[kMaxDevices] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return report_error(LODA_ERR_LAUNCH, "cudaGetDevice failed or device ordinal >= 64");
+  if (address[dev] == nullptr) {
+    unsigned char* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_attn_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      char msg[160];
+      snprintf(msg, sizeof(msg), "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+      return report_error(LODA_ERR_LAUNCH, msg);
+    }
+    address[dev] = p;
+  }
+  *out = address[dev];
+  return LODA_OK;
+}
+
 }  // namespace loda
+
+extern "C" int loda_gather_attend_static(const loda_geometry* g, const loda_layer* layer, const void* q,
+                                         const int32_t* gather, const int32_t* visible_lens,
+                                         const int32_t* query_to_req, int32_t n_query, int32_t n_req_rows,
+                                         float scale, void* out, void* stream) {
+  using namespace loda;
+  const int rc = check_gather_attend_args(g, layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, out);
+  if (rc != LODA_OK) return rc;
+  if (n_query == 0) return LODA_OK;
+  const int G = g->num_q_heads / g->num_kv_heads;
+  if (n_query * g->num_kv_heads > ATT_STATIC_MAX_PAIRS || G > ATT_STATIC_MAX_G || g->head_dim_v > ATT_STATIC_MAX_DV) {
+    char msg[200];
+    snprintf(msg, sizeof(msg),
+             "static-scratch gather attention is limited to n_query * num_kv_heads <= %d, group <= %d, "
+             "head_dim_v <= %d (got %d, %d, %d); use loda_gather_attend with a workspace",
+             ATT_STATIC_MAX_PAIRS, ATT_STATIC_MAX_G, ATT_STATIC_MAX_DV, n_query * g->num_kv_heads, G, g->head_dim_v);
+    return report_error(LODA_ERR_UNSUPPORTED, msg);
+  }
+  unsigned char* base = nullptr;
+  const int rc2 = static_scratch_address(&base);
+  if (rc2 != LODA_OK) return rc2;
+  AttnWorkspace ws;
+  ws.ticket = (int*)base;
+  ws.part_m = (float*)(base + ATT_STATIC_TICKET_BYTES);
+  ws.part_z = (float*)(base + ATT_STATIC_TICKET_BYTES + ATT_STATIC_MZ_BYTES);
+  ws.part_o = (float*)(base + ATT_STATIC_TICKET_BYTES + 2 * ATT_STATIC_MZ_BYTES);
+  // the array keeps whatever the previous call left: the tickets must start at zero
+  cudaError_t e = cudaMemsetAsync(ws.ticket, 0, ATT_STATIC_TICKET_BYTES, (cudaStream_t)stream);
+  if (e == cudaSuccess)
+    e = launch_attn(*g, *layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale, out, ws,
+                    (cudaStream_t)stream);
+  if (e != cudaSuccess) {
+    char msg[160];
+    snprintf(msg, sizeof(msg), "gather_attend_static: %s", cudaGetErrorString(e));
+    return report_error(LODA_ERR_LAUNCH, msg);
+  }
+  return LODA_OK;
+}

@@ -123,6 +123,25 @@ static int check_batch(const loda_geometry* g, const loda_batch* b) {
   return LODA_OK;
 }
 
+// Shared with entry points that live next to their kernels.
+int report_error(int code, const char* message) { return fail(code, "%s", message); }
+
+int check_gather_attend_args(const loda_geometry* g, const loda_layer* layer, const void* q,
+                             const int32_t* gather, const int32_t* visible_lens, const int32_t* query_to_req,
+                             int32_t n_query, int32_t n_req_rows, const void* out) {
+  int rc = check_geometry(g);
+  if (rc != LODA_OK) return rc;
+  rc = check_layer(layer, false);
+  if (rc != LODA_OK) return rc;
+  if (n_query < 0 || n_query > g->max_query_tokens)
+    return fail(LODA_ERR_ARGUMENT, "n_query must be in [0, max_query_tokens]");
+  if (n_query > 0 && (!q || !gather || !visible_lens || !query_to_req || !out || n_req_rows < 1))
+    return fail(LODA_ERR_ARGUMENT, "gather attention needs q, gather, visible_lens, query_to_req and out");
+  if (!((g->head_dim == 128 && g->head_dim_v == 128) || (g->head_dim == 64 && g->head_dim_v == 64)))
+    return fail(LODA_ERR_UNSUPPORTED, "gather attention supports head dims 64 and 128");
+  return LODA_OK;
+}
+
 }  // namespace loda
 
 using namespace loda;
