@@ -176,7 +176,7 @@ def preplan(torch, wl, first_len, n_steps):
     return lengths.to(cache.device), slots.to(cache.device)
 
 
-def launch_step(capi, lib, wl, s, lengths, slots, out, which=("append", "l1", "l2", "attn"), layers=None):
+def launch_step(capi, lib, wl, s, lengths, slots, out, which="fused", layers=None):
     """One decode step over the layers through the C ABI (device-resident inputs)."""
     rt, cache = wl.rt, wl.cache
     g = C.byref(rt.geometry)
@@ -190,6 +190,12 @@ def launch_step(capi, lib, wl, s, lengths, slots, out, which=("append", "l1", "l
         layer = C.byref(rt.layer_structs[li])
         sel = rt.selection_struct(cache.gather_indices_for_layer(li), cache.visible_lens_for_layer(li), False)
         qp = capi.ptr(wl.q[s, li])
+        if which == "fused":      # the product path: append rides in the L1 launch, then L2, then attention
+            capi.check(lib.loda_decode_step(
+                g, layer, C.byref(batch), qp, capi.ptr(wl.k[s, li]), capi.ptr(wl.v[s, li]),
+                capi.ptr(slots[s, li]), scale, C.byref(sel), capi.ptr(cache.query_to_req_buf),
+                capi.ptr(out[li]), status, ws, stream))
+            continue
         if "append" in which:
             capi.check(lib.loda_append_decode(g, layer, C.byref(batch), capi.ptr(wl.k[s, li]), capi.ptr(wl.v[s, li]),
                                               capi.ptr(slots[s, li]), status, stream))
@@ -463,7 +469,7 @@ def main():
                              "ours_over_dense": (us_layer / dense_us) if dense_us else None},
             "e2e": {"value": world * 1e3 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": K * N_LAYERS * 4, "device_status": status, "clocks": clocks,
+            "gpu_launches": K * N_LAYERS * 3, "device_status": status, "clocks": clocks,
         }
         if not args.skip_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(sample_steps=3)

@@ -170,6 +170,17 @@ int loda_select_l2(const loda_geometry* g, const loda_layer* layer, const loda_b
                    const void* q, float scale, const loda_selection* sel,
                    uint32_t* status, void* workspace, void* stream);
 
+/* Append + L1 + L2 of one layer in two launches: the append (or, with k_new ==
+ * v_new == NULL, the index refresh) rides in extra CTAs of the L1 launch — it
+ * only touches the newest token and its page, which this step's selection
+ * never reads.  This is what select_topk_for_layer_batched(decode_write=...)
+ * does in the reference with its fused owner write
+ * (nfa_layer_batch_selector.py:1005-1078, 2649-2720). */
+int loda_select_step(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
+                     const void* q, const void* k_new, const void* v_new, const int32_t* slots,
+                     float scale, const loda_selection* sel, uint32_t* status,
+                     void* workspace, void* stream);
+
 /* Gather attention over the selected slots with split-K and a log-sum-exp
  * merge.  Replaces sparse_paged_attention_gather (paged_region_kernels.py:
  * 800-1041).  q [n_query, Hq, head_dim], query_to_req [n_query] (<0: output

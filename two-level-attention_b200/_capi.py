@@ -51,7 +51,8 @@ class Selection(C.Structure):
 
 EXPORTS = ("loda_version", "loda_last_error", "loda_workspace_bytes", "loda_append_decode",
            "loda_write_prefill", "loda_build_index", "loda_select_l1", "loda_select_l2",
-           "loda_gather_attend", "loda_decode_step", "loda_gather_attend_static")
+           "loda_gather_attend", "loda_decode_step", "loda_gather_attend_static",
+           "loda_select_step")
 
 _lib = None
 
@@ -79,6 +80,7 @@ def lib():
     L.loda_select_l2.argtypes = [G, LY, B, P, F, S, P, P, V]
     L.loda_gather_attend.argtypes = [G, LY, P, P, P, P, I, I, F, P, P, V]
     L.loda_gather_attend_static.argtypes = [G, LY, P, P, P, P, I, I, F, P, V]
+    L.loda_select_step.argtypes = [G, LY, B, P, P, P, P, F, S, P, P, V]
     L.loda_decode_step.argtypes = [G, LY, B, P, P, P, P, F, S, P, P, P, P, V]
     for name in EXPORTS[3:]:
         getattr(L, name).restype = C.c_int

@@ -68,6 +68,8 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int split = blockIdx.x, kv = blockIdx.y, t = blockIdx.z;
   const int G = g.num_q_heads / g.num_kv_heads;
+  pdl_wait();
+  pdl_launch_dependents();
   const int req = query_to_req[t];
   int n = 0;
   if (req >= 0 && req < n_req_rows) n = min(max(visible_lens[(size_t)req * g.num_kv_heads + kv], 0), g.max_visible);
@@ -247,20 +249,52 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
   __syncthreads();
   if (!sh[0]) return;
   __threadfence();
-  for (int e = tid; e < G * DV; e += ATT_NT) {
-    const int gi = e / DV, dv = e % DV;
+  // all (m, z) pairs in one round of loads, weights once per (split, head), then
+  // every output element sums its splits in split order from independent loads
+  float* sm_m = wo;                          // [nsplit * G]
+  float* sm_z = wo + ATT_MAX_SPLIT * 16;     // [nsplit * G]
+  float* sm_w = wo + 2 * ATT_MAX_SPLIT * 16; // [nsplit * G] weight of each split
+  float* sm_zt = wo + 3 * ATT_MAX_SPLIT * 16;  // [G]
+  for (int i = tid; i < nsplit * G; i += ATT_NT) {
+    sm_m[i] = __ldcg(ws.part_m + pair * nsplit * G + i);
+    sm_z[i] = __ldcg(ws.part_z + pair * nsplit * G + i);
+  }
+  __syncthreads();
+  if (tid < G) {
     float M = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, __ldcg(ws.part_m + (pair * nsplit + s) * G + gi));
-    float z = 0.0f, o = 0.0f;
-    if (M != -INFINITY) {
-      for (int s = 0; s < nsplit; ++s) {
-        const size_t ps = pair * nsplit + s;
-        const float a = exp2f(__ldcg(ws.part_m + ps * G + gi) - M);
-        z += __ldcg(ws.part_z + ps * G + gi) * a;
-        o += __ldcg(ws.part_o + (ps * G + gi) * DV + dv) * a;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, sm_m[s * G + tid]);
+    float z = 0.0f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float a = M == -INFINITY ? 0.0f : exp2f(sm_m[s * G + tid] - M);
+      sm_w[s * G + tid] = a;
+      z += sm_z[s * G + tid] * a;
+    }
+    sm_zt[tid] = z;
+  }
+  __syncthreads();
+  const float* po = ws.part_o + pair * nsplit * G * DV;
+  for (int e = tid; e < G * DV / 4; e += ATT_NT) {
+    const int gi = e / (DV / 4), dv = (e % (DV / 4)) * 4;
+    float4 v[ATT_MAX_SPLIT];
+#pragma unroll
+    for (int s = 0; s < ATT_MAX_SPLIT; ++s)
+      v[s] = s < nsplit ? __ldcg((const float4*)(po + ((size_t)s * G + gi) * DV + dv)) : make_float4(0, 0, 0, 0);
+    float4 o = make_float4(0, 0, 0, 0);
+#pragma unroll
+    for (int s = 0; s < ATT_MAX_SPLIT; ++s) {
+      if (s < nsplit) {
+        const float a = sm_w[s * G + gi];
+        o.x += v[s].x * a; o.y += v[s].y * a; o.z += v[s].z * a; o.w += v[s].w * a;
       }
     }
-    out[((size_t)t * g.num_q_heads + kv * G + gi) * DV + dv] = __float2bfloat16_rn(z == 0.0f ? 0.0f : o / z);
+    const float z = sm_zt[gi];
+    const float inv = z == 0.0f ? 0.0f : 1.0f / z;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(o.x * inv, o.y * inv);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(o.z * inv, o.w * inv);
+    uint2 packed;
+    packed.x = *(uint32_t*)&lo;
+    packed.y = *(uint32_t*)&hi;
+    *(uint2*)(out + ((size_t)t * g.num_q_heads + kv * G + gi) * DV + dv) = packed;
   }
   if (tid == 0) ws.ticket[pair] = 0;
 }
@@ -268,7 +302,8 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
 size_t attn_smem_bytes(const loda_geometry& g) {
   const int G = g.num_q_heads / g.num_kv_heads;
   return (size_t)ATT_TILE * (g.head_dim + 8) * 2 + (size_t)ATT_TILE * (g.head_dim_v + 8) * 2 + ATT_TILE * 4 +
-         2 * ATT_WARPS * 16 * 4 + 16 + (size_t)ATT_WARPS * G * g.head_dim_v * 4;
+         2 * ATT_WARPS * 16 * 4 + 16 +
+         sizeof(float) * (size_t)((ATT_WARPS * G * g.head_dim_v) > 1024 ? (ATT_WARPS * G * g.head_dim_v) : 1024);
 }
 
 int attn_nsplit(const loda_geometry& g, int n_query) {
@@ -293,13 +328,15 @@ cudaError_t launch_attn(const loda_geometry& g, const loda_layer& L, const void*
   if (g.head_dim == 128 && g.head_dim_v == 128) {
     e = cudaFuncSetAttribute(attn_kernel<128, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    attn_kernel<128, 128><<<grid, ATT_NT, smem, st>>>(g, L, (const bf16*)q, gather, visible_lens, query_to_req,
-                                                      n_req_rows, scale_log2, (bf16*)out, ws, nsplit);
+    e = launch_pdl(attn_kernel<128, 128>, grid, dim3(ATT_NT), smem, st, g, L, (const bf16*)q, gather,
+                   visible_lens, query_to_req, n_req_rows, scale_log2, (bf16*)out, ws, nsplit);
+    if (e != cudaSuccess) return e;
   } else if (g.head_dim == 64 && g.head_dim_v == 64) {
     e = cudaFuncSetAttribute(attn_kernel<64, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    attn_kernel<64, 64><<<grid, ATT_NT, smem, st>>>(g, L, (const bf16*)q, gather, visible_lens, query_to_req,
-                                                    n_req_rows, scale_log2, (bf16*)out, ws, nsplit);
+    e = launch_pdl(attn_kernel<64, 64>, grid, dim3(ATT_NT), smem, st, g, L, (const bf16*)q, gather,
+                   visible_lens, query_to_req, n_req_rows, scale_log2, (bf16*)out, ws, nsplit);
+    if (e != cudaSuccess) return e;
   } else {
     return cudaErrorInvalidValue;
   }

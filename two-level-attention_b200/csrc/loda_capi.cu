@@ -14,7 +14,7 @@ cudaError_t launch_build_index(const loda_geometry&, const loda_layer&, int, int
 cudaError_t launch_write_prefill(const loda_geometry&, const loda_layer&, const void*, const void*,
                                  const int32_t*, int, cudaStream_t);
 cudaError_t launch_l1(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
-                      const loda_selection&, const L1Workspace&, cudaStream_t);
+                      const loda_selection&, const L1Workspace&, const AppendArgs&, cudaStream_t);
 cudaError_t launch_l2(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
                       const loda_selection&, uint32_t*, cudaStream_t);
 cudaError_t launch_attn(const loda_geometry&, const loda_layer&, const void*, const int32_t*, const int32_t*,
@@ -212,7 +212,31 @@ int loda_select_l1(const loda_geometry* g, const loda_layer* layer, const loda_b
   char* base = (char*)workspace;
   const L1Workspace ws{(int*)(base + w.l1_ticket), (int*)(base + w.l1_cnt_far), (int*)(base + w.l1_cnt_near),
                        (uint32_t*)(base + w.l1_part_far), (uint32_t*)(base + w.l1_part_near)};
-  return check_cuda(launch_l1(*g, *layer, *b, q, scale, *out, ws, (cudaStream_t)stream), "select_l1");
+  const AppendArgs none{nullptr, nullptr, nullptr, nullptr, 0};
+  return check_cuda(launch_l1(*g, *layer, *b, q, scale, *out, ws, none, (cudaStream_t)stream), "select_l1");
+}
+
+int loda_select_step(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
+                     const void* k_new, const void* v_new, const int32_t* slots, float scale,
+                     const loda_selection* sel, uint32_t* status, void* workspace, void* stream) {
+  LODA_TRY(check_geometry(g));
+  LODA_TRY(check_layer(layer));
+  LODA_TRY(check_batch(g, b));
+  if (b->batch == 0) return LODA_OK;
+  if (!q || !sel || !sel->i_far || !sel->i_near || !sel->n_far || !sel->n_near || !sel->gather ||
+      !sel->visible_lens || !workspace)
+    return fail(LODA_ERR_ARGUMENT, "select_step needs q, the selection buffers and a workspace");
+  if ((sel->middle == nullptr) != (sel->middle_counts == nullptr))
+    return fail(LODA_ERR_ARGUMENT, "middle and middle_counts must be given together");
+  if ((k_new == nullptr) != (v_new == nullptr) || (k_new && !slots))
+    return fail(LODA_ERR_ARGUMENT, "k_new, v_new and slots go together (all NULL = refresh the index only)");
+  const WsLayout w = ws_layout(*g);
+  char* base = (char*)workspace;
+  const L1Workspace ws{(int*)(base + w.l1_ticket), (int*)(base + w.l1_cnt_far), (int*)(base + w.l1_cnt_near),
+                       (uint32_t*)(base + w.l1_part_far), (uint32_t*)(base + w.l1_part_near)};
+  const AppendArgs ap{(const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, slots, status, 1};
+  LODA_TRY(check_cuda(launch_l1(*g, *layer, *b, q, scale, *sel, ws, ap, (cudaStream_t)stream), "select_step/l1"));
+  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, status, (cudaStream_t)stream), "select_step/l2");
 }
 
 int loda_select_l2(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
@@ -255,9 +279,7 @@ int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda
                      const void* k_new, const void* v_new, const int32_t* slots, float scale,
                      const loda_selection* sel, const int32_t* query_to_req, void* out, uint32_t* status,
                      void* workspace, void* stream) {
-  LODA_TRY(loda_append_decode(g, layer, b, k_new, v_new, slots, status, stream));
-  LODA_TRY(loda_select_l1(g, layer, b, q, scale, sel, workspace, stream));
-  LODA_TRY(loda_select_l2(g, layer, b, q, scale, sel, status, workspace, stream));
+  LODA_TRY(loda_select_step(g, layer, b, q, k_new, v_new, slots, scale, sel, status, workspace, stream));
   return loda_gather_attend(g, layer, q, sel->gather, sel->visible_lens, query_to_req, b->batch,
                             g->max_requests, scale, out, workspace, stream);
 }

@@ -130,9 +130,19 @@ __device__ __forceinline__ uint32_t block_kth_largest(const uint32_t* keys, int 
   for (int shift = 24; shift >= 0; shift -= 8) {
     for (int i = threadIdx.x; i < 256; i += NT) hist[i] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += NT) {
-      const uint32_t key = keys[i];
-      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
+    // warp-aggregated histogram: lanes holding the same digit elect one lane to
+    // add their count (scores share their leading bits, so un-aggregated atomics
+    // would serialise 32-way on one shared-memory word)
+    for (int base = 0; base < n; base += NT) {
+      const int i = base + threadIdx.x;
+      const uint32_t key = i < n ? keys[i] : 0u;
+      const bool live = i < n && (key & mask) == prefix;
+      const unsigned active = __ballot_sync(0xffffffffu, live);
+      if (live) {
+        const uint32_t digit = (key >> shift) & 255u;
+        const unsigned peers = __match_any_sync(active, digit);
+        if ((threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[digit], __popc(peers));
+      }
     }
     __syncthreads();
     if (threadIdx.x < 32) {
@@ -177,6 +187,42 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src,
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// ---------------------------------------------------------------------------
+// programmatic dependent launch: a kernel of the chain may be scheduled while
+// its predecessor in the stream still runs; it must not touch memory before
+// pdl_wait(), which returns once the predecessor has completed and flushed.
+// Both are no-ops for a kernel launched without the attribute.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// decode append carried by extra CTAs of the L1 launch (enabled == 0: none)
+struct AppendArgs {
+  const __nv_bfloat16* k_new;   // NULL with enabled != 0: refresh the index only
+  const __nv_bfloat16* v_new;
+  const int32_t* slots;
+  uint32_t* status;
+  int enabled;
+};
 
 // scratch views handed to the kernels (carved out of the caller's workspace)
 struct L1Workspace {

@@ -19,11 +19,9 @@
 // chunks); per-head scores are rounded to bf16, summed over the GQA group in
 // head order, divided by G and rounded to bf16.  bf16 x bf16 products are exact
 // in fp32, so fmaf equals a separate multiply and add here.
-#include "loda_common.cuh"
+#include "loda_append.cuh"
 
 namespace loda {
-
-using bf16 = __nv_bfloat16;
 
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xFFFF0000u);
@@ -69,20 +67,24 @@ __device__ void merge_partials(const uint32_t* part, const int* cnt, int nsplit,
                                uint32_t* buf, uint32_t* sel, int* ids_sorted, int* hist, int* sh,
                                int32_t* out_ids, int32_t* out_n, int max_blocks) {
   const int tid = threadIdx.x;
+  // counts of all splits in one round of loads, offsets by a short serial scan
+  int* cnts = hist;            // [nsplit] (hist is free until the select below)
+  int* offs = hist + 129;      // [nsplit]
+  for (int s = tid; s < nsplit; s += NT) cnts[s] = min(__ldcg(cnt + s), kcap);
+  __syncthreads();
   if (tid == 0) {
     int total = 0;
-    for (int s = 0; s < nsplit; ++s) total += min(__ldcg(cnt + s), kcap);
+    for (int s = 0; s < nsplit; ++s) { offs[s] = total; total += cnts[s]; }
     sh[0] = total;
     sh[1] = 0;
   }
   __syncthreads();
   const int total = sh[0];
-  // gather: split s occupies buf[offset_s, offset_s + c_s)
-  int offset = 0;
-  for (int s = 0; s < nsplit; ++s) {
-    const int c = min(__ldcg(cnt + s), kcap);
-    for (int i = tid; i < c; i += NT) buf[offset + i] = __ldcg(part + (size_t)s * kcap + i);
-    offset += c;
+  // gather every partial key with independent loads
+#pragma unroll 4
+  for (int idx = tid; idx < nsplit * kcap; idx += NT) {
+    const int s = idx / kcap, i = idx - s * kcap;
+    if (i < cnts[s]) buf[offs[s] + i] = __ldcg(part + idx);
   }
   __syncthreads();
   int n = total;
@@ -128,7 +130,8 @@ __device__ void merge_partials(const uint32_t* part, const int* cnt, int nsplit,
 template <int DSUB, int P>
 __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, loda_batch B,
                                                 const bf16* __restrict__ q, float scale,
-                                                loda_selection out, L1Workspace ws, int nsplit) {
+                                                loda_selection out, L1Workspace ws, int nsplit,
+                                                AppendArgs ap) {
   constexpr int NC = DSUB / 8;            // 8-dim chunks per statistic
   constexpr int CPR = 2 * NC;             // 16-byte chunks per min/max row
   constexpr int ROWB = 4 * DSUB + 16;     // padded row: conflict-free 16-byte reads
@@ -146,6 +149,15 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   const int tid = threadIdx.x;
   const int split = blockIdx.x, row = blockIdx.y;
   const int b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
+  pdl_wait();
+  pdl_launch_dependents();
+  if (split == nsplit) {
+    // extra CTA of the row: the decode append.  It touches only the newest token
+    // and its page, which lie in the sliding window and are read by neither L1
+    // nor L2 of this step; the attention kernel runs after this launch completes.
+    if (tid < 32) append_row<DSUB>(g, L, B, ap.k_new, ap.v_new, ap.slots, ap.status, b, kv, tid);
+    return;
+  }
   const bool active = B.active_req_ids[b] >= 0;
   const int length = active ? B.lengths[b] : 0;
   const int req = (int)B.valid_req_ids[b];
@@ -264,9 +276,10 @@ size_t l1_smem_bytes(const loda_geometry& g) {
 int l1_nsplit(const loda_geometry& g) { return (g.max_blocks + L1_P - 1) / L1_P; }
 
 cudaError_t launch_l1(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
-                      float scale, const loda_selection& out, const L1Workspace& ws, cudaStream_t st) {
+                      float scale, const loda_selection& out, const L1Workspace& ws, const AppendArgs& ap,
+                      cudaStream_t st) {
   const int nsplit = l1_nsplit(g);
-  const dim3 grid(nsplit, B.batch * g.num_kv_heads);
+  const dim3 grid(nsplit + (ap.enabled ? 1 : 0), B.batch * g.num_kv_heads);
   const size_t smem = l1_smem_bytes(g);
   cudaError_t e = cudaSuccess;
 #define LODA_L1_CASE(DS)                                                                            \
@@ -277,7 +290,9 @@ cudaError_t launch_l1(const loda_geometry& g, const loda_layer& L, const loda_ba
       if (e != cudaSuccess) return e;                                                               \
       attr_set = true;                                                                              \
     }                                                                                               \
-    l1_kernel<DS, L1_P><<<grid, L1_P, smem, st>>>(g, L, B, (const bf16*)q, scale, out, ws, nsplit); \
+    e = launch_pdl(l1_kernel<DS, L1_P>, grid, dim3(L1_P), smem, st, g, L, B, (const bf16*)q, scale, out, ws, \
+                   nsplit, ap);                                                                     \
+    if (e != cudaSuccess) return e;                                                                 \
   } break;
   switch (g.sub_dims) {
     LODA_L1_CASE(16)

@@ -110,6 +110,11 @@ __global__ void __launch_bounds__(NT) l2_kernel(loda_geometry g, loda_layer L, l
     m.qf[tid] = acc;
   }
 
+  // everything above depends only on inputs of the step; the L1 results below
+  // are produced by the preceding launch
+  pdl_wait();
+  pdl_launch_dependents();
+
   // ---- page list -------------------------------------------------------------
   int np = 0;
   const int n_f = rg.quota > 0 ? min(S.n_far[row], g.k_far) : 0;
@@ -275,7 +280,9 @@ cudaError_t launch_l2(const loda_geometry& g, const loda_layer& L, const loda_ba
   case DS:                                                                                               \
     e = cudaFuncSetAttribute(l2_kernel<DS, L2_NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e != cudaSuccess) return e;                                                                      \
-    l2_kernel<DS, L2_NT><<<grid, L2_NT, smem, st>>>(g, L, B, (const bf16*)q, scale, S, status);          \
+    e = launch_pdl(l2_kernel<DS, L2_NT>, grid, dim3(L2_NT), smem, st, g, L, B, (const bf16*)q, scale, S, \
+                   status);                                                                              \
+    if (e != cudaSuccess) return e;                                                                      \
     break;
   switch (g.sub_dims) {
     LODA_L2_CASE(16)

@@ -4,9 +4,10 @@ Mirrors select_topk_for_layer_batched (reference: sparse_attn/indexer/
 nfa_layer_batch_selector.py:2649-2720, implementation :2723-3091): same
 arguments, results written in place into ``cache.gather_indices_for_layer`` /
 ``cache.visible_lens_for_layer``, ValueError on contract violations and
-FallbackRequired for configurations the CUDA path does not cover.  Three
-launches replace the reference's eleven: append/refresh of the index, fused L1
-score + select, fused L2 score + select + union.
+FallbackRequired for configurations the CUDA path does not cover.  Two
+launches replace the reference's eleven: fused L1 score + select (which also
+carries the append / index refresh in extra CTAs) and fused L2 score + select
++ union.
 """
 from __future__ import annotations
 
@@ -96,17 +97,14 @@ def select_topk_for_layer_batched(cache, layer_idx, req_ids, query_states, atten
         k = keys.to(cache.dtype).contiguous()
         v = values.to(cache.dtype).contiguous()
         slots = slots.to(device=k.device, dtype=torch.int32).contiguous()
-        _capi.check(lib.loda_append_decode(g, layer, C.byref(batch), _capi.ptr(k), _capi.ptr(v),
-                                           _capi.ptr(slots), status, stream))
+        kp, vp, sp = _capi.ptr(k), _capi.ptr(v), _capi.ptr(slots)
     else:
-        _capi.check(lib.loda_append_decode(g, layer, C.byref(batch), None, None, None, status, stream))
+        kp = vp = sp = None      # K/V already in the pool: refresh the index of the newest token
     gather = cache.gather_indices_for_layer(layer_idx)
     lens = cache.visible_lens_for_layer(layer_idx)
     sel = rt.selection_struct(gather, lens)
-    _capi.check(lib.loda_select_l1(g, layer, C.byref(batch), _capi.ptr(q), scale, C.byref(sel),
-                                   _capi.ptr(rt.workspace), stream))
-    _capi.check(lib.loda_select_l2(g, layer, C.byref(batch), _capi.ptr(q), scale, C.byref(sel), status,
-                                   _capi.ptr(rt.workspace), stream))
+    _capi.check(lib.loda_select_step(g, layer, C.byref(batch), _capi.ptr(q), kp, vp, sp, scale, C.byref(sel),
+                                     status, _capi.ptr(rt.workspace), stream))
 
 
 def last_middle_selection(cache, batch):
