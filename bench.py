@@ -188,7 +188,7 @@ def launch_step(capi, lib, wl, s, lengths, slots, out, which="fused", layers=Non
                        active_req_ids=cache.active_req_ids_buf.data_ptr())
     for li in (range(N_LAYERS) if layers is None else layers):
         layer = C.byref(rt.layer_structs[li])
-        sel = rt.selection_struct(cache.gather_indices_for_layer(li), cache.visible_lens_for_layer(li), False)
+        sel = rt.selection_struct(cache.gather_indices_for_layer(li), cache.visible_lens_for_layer(li), False, False)
         qp = capi.ptr(wl.q[s, li])
         if which == "fused":      # the product path: append rides in the L1 launch, then L2, then attention
             capi.check(lib.loda_decode_step(

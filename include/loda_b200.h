@@ -101,8 +101,11 @@ typedef struct loda_batch {
 } loda_batch;
 
 /* Selection outputs (workspace tensors of the reference selector).
- *   i_far [batch, Hkv, k_far], i_near [batch, Hkv, k_near]: page ids, best first;
- *   n_far / n_near [batch, Hkv]: how many leading entries carry a finite score
+ *   i_far [batch, Hkv, k_far], i_near [batch, Hkv, k_near]: page ids, best first,
+ *   then fillers; n_far / n_near [batch, Hkv]: how many leading entries carry a
+ *   finite score.  These four are OPTIONAL (all NULL or all given): the page
+ *   list travels from L1 to L2 inside the workspace in ascending page order,
+ *   and the best-first lists are only written when asked for (parity checks).
  *   gather [>=batch, Hkv, max_visible] physical slots in ascending logical order
  *   visible_lens [>=batch, Hkv]
  *   middle / middle_counts (optional, may be NULL): the L2 survivors as logical
@@ -156,14 +159,17 @@ int loda_build_index(const loda_geometry* g, const loda_layer* layer, int32_t re
 /* L1: page scores from the min/max bound (far pool) and page mean (near pool),
  * exact top-k per pool with ties toward the lower page id.  Replaces
  * _l1_scores + the L1 top-k kernels (nfa_layer_batch_selector.py:174-354,
- * 1473-1863).  q [batch, Hq, head_dim]. */
+ * 1473-1863).  q [batch, Hq, head_dim].  Leaves the surviving pages of every
+ * row (ascending, bypass pages included, with their physical page ids) in the
+ * workspace for loda_select_l2. */
 int loda_select_l1(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
                    const void* q, float scale, const loda_selection* out,
                    void* workspace, void* stream);
 
 /* L2: grouped-query logits on the packed 4-bit tail keys of the surviving
  * pages, exact top-quota with ties toward the lower token id, hole fill, union
- * with sink and window tokens, logical -> physical slots.  Replaces candidate
+ * with sink and window tokens, logical -> physical slots.  Must follow
+ * loda_select_l1 of the same batch on the same workspace.  Replaces candidate
  * expansion, fine scores, filtered top-k and the final union
  * (nfa_layer_batch_selector.py:422-848, 1116-1437). */
 int loda_select_l2(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,

@@ -15,7 +15,7 @@ ATOL = RTOL = 2e-2      # bf16 attention tolerance of the specification
 # ragged, tiny, page-aligned and long requests in one batch
 LENGTHS_A = [1, 3, 4, 5, 16, 17, 100, 131]
 LENGTHS_B = [132, 133, 200, 1003, 1280, 1500, 2500, 4400]
-LENGTHS_C = [6000, 12289, 20000, 4229, 4240, 4241]
+LENGTHS_C = [6000, 12289, 20000, 4229, 4240, 4241, 40000]
 
 
 def _run_step(setup, fused_write=True):

@@ -10,7 +10,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libloda_b200.so")
+LIB_PATH = os.environ.get("LODA_B200_LIBRARY") or os.path.join(HERE, "libloda_b200.so")
 
 LODA_DTYPE_BF16 = 0
 LODA_DTYPE_FP32 = 1

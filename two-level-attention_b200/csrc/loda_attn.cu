@@ -13,8 +13,15 @@
 // owns 16 tokens of a tile: S = Q K^T with mma.sync m16n8k16 (M = the GQA group
 // padded to 16 rows, operands bf16, fp32 accumulate), fp32 online softmax in the
 // exp2 domain, O += P V with P rounded to bf16.  Warps, then splits, are merged
-// by log-sum-exp in a fixed order; the last CTA of a (t, h) pair to finish
-// (atomic ticket, no spinning) performs the split merge and writes bf16.
+// by log-sum-exp in a fixed order.  The splits of a (t, h) pair form one thread
+// block cluster: after a cluster barrier each CTA reduces its slice of the
+// output columns straight out of its peers' shared memory (DSMEM), so the
+// partials never touch global memory.  Where a cluster of that size cannot be
+// launched, and for the static-scratch entry point, the partials go through
+// global scratch and the last CTA of the pair to finish (atomic ticket, no
+// spinning) performs the merge.
+#include <cooperative_groups.h>
+
 #include <cstdio>
 
 #include "loda_common.cuh"
@@ -22,6 +29,7 @@
 namespace loda {
 
 using bf16 = __nv_bfloat16;
+namespace cg = cooperative_groups;
 
 constexpr int ATT_TILE = 64;
 constexpr int ATT_WARPS = 4;
@@ -49,7 +57,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *(uint32_t*)&v;
 }
 
-template <int D, int DV>
+LODA_PHASE_STORAGE(attn)
+
+template <int D, int DV, bool CLUSTER>
 __global__ void __launch_bounds__(ATT_NT) attn_kernel(
     loda_geometry g, loda_layer L, const bf16* __restrict__ q, const int32_t* __restrict__ gather,
     const int32_t* __restrict__ visible_lens, const int32_t* __restrict__ query_to_req,
@@ -63,13 +73,20 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
   float* wm = (float*)(slot_s + ATT_TILE);         // [WARPS][16]
   float* wz = wm + ATT_WARPS * 16;                 // [WARPS][16]
   int* sh = (int*)(wz + ATT_WARPS * 16);           // 4
-  float* wo = (float*)(sh + 4);                    // [WARPS][G][DV]
+  float* fm = (float*)(sh + 4);                    // [16] merged max of this CTA
+  float* fz = fm + 16;                             // [16] merged sum of this CTA
+  long long* rowoff = (long long*)(fz + 16);       // [TILE] pool row of each staged token
+  float* wo = (float*)(rowoff + ATT_TILE);         // [WARPS][G][DV]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int split = blockIdx.x, kv = blockIdx.y, t = blockIdx.z;
   const int G = g.num_q_heads / g.num_kv_heads;
+  const int page_log2 = 31 - __clz(g.page);
+  const int cta_id = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  LODA_PHASE(attn, cta_id, 0);
   pdl_wait();
   pdl_launch_dependents();
+  LODA_PHASE(attn, cta_id, 1);
   const int req = query_to_req[t];
   int n = 0;
   if (req >= 0 && req < n_req_rows) n = min(max(visible_lens[(size_t)req * g.num_kv_heads + kv], 0), g.max_visible);
@@ -92,6 +109,7 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
     }
   }
 
+  LODA_PHASE(attn, cta_id, 2);
   float oacc[NTV][4];
 #pragma unroll
   for (int i = 0; i < NTV; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.0f; }
@@ -104,25 +122,27 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
       int s = tid < ntok ? list[base + tid] : -1;
       if (s >= g.num_pages * g.page) s = -1;
       slot_s[tid] = s;
+      // page is a power of two: slot -> pool row without a division
+      rowoff[tid] = s >= 0 ? ((long long)(s >> page_log2) * g.num_kv_heads + kv) * g.page + (s & (g.page - 1)) : 0;
     }
     __syncthreads();
     // stage K and V rows: 16 lanes per 256-byte row
     constexpr int KCH = D / 8, VCH = DV / 8;
+#pragma unroll 4
     for (int c = tid; c < ATT_TILE * KCH; c += ATT_NT) {
       const int r = c / KCH, cc = c % KCH;
-      const int s = slot_s[r];
-      const size_t rowi = s >= 0 ? ((size_t)(s / g.page) * g.num_kv_heads + kv) * g.page + (s % g.page) : 0;
-      cp_async16(Ks + r * KSTR + cc * 8, (const bf16*)L.pool_k + rowi * D + cc * 8, s >= 0);
+      cp_async16(Ks + r * KSTR + cc * 8, (const bf16*)L.pool_k + rowoff[r] * D + cc * 8, slot_s[r] >= 0);
     }
+#pragma unroll 4
     for (int c = tid; c < ATT_TILE * VCH; c += ATT_NT) {
       const int r = c / VCH, cc = c % VCH;
-      const int s = slot_s[r];
-      const size_t rowi = s >= 0 ? ((size_t)(s / g.page) * g.num_kv_heads + kv) * g.page + (s % g.page) : 0;
-      cp_async16(Vs + r * VSTR + cc * 8, (const bf16*)L.pool_v + rowi * DV + cc * 8, s >= 0);
+      cp_async16(Vs + r * VSTR + cc * 8, (const bf16*)L.pool_v + rowoff[r] * DV + cc * 8, slot_s[r] >= 0);
     }
     cp_async_commit();
+    LODA_PHASE(attn, cta_id, 3);
     cp_async_wait<0>();
     __syncthreads();
+    LODA_PHASE(attn, cta_id, 4);
 
     const int tok0 = warp * 16;
     if (tok0 < ntok) {
@@ -203,6 +223,7 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
 
   // ---- merge the warps of this CTA (fixed order) -------------------------------
   __syncthreads();
+  LODA_PHASE(attn, cta_id, 5);
   {
     const int r0 = lane >> 2;
     if ((lane & 3) == 0) {
@@ -218,6 +239,7 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
   }
   __syncthreads();
   const size_t pair = (size_t)t * g.num_kv_heads + kv;
+  float* fo = (float*)Ks;   // [G][DV] merged output of this CTA (the K tile has been consumed)
   for (int e = tid; e < G * DV; e += ATT_NT) {
     const int gi = e / DV, dv = e % DV;
     float M = -INFINITY;
@@ -234,19 +256,63 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
     }
     if (nsplit == 1) {
       out[((size_t)t * g.num_q_heads + kv * G + gi) * DV + dv] = __float2bfloat16_rn(z == 0.0f ? 0.0f : o / z);
+    } else if (CLUSTER) {
+      fo[e] = o;
+      if (dv == 0) { fm[gi] = M; fz[gi] = z; }
     } else {
       const size_t ps = pair * nsplit + split;
       ws.part_o[(ps * G + gi) * DV + dv] = o;
       if (dv == 0) { ws.part_m[ps * G + gi] = M; ws.part_z[ps * G + gi] = z; }
     }
   }
+  LODA_PHASE(attn, cta_id, 6);
   if (nsplit == 1) return;
+  if constexpr (CLUSTER) {
+    // the nsplit CTAs of this (t, kv) pair are one cluster (rank == split): each
+    // reduces its slice of the G * DV outputs from every peer's shared memory
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    LODA_PHASE(attn, cta_id, 7);
+    const int per = (G * DV + nsplit - 1) / nsplit;
+    const int e = split * per + tid;
+    if (tid < per && e < G * DV) {
+      const int gi = e / DV, dv = e % DV;
+      float pm[ATT_MAX_SPLIT], pz[ATT_MAX_SPLIT], po[ATT_MAX_SPLIT];
+#pragma unroll
+      for (int s = 0; s < ATT_MAX_SPLIT; ++s) {
+        if (s < nsplit) {
+          pm[s] = cluster.map_shared_rank(fm, s)[gi];
+          pz[s] = cluster.map_shared_rank(fz, s)[gi];
+          po[s] = cluster.map_shared_rank(fo, s)[e];
+        } else {
+          pm[s] = -INFINITY; pz[s] = 0.0f; po[s] = 0.0f;
+        }
+      }
+      float M = -INFINITY;
+#pragma unroll
+      for (int s = 0; s < ATT_MAX_SPLIT; ++s) M = fmaxf(M, pm[s]);
+      float z = 0.0f, o = 0.0f;
+      if (M != -INFINITY) {
+#pragma unroll
+        for (int s = 0; s < ATT_MAX_SPLIT; ++s) {
+          const float a = exp2f(pm[s] - M);
+          z += pz[s] * a;
+          o += po[s] * a;
+        }
+      }
+      out[((size_t)t * g.num_q_heads + kv * G + gi) * DV + dv] = __float2bfloat16_rn(z == 0.0f ? 0.0f : o / z);
+    }
+    cluster.sync();   // nobody leaves while a peer may still read its shared memory
+    LODA_PHASE(attn, cta_id, 8);
+    return;
+  }
 
   // ---- last CTA of the (t, kv) pair merges the splits in split order -------------
   __threadfence();
   __syncthreads();
   if (tid == 0) sh[0] = (atomicAdd(ws.ticket + pair, 1) == nsplit - 1);
   __syncthreads();
+  LODA_PHASE(attn, cta_id, 7);
   if (!sh[0]) return;
   __threadfence();
   // all (m, z) pairs in one round of loads, weights once per (split, head), then
@@ -296,51 +362,88 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
     packed.y = *(uint32_t*)&hi;
     *(uint2*)(out + ((size_t)t * g.num_q_heads + kv * G + gi) * DV + dv) = packed;
   }
+  LODA_PHASE(attn, cta_id, 8);
   if (tid == 0) ws.ticket[pair] = 0;
 }
 
 size_t attn_smem_bytes(const loda_geometry& g) {
   const int G = g.num_q_heads / g.num_kv_heads;
+  const size_t wo = (size_t)ATT_WARPS * G * g.head_dim_v;
   return (size_t)ATT_TILE * (g.head_dim + 8) * 2 + (size_t)ATT_TILE * (g.head_dim_v + 8) * 2 + ATT_TILE * 4 +
-         2 * ATT_WARPS * 16 * 4 + 16 +
-         sizeof(float) * (size_t)((ATT_WARPS * G * g.head_dim_v) > 1024 ? (ATT_WARPS * G * g.head_dim_v) : 1024);
+         2 * ATT_WARPS * 16 * 4 + 16 + 2 * 16 * 4 + ATT_TILE * 8 + sizeof(float) * (wo > 1024 ? wo : 1024);
 }
 
+// power-of-two split count: enough CTAs to cover the GPU about twice, at least
+// one 64-token tile per split, at most ATT_MAX_SPLIT (the largest cluster)
 int attn_nsplit(const loda_geometry& g, int n_query) {
   const int pairs = n_query * g.num_kv_heads;
-  int ns = (2 * 148 + pairs - 1) / pairs;
-  const int by_len = (g.max_visible + ATT_TILE - 1) / ATT_TILE;   // at least one tile per split
-  if (ns > by_len) ns = by_len;
-  if (ns > ATT_MAX_SPLIT) ns = ATT_MAX_SPLIT;
-  if (ns < 1) ns = 1;
+  const int want = (2 * 148 + pairs - 1) / pairs;
+  const int by_len = (g.max_visible + ATT_TILE - 1) / ATT_TILE;
+  int ns = 1;
+  while (ns * 2 <= want && ns * 2 <= by_len && ns * 2 <= ATT_MAX_SPLIT) ns *= 2;
   return ns;
+}
+
+template <int D, int DV>
+static cudaError_t launch_attn_dims(const loda_geometry& g, const loda_layer& L, const void* q,
+                                    const int32_t* gather, const int32_t* visible_lens,
+                                    const int32_t* query_to_req, int n_query, int n_req_rows, float scale_log2,
+                                    void* out, const AttnWorkspace& ws, bool allow_cluster, cudaStream_t st) {
+  const int nsplit = attn_nsplit(g, n_query);
+  const dim3 grid(nsplit, g.num_kv_heads, n_query);
+  const size_t smem = attn_smem_bytes(g);
+  static bool cluster_ok = true;     // cleared if this GPU / driver refuses the cluster launch
+  cudaError_t e;
+  if (allow_cluster && cluster_ok && nsplit > 1) {
+    auto kernel = attn_kernel<D, DV, true>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess && nsplit > 8)
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = grid;
+      cfg.blockDim = dim3(ATT_NT);
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      attr[1].id = cudaLaunchAttributeClusterDimension;
+      attr[1].val.clusterDim.x = nsplit;
+      attr[1].val.clusterDim.y = 1;
+      attr[1].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 2;
+      e = cudaLaunchKernelEx(&cfg, kernel, g, L, (const bf16*)q, gather, visible_lens, query_to_req, n_req_rows,
+                             scale_log2, (bf16*)out, ws, nsplit);
+    }
+    if (e == cudaSuccess) return cudaSuccess;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(st, &cap);
+    if (cap != cudaStreamCaptureStatusNone) return e;   // cannot retry inside a capture
+    (void)cudaGetLastError();
+    cluster_ok = false;
+  }
+  auto kernel = attn_kernel<D, DV, false>;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  return launch_pdl(kernel, grid, dim3(ATT_NT), smem, st, g, L, (const bf16*)q, gather, visible_lens, query_to_req,
+                    n_req_rows, scale_log2, (bf16*)out, ws, nsplit);
 }
 
 cudaError_t launch_attn(const loda_geometry& g, const loda_layer& L, const void* q, const int32_t* gather,
                         const int32_t* visible_lens, const int32_t* query_to_req, int n_query,
-                        int n_req_rows, float scale, void* out, const AttnWorkspace& ws, cudaStream_t st) {
+                        int n_req_rows, float scale, void* out, const AttnWorkspace& ws, bool allow_cluster,
+                        cudaStream_t st) {
   if (n_query <= 0) return cudaSuccess;
-  const int nsplit = attn_nsplit(g, n_query);
-  const dim3 grid(nsplit, g.num_kv_heads, n_query);
-  const size_t smem = attn_smem_bytes(g);
   const float scale_log2 = scale * 1.4426950408889634f;
-  cudaError_t e;
-  if (g.head_dim == 128 && g.head_dim_v == 128) {
-    e = cudaFuncSetAttribute(attn_kernel<128, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    e = launch_pdl(attn_kernel<128, 128>, grid, dim3(ATT_NT), smem, st, g, L, (const bf16*)q, gather,
-                   visible_lens, query_to_req, n_req_rows, scale_log2, (bf16*)out, ws, nsplit);
-    if (e != cudaSuccess) return e;
-  } else if (g.head_dim == 64 && g.head_dim_v == 64) {
-    e = cudaFuncSetAttribute(attn_kernel<64, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    e = launch_pdl(attn_kernel<64, 64>, grid, dim3(ATT_NT), smem, st, g, L, (const bf16*)q, gather,
-                   visible_lens, query_to_req, n_req_rows, scale_log2, (bf16*)out, ws, nsplit);
-    if (e != cudaSuccess) return e;
-  } else {
-    return cudaErrorInvalidValue;
-  }
-  return cudaGetLastError();
+  if (g.head_dim == 128 && g.head_dim_v == 128)
+    return launch_attn_dims<128, 128>(g, L, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale_log2,
+                                      out, ws, allow_cluster, st);
+  if (g.head_dim == 64 && g.head_dim_v == 64)
+    return launch_attn_dims<64, 64>(g, L, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale_log2,
+                                    out, ws, allow_cluster, st);
+  return cudaErrorInvalidValue;
 }
 
 // ---------------------------------------------------------------------------
@@ -421,7 +524,7 @@ extern "C" int loda_gather_attend_static(const loda_geometry* g, const loda_laye
   cudaError_t e = cudaMemsetAsync(ws.ticket, 0, ATT_STATIC_TICKET_BYTES, (cudaStream_t)stream);
   if (e == cudaSuccess)
     e = launch_attn(*g, *layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale, out, ws,
-                    (cudaStream_t)stream);
+                    /*allow_cluster=*/false, (cudaStream_t)stream);   // this entry point exists for the scratch path
   if (e != cudaSuccess) {
     char msg[160];
     snprintf(msg, sizeof(msg), "gather_attend_static: %s", cudaGetErrorString(e));

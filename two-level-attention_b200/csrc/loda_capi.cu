@@ -14,11 +14,12 @@ cudaError_t launch_build_index(const loda_geometry&, const loda_layer&, int, int
 cudaError_t launch_write_prefill(const loda_geometry&, const loda_layer&, const void*, const void*,
                                  const int32_t*, int, cudaStream_t);
 cudaError_t launch_l1(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
-                      const loda_selection&, const L1Workspace&, const AppendArgs&, cudaStream_t);
+                      const loda_selection&, const SelectWorkspace&, const AppendArgs&, cudaStream_t);
 cudaError_t launch_l2(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
-                      const loda_selection&, uint32_t*, cudaStream_t);
+                      const loda_selection&, const SelectWorkspace&, uint32_t*, cudaStream_t);
+int l1_score_stride(const loda_geometry&);
 cudaError_t launch_attn(const loda_geometry&, const loda_layer&, const void*, const int32_t*, const int32_t*,
-                        const int32_t*, int, int, float, void*, const AttnWorkspace&, cudaStream_t);
+                        const int32_t*, int, int, float, void*, const AttnWorkspace&, bool, cudaStream_t);
 int l1_nsplit(const loda_geometry&);
 size_t l1_smem_bytes(const loda_geometry&);
 size_t l2_smem_bytes(const loda_geometry&);
@@ -44,29 +45,45 @@ static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 constexpr int kAttnMaxSplit = 16;
 
 struct WsLayout {
-  size_t l1_ticket, l1_cnt_far, l1_cnt_near, l1_part_far, l1_part_near;
-  size_t at_ticket, at_m, at_z, at_o, total;
+  size_t l1_ticket, l2_ticket, at_ticket, l1_scores, pages, phys, np, l2_scores;
+  size_t at_m, at_z, at_o, total;
 };
 
 static WsLayout ws_layout(const loda_geometry& g) {
-  const int max_batch = g.max_query_tokens, max_query = g.max_query_tokens;
   WsLayout w;
-  const size_t rows = (size_t)max_batch * g.num_kv_heads;
-  const size_t ns = l1_nsplit(g);
-  const size_t pairs = (size_t)max_query * g.num_kv_heads;
+  const size_t rows = (size_t)g.max_query_tokens * g.num_kv_heads;
+  const size_t pairs = rows;
   const size_t G = g.num_q_heads / g.num_kv_heads;
+  const size_t np_max = g.k_far + g.k_near + 2;
   size_t off = 0;
   w.l1_ticket = off; off = align_up(off + rows * 4, 256);
+  w.l2_ticket = off; off = align_up(off + rows * 4, 256);
   w.at_ticket = off; off = align_up(off + pairs * 4, 256);
-  w.l1_cnt_far = off; off = align_up(off + rows * ns * 4, 256);
-  w.l1_cnt_near = off; off = align_up(off + rows * ns * 4, 256);
-  w.l1_part_far = off; off = align_up(off + rows * ns * g.k_far * 4, 256);
-  w.l1_part_near = off; off = align_up(off + rows * ns * g.k_near * 4, 256);
+  w.np = off; off = align_up(off + rows * 4, 256);
+  w.pages = off; off = align_up(off + rows * np_max * 4, 256);
+  w.phys = off; off = align_up(off + rows * np_max * 4, 256);
+  w.l1_scores = off; off = align_up(off + rows * (size_t)l1_score_stride(g) * 2, 256);
+  w.l2_scores = off; off = align_up(off + rows * np_max * g.page * 2, 256);
   w.at_m = off; off = align_up(off + pairs * kAttnMaxSplit * G * 4, 256);
   w.at_z = off; off = align_up(off + pairs * kAttnMaxSplit * G * 4, 256);
   w.at_o = off; off = align_up(off + pairs * kAttnMaxSplit * G * g.head_dim_v * 4, 256);
   w.total = off;
   return w;
+}
+
+static SelectWorkspace select_ws(const loda_geometry& g, void* workspace) {
+  const WsLayout w = ws_layout(g);
+  char* base = (char*)workspace;
+  SelectWorkspace ws;
+  ws.l1_ticket = (int*)(base + w.l1_ticket);
+  ws.l2_ticket = (int*)(base + w.l2_ticket);
+  ws.l1_scores = (uint16_t*)(base + w.l1_scores);
+  ws.score_stride = l1_score_stride(g);
+  ws.pages = (int*)(base + w.pages);
+  ws.phys = (int*)(base + w.phys);
+  ws.np = (int*)(base + w.np);
+  ws.l2_scores = (uint16_t*)(base + w.l2_scores);
+  return ws;
 }
 
 static int check_geometry(const loda_geometry* g) {
@@ -93,15 +110,17 @@ static int check_geometry(const loda_geometry* g) {
     return fail(LODA_ERR_UNSUPPORTED, "k_far / k_near must be in [0, 512]");
   if (g->k_far > g->max_blocks || g->k_near > g->max_blocks)
     return fail(LODA_ERR_ARGUMENT, "k_far / k_near exceed max_blocks");
-  if ((size_t)(g->k_far + g->k_near + 2) * g->page > 65535)
-    return fail(LODA_ERR_UNSUPPORTED, "more than 65535 L2 candidates per row");
+  if ((size_t)(g->k_far + g->k_near + 2) * g->page > 32768)
+    return fail(LODA_ERR_UNSUPPORTED, "more than 32768 L2 candidate slots per row");
+  if (g->page < 8) return fail(LODA_ERR_UNSUPPORTED, "page must be at least 8 tokens");
+  if (g->pool_near_len / g->page + 1 > 512)
+    return fail(LODA_ERR_UNSUPPORTED, "near pool wider than 512 pages");
   if (g->level2_topk < g->sink + g->swa) return fail(LODA_ERR_ARGUMENT, "level2_topk < sink + swa");
   if (g->max_visible < g->level2_topk) return fail(LODA_ERR_ARGUMENT, "max_visible < level2_topk");
   if (g->sink < 0 || g->near_len < 0 || g->pool_near_len < g->page)
     return fail(LODA_ERR_ARGUMENT, "bad sink / near_len / pool_near_len");
-  if ((size_t)l1_nsplit(*g) * (g->k_far > g->k_near ? g->k_far : g->k_near) * 4 >
-      (size_t)512 * (4 * g->sub_dims + 16))
-    return fail(LODA_ERR_UNSUPPORTED, "L1 merge list does not fit in shared memory");
+  if ((size_t)g->max_blocks * 2 + 16 > 40 * 1024)
+    return fail(LODA_ERR_UNSUPPORTED, "max_blocks too large: a row's page scores must fit in shared memory");
   if (l1_smem_bytes(*g) > 200 * 1024 || l2_smem_bytes(*g) > 200 * 1024)
     return fail(LODA_ERR_UNSUPPORTED, "geometry needs more than 200 KB of shared memory");
   return LODA_OK;
@@ -206,14 +225,12 @@ int loda_select_l1(const loda_geometry* g, const loda_layer* layer, const loda_b
   LODA_TRY(check_layer(layer));
   LODA_TRY(check_batch(g, b));
   if (b->batch == 0) return LODA_OK;
-  if (!q || !out || !out->i_far || !out->i_near || !out->n_far || !out->n_near || !workspace)
-    return fail(LODA_ERR_ARGUMENT, "L1 needs q, i_far, n_far, i_near, n_near and a workspace");
-  const WsLayout w = ws_layout(*g);
-  char* base = (char*)workspace;
-  const L1Workspace ws{(int*)(base + w.l1_ticket), (int*)(base + w.l1_cnt_far), (int*)(base + w.l1_cnt_near),
-                       (uint32_t*)(base + w.l1_part_far), (uint32_t*)(base + w.l1_part_near)};
+  if (!q || !out || !workspace) return fail(LODA_ERR_ARGUMENT, "L1 needs q, a selection struct and a workspace");
+  if (out->i_far && (!out->i_near || !out->n_far || !out->n_near))
+    return fail(LODA_ERR_ARGUMENT, "i_far, n_far, i_near, n_near are given together or not at all");
   const AppendArgs none{nullptr, nullptr, nullptr, nullptr, 0};
-  return check_cuda(launch_l1(*g, *layer, *b, q, scale, *out, ws, none, (cudaStream_t)stream), "select_l1");
+  return check_cuda(launch_l1(*g, *layer, *b, q, scale, *out, select_ws(*g, workspace), none, (cudaStream_t)stream),
+                    "select_l1");
 }
 
 int loda_select_step(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
@@ -223,35 +240,32 @@ int loda_select_step(const loda_geometry* g, const loda_layer* layer, const loda
   LODA_TRY(check_layer(layer));
   LODA_TRY(check_batch(g, b));
   if (b->batch == 0) return LODA_OK;
-  if (!q || !sel || !sel->i_far || !sel->i_near || !sel->n_far || !sel->n_near || !sel->gather ||
-      !sel->visible_lens || !workspace)
-    return fail(LODA_ERR_ARGUMENT, "select_step needs q, the selection buffers and a workspace");
+  if (!q || !sel || !sel->gather || !sel->visible_lens || !workspace)
+    return fail(LODA_ERR_ARGUMENT, "select_step needs q, gather, visible_lens and a workspace");
+  if (sel->i_far && (!sel->i_near || !sel->n_far || !sel->n_near))
+    return fail(LODA_ERR_ARGUMENT, "i_far, n_far, i_near, n_near are given together or not at all");
   if ((sel->middle == nullptr) != (sel->middle_counts == nullptr))
     return fail(LODA_ERR_ARGUMENT, "middle and middle_counts must be given together");
   if ((k_new == nullptr) != (v_new == nullptr) || (k_new && !slots))
     return fail(LODA_ERR_ARGUMENT, "k_new, v_new and slots go together (all NULL = refresh the index only)");
-  const WsLayout w = ws_layout(*g);
-  char* base = (char*)workspace;
-  const L1Workspace ws{(int*)(base + w.l1_ticket), (int*)(base + w.l1_cnt_far), (int*)(base + w.l1_cnt_near),
-                       (uint32_t*)(base + w.l1_part_far), (uint32_t*)(base + w.l1_part_near)};
+  const SelectWorkspace ws = select_ws(*g, workspace);
   const AppendArgs ap{(const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, slots, status, 1};
   LODA_TRY(check_cuda(launch_l1(*g, *layer, *b, q, scale, *sel, ws, ap, (cudaStream_t)stream), "select_step/l1"));
-  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, status, (cudaStream_t)stream), "select_step/l2");
+  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, ws, status, (cudaStream_t)stream), "select_step/l2");
 }
 
 int loda_select_l2(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
                    float scale, const loda_selection* sel, uint32_t* status, void* workspace, void* stream) {
-  (void)workspace;
   LODA_TRY(check_geometry(g));
   LODA_TRY(check_layer(layer));
   LODA_TRY(check_batch(g, b));
   if (b->batch == 0) return LODA_OK;
-  if (!q || !sel || !sel->i_far || !sel->i_near || !sel->n_far || !sel->n_near || !sel->gather ||
-      !sel->visible_lens)
-    return fail(LODA_ERR_ARGUMENT, "L2 needs q, the L1 outputs, gather and visible_lens");
+  if (!q || !sel || !sel->gather || !sel->visible_lens || !workspace)
+    return fail(LODA_ERR_ARGUMENT, "L2 needs q, gather, visible_lens and the workspace L1 ran on");
   if ((sel->middle == nullptr) != (sel->middle_counts == nullptr))
     return fail(LODA_ERR_ARGUMENT, "middle and middle_counts must be given together");
-  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, status, (cudaStream_t)stream), "select_l2");
+  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, select_ws(*g, workspace), status, (cudaStream_t)stream),
+                    "select_l2");
 }
 
 int loda_gather_attend(const loda_geometry* g, const loda_layer* layer, const void* q, const int32_t* gather,
@@ -271,7 +285,7 @@ int loda_gather_attend(const loda_geometry* g, const loda_layer* layer, const vo
   const AttnWorkspace ws{(int*)(base + w.at_ticket), (float*)(base + w.at_m), (float*)(base + w.at_z),
                          (float*)(base + w.at_o)};
   return check_cuda(launch_attn(*g, *layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale,
-                                out, ws, (cudaStream_t)stream),
+                                out, ws, /*allow_cluster=*/true, (cudaStream_t)stream),
                     "gather_attend");
 }
 

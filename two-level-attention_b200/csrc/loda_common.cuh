@@ -177,6 +177,323 @@ __device__ __forceinline__ uint32_t block_kth_largest(const uint32_t* keys, int 
 }
 
 // ---------------------------------------------------------------------------
+// Exact top-k over a row of 16-bit ordered scores in shared memory (0 = no
+// score), ties toward the lower index, kept indices written in ASCENDING order.
+// Three routines for three regimes; all return the number kept
+// (min(k, #scored)).  A single CTA runs them, so what costs is latency, not
+// throughput: the loops are written for instruction-level parallelism, block
+// sums go through per-warp columns and one barrier (contended shared atomics
+// serialise at ~65 cycles each), 1-bit flags are scanned with ballots, and the
+// packed 16x2 compare intrinsics (emulated on this architecture) are avoided.
+// The row must be 16-byte aligned and readable (zero) up to a multiple of 8.
+// ---------------------------------------------------------------------------
+
+// key that orders by (score descending, index ascending); 0 = no score
+__device__ __forceinline__ uint32_t rank_key(uint32_t score, int idx) {
+  return score ? (score << 16) | (uint32_t)(0xFFFF - idx) : 0u;
+}
+
+// how many of the n4 * 4 keys are greater than `key` (four independent chains)
+__device__ __forceinline__ int count_greater(const uint32_t* keys, int n4, uint32_t key) {
+  int r0 = 0, r1 = 0, r2 = 0, r3 = 0;
+#pragma unroll 4
+  for (int j = 0; j < n4; ++j) {
+    const uint4 o = ((const uint4*)keys)[j];
+    r0 += o.x > key; r1 += o.y > key; r2 += o.z > key; r3 += o.w > key;
+  }
+  return (r0 + r1) + (r2 + r3);
+}
+
+// exclusive scan of one flag per thread: ballot inside the warp, per-warp totals
+// through shared memory, one barrier.  wtot: 2 x 32 ints (16-byte aligned), the
+// caller alternates `buf` between back-to-back calls.
+template <int NT>
+__device__ __forceinline__ int block_flag_scan(bool flag, int* wtot, int buf, int* total) {
+  constexpr int NW = NT / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned bal = __ballot_sync(0xffffffffu, flag);
+  if (lane == 0) wtot[buf * 32 + warp] = __popc(bal);
+  __syncthreads();
+  int before = 0, all = 0;
+#pragma unroll
+  for (int w = 0; w < NW; ++w) {
+    const int c = wtot[buf * 32 + w];
+    all += c;
+    before += w < warp ? c : 0;
+  }
+  *total = all;
+  return before + __popc(bal & ((1u << lane) - 1u));
+}
+
+// sum of one int per thread: redux, per-warp column, one barrier (same buffers)
+template <int NT>
+__device__ __forceinline__ int block_sum_cols(int v, int* wtot, int buf) {
+  constexpr int NW = NT / 32;
+  const int r = __reduce_add_sync(0xffffffffu, v);
+  if ((threadIdx.x & 31) == 0) wtot[buf * 32 + (threadIdx.x >> 5)] = r;
+  __syncthreads();
+  const int4* col = (const int4*)(wtot + buf * 32);
+  int s = 0;
+#pragma unroll
+  for (int w4 = 0; w4 < (NW + 3) / 4; ++w4) {
+    const int4 x = col[w4];
+    s += (x.x + x.y) + (x.z + x.w);
+  }
+  return s;
+}
+
+__device__ __forceinline__ void unpack_u16x8(const uint4& u, uint32_t (&v)[8]) {
+  v[0] = u.x & 0xFFFFu; v[1] = u.x >> 16; v[2] = u.y & 0xFFFFu; v[3] = u.y >> 16;
+  v[4] = u.z & 0xFFFFu; v[5] = u.z >> 16; v[6] = u.w & 0xFFFFu; v[7] = u.w >> 16;
+}
+
+// (1) n <= NT scores: every thread ranks its own element against all others.
+// keys: NT words (16-byte aligned); wtot: 64 ints.
+template <int NT>
+__device__ __forceinline__ int block_rank_topk_small(const uint16_t* sc, int n, int k, int* out, uint32_t* keys,
+                                                     int* wtot) {
+  const int tid = threadIdx.x;
+  const uint32_t key = tid < n ? rank_key(sc[tid], tid) : 0u;
+  keys[tid] = key;
+  __syncthreads();
+  const int rank = key ? count_greater(keys, (n + 3) >> 2, key) : 0;
+  const bool sel = key != 0 && rank < k;
+  int total;
+  const int pos = block_flag_scan<NT>(sel, wtot, 0, &total);
+  if (sel) out[pos] = tid;
+  __syncthreads();
+  return total;
+}
+
+// (2) any n < 65536, any k: bisection over the 16 score bits, two bits per round.
+// The row is cut into chunks of 8 scores dealt round-robin to the threads; per
+// round every thread counts its scores at or above three candidate thresholds
+// (independent chains), one barrier publishes the block sums.  The compaction
+// runs over the same chunks, one flag scan per score position.
+// wtot: 6 x 32 ints (16-byte aligned).
+template <int NT>
+__device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int k, int* out, int* wtot) {
+  constexpr int NW = NT / 32;
+  constexpr int MAXC = 4;                        // chunks a thread keeps in registers
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nchunks = (n + 7) >> 3;
+  const bool in_regs = nchunks <= NT * MAXC;
+  uint4 mine[MAXC];
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = tid + c * NT;
+    mine[c] = (in_regs && ch < nchunks) ? ((const uint4*)sc)[ch] : make_uint4(0, 0, 0, 0);
+  }
+  auto count3 = [&](uint32_t t1, uint32_t t2, uint32_t t3, int& c1, int& c2, int& c3) {
+    c1 = c2 = c3 = 0;
+    if (in_regs) {
+#pragma unroll
+      for (int c = 0; c < MAXC; ++c) {
+        if (c * NT < nchunks) {                  // uniform: skip register slots no thread uses
+          uint32_t v[8];
+          unpack_u16x8(mine[c], v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { c1 += v[j] >= t1; c2 += v[j] >= t2; c3 += v[j] >= t3; }
+        }
+      }
+    } else {
+      for (int ch = tid; ch < nchunks; ch += NT) {
+        uint32_t v[8];
+        unpack_u16x8(((const uint4*)sc)[ch], v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { c1 += v[j] >= t1; c2 += v[j] >= t2; c3 += v[j] >= t3; }
+      }
+    }
+  };
+  // three sums with one barrier: columns [buf][counter][warp]
+  auto sum3 = [&](int buf, int& c1, int& c2, int& c3) {
+    c1 = __reduce_add_sync(0xffffffffu, c1);
+    c2 = __reduce_add_sync(0xffffffffu, c2);
+    c3 = __reduce_add_sync(0xffffffffu, c3);
+    if (lane == 0) {
+      wtot[(buf * 3 + 0) * 32 + warp] = c1;
+      wtot[(buf * 3 + 1) * 32 + warp] = c2;
+      wtot[(buf * 3 + 2) * 32 + warp] = c3;
+    }
+    __syncthreads();
+    int s[3] = {0, 0, 0};
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+      const int4* col = (const int4*)(wtot + (buf * 3 + q) * 32);
+#pragma unroll
+      for (int w4 = 0; w4 < (NW + 3) / 4; ++w4) {
+        const int4 x = col[w4];
+        s[q] += (x.x + x.y) + (x.z + x.w);
+      }
+    }
+    c1 = s[0]; c2 = s[1]; c3 = s[2];
+  };
+  for (int i = tid; i < 6 * 32; i += NT) wtot[i] = 0;      // columns of absent warps stay 0
+  __syncthreads();
+  int nv, d1, d2;
+  count3(1u, 0x10000u, 0x10000u, nv, d1, d2);
+  sum3(0, nv, d1, d2);
+  const int nvalid = nv;
+  if (k <= 0 || nvalid == 0) { __syncthreads(); return 0; }
+  const bool all = nvalid <= k;
+  uint32_t thr = 1u;     // keep v >= thr ...
+  int rem = 0;           // ... but of those equal to thr only the first `rem` (all == true: everything scored)
+  if (!all) {
+    thr = 0;
+#pragma unroll 1
+    for (int round = 0; round < 8; ++round) {
+      const int shift = 14 - 2 * round;
+      int c1, c2, c3;
+      count3(thr | (1u << shift), thr | (2u << shift), thr | (3u << shift), c1, c2, c3);
+      sum3((round + 1) & 1, c1, c2, c3);
+      thr |= (c3 >= k ? 3u : c2 >= k ? 2u : c1 >= k ? 1u : 0u) << shift;   // largest candidate with >= k at or above
+    }
+    int gt, e1, e2;
+    count3(thr + 1u, 0x10000u, 0x10000u, gt, e1, e2);
+    sum3(1, gt, e1, e2);
+    rem = k - gt;
+  }
+  // compaction in index order over a blocked layout (ept consecutive scores per
+  // thread): strictly above the threshold, then the first `rem` ties
+  const int ept = (((n + NT - 1) / NT) + 7) & ~7;
+  const int base = tid * ept;
+  const int nch = base < n ? min(ept, ((n - base + 7) & ~7)) >> 3 : 0;
+  const uint4* blk = (const uint4*)(sc + base);
+  int gt = 0, tie = 0;
+  for (int ch = 0; ch < nch; ++ch) {
+    uint32_t v[8];
+    unpack_u16x8(blk[ch], v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { gt += all ? v[j] != 0 : v[j] > thr; tie += (!all) && v[j] == thr; }
+  }
+  // exclusive scan of (gt | tie << 16): shuffles inside the warp, columns across warps
+  int incl = gt | (tie << 16);
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int nb = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += nb;
+  }
+  __syncthreads();                             // the columns may still be read by slower warps
+  if (lane == 31) wtot[warp] = incl;
+  __syncthreads();
+  int before = 0;
+#pragma unroll
+  for (int w = 0; w < NW; ++w) before += w < warp ? wtot[w] : 0;
+  const int excl = before + incl - (gt | (tie << 16));
+  int tb = excl >> 16;
+  int pos = (excl & 0xFFFF) + min(tb, rem);
+  for (int ch = 0; ch < nch; ++ch) {
+    uint32_t v[8];
+    unpack_u16x8(blk[ch], v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = base + ch * 8 + j;
+      if (all ? v[j] != 0 : v[j] > thr) out[pos++] = i;
+      else if (!all && v[j] == thr) { if (tb < rem) out[pos++] = i; ++tb; }
+    }
+  }
+  __syncthreads();
+  return all ? nvalid : k;
+}
+
+// (3) large n, small k (k <= 128): a cheap lower bound on the k-th largest score
+// discards almost everything, the survivors are ranked exactly.  The chunks of
+// the row are dealt round-robin to the threads, the threads form 128 groups;
+// the k-th largest of the 128 group maxima is a lower bound of the k-th largest
+// score (k groups each hold a score at or above it).  Scores at or above the
+// bound (about 1.5-2 k of them for unclustered scores) are compacted in index
+// order and ranked against each other.  Returns -1 without writing anything
+// when more than NT survive (heavily tied or sorted scores): the caller then
+// bisects.  keys: NT + 8 words (16-byte aligned); wtot: 64 ints; sh: 2 ints.
+template <int NT>
+__device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, int k, int* out, uint32_t* keys,
+                                                    int* wtot, int* sh) {
+  static_assert(NT % 128 == 0 && NT / 128 <= 32, "group layout");
+  constexpr int GS = NT / 128;                   // threads per group
+  constexpr int NW = NT / 32;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nchunks = (n + 7) >> 3;
+  // thread maximum (two independent chains)
+  uint32_t m0 = 0, m1 = 0;
+  for (int ch = tid; ch < nchunks; ch += NT) {
+    uint32_t v[8];
+    unpack_u16x8(((const uint4*)sc)[ch], v);
+    m0 = max(max(m0, max(v[0], v[1])), max(v[2], v[3]));
+    m1 = max(max(m1, max(v[4], v[5])), max(v[6], v[7]));
+  }
+  uint32_t m = max(m0, m1);
+#pragma unroll
+  for (int o = 1; o < GS; o <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((tid & (GS - 1)) == 0) keys[tid / GS] = rank_key(m, tid / GS);
+  __syncthreads();
+  int is_kth = 0;
+  uint32_t gkey = 0;
+  if (tid < 128) {
+    gkey = keys[tid];
+    is_kth = gkey != 0 && count_greater(keys, 32, gkey) == k - 1;
+    if (is_kth) sh[0] = (int)(gkey >> 16);
+  }
+  // fewer than k non-empty groups: nothing can be discarded
+  const int found = __syncthreads_or(is_kth);
+  const uint32_t bound = found ? (uint32_t)sh[0] : 1u;
+  // survivors, counted per thread then placed in index order round by round
+  int total = 0;
+  {
+    int cnt = 0;
+    for (int ch = tid; ch < nchunks; ch += NT) {
+      uint32_t v[8];
+      unpack_u16x8(((const uint4*)sc)[ch], v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) cnt += v[j] >= bound;
+    }
+    total = block_sum_cols<NT>(cnt, wtot, 0);
+  }
+  if (total > NT) return -1;
+  int base_out = 0, buf = 1;
+  for (int c0 = 0; c0 < nchunks; c0 += NT) {
+    const int ch = c0 + tid;
+    uint32_t v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (ch < nchunks) unpack_u16x8(((const uint4*)sc)[ch], v);
+    int cnt = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cnt += v[j] >= bound;
+    int incl = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int nb = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += nb;
+    }
+    if (lane == 31) wtot[buf * 32 + warp] = incl;
+    __syncthreads();
+    int before = 0, tot = 0;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const int x = wtot[buf * 32 + w];
+      tot += x;
+      before += w < warp ? x : 0;
+    }
+    buf ^= 1;
+    int pos = base_out + before + incl - cnt;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (v[j] >= bound) keys[pos++] = rank_key(v[j], ch * 8 + j);
+    }
+    base_out += tot;
+  }
+  if (tid < 4) keys[total + tid] = 0;            // pad the last vector of keys
+  __syncthreads();
+  // exact ranking of the survivors (already in ascending index order)
+  const uint32_t key = tid < total ? keys[tid] : 0u;
+  const int rank = key ? count_greater(keys, (total + 3) >> 2, key) : 0;
+  const bool sel = key != 0 && rank < k;
+  int kept;
+  const int opos = block_flag_scan<NT>(sel, wtot, buf, &kept);
+  if (sel) out[opos] = 0xFFFF - (int)(key & 0xFFFFu);
+  __syncthreads();
+  return kept;
+}
+
+// ---------------------------------------------------------------------------
 // async copy
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {
@@ -224,13 +541,36 @@ struct AppendArgs {
   int enabled;
 };
 
+// ---------------------------------------------------------------------------
+// optional phase timestamps (compile with -DLODA_PHASES): thread 0 of each CTA
+// records clock64() at numbered points; LODA_PHASE_STORAGE defines the per-file
+// array and a C reader.  Compiled out of the shipped library.
+// ---------------------------------------------------------------------------
+#ifdef LODA_PHASES
+#define LODA_PHASE_STORAGE(name)                                                        \
+  static __device__ long long g_phase_##name[512][16];                                  \
+  extern "C" int loda_phase_read_##name(long long* host) {                              \
+    return (int)cudaMemcpyFromSymbol(host, g_phase_##name, sizeof(long long) * 512 * 16); \
+  }
+#define LODA_PHASE(name, cta, i)                                                        \
+  do {                                                                                  \
+    if (threadIdx.x == 0 && (cta) < 512) g_phase_##name[(cta)][(i)] = clock64();        \
+  } while (0)
+#else
+#define LODA_PHASE_STORAGE(name)
+#define LODA_PHASE(name, cta, i)
+#endif
+
 // scratch views handed to the kernels (carved out of the caller's workspace)
-struct L1Workspace {
-  int* ticket;          // [rows], zero between launches
-  int* cnt_far;         // [rows, nsplit]
-  int* cnt_near;        // [rows, nsplit]
-  uint32_t* part_far;   // [rows, nsplit, k_far]
-  uint32_t* part_near;  // [rows, nsplit, k_near]
+struct SelectWorkspace {
+  int* l1_ticket;        // [rows], zero between launches
+  int* l2_ticket;        // [rows], zero between launches
+  uint16_t* l1_scores;   // [rows, score_stride]: ordered bf16 score of every logical page (0 = not in a pool)
+  int score_stride;
+  int* pages;            // [rows, k_far + k_near + 2]: surviving pages, ascending, bypass pages included
+  int* phys;             // [rows, k_far + k_near + 2]: their physical page ids (-1 = invalid)
+  int* np;               // [rows]
+  uint16_t* l2_scores;   // [rows, (k_far + k_near + 2) * page]: ordered bf16 logit per candidate slot
 };
 struct AttnWorkspace {
   int* ticket;    // [n_query * Hkv], zero between launches

@@ -5,13 +5,16 @@
 // Restates _nfa_l1_scores_kernel (nfa_layer_batch_selector.py:174-354) and the
 // packed-key top-k (nfa_layer_batch_selector.py:1473-1532, 1765-1793).
 //
-// Work split: grid = (ceil(max_blocks / P), batch * Hkv).  CTA (s, row) owns the
-// P consecutive logical pages [s P, s P + P) of one (request, kv head) row: it
-// stages their metadata (one contiguous run in HBM) into shared memory with
-// 16-byte cp.async copies, scores one page per thread, keeps its best k_far /
-// k_near keys with a radix select and appends them to the row's partial list.
-// The last CTA of a row to finish (atomic ticket, no spinning) merges the
-// partial lists, sorts the survivors and writes the page ids.
+// Work split: grid = (ceil(max_blocks / P) [+1], batch * Hkv).  CTA (s, row) owns
+// the P consecutive logical pages [s P, s P + P) of one (request, kv head) row:
+// it stages their metadata (one contiguous run in HBM) into shared memory with
+// 16-byte cp.async copies, scores one page per thread and writes the 16-bit
+// ordered score of every page to the row's score array.  The last CTA of a row
+// to finish (atomic ticket, no spinning) reads the row's scores back (L2-cache
+// resident, 2 bytes per page), selects each pool's top-k with two radix passes
+// and a tie-resolving scan in page order, and hands the ascending page list
+// (bypass pages included) with its physical page ids to the L2 launch.  An
+// optional extra CTA per row carries the decode append.
 //
 // Canonical arithmetic (must match the CPU oracle bit for bit): a length-d' dot
 // is split into chunks of 8 dims summed left to right from 0.0f, chunk sums are
@@ -60,97 +63,67 @@ __device__ __forceinline__ float dot_chunks(const float (&k)[DSUB], const float*
   return chunk_tree<NC>(p);
 }
 
-// Merge the partial key lists of one row, keep the best k, write ids sorted by
-// key descending followed by fillers (lowest page ids not selected).
+LODA_PHASE_STORAGE(l1)
+
+// the selecting CTA reuses the staging area: 40 KB for the far pool's scores (2 bytes per page)
+// and 1 KB for the near pool's
+constexpr size_t L1_TAIL_BYTES = 41 * 1024;
+
+// Rank the n kept pages of one pool best-first (score descending, lower id
+// first) and append fillers (lowest page ids not kept): the page-id lists the
+// reference selector exposes.  Optional output, used by parity checks.
 template <int NT>
-__device__ void merge_partials(const uint32_t* part, const int* cnt, int nsplit, int k, int kcap,
-                               uint32_t* buf, uint32_t* sel, int* ids_sorted, int* hist, int* sh,
-                               int32_t* out_ids, int32_t* out_n, int max_blocks) {
+__device__ void emit_best_first(const int* kept, int n, int k, const uint16_t* sc, int32_t* out_ids,
+                                int32_t* out_n, int max_blocks) {
   const int tid = threadIdx.x;
-  // counts of all splits in one round of loads, offsets by a short serial scan
-  int* cnts = hist;            // [nsplit] (hist is free until the select below)
-  int* offs = hist + 129;      // [nsplit]
-  for (int s = tid; s < nsplit; s += NT) cnts[s] = min(__ldcg(cnt + s), kcap);
-  __syncthreads();
-  if (tid == 0) {
-    int total = 0;
-    for (int s = 0; s < nsplit; ++s) { offs[s] = total; total += cnts[s]; }
-    sh[0] = total;
-    sh[1] = 0;
-  }
-  __syncthreads();
-  const int total = sh[0];
-  // gather every partial key with independent loads
-#pragma unroll 4
-  for (int idx = tid; idx < nsplit * kcap; idx += NT) {
-    const int s = idx / kcap, i = idx - s * kcap;
-    if (i < cnts[s]) buf[offs[s] + i] = __ldcg(part + idx);
-  }
-  __syncthreads();
-  int n = total;
-  if (total > k) {
-    const uint32_t thr = block_kth_largest<NT>(buf, total, k, hist);
-    for (int i = tid; i < total; i += NT) {
-      const uint32_t key = buf[i];
-      if (key >= thr) sel[atomicAdd(&sh[1], 1)] = key;
-    }
-    n = k;
-  } else {
-    for (int i = tid; i < total; i += NT) sel[i] = buf[i];
-  }
-  __syncthreads();
-  // rank by key (descending) and by page id (ascending); keys are unique
   for (int i = tid; i < n; i += NT) {
-    const uint32_t key = sel[i];
+    const int id = kept[i];
+    const uint32_t key = ((uint32_t)sc[id] << 16) | (uint32_t)(0xFFFF - id);
     int rank = 0;
-    for (int j = 0; j < n; ++j) rank += sel[j] > key;
-    const int id = 0xFFFF - (int)(key & 0xFFFFu);
+    for (int j = 0; j < n; ++j) {
+      const int idj = kept[j];
+      rank += (((uint32_t)sc[idj] << 16) | (uint32_t)(0xFFFF - idj)) > key;
+    }
     out_ids[rank] = id;
   }
-  __syncthreads();
-  for (int i = tid; i < n; i += NT) {
-    const int id = 0xFFFF - (int)(sel[i] & 0xFFFFu);
-    int rank = 0;
-    for (int j = 0; j < n; ++j) rank += (0xFFFF - (int)(sel[j] & 0xFFFFu)) < id;
-    ids_sorted[rank] = id;
-  }
-  __syncthreads();
-  // fillers: the j-th smallest page id that was not selected
-  for (int j = tid; j < k - n; j += NT) {
+  for (int j = tid; j < k - n; j += NT) {   // kept[] is ascending: j-th smallest id not kept
     int c = j;
     for (int i = 0; i < n; ++i) {
-      if (ids_sorted[i] <= c) ++c; else break;
+      if (kept[i] <= c) ++c; else break;
     }
     out_ids[n + j] = min(c, max_blocks - 1);
   }
   if (tid == 0) *out_n = n;
-  __syncthreads();
 }
 
 template <int DSUB, int P>
 __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, loda_batch B,
                                                 const bf16* __restrict__ q, float scale,
-                                                loda_selection out, L1Workspace ws, int nsplit,
+                                                loda_selection out, SelectWorkspace ws, int nsplit,
                                                 AppendArgs ap) {
   constexpr int NC = DSUB / 8;            // 8-dim chunks per statistic
   constexpr int CPR = 2 * NC;             // 16-byte chunks per min/max row
   constexpr int ROWB = 4 * DSUB + 16;     // padded row: conflict-free 16-byte reads
   extern __shared__ __align__(16) unsigned char smem[];
-  unsigned char* rows = smem;                                    // P * ROWB
-  float* qhat = (float*)(smem + (size_t)P * ROWB);               // [G, DSUB] x3
+  constexpr size_t ROWS_BYTES = (size_t)P * ROWB > L1_TAIL_BYTES ? (size_t)P * ROWB : L1_TAIL_BYTES;
+  unsigned char* rows = smem;                                    // staging rows, later scores + histograms
+  float* qhat = (float*)(smem + ROWS_BYTES);                     // [G, DSUB] x3
   const int G = g.num_q_heads / g.num_kv_heads;
   float* qlow = qhat + G * DSUB;
   float* qhigh = qlow + G * DSUB;
-  uint32_t* keys_f = (uint32_t*)(qhigh + G * DSUB);              // P
-  uint32_t* keys_n = keys_f + P;                                 // P
-  int* hist = (int*)(keys_n + P);                                // 258
-  int* sh = hist + 258;                                          // 40
+  int* kept = (int*)(qhigh + G * DSUB);                          // k_far + k_near + 2
+  uint32_t* keys = (uint32_t*)(((uintptr_t)(kept + (g.k_far + g.k_near + 2)) + 15) & ~(uintptr_t)15);   // P + 8
+  int* wtot = (int*)(keys + P + 8);                              // 6 x 32
+  int* sh = wtot + 192;                                          // 8
 
   const int tid = threadIdx.x;
   const int split = blockIdx.x, row = blockIdx.y;
   const int b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
+  const int cta_id = blockIdx.y * gridDim.x + blockIdx.x;
+  LODA_PHASE(l1, cta_id, 0);
   pdl_wait();
   pdl_launch_dependents();
+  LODA_PHASE(l1, cta_id, 1);
   if (split == nsplit) {
     // extra CTA of the row: the decode append.  It touches only the newest token
     // and its page, which lie in the sliding window and are read by neither L1
@@ -158,23 +131,14 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
     if (tid < 32) append_row<DSUB>(g, L, B, ap.k_new, ap.v_new, ap.slots, ap.status, b, kv, tid);
     return;
   }
-  const bool active = B.active_req_ids[b] >= 0;
-  const int length = active ? B.lengths[b] : 0;
+  const long long act = B.active_req_ids[b];
+  const int len_raw = B.lengths[b];
   const int req = (int)B.valid_req_ids[b];
+  const int length = act >= 0 ? len_raw : 0;
   const Regions rg = make_regions(g, length);
   const int p0 = split * P;
 
-  // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
-  for (int i = tid; i < G * DSUB; i += P) {
-    const int j = i / DSUB, d = i % DSUB;
-    const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, d)]);
-    const float qh = bf16r(__fmul_rn(qv, scale));
-    qhat[i] = qh;
-    qlow[i] = fminf(qh, 0.0f);
-    qhigh[i] = fmaxf(qh, 0.0f);
-  }
-
-  // stage metadata rows of this CTA's pages
+  // stage metadata rows of this CTA's pages (issued first: the longest latency)
   const size_t pg0 = ((size_t)req * g.num_kv_heads + kv) * g.max_blocks;
   const unsigned char* mm_base = (const unsigned char*)L.page_mm + pg0 * (4 * DSUB);
   const unsigned char* sum_base = (const unsigned char*)L.page_sum + pg0 * (2 * DSUB);
@@ -188,12 +152,23 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
     }
   }
   cp_async_commit();
+  // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
+  for (int i = tid; i < G * DSUB; i += P) {
+    const int j = i / DSUB, d = i % DSUB;
+    const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, d)]);
+    const float qh = bf16r(__fmul_rn(qv, scale));
+    qhat[i] = qh;
+    qlow[i] = fminf(qh, 0.0f);
+    qhigh[i] = fmaxf(qh, 0.0f);
+  }
+  LODA_PHASE(l1, cta_id, 2);
   cp_async_wait<0>();
   __syncthreads();
+  LODA_PHASE(l1, cta_id, 3);
 
   // one page per thread
   const int page = p0 + tid;
-  uint32_t key_f = 0, key_n = 0;
+  uint32_t ord = 0;
   const unsigned char* myrow = rows + (size_t)tid * ROWB;
   const float gf = (float)G;
   if (in_far_pool(rg, page)) {
@@ -209,9 +184,7 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
       const float mm = __fadd_rn(dot_chunks<DSUB>(kmin, qlow + j * DSUB), dot_chunks<DSUB>(kmax, qhigh + j * DSUB));
       acc = __fadd_rn(acc, bf16r(mm));
     }
-    const float score = bf16r(__fdiv_rn(acc, gf));
-    const uint32_t o = ord16(score);
-    if (o != ORD16_NEG_INF) key_f = (o << 16) | (uint32_t)(0xFFFF - page);
+    ord = ord16(bf16r(__fdiv_rn(acc, gf)));
   } else if (in_near_pool(rg, page)) {
     float kavg[DSUB];
     const float bsf = (float)g.page;
@@ -222,86 +195,141 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
     float acc = 0.0f;
 #pragma unroll 1
     for (int j = 0; j < G; ++j) acc = __fadd_rn(acc, bf16r(dot_chunks<DSUB>(kavg, qhat + j * DSUB)));
-    const float score = bf16r(__fdiv_rn(acc, gf));
-    const uint32_t o = ord16(score);
-    if (o != ORD16_NEG_INF) key_n = (o << 16) | (uint32_t)(0xFFFF - page);
+    ord = ord16(bf16r(__fdiv_rn(acc, gf)));
   }
-  keys_f[tid] = key_f;
-  keys_n[tid] = key_n;
-  if (tid == 0) { sh[2] = 0; sh[3] = 0; }
-  const int nf = __syncthreads_count(key_f != 0);
-  const int nn = __syncthreads_count(key_n != 0);
+  if (ord == ORD16_NEG_INF) ord = 0;   // a -inf score never competes (it equals "not in the pool")
+  uint16_t* row_scores = ws.l1_scores + (size_t)row * ws.score_stride;
+  row_scores[page] = (uint16_t)ord;
+  LODA_PHASE(l1, cta_id, 4);
 
-  const size_t pslot = (size_t)row * nsplit + split;
-  if (nf > 0) {
-    const uint32_t thr = nf > g.k_far ? block_kth_largest<P>(keys_f, P, g.k_far, hist) : 1u;
-    if (key_f >= thr && key_f != 0) ws.part_far[pslot * g.k_far + atomicAdd(&sh[2], 1)] = key_f;
+  // last CTA of the row selects
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) sh[0] = (atomicAdd(ws.l1_ticket + row, 1) == nsplit - 1);
+  __syncthreads();
+  LODA_PHASE(l1, cta_id, 5);
+  if (!sh[0]) return;
+  __threadfence();
+  // the staging rows are consumed: the row's scores are copied into two rows of
+  // shared memory, one per pool, each holding 0 outside its pool
+  const int near_hi = min(min(rg.swa_lo_blk, rg.kt_eff), g.max_blocks);
+  const int far_lo = rg.far_lo, far_hi = max(rg.far_hi, rg.far_lo);
+  const int near_lo = rg.near_blks, near_lo8 = near_lo & ~7;
+  const int n_far = far_hi;                                                   // far row: pages [0, far_hi)
+  const int n_near = near_hi > near_lo ? min(near_hi - near_lo8, P) : 0;      // near row: pages [near_lo8, ...)
+  uint16_t* scf = (uint16_t*)rows;                       // up to 40 KB
+  uint16_t* scn = (uint16_t*)(rows + 40 * 1024);         // P scores
+  {
+    const uint4* src = (const uint4*)row_scores;         // 8 scores per load; unscored pages hold 0
+    for (int c = tid; c < (n_far + 7) / 8; c += P) {
+      uint32_t v[8];
+      unpack_u16x8(__ldcg(src + c), v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const int i = c * 8 + j; v[j] = (i >= far_lo && i < far_hi) ? v[j] : 0u; }
+      ((uint4*)scf)[c] = make_uint4(v[0] | v[1] << 16, v[2] | v[3] << 16, v[4] | v[5] << 16, v[6] | v[7] << 16);
+    }
+    for (int c = tid; c < (n_near + 7) / 8; c += P) {
+      uint32_t v[8];
+      unpack_u16x8(__ldcg(src + near_lo8 / 8 + c), v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const int i = near_lo8 + c * 8 + j; v[j] = (i >= near_lo && i < near_hi) ? v[j] : 0u; }
+      ((uint4*)scn)[c] = make_uint4(v[0] | v[1] << 16, v[2] | v[3] << 16, v[4] | v[5] << 16, v[6] | v[7] << 16);
+    }
   }
-  if (nn > 0) {
-    const uint32_t thr = nn > g.k_near ? block_kth_largest<P>(keys_n, P, g.k_near, hist) : 1u;
-    if (key_n >= thr && key_n != 0) ws.part_near[pslot * g.k_near + atomicAdd(&sh[3], 1)] = key_n;
+  __syncthreads();
+  LODA_PHASE(l1, cta_id, 6);
+  int np = 0;
+  const bool want_lists = out.i_far != nullptr;
+  if (rg.quota > 0 || want_lists) {
+    if (rg.quota > 0 && rg.sink_byp && rg.spl < rg.kt_eff) { if (tid == 0) kept[0] = rg.spl; np = 1; }
+    int* kept_near = kept + np + g.k_far;                // compacted below
+    int n_f = 0, n_n = 0;
+    if (n_far > far_lo) {
+      if (n_far <= P) {
+        n_f = block_rank_topk_small<P>(scf, n_far, g.k_far, kept + np, keys, wtot);
+      } else {
+        n_f = g.k_far <= 128 ? block_prefilter_topk<P>(scf, n_far, g.k_far, kept + np, keys, wtot, sh) : -1;
+        if (n_f < 0) n_f = block_bisect_topk<P>(scf, n_far, g.k_far, kept + np, wtot);   // heavily tied scores
+      }
+    }
+    if (n_near > 0) {
+      n_n = block_rank_topk_small<P>(scn, n_near, g.k_near, kept_near, keys, wtot);
+      for (int i = tid; i < n_n; i += P) kept_near[i] += near_lo8;
+      __syncthreads();
+    }
+    LODA_PHASE(l1, cta_id, 7);
+    if (want_lists) {
+      // best-first lists need the scores by page id: near scores go back beside the far ones
+      for (int i = near_lo + tid; i < near_hi; i += P) scf[i] = scn[i - near_lo8];
+      __syncthreads();
+      emit_best_first<P>(kept + np, n_f, g.k_far, scf, out.i_far + (size_t)row * g.k_far, out.n_far + row, g.max_blocks);
+      emit_best_first<P>(kept_near, n_n, g.k_near, scf, out.i_near + (size_t)row * g.k_near, out.n_near + row,
+                         g.max_blocks);
+      __syncthreads();
+    }
+    if (rg.quota > 0) {
+      // ascending list: [sink bypass] far... near... [window bypass]
+      const int v = tid < n_n ? kept_near[tid] : 0;      // k_near <= P
+      __syncthreads();
+      if (tid < n_n) kept[np + n_f + tid] = v;
+      np += n_f + n_n;
+      if (rg.swa_byp) { if (tid == 0) kept[np] = rg.swa_byp_blk; ++np; }
+    }
+    __syncthreads();
+    LODA_PHASE(l1, cta_id, 8);
+  }
+  // hand the ascending page list and its physical pages to the L2 launch
+  const int np_max = g.k_far + g.k_near + 2;
+  const int32_t* table = L.block_table + (size_t)req * g.max_blocks;
+  for (int i = tid; i < np; i += P) {
+    const int pg = kept[i];
+    int ph = (pg >= 0 && pg < g.max_blocks) ? table[pg] : -1;
+    if (ph < 0 || ph >= g.num_pages) ph = -1;
+    ws.pages[(size_t)row * np_max + i] = pg;
+    ws.phys[(size_t)row * np_max + i] = ph;
   }
   if (tid == 0) {
-    ws.cnt_far[pslot] = min(nf, g.k_far);
-    ws.cnt_near[pslot] = min(nn, g.k_near);
+    ws.np[row] = np;
+    ws.l1_ticket[row] = 0;
   }
-
-  // last CTA of the row merges
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) sh[4] = (atomicAdd(ws.ticket + row, 1) == nsplit - 1);
-  __syncthreads();
-  if (!sh[4]) return;
-  __threadfence();
-  uint32_t* buf = (uint32_t*)rows;                    // nsplit * k entries fit in the staging area
-  uint32_t* selk = keys_f;                            // k <= P
-  int* ids_sorted = (int*)keys_n;
-  merge_partials<P>(ws.part_far + (size_t)row * nsplit * g.k_far, ws.cnt_far + (size_t)row * nsplit,
-                    nsplit, g.k_far, g.k_far, buf, selk, ids_sorted, hist, sh,
-                    out.i_far + (size_t)row * g.k_far, out.n_far + row, g.max_blocks);
-  merge_partials<P>(ws.part_near + (size_t)row * nsplit * g.k_near, ws.cnt_near + (size_t)row * nsplit,
-                    nsplit, g.k_near, g.k_near, buf, selk, ids_sorted, hist, sh,
-                    out.i_near + (size_t)row * g.k_near, out.n_near + row, g.max_blocks);
-  if (tid == 0) ws.ticket[row] = 0;
+  LODA_PHASE(l1, cta_id, 9);
 }
 
 constexpr int L1_P = 512;
 
 size_t l1_smem_bytes(const loda_geometry& g) {
   const int G = g.num_q_heads / g.num_kv_heads;
-  return (size_t)L1_P * (4 * g.sub_dims + 16) + (size_t)3 * G * g.sub_dims * 4 + (size_t)2 * L1_P * 4 +
-         (258 + 40) * 4;
+  const size_t rows = (size_t)L1_P * (4 * g.sub_dims + 16);
+  return (rows > L1_TAIL_BYTES ? rows : L1_TAIL_BYTES) + (size_t)3 * G * g.sub_dims * 4 +
+         (size_t)(g.k_far + g.k_near + 2) * 4 + (size_t)(L1_P + 8) * 4 + (192 + 8) * 4 + 32;
 }
 
 int l1_nsplit(const loda_geometry& g) { return (g.max_blocks + L1_P - 1) / L1_P; }
 
-cudaError_t launch_l1(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
-                      float scale, const loda_selection& out, const L1Workspace& ws, const AppendArgs& ap,
-                      cudaStream_t st) {
+int l1_score_stride(const loda_geometry& g) { return l1_nsplit(g) * L1_P; }
+
+template <int DS>
+static cudaError_t launch_l1_d(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
+                               float scale, const loda_selection& out, const SelectWorkspace& ws,
+                               const AppendArgs& ap, cudaStream_t st) {
   const int nsplit = l1_nsplit(g);
   const dim3 grid(nsplit + (ap.enabled ? 1 : 0), B.batch * g.num_kv_heads);
   const size_t smem = l1_smem_bytes(g);
-  cudaError_t e = cudaSuccess;
-#define LODA_L1_CASE(DS)                                                                            \
-  case DS: {                                                                                        \
-    static bool attr_set = false;                                                                   \
-    if (!attr_set) {                                                                                \
-      e = cudaFuncSetAttribute(l1_kernel<DS, L1_P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); \
-      if (e != cudaSuccess) return e;                                                               \
-      attr_set = true;                                                                              \
-    }                                                                                               \
-    e = launch_pdl(l1_kernel<DS, L1_P>, grid, dim3(L1_P), smem, st, g, L, B, (const bf16*)q, scale, out, ws, \
-                   nsplit, ap);                                                                     \
-    if (e != cudaSuccess) return e;                                                                 \
-  } break;
+  cudaError_t e = cudaFuncSetAttribute(l1_kernel<DS, L1_P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  return launch_pdl(l1_kernel<DS, L1_P>, grid, dim3(L1_P), smem, st, g, L, B, (const bf16*)q, scale, out, ws,
+                    nsplit, ap);
+}
+
+cudaError_t launch_l1(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
+                      float scale, const loda_selection& out, const SelectWorkspace& ws, const AppendArgs& ap,
+                      cudaStream_t st) {
   switch (g.sub_dims) {
-    LODA_L1_CASE(16)
-    LODA_L1_CASE(32)
-    LODA_L1_CASE(64)
+    case 16: return launch_l1_d<16>(g, L, B, q, scale, out, ws, ap, st);
+    case 32: return launch_l1_d<32>(g, L, B, q, scale, out, ws, ap, st);
+    case 64: return launch_l1_d<64>(g, L, B, q, scale, out, ws, ap, st);
     default: return cudaErrorInvalidValue;
   }
-#undef LODA_L1_CASE
-  return cudaGetLastError();
 }
 
 }  // namespace loda

@@ -125,6 +125,9 @@ class GraphReadyPagedRegionCache:
         self._cpu_meta32 = torch.zeros((2, max_query_tokens), dtype=torch.int32).pin_memory()
         self._runtime = None
         self._nfa_selector_workspace = {}
+        # True: selector calls also write the best-first page lists and the L2
+        # survivors before the union (parity checks); off on the hot path
+        self.selector_diagnostics = False
 
     # -- accessors (reference: paged_region_cache.py:351-365) ----------------
     def gather_indices_for_layer(self, layer_idx):
@@ -390,9 +393,13 @@ class SelectorRuntime:
                            valid_req_ids=c.valid_req_ids_buf.data_ptr(),
                            active_req_ids=c.active_req_ids_buf.data_ptr())
 
-    def selection_struct(self, gather, visible_lens, with_middle=True):
+    def selection_struct(self, gather, visible_lens, with_middle=True, with_page_lists=True):
+        """`with_page_lists` / `with_middle` add the optional diagnostic outputs
+        (best-first page lists, L2 survivors before the union)."""
+        pl = with_page_lists
         return _capi.Selection(
-            i_far=self.i_far.data_ptr(), n_far=self.n_far.data_ptr(), i_near=self.i_near.data_ptr(),
-            n_near=self.n_near.data_ptr(), gather=gather.data_ptr(), visible_lens=visible_lens.data_ptr(),
+            i_far=self.i_far.data_ptr() if pl else None, n_far=self.n_far.data_ptr() if pl else None,
+            i_near=self.i_near.data_ptr() if pl else None, n_near=self.n_near.data_ptr() if pl else None,
+            gather=gather.data_ptr(), visible_lens=visible_lens.data_ptr(),
             middle=self.middle.data_ptr() if with_middle else None,
             middle_counts=self.middle_counts.data_ptr() if with_middle else None)

@@ -102,14 +102,16 @@ def select_topk_for_layer_batched(cache, layer_idx, req_ids, query_states, atten
         kp = vp = sp = None      # K/V already in the pool: refresh the index of the newest token
     gather = cache.gather_indices_for_layer(layer_idx)
     lens = cache.visible_lens_for_layer(layer_idx)
-    sel = rt.selection_struct(gather, lens)
+    diag = bool(getattr(cache, "selector_diagnostics", False))
+    sel = rt.selection_struct(gather, lens, with_middle=diag, with_page_lists=diag)
     _capi.check(lib.loda_select_step(g, layer, C.byref(batch), _capi.ptr(q), kp, vp, sp, scale, C.byref(sel),
                                      status, _capi.ptr(rt.workspace), stream))
 
 
 def last_middle_selection(cache, batch):
     """The L2 survivors of the most recent call as a TokenSelection
-    (logical ids ascending, before the union with sink and window)."""
+    (logical ids ascending, before the union with sink and window).  Only
+    written when ``cache.selector_diagnostics`` is True."""
     rt = cache._runtime
     return TokenSelection(rt.middle[:batch], rt.middle_counts[:batch])
 
@@ -129,7 +131,9 @@ def decode_step_fused(cache, layer_idx, req_ids, query_states, attention, decode
     if out is None:
         out = q.new_empty((b, cache.num_query_heads, cache.layers[layer_idx].head_dim_v))
     batch = rt.batch_struct(b)
-    sel = rt.selection_struct(cache.gather_indices_for_layer(layer_idx), cache.visible_lens_for_layer(layer_idx))
+    diag = bool(getattr(cache, "selector_diagnostics", False))
+    sel = rt.selection_struct(cache.gather_indices_for_layer(layer_idx), cache.visible_lens_for_layer(layer_idx),
+                              with_middle=diag, with_page_lists=diag)
     _capi.check(_capi.lib().loda_decode_step(
         C.byref(rt.geometry), C.byref(rt.layer_structs[layer_idx]), C.byref(batch), _capi.ptr(q),
         _capi.ptr(k), _capi.ptr(v), _capi.ptr(slots), float(attention.scaling), C.byref(sel),

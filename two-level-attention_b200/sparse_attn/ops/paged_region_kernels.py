@@ -29,7 +29,7 @@ def _layer_runtime(cache_layer, *, n_rows, n_query, max_visible, num_q_heads):
     g = _capi.Geometry(
         dtype=_capi.LODA_DTYPE_BF16, num_q_heads=num_q_heads, num_kv_heads=cache_layer.num_kv_heads,
         head_dim=cache_layer.head_dim_k, head_dim_v=cache_layer.head_dim_v, sub_dims=32, sub_lo0=0,
-        sub_lo1=16, page=page, num_pages=cache_layer.max_physical_pages + 1, max_blocks=65536,
+        sub_lo1=16, page=page, num_pages=cache_layer.max_physical_pages + 1, max_blocks=16384,
         max_requests=max(n_rows, 1), max_query_tokens=max(n_query, 1), max_visible=max(max_visible, page),
         k_far=0, k_near=0, level2_topk=max(max_visible, page), sink=0, swa=page, near_len=page,
         pool_near_len=page)

@@ -33,6 +33,7 @@ def make_setup(lengths, *, seed=0, page=16, hq=32, hkv=8, d=128, n_layers=1, max
         n_layers, geometry, max_requests=max_requests or b, max_physical_pages=total_pages,
         max_blocks=max_blocks, max_visible_len=max_visible, max_query_tokens=b, num_kv_heads=hkv,
         num_query_heads=hq, head_dim_k=d, head_dim_v=d, dtype=torch.bfloat16, device=dev)
+    cache.selector_diagnostics = True
     rng = np.random.default_rng(seed)
     free = [int(p) for p in rng.permutation(total_pages)] if shuffle_pages else list(range(total_pages))
     cases, req_ids = [], []
