@@ -123,6 +123,10 @@ class GraphReadyPagedRegionCache:
         self._cpu_slots = torch.full((n_layers, max_query_tokens), PAD_SLOT, dtype=torch.int32).pin_memory()
         self._cpu_meta64 = torch.zeros((2, max_query_tokens), dtype=torch.int64).pin_memory()
         self._cpu_meta32 = torch.zeros((2, max_query_tokens), dtype=torch.int32).pin_memory()
+        # numpy views of the same pinned memory: scalar writes without tensor dispatch
+        self._np_slots = self._cpu_slots.numpy()
+        self._np_meta64 = self._cpu_meta64.numpy()
+        self._np_meta32 = self._cpu_meta32.numpy()
         self._runtime = None
         self._nfa_selector_workspace = {}
         # True: selector calls also write the best-first page lists and the L2
@@ -255,13 +259,14 @@ class GraphReadyPagedRegionCache:
         page = self.geometry.page
         self.active_req_ids = list(active_req_ids)
         self.pending_lengths.clear()
-        act, val = self._cpu_meta64[0], self._cpu_meta64[1]
-        lens, q2r = self._cpu_meta32[0], self._cpu_meta32[1]
+        act, val = self._np_meta64[0], self._np_meta64[1]
+        lens, q2r = self._np_meta32[0], self._np_meta32[1]
         act[:batch] = self.INVALID_REQ_ID
         val[:batch] = 0
         lens[:batch] = 0
-        q2r.fill_(-1)
-        self._cpu_slots[:, :batch] = PAD_SLOT
+        q2r[:] = -1
+        slots_np = self._np_slots
+        slots_np[:, :batch] = PAD_SLOT
         for b, request_id in enumerate(active_req_ids):
             qlen = 1 if query_lengths is None else int(query_lengths[b])
             if request_id is None or request_id < 0 or request_id not in self.states or qlen == 0:
@@ -273,15 +278,19 @@ class GraphReadyPagedRegionCache:
             pos = planned - 1
             lp, off = divmod(pos, page)
             for layer_idx in range(self.n_layers):
-                if self._grow_table(state, request_id, layer_idx, lp + 1):
+                table = state.block_tables[layer_idx]
+                if len(table) <= lp:
+                    self._grow_table(state, request_id, layer_idx, lp + 1)
                     self.block_table_buf[layer_idx, request_id, lp:lp + 1].copy_(
                         self._cpu_block_table[layer_idx, request_id, lp:lp + 1], non_blocking=True)
-                self._cpu_slots[layer_idx, b] = state.block_tables[layer_idx][lp] * page + off
+                slots_np[layer_idx, b] = table[lp] * page + off
             act[b] = request_id
             val[b] = request_id
             lens[b] = planned
             q2r[b] = b
             self.pending_lengths[request_id] = planned
+        act, val = self._cpu_meta64[0], self._cpu_meta64[1]
+        lens, q2r = self._cpu_meta32[0], self._cpu_meta32[1]
         self.slot_mapping_buf[:, :batch].copy_(self._cpu_slots[:, :batch], non_blocking=True)
         self.active_req_ids_buf[:batch].copy_(act[:batch], non_blocking=True)
         self.valid_req_ids_buf[:batch].copy_(val[:batch], non_blocking=True)
