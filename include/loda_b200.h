@@ -225,6 +225,29 @@ int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda
                      float scale, const loda_selection* sel, const int32_t* query_to_req,
                      void* out, uint32_t* status, void* workspace, void* stream);
 
+/* ---- kernels under the TIA indexer's method surface -------------------------
+ * (sparse_attn/indexer/tia_indexer.py; tensors bf16 or fp32, dtype = LODA_DTYPE_*) */
+
+/* y = 4-bit per-token quantise + de-quantise of n_rows rows of `dim` <= 128
+ * values (row strides in elements).  Replaces TIAIndexer.min_max_per_token_quant
+ * (tia_indexer.py:22-31), bit for bit. */
+int loda_tia_quant4(const void* x, void* y, int64_t n_rows, int32_t dim, int64_t x_stride,
+                    int64_t y_stride, int32_t dtype, void* stream);
+
+/* k [S, H, D] -> kmin, kmax [ceil(S / block_size), H, D]; the ragged last block
+ * is padded with zeros before reducing.  Replaces the amin / amax of
+ * TIAIndexer.prepare_index (tia_indexer.py:39-46). */
+int loda_tia_block_minmax(const void* k, void* kmin, void* kmax, int32_t S, int32_t H, int32_t D,
+                          int32_t block_size, int32_t dtype, void* stream);
+
+/* coarse [Hq, T] = sum_d min(q s, 0) kmin + max(q s, 0) kmax and
+ * fine [Hq, S] = sum_d (q s) kqat for q [Hq, D], kmin / kmax [T, Hkv, D],
+ * kqat [S, Hkv, D], s = scale; fp32 accumulate, one rounding to the dtype.
+ * Replaces TIAIndexer.compute_score (tia_indexer.py:64-99). */
+int loda_tia_scores(const void* q, const void* kmin, const void* kmax, const void* kqat,
+                    void* coarse, void* fine, int32_t Hq, int32_t Hkv, int32_t D, int32_t T,
+                    int32_t S, float scale, int32_t dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

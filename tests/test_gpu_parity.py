@@ -211,3 +211,40 @@ def test_graph_replay_equals_eager():
                        < l_eager[..., None]), g_eager * (torch.arange(1024, device=setup.dev) < l_eager[..., None]))
     assert torch.equal(cache.visible_lens_for_layer(0), l_eager)
     assert torch.equal(static_out[0], out_eager)
+
+
+@pytest.mark.parametrize("mode,dtype", [("bf16", torch.bfloat16), ("fp32", torch.float32)])
+def test_tia_surface_matches_reference_golden_outputs(mode, dtype):
+    """TIAIndexer primitives (CUDA kernels) against outputs of the reference's own
+    PyTorch TIAIndexer stored in tests/golden: quantiser and block min/max bit
+    exact, scores to fp32 re-association."""
+    from conftest import golden
+    from helpers import mod
+    tia = mod("sparse_attn.indexer.tia_indexer")
+    nfa = mod("sparse_attn.ops.paged_region_kernels_nfa")
+    ix = tia.TIAIndexer(nfa.nfa_args("tail", tia_block_size=16))
+    dev = "cuda:0"
+
+    def load(g, name):
+        a = g[f"{name}_{mode}"]
+        return torch.from_numpy(O.bits_to_f32(a) if mode == "bf16" else a).to(dev).to(dtype)
+
+    gq = golden("quant4.npz")
+    x = torch.from_numpy(O.bits_to_f32(gq["x_bf16"]) if mode == "bf16" else gq["x_fp32"]).to(dev).to(dtype)
+    want = torch.from_numpy(O.bits_to_f32(gq["y_bf16"]) if mode == "bf16" else gq["y_fp32"]).to(dev).to(dtype)
+    assert torch.equal(ix.min_max_per_token_quant(x), want)
+
+    g = golden("tia_index.npz")
+    length = int(g["length"])
+    k, q = load(g, "k"), load(g, "q")
+    idx = ix.prepare_index(k[None], torch.tensor([0, length], device=dev))
+    assert torch.equal(idx["k_min"][0], load(g, "kmin"))
+    assert torch.equal(idx["k_max"][0], load(g, "kmax"))
+    assert torch.equal(idx["k_qat"][0], load(g, "kqat"))
+    sc = ix.compute_score(q[None, None], torch.tensor([length - 1], device=dev), idx, 128 ** -0.5)
+    tol = 2e-2 if mode == "bf16" else 2e-5
+    torch.testing.assert_close(sc["score_coarse"][0, 0].float(), load(g, "coarse").float(), atol=tol, rtol=tol)
+    torch.testing.assert_close(sc["score_fine"][0, 0].float(), load(g, "fine").float(), atol=tol, rtol=tol)
+    mask, bs = ix.prepare_mask(q[None, None], torch.tensor([length - 1], device=dev), k[None],
+                               torch.tensor([0, length], device=dev))
+    assert bs == 1 and mask.shape == (1, 1, 2, length) and mask[..., -128:].all()

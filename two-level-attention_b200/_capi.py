@@ -52,7 +52,7 @@ class Selection(C.Structure):
 EXPORTS = ("loda_version", "loda_last_error", "loda_workspace_bytes", "loda_append_decode",
            "loda_write_prefill", "loda_build_index", "loda_select_l1", "loda_select_l2",
            "loda_gather_attend", "loda_decode_step", "loda_gather_attend_static",
-           "loda_select_step")
+           "loda_select_step", "loda_tia_quant4", "loda_tia_block_minmax", "loda_tia_scores")
 
 _lib = None
 
@@ -81,6 +81,10 @@ def lib():
     L.loda_gather_attend.argtypes = [G, LY, P, P, P, P, I, I, F, P, P, V]
     L.loda_gather_attend_static.argtypes = [G, LY, P, P, P, P, I, I, F, P, V]
     L.loda_select_step.argtypes = [G, LY, B, P, P, P, P, F, S, P, P, V]
+    I64 = C.c_int64
+    L.loda_tia_quant4.argtypes = [P, P, I64, I, I64, I64, I, V]
+    L.loda_tia_block_minmax.argtypes = [P, P, P, I, I, I, I, I, V]
+    L.loda_tia_scores.argtypes = [P, P, P, P, P, P, I, I, I, I, I, F, I, V]
     L.loda_decode_step.argtypes = [G, LY, B, P, P, P, P, F, S, P, P, P, P, V]
     for name in EXPORTS[3:]:
         getattr(L, name).restype = C.c_int
