@@ -118,62 +118,74 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def build_workload(torch, dev, total_steps, seed):
-    """Cache with N_LAYERS layers holding one CONTEXT-token request each, index
-    built, plus device-resident inputs and metadata for `total_steps` steps."""
+def build_workload(torch, dev, total_steps, seed, lengths=None, n_layers=None):
+    """Cache with `n_layers` layers holding one request per entry of `lengths`
+    (tokens already in the cache), index buffers allocated, plus device-resident
+    inputs for `total_steps` steps."""
     cache_mod = mod("sparse_attn.cache.paged_region_cache")
     geo_mod = mod("sparse_attn.policies.region_geometry")
     nfa = mod("sparse_attn.ops.paged_region_kernels_nfa")
     idx_mod = mod("sparse_attn.indexer.nfa_indexer")
     synth = mod("synth")
     from types import SimpleNamespace
+    lengths = [CONTEXT - 1] if lengths is None else list(lengths)
+    n_layers = N_LAYERS if n_layers is None else n_layers
+    nb = len(lengths)
     args = nfa.nfa_args("tail", tia_block_size=PAGE)
     indexer = idx_mod.NFAIndexer(args)
     geometry = geo_mod.RegionGeometry(sink=4, near=4096, window=128, page=PAGE, max_new_tokens=4096)
-    n_pre = CONTEXT - 1
-    max_blocks = (CONTEXT + 4096 + PAGE - 1) // PAGE
-    pages = max_blocks + 8
+    max_blocks = (max(lengths) + 1 + 4096 + PAGE - 1) // PAGE
+    pages = sum((n + 4096 + PAGE - 1) // PAGE for n in lengths) + 8
     cache = cache_mod.GraphReadyPagedRegionCache(
-        N_LAYERS, geometry, max_requests=1, max_physical_pages=pages, max_blocks=max_blocks,
-        max_visible_len=1024, max_query_tokens=1, num_kv_heads=HKV, num_query_heads=HQ,
+        n_layers, geometry, max_requests=nb, max_physical_pages=pages, max_blocks=max_blocks,
+        max_visible_len=1024, max_query_tokens=nb, num_kv_heads=HKV, num_query_heads=HQ,
         head_dim_k=D, head_dim_v=D, dtype=torch.bfloat16, device=dev)
-    rid = cache.add_request()
     g = torch.Generator(device=dev)
     g.manual_seed(seed)
-    need = (n_pre + PAGE - 1) // PAGE
-    for li in range(N_LAYERS):
-        case = synth.make_decode_case(n_pre, num_q_heads=HQ, num_kv_heads=HKV, head_dim=D,
-                                      seed=seed * 100 + li, dtype=torch.bfloat16, device=dev)
-        perm = torch.randperm(pages, generator=g, device=dev)[:need].tolist()
-        cache.write_prefill(li, rid, case.k.permute(1, 0, 2)[None], case.v.permute(1, 0, 2)[None],
-                            physical_pages=perm)
-        del case
-    cache.freeze(rid)
+    rids = [cache.add_request() for _ in lengths]
+    for li in range(n_layers):
+        perm = torch.randperm(pages, generator=g, device=dev).tolist()     # shuffled free list of this layer
+        used = 0
+        for r, n_pre in enumerate(lengths):
+            need = (n_pre + PAGE - 1) // PAGE
+            case = synth.make_decode_case(n_pre, num_q_heads=HQ, num_kv_heads=HKV, head_dim=D,
+                                          seed=seed * 1000 + li * 97 + r, dtype=torch.bfloat16, device=dev)
+            cache.write_prefill(li, rids[r], case.k.permute(1, 0, 2)[None], case.v.permute(1, 0, 2)[None],
+                                physical_pages=perm[used:used + need])
+            used += need
+            del case
+    for rid in rids:
+        cache.freeze(rid)
     attention = SimpleNamespace(indexer=indexer, scaling=float(D) ** -0.5, layer_idx=0)
     rt = cache.ensure_index(indexer)
-    q = torch.randn(total_steps, N_LAYERS, 1, HQ, D, generator=g, device=dev).to(torch.bfloat16)
-    k = torch.randn(total_steps, N_LAYERS, 1, HKV, 1, D, generator=g, device=dev).to(torch.bfloat16)
-    v = torch.randn(total_steps, N_LAYERS, 1, HKV, 1, D, generator=g, device=dev).to(torch.bfloat16)
-    return SimpleNamespace(cache=cache, rid=rid, attention=attention, rt=rt, q=q, k=k, v=v, indexer=indexer)
+    q = torch.randn(total_steps, n_layers, nb, HQ, D, generator=g, device=dev).to(torch.bfloat16)
+    k = torch.randn(total_steps, n_layers, nb, HKV, 1, D, generator=g, device=dev).to(torch.bfloat16)
+    v = torch.randn(total_steps, n_layers, nb, HKV, 1, D, generator=g, device=dev).to(torch.bfloat16)
+    return SimpleNamespace(cache=cache, rid=rids[0], rids=rids, attention=attention, rt=rt, q=q, k=k, v=v,
+                           indexer=indexer, lengths=lengths, n_layers=n_layers, batch=nb)
 
 
-def preplan(torch, wl, first_len, n_steps):
-    """Device-resident lengths / slots for steps first_len+1 ... and grown block tables."""
-    cache, rid = wl.cache, wl.rid
-    state = cache.states[rid]
-    lengths = torch.zeros(n_steps, 1, dtype=torch.int32)
-    slots = torch.zeros(n_steps, N_LAYERS, 1, dtype=torch.int32)
-    for s in range(n_steps):
-        planned = first_len + s + 1
-        lp, off = divmod(planned - 1, PAGE)
-        lengths[s, 0] = planned
-        for li in range(N_LAYERS):
-            cache._grow_table(state, rid, li, lp + 1)
-            slots[s, li, 0] = state.block_tables[li][lp] * PAGE + off
-    cache.block_table_buf[:, rid].copy_(cache._cpu_block_table[:, rid])
-    cache.active_req_ids_buf[:1] = rid
-    cache.valid_req_ids_buf[:1] = rid
-    cache.query_to_req_buf[:1] = 0
+def preplan(torch, wl, n_steps):
+    """Device-resident lengths / slots of the next `n_steps` decode steps; grows the block tables."""
+    cache = wl.cache
+    nb, nl = wl.batch, wl.n_layers
+    lengths = torch.zeros(n_steps, nb, dtype=torch.int32)
+    slots = torch.zeros(n_steps, nl, nb, dtype=torch.int32)
+    for r, rid in enumerate(wl.rids):
+        state = cache.states[rid]
+        first_len = state.logical_length
+        for s in range(n_steps):
+            planned = first_len + s + 1
+            lp, off = divmod(planned - 1, PAGE)
+            lengths[s, r] = planned
+            for li in range(nl):
+                cache._grow_table(state, rid, li, lp + 1)
+                slots[s, li, r] = state.block_tables[li][lp] * PAGE + off
+        cache.block_table_buf[:, rid].copy_(cache._cpu_block_table[:, rid])
+    ids = torch.tensor(wl.rids, dtype=torch.int64)
+    cache.active_req_ids_buf[:nb] = ids.to(cache.device)
+    cache.valid_req_ids_buf[:nb] = ids.to(cache.device)
+    cache.query_to_req_buf[:nb] = torch.arange(nb, dtype=torch.int32, device=cache.device)
     return lengths.to(cache.device), slots.to(cache.device)
 
 
@@ -185,9 +197,10 @@ def launch_step(capi, lib, wl, s, lengths, slots, out, which="fused", layers=Non
     status = C.c_void_p(cache.status_buf.data_ptr())
     ws = capi.ptr(rt.workspace)
     scale = float(wl.attention.scaling)
-    batch = capi.Batch(batch=1, lengths=lengths[s].data_ptr(), valid_req_ids=cache.valid_req_ids_buf.data_ptr(),
+    nb = wl.batch
+    batch = capi.Batch(batch=nb, lengths=lengths[s].data_ptr(), valid_req_ids=cache.valid_req_ids_buf.data_ptr(),
                        active_req_ids=cache.active_req_ids_buf.data_ptr())
-    for li in (range(N_LAYERS) if layers is None else layers):
+    for li in (range(wl.n_layers) if layers is None else layers):
         layer = C.byref(rt.layer_structs[li])
         sel = rt.selection_struct(cache.gather_indices_for_layer(li), cache.visible_lens_for_layer(li), False, False)
         qp = capi.ptr(wl.q[s, li])
@@ -207,7 +220,7 @@ def launch_step(capi, lib, wl, s, lengths, slots, out, which="fused", layers=Non
         if "attn" in which:
             capi.check(lib.loda_gather_attend(g, layer, qp, capi.ptr(cache.gather_indices_for_layer(li)),
                                               capi.ptr(cache.visible_lens_for_layer(li)),
-                                              capi.ptr(cache.query_to_req_buf), 1, 1, scale, capi.ptr(out[li]),
+                                              capi.ptr(cache.query_to_req_buf), nb, nb, scale, capi.ptr(out[li]),
                                               ws, stream))
 
 
@@ -247,6 +260,89 @@ def dense_decode_us(torch, wl):
         return time_kernel(torch, call, 30), "flash_attn_with_kvcache, contiguous KV, 131072 tokens"
     except Exception as exc:      # noqa: BLE001
         return None, f"flash_attn failed: {type(exc).__name__}: {exc}"
+
+
+def measure_device(torch, capi, lib, wl, W, K, barrier):
+    """Device-resident timing of a workload: W eager warm-up steps, K steps in one
+    CUDA graph between events, then each kernel kind alone over all layers."""
+    cache = wl.cache
+    sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
+    lengths, slots = preplan(torch, wl, W + K)
+    out = torch.zeros(wl.n_layers, wl.batch, HQ, D, dtype=torch.bfloat16, device=cache.device)
+    # the index of the prefilled pages is built by one bulk pass before the first step
+    for li in range(wl.n_layers):
+        sel_mod._ensure_index_built(cache, wl.rt, li, wl.rids, has_current_token_in_pool=True)
+    torch.cuda.synchronize()
+    for s in range(W):
+        launch_step(capi, lib, wl, s, lengths, slots, out)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            for s in range(W, W + K):
+                launch_step(capi, lib, wl, s, lengths, slots, out)
+    time.sleep(0.3)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        graph.replay()
+        e1.record(stream)
+    stream.synchronize()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    status = cache.read_status()
+    # Each kernel kind is captured alone in a graph over all layers (rotating pools defeat the
+    # L2 cache like the real chain does) so that host launch cost is not part of the figure.
+    s_last = W + K - 1
+    per_kernel = {}
+    for name in ("append", "l1", "l2", "attn"):
+        launch_step(capi, lib, wl, s_last, lengths, slots, out, which=(name,))
+        torch.cuda.synchronize()
+        kgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(kgraph, stream=stream):
+                launch_step(capi, lib, wl, s_last, lengths, slots, out, which=(name,))
+        with torch.cuda.stream(stream):
+            kgraph.replay()
+            ke0, ke1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ke0.record(stream)
+            for _ in range(5):
+                kgraph.replay()
+            ke1.record(stream)
+        stream.synchronize()
+        per_kernel[name] = ke0.elapsed_time(ke1) * 1e3 / (5 * wl.n_layers)
+    for rid in wl.rids:      # the cache now holds W + K more tokens per request
+        st = cache.states[rid]
+        st.logical_length += W + K
+        for li in range(wl.n_layers):
+            st.index_len[li] = st.logical_length
+    return ms_total, per_kernel, status, stream, out
+
+
+def batched_arm(torch, capi, lib, dev, seed, barrier):
+    """Config 3 shape: 32 requests with lengths uniform in [8192, 65536] in one shared pool with
+    shuffled page tables, two layers (so that a step's touched bytes exceed L2); reports the
+    kernels' durations and the L1 kernel's bandwidth at a batch where it is not latency bound."""
+    import random
+    rnd = random.Random(seed)
+    lens = [rnd.randint(8192, 65536) for _ in range(32)]
+    wl = build_workload(torch, dev, 3 + 5 + 2, seed, lengths=lens, n_layers=2)
+    ms_total, per_kernel, status, _, _ = measure_device(torch, capi, lib, wl, 3, 5, barrier)
+    l1_bytes = sum(algorithmic_bytes(n + 1)["l1"] for n in lens)
+    tot_bytes = sum(algorithmic_bytes(n + 1)["total"] for n in lens)
+    peak, kind = peaks()
+    us_layer = ms_total * 1e3 / (5 * wl.n_layers)
+    return {"workload": "cfg3: 32 requests, context uniform in [8192, 65536], shuffled pages, 2 layers",
+            "tokens_in_cache": sum(lens), "us_per_decode_step_per_layer": us_layer,
+            "tok_s_per_layer_stack": 32 / (us_layer * 1e-6 * N_LAYERS),
+            "kernel_us_per_launch": per_kernel, "device_status": status,
+            "l1_roofline": {"bound": "hbm", "achieved": l1_bytes / (per_kernel["l1"] * 1e-6) / 1e9, "peak": peak,
+                            "unit": "GB/s", "frac": l1_bytes / (per_kernel["l1"] * 1e-6) / 1e9 / peak,
+                            "peak_kind": f"of {kind}", "algorithmic_bytes": l1_bytes},
+            "chain_hbm_frac_of_8TBs": tot_bytes / (us_layer * 1e-6) / 8e12}
 
 
 def cpu_baseline(sample_steps=3, threads=1):
@@ -314,6 +410,7 @@ def main():
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-dense", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-batched", action="store_true")
     ap.add_argument("--layers", type=int, default=N_LAYERS,
                     help="profiling aid: fewer layers than the 36 of the named workload (not a bench line)")
     args = ap.parse_args()
@@ -346,61 +443,9 @@ def main():
     total = W + K + W + e2e_steps + 8
     wl = build_workload(torch, dev, total, seed=11 + rank)
     cache = wl.cache
-    lengths, slots = preplan(torch, wl, CONTEXT - 1, W + K)
-    out = torch.zeros(N_LAYERS, 1, HQ, D, dtype=torch.bfloat16, device=dev)
-
-    # first eager step builds the index of the prefilled pages
-    sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
-    for li in range(N_LAYERS):
-        sel_mod._ensure_index_built(cache, wl.rt, li, [wl.rid], has_current_token_in_pool=False)
-    torch.cuda.synchronize()
-
-    # ---- device-resident timing: warm-up eager, K steps in one CUDA graph ----------
-    for s in range(W):
-        launch_step(capi, lib, wl, s, lengths, slots, out)
-    torch.cuda.synchronize()
-    stream = torch.cuda.Stream()
-    stream.wait_stream(torch.cuda.current_stream())
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(stream):
-        with torch.cuda.graph(graph, stream=stream):
-            for s in range(W, W + K):
-                launch_step(capi, lib, wl, s, lengths, slots, out)
     sampler = ClockSampler(local)
     sampler.start()
-    time.sleep(0.3)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    with torch.cuda.stream(stream):
-        e0.record(stream)
-        graph.replay()
-        e1.record(stream)
-    stream.synchronize()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
-    status = cache.read_status()
-
-    # ---- per-kernel durations (CUDA events on the launching stream, rotating layers) ----
-    # Each kernel kind is captured alone in a graph over all layers (rotating pools defeat the
-    # L2 cache like the real chain does) so that host launch cost is not part of the figure.
-    s_last = W + K - 1
-    per_kernel = {}
-    for name in ("append", "l1", "l2", "attn"):
-        launch_step(capi, lib, wl, s_last, lengths, slots, out, which=(name,))
-        torch.cuda.synchronize()
-        kgraph = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(stream):
-            with torch.cuda.graph(kgraph, stream=stream):
-                launch_step(capi, lib, wl, s_last, lengths, slots, out, which=(name,))
-        with torch.cuda.stream(stream):
-            kgraph.replay()
-            ke0, ke1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            ke0.record(stream)
-            for _ in range(5):
-                kgraph.replay()
-            ke1.record(stream)
-        stream.synchronize()
-        per_kernel[name] = ke0.elapsed_time(ke1) * 1e3 / (5 * N_LAYERS)
+    ms_total, per_kernel, status, stream, out = measure_device(torch, capi, lib, wl, W, K, barrier)
     clocks = sampler.stop()
 
     t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
@@ -411,9 +456,6 @@ def main():
     tok_s = world * 1.0 / (ms_per_step * 1e-3)
 
     # ---- end to end through the public Python API with host buffers ----------------
-    cache.states[wl.rid].logical_length = CONTEXT - 1 + W + K
-    for li in range(N_LAYERS):
-        cache.states[wl.rid].index_len[li] = CONTEXT - 1 + W + K
     base_s = W + K
     hq_ = wl.q[base_s:base_s + W + e2e_steps].cpu().pin_memory()
     hk_ = wl.k[base_s:base_s + W + e2e_steps].cpu().pin_memory()
@@ -476,6 +518,10 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": K * N_LAYERS * 3, "device_status": status, "clocks": clocks,
         }
+        if not args.skip_batched:
+            del wl, runner, cache
+            torch.cuda.empty_cache()
+            line["batched"] = batched_arm(torch, capi, lib, dev, 5, lambda: torch.cuda.synchronize())
         if not args.skip_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(sample_steps=3)
         print(json.dumps(line), flush=True)
