@@ -248,3 +248,41 @@ def test_tia_surface_matches_reference_golden_outputs(mode, dtype):
     mask, bs = ix.prepare_mask(q[None, None], torch.tensor([length - 1], device=dev), k[None],
                                torch.tensor([0, length], device=dev))
     assert bs == 1 and mask.shape == (1, 1, 2, length) and mask[..., -128:].all()
+
+
+def test_tls_attn_sparse_and_dense_mha_match_softmax_reference():
+    """tls_attn.ops SparseMHAInterface / MHAInterface on a contiguous cache against
+    a float64 softmax (the semantics of the reference's ref_attn), holes included."""
+    from helpers import mod
+    ops = mod("tls_attn.ops")
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(3)
+    B, S, Hq, Hkv, D, topk = 3, 700, 8, 2, 128, 256
+    q = torch.randn(B, 1, Hq, D, generator=g).bfloat16().to(dev)
+    k = torch.randn(B + 1, S, Hkv, D, generator=g).bfloat16().to(dev)
+    v = torch.randn(B + 1, S, Hkv, D, generator=g).bfloat16().to(dev)
+    idx = torch.stack([torch.stack([torch.randperm(S, generator=g)[:topk].sort().values for _ in range(Hkv)])
+                       for _ in range(B)]).int()
+    idx[0, 1, 10:40] = -1
+    idx[2, 0, -5:] = -1
+    lengths = torch.tensor([700, 123, 512, 9], dtype=torch.int32)
+
+    def ref(sel):      # sel(b, h) -> token ids
+        out = torch.zeros(B, Hq, D, dtype=torch.float64)
+        for b in range(B):
+            for h in range(Hkv):
+                t = sel(b, h)
+                kk, vv = k[b, t, h].double().cpu(), v[b, t, h].double().cpu()
+                qq = q[b, 0, h * 4:(h + 1) * 4].double().cpu()
+                p = torch.softmax(qq @ kk.T * D ** -0.5, dim=-1)
+                out[b, h * 4:(h + 1) * 4] = p @ vv
+        return out
+
+    sparse = ops.SparseMHAInterface(Hq, Hkv, D, D, topk)
+    got = sparse.forward(q, k, v, idx.to(dev))
+    want = ref(lambda b, h: idx[b, h][idx[b, h] >= 0].long())
+    torch.testing.assert_close(got[:, 0].double().cpu(), want, atol=ATOL, rtol=RTOL)
+    dense = ops.MHAInterface(Hq, Hkv, D, D)
+    got = dense.forward(q, k, v, lengths.to(dev))
+    want = ref(lambda b, h: torch.arange(int(lengths[b])))
+    torch.testing.assert_close(got[:, 0].double().cpu(), want, atol=ATOL, rtol=RTOL)

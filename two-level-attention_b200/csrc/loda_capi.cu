@@ -112,7 +112,8 @@ static int check_geometry(const loda_geometry* g) {
     return fail(LODA_ERR_ARGUMENT, "k_far / k_near exceed max_blocks");
   if ((size_t)(g->k_far + g->k_near + 2) * g->page > 32768)
     return fail(LODA_ERR_UNSUPPORTED, "more than 32768 L2 candidate slots per row");
-  if (g->page < 8) return fail(LODA_ERR_UNSUPPORTED, "page must be at least 8 tokens");
+  if (g->page < 8 && g->k_far + g->k_near > 0)
+    return fail(LODA_ERR_UNSUPPORTED, "the selector needs pages of at least 8 tokens");
   if (g->pool_near_len / g->page + 1 > 512)
     return fail(LODA_ERR_UNSUPPORTED, "near pool wider than 512 pages");
   if (g->level2_topk < g->sink + g->swa) return fail(LODA_ERR_ARGUMENT, "level2_topk < sink + swa");
