@@ -511,7 +511,9 @@ def main():
             "chain_hbm_frac_of_8TBs": ab["total"] / (us_layer * 1e-6) / 8e12,
             "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                         "traffic": None},
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel on
+                         # this workload (profiles/fused_chain_cfg2_128k_batch1.md); not measured live
+                         "traffic": 8371456 if dominant == "l1" else None},
             "dense_decode": {"us_per_layer": dense_us, "note": dense_note,
                              "ours_over_dense": (us_layer / dense_us) if dense_us else None},
             "e2e": {"value": world * 1e3 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
