@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(NT) l2_kernel(loda_geometry g, loda_layer L, l
   unsigned char* p = smem + (((size_t)np_max * g.page * 2 + 15) & ~(size_t)15);
   float* qf = (float*)p; p += DSUB * 4;
   int* pages = (int*)p; p += np_max * 4;
+  int* physs = (int*)p; p += np_max * 4;
   int* mid_a = (int*)p; p += K2 * 4;
   int* mid_b = (int*)p; p += K2 * 4;
   p = (unsigned char*)(((uintptr_t)p + 15) & ~(uintptr_t)15);
@@ -145,13 +146,56 @@ __global__ void __launch_bounds__(NT) l2_kernel(loda_geometry g, loda_layer L, l
   if (!sh[0]) return;
   __threadfence();
   for (int i = tid; i < (nitems + 7) / 8; i += NT) ((uint4*)sc)[i] = __ldcg((const uint4*)row_scores + i);
-  for (int i = tid; i < np; i += NT) pages[i] = __ldcg(ws.pages + (size_t)row * np_max + i);
+  for (int i = tid; i < np; i += NT) {
+    pages[i] = __ldcg(ws.pages + (size_t)row * np_max + i);
+    physs[i] = __ldcg(ws.phys + (size_t)row * np_max + i);
+  }
   __syncthreads();
   LODA_PHASE(l2, cta_id, 5);
   const int quota = rg.quota;
   int* slots_sel = mid_b;      // ascending candidate slots kept by the select
   const int take = block_bisect_topk<NT>(sc, nitems, min(quota, K2), slots_sel, wtot);
   LODA_PHASE(l2, cta_id, 6);
+  if (take == quota) {
+    // Common case: the quota is filled by scored candidates (all of them >= sink, no holes).
+    // The survivors' physical pages came with the page list, so only the sink and window ids
+    // need a block-table lookup: sink ++ middle ++ window, one pass.
+    const int cap = g.max_blocks * g.page;
+    const int sk = min(length, g.sink);
+    const int count_s = min(length, g.sink + g.swa) - sk;
+    const int s_lo = max(max(length - g.swa, 0), sk);
+    const int s_hi = min(length - g.swa + count_s, cap);
+    const int n_s = max(s_hi - s_lo, 0);
+    const int total = sk + take + n_s;
+    const int n_out = min(total, g.max_visible);
+    int32_t* gout = S.gather + ((size_t)b * g.num_kv_heads + kv) * g.max_visible;
+    for (int i = tid; i < n_out; i += NT) {
+      int slot;
+      if (i >= sk && i < sk + take) {
+        const int sl = slots_sel[i - sk];
+        slot = physs[sl / g.page] * g.page + sl % g.page;
+        if (S.middle != nullptr) S.middle[(size_t)row * K2 + (i - sk)] = pages[sl / g.page] * g.page + sl % g.page;
+      } else {
+        const int id = i < sk ? i : s_lo + (i - sk - take);
+        const int lp = id / g.page;
+        int ph = lp < g.max_blocks ? table[lp] : -1;
+        if (ph < 0 || ph >= g.num_pages) {
+          if (status) atomicOr(status, LODA_STATUS_BAD_PAGE);
+          ph = g.num_pages - 1;
+        }
+        slot = ph * g.page + id % g.page;
+      }
+      gout[i] = slot;
+    }
+    if (tid == 0) {
+      if (S.middle != nullptr) S.middle_counts[row] = take;
+      S.visible_lens[(size_t)b * g.num_kv_heads + kv] = n_out;
+      if (total > g.max_visible && status) atomicOr(status, LODA_STATUS_TRUNCATED);
+      ws.l2_ticket[row] = 0;
+    }
+    LODA_PHASE(l2, cta_id, 9);
+    return;
+  }
   for (int i = tid; i < take; i += NT) {
     const int sl = slots_sel[i];
     mid_a[i] = pages[sl / g.page] * g.page + sl % g.page;
@@ -242,7 +286,7 @@ __global__ void __launch_bounds__(NT) l2_kernel(loda_geometry g, loda_layer L, l
 
 size_t l2_smem_bytes(const loda_geometry& g) {
   const size_t np_max = g.k_far + g.k_near + 2;
-  return ((np_max * g.page * 2 + 15) & ~(size_t)15) + g.sub_dims * 4 + np_max * 4 +
+  return ((np_max * g.page * 2 + 15) & ~(size_t)15) + g.sub_dims * 4 + 2 * np_max * 4 +
          2 * (size_t)g.level2_topk * 4 + 192 * 4 + (40 + 16) * 4 + g.level2_topk + 48;
 }
 
