@@ -401,7 +401,7 @@ def run_reference(args, rank, world):
 
 
 def main():
-    global N_LAYERS
+    global N_LAYERS, HQ, HKV
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -411,6 +411,9 @@ def main():
     ap.add_argument("--skip-dense", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-batched", action="store_true")
+    ap.add_argument("--shard", default="request", choices=("request", "kvhead"),
+                    help="multi-GPU partition: one independent request shard per GPU (weak scaling, default) "
+                         "or the KV-head groups of ONE request split over the GPUs (strong scaling)")
     ap.add_argument("--layers", type=int, default=N_LAYERS,
                     help="profiling aid: fewer layers than the 36 of the named workload (not a bench line)")
     args = ap.parse_args()
@@ -423,6 +426,10 @@ def main():
         return
     if args.warmup < 3:
         args.warmup = 3
+    kvhead = args.shard == "kvhead" and world > 1
+    if kvhead:
+        shard = mod("sharding").kv_head_shard(HQ, HKV, world, rank)
+        HQ, HKV = shard.num_q_heads, shard.num_kv_heads      # this rank's heads of the same request
 
     import torch
     import torch.distributed as dist
@@ -441,7 +448,7 @@ def main():
     K, W = args.steps, args.warmup
     e2e_steps = K
     total = W + K + W + e2e_steps + 8
-    wl = build_workload(torch, dev, total, seed=11 + rank)
+    wl = build_workload(torch, dev, total, seed=11 + (0 if kvhead else rank))
     cache = wl.cache
     sampler = ClockSampler(local)
     sampler.start()
@@ -453,7 +460,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total = float(t.item())
     ms_per_step = ms_total / K
-    tok_s = world * 1.0 / (ms_per_step * 1e-3)
+    tok_s = (1.0 if kvhead else world) / (ms_per_step * 1e-3)
 
     # ---- end to end through the public Python API with host buffers ----------------
     base_s = W + K
@@ -498,13 +505,15 @@ def main():
         us_layer = ms_per_step * 1e3 / N_LAYERS
         line = {
             "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if kvhead else "weak",
+            "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "cfg2-qwen3-8b-128k", "layers": N_LAYERS, "context": CONTEXT, "batch": 1,
                        "page": PAGE, "heads": f"{HQ}q/{HKV}kv", "head_dim": D,
                        "selector": "K1=128 (32 near), K2=1024, tail32 int4, sink 4, swa 128",
                        "l2_flush": "none needed: 36 layers x 12.8 MB touched per step exceeds the 126 MB L2",
-                       "sharding": "one independent request shard per GPU, no data-path collective"},
+                       "sharding": (f"KV-head groups of one request, {HKV} KV heads per GPU, no data-path collective"
+                                    if kvhead else "one independent request shard per GPU, no data-path collective")},
             "us_per_decode_step_per_layer": us_layer,
             "kernel_us_per_launch": per_kernel,
             "algorithmic_bytes_per_layer_step": ab,
@@ -516,14 +525,16 @@ def main():
                          "traffic": 8371456 if dominant == "l1" else None},
             "dense_decode": {"us_per_layer": dense_us, "note": dense_note,
                              "ours_over_dense": (us_layer / dense_us) if dense_us else None},
-            "e2e": {"value": world * 1e3 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
+            "e2e": {"value": (1 if kvhead else world) * 1e3 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": K * N_LAYERS * 3, "device_status": status, "clocks": clocks,
         }
-        if not args.skip_batched:
+        if not args.skip_batched and not kvhead:
             del wl, runner, cache
             torch.cuda.empty_cache()
             line["batched"] = batched_arm(torch, capi, lib, dev, 5, lambda: torch.cuda.synchronize())
+        if kvhead:
+            line.pop("batched", None)
         if not args.skip_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(sample_steps=3)
         print(json.dumps(line), flush=True)

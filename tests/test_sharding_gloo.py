@@ -1,0 +1,83 @@
+"""World-size-2 checks of the multi-GPU host logic on CPU (gloo): KV-head
+partition, output all-gather, max-over-ranks timing and the log-sum-exp merge."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT, load_pkg
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        sh = load_pkg("sharding")
+        hq, hkv, d, b = 32, 8, 16, 3
+        shard = sh.kv_head_shard(hq, hkv, world, rank)
+        gen = torch.Generator().manual_seed(0)
+        full = torch.randn(b, hq, d, generator=gen)                 # same on every rank
+        local = full[:, shard.q_lo:shard.q_hi]
+        got = sh.gather_head_outputs(local)
+        ok = torch.equal(got, full)
+        slow = sh.max_over_ranks(1.0 + rank, "cpu")
+        q.put((rank, ok, slow, (shard.kv_lo, shard.kv_hi, shard.q_lo, shard.q_hi)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_kv_head_partition_and_output_gather_world2():
+    world, port = 2, 29000 + os.getpid() % 2000
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert [r[1] for r in res] == [True, True]
+    assert [r[2] for r in res] == [2.0, 2.0]                       # the slowest rank's time everywhere
+    assert res[0][3] == (0, 4, 0, 16) and res[1][3] == (4, 8, 16, 32)
+
+
+def test_partition_helpers_reject_uneven_splits():
+    sh = load_pkg("sharding")
+    with pytest.raises(ValueError):
+        sh.kv_head_shard(32, 8, 3, 0)
+    with pytest.raises(ValueError):
+        sh.kv_head_shard(30, 8, 2, 0)
+    assert sh.request_shard(7, 2, 1) == [1, 3, 5]
+    covered = sorted(sum((sh.request_shard(7, 3, r) for r in range(3)), []))
+    assert covered == list(range(7))
+
+
+def test_lse_merge_of_disjoint_token_sets_equals_full_attention():
+    sh = load_pkg("sharding")
+    g = torch.Generator().manual_seed(1)
+    n, d, heads = 300, 32, 4
+    q = torch.randn(heads, d, generator=g, dtype=torch.float64)
+    k = torch.randn(n, d, generator=g, dtype=torch.float64)
+    v = torch.randn(n, d, generator=g, dtype=torch.float64)
+    log2e = 1.4426950408889634
+    s = (q @ k.T) * d ** -0.5 * log2e                      # exp2 domain, as the kernels keep it
+    full = torch.softmax(s / log2e, dim=-1) @ v
+    parts = [torch.arange(0, n, 3), torch.arange(1, n, 3), torch.arange(2, n, 3), torch.arange(0, 0)]
+    outs, ms, zs = [], [], []
+    for idx in parts:
+        if len(idx) == 0:
+            outs.append(torch.zeros(heads, d)); ms.append(torch.full((heads,), float("-inf"))); zs.append(torch.zeros(heads))
+            continue
+        sp = s[:, idx]
+        m = sp.max(dim=-1).values
+        p = torch.exp2(sp - m[:, None])
+        z = p.sum(-1)
+        outs.append(((p @ v[idx]) / z[:, None]).float()); ms.append(m.float()); zs.append(z.float())
+    merged = sh.lse_merge(torch.stack(outs), torch.stack(ms), torch.stack(zs))
+    np.testing.assert_allclose(merged.numpy(), full.float().numpy(), rtol=2e-5, atol=2e-5)
