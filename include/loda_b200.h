@@ -196,6 +196,17 @@ int loda_gather_attend(const loda_geometry* g, const loda_layer* layer,
                        const int32_t* query_to_req, int32_t n_query, int32_t n_req_rows,
                        float scale, void* out, void* workspace, void* stream);
 
+/* Same as loda_gather_attend, additionally writing lse [n_query, Hq, 2] float:
+ * the row maximum of the scaled scores in the exp2 domain and the softmax sum.
+ * Partial attentions over disjoint token sets (pages of one long request held
+ * by different GPUs) merge exactly from (out, lse): see lse_merge in
+ * two-level-attention_b200/sharding.py.  Extends the split combine of the
+ * reference (paged_region_kernels.py:578-607) across devices. */
+int loda_gather_attend_lse(const loda_geometry* g, const loda_layer* layer,
+                           const void* q, const int32_t* gather, const int32_t* visible_lens,
+                           const int32_t* query_to_req, int32_t n_query, int32_t n_req_rows,
+                           float scale, void* out, float* lse, void* workspace, void* stream);
+
 /* Gather attention without a caller-provided workspace and without any
  * allocation.  (No counterpart in the reference: its Triton operators always
  * allocate their split buffers through torch.)

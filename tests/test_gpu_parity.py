@@ -286,3 +286,33 @@ def test_tls_attn_sparse_and_dense_mha_match_softmax_reference():
     got = dense.forward(q, k, v, lengths.to(dev))
     want = ref(lambda b, h: torch.arange(int(lengths[b])))
     torch.testing.assert_close(got[:, 0].double().cpu(), want, atol=ATOL, rtol=RTOL)
+
+
+def test_partial_attentions_merge_by_lse_to_the_full_attention():
+    """Sequence sharding building block: the selected tokens of a request are dealt
+    to two "owners" by logical page parity; each attends over its own tokens and
+    reports (out, lse); the fixed-order merge equals the unsharded attention."""
+    from helpers import make_setup, mod
+    ops = mod("sparse_attn.ops.paged_region_kernels")
+    sharding = mod("sharding")
+    setup = make_setup([9000, 300, 2500], seed=6)
+    out_full = _run_step(setup)
+    cache = setup.cache
+    layer = cache.layers[0]
+    gather = cache.gather_indices_for_layer(0)
+    lens = cache.visible_lens_for_layer(0)
+    q2r = cache.query_to_req_buf
+    # owner of a slot: parity of its physical page (any disjoint split works)
+    col = torch.arange(gather.shape[-1], device=setup.dev)
+    valid = col < lens[..., None]
+    parts = []
+    for owner in range(2):
+        mine = valid & (((gather // 16) % 2) == owner)
+        parts.append(torch.where(mine, gather, torch.full_like(gather, -1)))   # holes are skipped by the kernel
+    outs, ms, zs = [], [], []
+    for g_part in parts:
+        o, lse = ops.sparse_paged_attention_gather(layer, setup.q, g_part, lens, q2r,
+                                                   scale=setup.attention.scaling, return_lse=True)
+        outs.append(o.float()); ms.append(lse[..., 0]); zs.append(lse[..., 1])
+    merged = sharding.lse_merge(torch.stack(outs), torch.stack(ms), torch.stack(zs))
+    torch.testing.assert_close(merged, out_full.float(), atol=ATOL, rtol=RTOL)

@@ -52,7 +52,7 @@ class Selection(C.Structure):
 EXPORTS = ("loda_version", "loda_last_error", "loda_workspace_bytes", "loda_append_decode",
            "loda_write_prefill", "loda_build_index", "loda_select_l1", "loda_select_l2",
            "loda_gather_attend", "loda_decode_step", "loda_gather_attend_static",
-           "loda_select_step", "loda_tia_quant4", "loda_tia_block_minmax", "loda_tia_scores")
+           "loda_select_step", "loda_tia_quant4", "loda_tia_block_minmax", "loda_tia_scores", "loda_gather_attend_lse")
 
 _lib = None
 
@@ -79,6 +79,7 @@ def lib():
     L.loda_select_l1.argtypes = [G, LY, B, P, F, S, P, V]
     L.loda_select_l2.argtypes = [G, LY, B, P, F, S, P, P, V]
     L.loda_gather_attend.argtypes = [G, LY, P, P, P, P, I, I, F, P, P, V]
+    L.loda_gather_attend_lse.argtypes = [G, LY, P, P, P, P, I, I, F, P, P, P, V]
     L.loda_gather_attend_static.argtypes = [G, LY, P, P, P, P, I, I, F, P, V]
     L.loda_select_step.argtypes = [G, LY, B, P, P, P, P, F, S, P, P, V]
     I64 = C.c_int64

@@ -63,7 +63,8 @@ template <int D, int DV, bool CLUSTER>
 __global__ void __launch_bounds__(ATT_NT) attn_kernel(
     loda_geometry g, loda_layer L, const bf16* __restrict__ q, const int32_t* __restrict__ gather,
     const int32_t* __restrict__ visible_lens, const int32_t* __restrict__ query_to_req,
-    int n_req_rows, float scale_log2, bf16* __restrict__ out, AttnWorkspace ws, int nsplit) {
+    int n_req_rows, float scale_log2, bf16* __restrict__ out, float* __restrict__ lse, AttnWorkspace ws,
+    int nsplit) {
   constexpr int KSTR = D + 8, VSTR = DV + 8;   // padded rows: conflict-free ldmatrix
   constexpr int KSTEPS = D / 16, NTV = DV / 8;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -256,6 +257,10 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
     }
     if (nsplit == 1) {
       out[((size_t)t * g.num_q_heads + kv * G + gi) * DV + dv] = __float2bfloat16_rn(z == 0.0f ? 0.0f : o / z);
+      if (lse != nullptr && dv == 0) {
+        lse[((size_t)t * g.num_q_heads + kv * G + gi) * 2 + 0] = M;
+        lse[((size_t)t * g.num_q_heads + kv * G + gi) * 2 + 1] = z;
+      }
     } else if (CLUSTER) {
       fo[e] = o;
       if (dv == 0) { fm[gi] = M; fz[gi] = z; }
@@ -301,6 +306,10 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
         }
       }
       out[((size_t)t * g.num_q_heads + kv * G + gi) * DV + dv] = __float2bfloat16_rn(z == 0.0f ? 0.0f : o / z);
+      if (lse != nullptr && dv == 0) {
+        lse[((size_t)t * g.num_q_heads + kv * G + gi) * 2 + 0] = M;
+        lse[((size_t)t * g.num_q_heads + kv * G + gi) * 2 + 1] = z;
+      }
     }
     cluster.sync();   // nobody leaves while a peer may still read its shared memory
     LODA_PHASE(attn, cta_id, 8);
@@ -336,6 +345,10 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
       z += sm_z[s * G + tid] * a;
     }
     sm_zt[tid] = z;
+    if (lse != nullptr) {
+      lse[((size_t)t * g.num_q_heads + kv * G + tid) * 2 + 0] = M;
+      lse[((size_t)t * g.num_q_heads + kv * G + tid) * 2 + 1] = z;
+    }
   }
   __syncthreads();
   const float* po = ws.part_o + pair * nsplit * G * DV;
@@ -388,7 +401,8 @@ template <int D, int DV>
 static cudaError_t launch_attn_dims(const loda_geometry& g, const loda_layer& L, const void* q,
                                     const int32_t* gather, const int32_t* visible_lens,
                                     const int32_t* query_to_req, int n_query, int n_req_rows, float scale_log2,
-                                    void* out, const AttnWorkspace& ws, bool allow_cluster, cudaStream_t st) {
+                                    void* out, float* lse, const AttnWorkspace& ws, bool allow_cluster,
+                                    cudaStream_t st) {
   const int nsplit = attn_nsplit(g, n_query);
   const dim3 grid(nsplit, g.num_kv_heads, n_query);
   const size_t smem = attn_smem_bytes(g);
@@ -415,7 +429,7 @@ static cudaError_t launch_attn_dims(const loda_geometry& g, const loda_layer& L,
       cfg.attrs = attr;
       cfg.numAttrs = 2;
       e = cudaLaunchKernelEx(&cfg, kernel, g, L, (const bf16*)q, gather, visible_lens, query_to_req, n_req_rows,
-                             scale_log2, (bf16*)out, ws, nsplit);
+                             scale_log2, (bf16*)out, lse, ws, nsplit);
     }
     if (e == cudaSuccess) return cudaSuccess;
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
@@ -428,21 +442,21 @@ static cudaError_t launch_attn_dims(const loda_geometry& g, const loda_layer& L,
   e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   return launch_pdl(kernel, grid, dim3(ATT_NT), smem, st, g, L, (const bf16*)q, gather, visible_lens, query_to_req,
-                    n_req_rows, scale_log2, (bf16*)out, ws, nsplit);
+                    n_req_rows, scale_log2, (bf16*)out, lse, ws, nsplit);
 }
 
 cudaError_t launch_attn(const loda_geometry& g, const loda_layer& L, const void* q, const int32_t* gather,
                         const int32_t* visible_lens, const int32_t* query_to_req, int n_query,
-                        int n_req_rows, float scale, void* out, const AttnWorkspace& ws, bool allow_cluster,
-                        cudaStream_t st) {
+                        int n_req_rows, float scale, void* out, float* lse, const AttnWorkspace& ws,
+                        bool allow_cluster, cudaStream_t st) {
   if (n_query <= 0) return cudaSuccess;
   const float scale_log2 = scale * 1.4426950408889634f;
   if (g.head_dim == 128 && g.head_dim_v == 128)
     return launch_attn_dims<128, 128>(g, L, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale_log2,
-                                      out, ws, allow_cluster, st);
+                                      out, lse, ws, allow_cluster, st);
   if (g.head_dim == 64 && g.head_dim_v == 64)
     return launch_attn_dims<64, 64>(g, L, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale_log2,
-                                    out, ws, allow_cluster, st);
+                                    out, lse, ws, allow_cluster, st);
   return cudaErrorInvalidValue;
 }
 
@@ -523,7 +537,7 @@ extern "C" int loda_gather_attend_static(const loda_geometry* g, const loda_laye
   // the array keeps whatever the previous call left: the tickets must start at zero
   cudaError_t e = cudaMemsetAsync(ws.ticket, 0, ATT_STATIC_TICKET_BYTES, (cudaStream_t)stream);
   if (e == cudaSuccess)
-    e = launch_attn(*g, *layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale, out, ws,
+    e = launch_attn(*g, *layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale, out, nullptr, ws,
                     /*allow_cluster=*/false, (cudaStream_t)stream);   // this entry point exists for the scratch path
   if (e != cudaSuccess) {
     char msg[160];

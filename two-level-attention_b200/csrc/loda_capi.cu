@@ -19,7 +19,7 @@ cudaError_t launch_l2(const loda_geometry&, const loda_layer&, const loda_batch&
                       const loda_selection&, const SelectWorkspace&, uint32_t*, cudaStream_t);
 int l1_score_stride(const loda_geometry&);
 cudaError_t launch_attn(const loda_geometry&, const loda_layer&, const void*, const int32_t*, const int32_t*,
-                        const int32_t*, int, int, float, void*, const AttnWorkspace&, bool, cudaStream_t);
+                        const int32_t*, int, int, float, void*, float*, const AttnWorkspace&, bool, cudaStream_t);
 int l1_nsplit(const loda_geometry&);
 size_t l1_smem_bytes(const loda_geometry&);
 size_t l2_smem_bytes(const loda_geometry&);
@@ -269,25 +269,27 @@ int loda_select_l2(const loda_geometry* g, const loda_layer* layer, const loda_b
                     "select_l2");
 }
 
-int loda_gather_attend(const loda_geometry* g, const loda_layer* layer, const void* q, const int32_t* gather,
-                       const int32_t* visible_lens, const int32_t* query_to_req, int32_t n_query,
-                       int32_t n_req_rows, float scale, void* out, void* workspace, void* stream) {
-  LODA_TRY(check_geometry(g));
-  LODA_TRY(check_layer(layer, false));
-  if (n_query < 0 || n_query > g->max_query_tokens)
-    return fail(LODA_ERR_ARGUMENT, "n_query must be in [0, max_query_tokens]");
+int loda_gather_attend_lse(const loda_geometry* g, const loda_layer* layer, const void* q, const int32_t* gather,
+                           const int32_t* visible_lens, const int32_t* query_to_req, int32_t n_query,
+                           int32_t n_req_rows, float scale, void* out, float* lse, void* workspace,
+                           void* stream) {
+  LODA_TRY(check_gather_attend_args(g, layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, out));
   if (n_query == 0) return LODA_OK;
-  if (!q || !gather || !visible_lens || !query_to_req || !out || !workspace || n_req_rows < 1)
-    return fail(LODA_ERR_ARGUMENT, "gather attention needs q, gather, visible_lens, query_to_req, out, workspace");
-  if (!((g->head_dim == 128 && g->head_dim_v == 128) || (g->head_dim == 64 && g->head_dim_v == 64)))
-    return fail(LODA_ERR_UNSUPPORTED, "gather attention supports head dims 64 and 128");
+  if (!workspace) return fail(LODA_ERR_ARGUMENT, "gather attention needs a workspace");
   const WsLayout w = ws_layout(*g);
   char* base = (char*)workspace;
   const AttnWorkspace ws{(int*)(base + w.at_ticket), (float*)(base + w.at_m), (float*)(base + w.at_z),
                          (float*)(base + w.at_o)};
   return check_cuda(launch_attn(*g, *layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale,
-                                out, ws, /*allow_cluster=*/true, (cudaStream_t)stream),
+                                out, lse, ws, /*allow_cluster=*/true, (cudaStream_t)stream),
                     "gather_attend");
+}
+
+int loda_gather_attend(const loda_geometry* g, const loda_layer* layer, const void* q, const int32_t* gather,
+                       const int32_t* visible_lens, const int32_t* query_to_req, int32_t n_query,
+                       int32_t n_req_rows, float scale, void* out, void* workspace, void* stream) {
+  return loda_gather_attend_lse(g, layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale, out,
+                                nullptr, workspace, stream);
 }
 
 int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,

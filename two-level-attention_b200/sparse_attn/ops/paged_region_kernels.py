@@ -108,13 +108,15 @@ def paged_write_decode(cache_layer, key_states, value_states, slot_mapping, *, w
 
 
 def sparse_paged_attention_gather(cache_layer, q, gather_indices, visible_lens, query_to_req, *,
-                                  scale, workspace=None, split_kv=False):
+                                  scale, workspace=None, split_kv=False, return_lse=False):
     """q [T, HQ, D]; gather_indices [B, HK, K] absolute physical slots
     (page * PAGE + offset) in ascending logical order; visible_lens [B, HK];
     query_to_req [T] maps a query row to its row of the gather list (< 0: the
     output row is zero).  Returns [T, HQ, DV] in q's dtype.  The list is always
     processed split-K with a deterministic merge; ``split_kv`` is accepted for
-    signature compatibility."""
+    signature compatibility.  ``return_lse=True`` also returns [T, HQ, 2] fp32
+    (row maximum in the exp2 domain, softmax sum) for merging partial attentions
+    over disjoint token sets (``sharding.lse_merge``)."""
     if q.ndim != 3 or q.shape[-1] != cache_layer.head_dim_k:
         raise ValueError("sparse gather attention expects flat [T,HQ,D] query")
     hq, hk = q.shape[1], cache_layer.num_kv_heads
@@ -141,8 +143,9 @@ def sparse_paged_attention_gather(cache_layer, q, gather_indices, visible_lens, 
     gi = gather_indices if gather_indices.is_contiguous() else gather_indices.contiguous()
     vl = visible_lens if visible_lens.is_contiguous() else visible_lens.contiguous()
     q2r = query_to_req[:total_q].to(torch.int32).contiguous()
-    _capi.check(_capi.lib().loda_gather_attend(
+    lse = torch.empty((total_q, hq, 2), dtype=torch.float32, device=q.device) if return_lse else None
+    _capi.check(_capi.lib().loda_gather_attend_lse(
         C.byref(g), C.byref(rt["layer"]), _capi.ptr(qc), _capi.ptr(gi), _capi.ptr(vl), _capi.ptr(q2r),
-        total_q, gather_indices.shape[0], float(scale), _capi.ptr(out), _capi.ptr(rt["workspace"]),
-        _capi.current_stream()))
-    return out
+        total_q, gather_indices.shape[0], float(scale), _capi.ptr(out), _capi.ptr(lse),
+        _capi.ptr(rt["workspace"]), _capi.current_stream()))
+    return (out, lse) if return_lse else out
