@@ -316,3 +316,18 @@ def test_partial_attentions_merge_by_lse_to_the_full_attention():
         outs.append(o.float()); ms.append(lse[..., 0]); zs.append(lse[..., 1])
     merged = sharding.lse_merge(torch.stack(outs), torch.stack(ms), torch.stack(zs))
     torch.testing.assert_close(merged, out_full.float(), atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("page,overrides,lengths", [
+    (64, {}, [30000, 5000, 700, 9000]),                                   # the reference's production page size
+    (16, {"tia_level2_cmp_ratio": 2}, [9000, 3000]),                      # 64-dim subspace
+    (16, {"tia_level2_cmp_ratio": 8}, [9000, 3000]),                      # 16-dim subspace
+    (16, {"tia_level1_topk": 64, "nfa_near_pages": 16, "tia_level2_topk": 512, "nfa_sink_tokens": 16,
+          "nfa_swa_size": 64, "nfa_near_len": 2048}, [7000, 1200, 40]),    # other budgets, page-aligned sink
+], ids=["page64", "sub64", "sub16", "small-budgets"])
+def test_other_geometries_match_oracle(page, overrides, lengths):
+    from helpers import make_setup
+    mv = int(overrides.get("tia_level2_topk", 1024))
+    setup = make_setup(lengths, seed=8, page=page, selector_overrides=overrides, max_visible=mv)
+    out = _run_step(setup)
+    _check_against_oracle(setup, out)
