@@ -100,7 +100,7 @@ template <int DSUB, int P>
 __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, loda_batch B,
                                                 const bf16* __restrict__ q, float scale,
                                                 loda_selection out, SelectWorkspace ws, int nsplit,
-                                                AppendArgs ap) {
+                                                int tiles_per_cta, AppendArgs ap) {
   constexpr int NC = DSUB / 8;            // 8-dim chunks per statistic
   constexpr int CPR = 2 * NC;             // 16-byte chunks per min/max row
   constexpr int ROWB = 4 * DSUB + 16;     // padded row: conflict-free 16-byte reads
@@ -136,70 +136,78 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   const int req = (int)B.valid_req_ids[b];
   const int length = act >= 0 ? len_raw : 0;
   const Regions rg = make_regions(g, length);
-  const int p0 = split * P;
-
-  // stage metadata rows of this CTA's pages (issued first: the longest latency)
+  // this CTA's tiles of P pages; tiles past the request's last page are neither read nor written
   const size_t pg0 = ((size_t)req * g.num_kv_heads + kv) * g.max_blocks;
   const unsigned char* mm_base = (const unsigned char*)L.page_mm + pg0 * (4 * DSUB);
   const unsigned char* sum_base = (const unsigned char*)L.page_sum + pg0 * (2 * DSUB);
-  for (int c = tid; c < P * CPR; c += P) {
-    const int pl = c / CPR, cc = c % CPR;
-    const int page = p0 + pl;
-    if (in_far_pool(rg, page)) {
-      cp_async16(rows + (size_t)pl * ROWB + cc * 16, mm_base + (size_t)page * (4 * DSUB) + cc * 16, true);
-    } else if (cc < NC && in_near_pool(rg, page)) {
-      cp_async16(rows + (size_t)pl * ROWB + cc * 16, sum_base + (size_t)page * (2 * DSUB) + cc * 16, true);
-    }
-  }
-  cp_async_commit();
-  // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
-  for (int i = tid; i < G * DSUB; i += P) {
-    const int j = i / DSUB, d = i % DSUB;
-    const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, d)]);
-    const float qh = bf16r(__fmul_rn(qv, scale));
-    qhat[i] = qh;
-    qlow[i] = fminf(qh, 0.0f);
-    qhigh[i] = fmaxf(qh, 0.0f);
-  }
-  LODA_PHASE(l1, cta_id, 2);
-  cp_async_wait<0>();
-  __syncthreads();
-  LODA_PHASE(l1, cta_id, 3);
-
-  // one page per thread
-  const int page = p0 + tid;
-  uint32_t ord = 0;
-  const unsigned char* myrow = rows + (size_t)tid * ROWB;
-  const float gf = (float)G;
-  if (in_far_pool(rg, page)) {
-    float kmin[DSUB], kmax[DSUB];
-#pragma unroll
-    for (int c = 0; c < NC; ++c) {
-      unpack8(*(const uint4*)(myrow + c * 16), *(float(*)[8])(kmin + 8 * c));
-      unpack8(*(const uint4*)(myrow + (NC + c) * 16), *(float(*)[8])(kmax + 8 * c));
-    }
-    float acc = 0.0f;
-#pragma unroll 1
-    for (int j = 0; j < G; ++j) {
-      const float mm = __fadd_rn(dot_chunks<DSUB>(kmin, qlow + j * DSUB), dot_chunks<DSUB>(kmax, qhigh + j * DSUB));
-      acc = __fadd_rn(acc, bf16r(mm));
-    }
-    ord = ord16(bf16r(__fdiv_rn(acc, gf)));
-  } else if (in_near_pool(rg, page)) {
-    float kavg[DSUB];
-    const float bsf = (float)g.page;
-#pragma unroll
-    for (int c = 0; c < NC; ++c) unpack8(*(const uint4*)(myrow + c * 16), *(float(*)[8])(kavg + 8 * c));
-#pragma unroll
-    for (int i = 0; i < DSUB; ++i) kavg[i] = bf16r(__fdiv_rn(kavg[i], bsf));
-    float acc = 0.0f;
-#pragma unroll 1
-    for (int j = 0; j < G; ++j) acc = __fadd_rn(acc, bf16r(dot_chunks<DSUB>(kavg, qhat + j * DSUB)));
-    ord = ord16(bf16r(__fdiv_rn(acc, gf)));
-  }
-  if (ord == ORD16_NEG_INF) ord = 0;   // a -inf score never competes (it equals "not in the pool")
   uint16_t* row_scores = ws.l1_scores + (size_t)row * ws.score_stride;
-  row_scores[page] = (uint16_t)ord;
+  const int page_end = min(rg.kt_eff, g.max_blocks);
+  const int tile0 = split * tiles_per_cta;
+  for (int tile = tile0; tile < tile0 + tiles_per_cta; ++tile) {
+    const int p0 = tile * P;
+    if (p0 >= page_end && tile > tile0) break;           // the first tile always runs (it prepares nothing else)
+    if (tile > tile0) __syncthreads();                   // the staging rows are reused
+    // stage the metadata rows of the tile (issued first: the longest latency)
+    for (int c = tid; c < P * CPR; c += P) {
+      const int pl = c / CPR, cc = c % CPR;
+      const int page = p0 + pl;
+      if (in_far_pool(rg, page)) {
+        cp_async16(rows + (size_t)pl * ROWB + cc * 16, mm_base + (size_t)page * (4 * DSUB) + cc * 16, true);
+      } else if (cc < NC && in_near_pool(rg, page)) {
+        cp_async16(rows + (size_t)pl * ROWB + cc * 16, sum_base + (size_t)page * (2 * DSUB) + cc * 16, true);
+      }
+    }
+    cp_async_commit();
+    if (tile == tile0) {
+      // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
+      for (int i = tid; i < G * DSUB; i += P) {
+        const int j = i / DSUB, d = i % DSUB;
+        const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, d)]);
+        const float qh = bf16r(__fmul_rn(qv, scale));
+        qhat[i] = qh;
+        qlow[i] = fminf(qh, 0.0f);
+        qhigh[i] = fmaxf(qh, 0.0f);
+      }
+    }
+    LODA_PHASE(l1, cta_id, 2);
+    cp_async_wait<0>();
+    __syncthreads();
+    LODA_PHASE(l1, cta_id, 3);
+
+    // one page per thread
+    const int page = p0 + tid;
+    uint32_t ord = 0;
+    const unsigned char* myrow = rows + (size_t)tid * ROWB;
+    const float gf = (float)G;
+    if (in_far_pool(rg, page)) {
+      float kmin[DSUB], kmax[DSUB];
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        unpack8(*(const uint4*)(myrow + c * 16), *(float(*)[8])(kmin + 8 * c));
+        unpack8(*(const uint4*)(myrow + (NC + c) * 16), *(float(*)[8])(kmax + 8 * c));
+      }
+      float acc = 0.0f;
+#pragma unroll 1
+      for (int j = 0; j < G; ++j) {
+        const float mm = __fadd_rn(dot_chunks<DSUB>(kmin, qlow + j * DSUB), dot_chunks<DSUB>(kmax, qhigh + j * DSUB));
+        acc = __fadd_rn(acc, bf16r(mm));
+      }
+      ord = ord16(bf16r(__fdiv_rn(acc, gf)));
+    } else if (in_near_pool(rg, page)) {
+      float kavg[DSUB];
+      const float bsf = (float)g.page;
+#pragma unroll
+      for (int c = 0; c < NC; ++c) unpack8(*(const uint4*)(myrow + c * 16), *(float(*)[8])(kavg + 8 * c));
+#pragma unroll
+      for (int i = 0; i < DSUB; ++i) kavg[i] = bf16r(__fdiv_rn(kavg[i], bsf));
+      float acc = 0.0f;
+#pragma unroll 1
+      for (int j = 0; j < G; ++j) acc = __fadd_rn(acc, bf16r(dot_chunks<DSUB>(kavg, qhat + j * DSUB)));
+      ord = ord16(bf16r(__fdiv_rn(acc, gf)));
+    }
+    if (ord == ORD16_NEG_INF) ord = 0;   // a -inf score never competes (it equals "not in the pool")
+    if (p0 < page_end) row_scores[page] = (uint16_t)ord;   // the selecting CTA reads pages below page_end (rounded up to 8)
+  }
   LODA_PHASE(l1, cta_id, 4);
 
   // last CTA of the row selects
@@ -308,17 +316,29 @@ int l1_nsplit(const loda_geometry& g) { return (g.max_blocks + L1_P - 1) / L1_P;
 
 int l1_score_stride(const loda_geometry& g) { return l1_nsplit(g) * L1_P; }
 
+// CTAs per row: one tile of 512 pages each while the grid is small (batch 1: latency), several
+// tiles per CTA once rows x tiles exceeds about four waves (fewer prologues, tickets and waves)
+void l1_split(const loda_geometry& g, int rows, int* ctas_per_row, int* tiles_per_cta) {
+  const int ntiles = l1_nsplit(g);
+  int tpc = (rows * ntiles + 4 * 148 - 1) / (4 * 148);
+  tpc = tpc < 1 ? 1 : tpc > ntiles ? ntiles : tpc;
+  *tiles_per_cta = tpc;
+  *ctas_per_row = (ntiles + tpc - 1) / tpc;
+}
+
 template <int DS>
 static cudaError_t launch_l1_d(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                float scale, const loda_selection& out, const SelectWorkspace& ws,
                                const AppendArgs& ap, cudaStream_t st) {
-  const int nsplit = l1_nsplit(g);
-  const dim3 grid(nsplit + (ap.enabled ? 1 : 0), B.batch * g.num_kv_heads);
+  const int rows = B.batch * g.num_kv_heads;
+  int nsplit, tpc;
+  l1_split(g, rows, &nsplit, &tpc);
+  const dim3 grid(nsplit + (ap.enabled ? 1 : 0), rows);
   const size_t smem = l1_smem_bytes(g);
   cudaError_t e = cudaFuncSetAttribute(l1_kernel<DS, L1_P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   return launch_pdl(l1_kernel<DS, L1_P>, grid, dim3(L1_P), smem, st, g, L, B, (const bf16*)q, scale, out, ws,
-                    nsplit, ap);
+                    nsplit, tpc, ap);
 }
 
 cudaError_t launch_l1(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,

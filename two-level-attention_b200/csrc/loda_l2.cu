@@ -62,7 +62,8 @@ constexpr int L2_NT = 256;
 template <int DSUB, int NT>
 __global__ void __launch_bounds__(NT) l2_kernel(loda_geometry g, loda_layer L, loda_batch B,
                                                  const bf16* __restrict__ q, float scale,
-                                                 loda_selection S, SelectWorkspace ws, uint32_t* status) {
+                                                 loda_selection S, SelectWorkspace ws, uint32_t* status,
+                                                 int nsplit) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int np_max = g.k_far + g.k_near + 2;
   const int K2 = g.level2_topk;
@@ -116,7 +117,7 @@ __global__ void __launch_bounds__(NT) l2_kernel(loda_geometry g, loda_layer L, l
   uint16_t* row_scores = ws.l2_scores + (size_t)row * np_max * g.page;
   // ---- score this CTA's share of the candidate slots ---------------------------
   {
-    const int per = ((nitems + L2_SPLIT - 1) / L2_SPLIT + 7) & ~7;     // multiple of 8 slots
+    const int per = ((nitems + nsplit - 1) / nsplit + 7) & ~7;         // multiple of 8 slots
     const int lo = min(split * per, nitems), hi = min(lo + per, nitems);
     for (int idx = lo + tid; idx < hi; idx += NT) {
       const int i = idx / g.page, o = idx % g.page;
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(NT) l2_kernel(loda_geometry g, loda_layer L, l
   // ---- last CTA of the row selects ----------------------------------------------
   __threadfence();
   __syncthreads();
-  if (tid == 0) sh[0] = (atomicAdd(ws.l2_ticket + row, 1) == L2_SPLIT - 1);
+  if (tid == 0) sh[0] = (atomicAdd(ws.l2_ticket + row, 1) == nsplit - 1);
   __syncthreads();
   LODA_PHASE(l2, cta_id, 4);
   if (!sh[0]) return;
@@ -294,11 +295,16 @@ template <int DS>
 static cudaError_t launch_l2_d(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                float scale, const loda_selection& S, const SelectWorkspace& ws, uint32_t* status,
                                cudaStream_t st) {
-  const dim3 grid(L2_SPLIT, B.batch * g.num_kv_heads);
+  // scoring CTAs per row: 8 at batch 1 (latency), fewer once the rows alone fill the GPU
+  const int rows = B.batch * g.num_kv_heads;
+  int nsplit = (2 * 148 + rows - 1) / rows;
+  nsplit = nsplit < 1 ? 1 : nsplit > L2_SPLIT ? L2_SPLIT : nsplit;
+  const dim3 grid(nsplit, rows);
   const size_t smem = l2_smem_bytes(g);
   cudaError_t e = cudaFuncSetAttribute(l2_kernel<DS, L2_NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  return launch_pdl(l2_kernel<DS, L2_NT>, grid, dim3(L2_NT), smem, st, g, L, B, (const bf16*)q, scale, S, ws, status);
+  return launch_pdl(l2_kernel<DS, L2_NT>, grid, dim3(L2_NT), smem, st, g, L, B, (const bf16*)q, scale, S, ws, status,
+                    nsplit);
 }
 
 cudaError_t launch_l2(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
