@@ -35,6 +35,10 @@ constexpr int ATT_TILE = 64;
 constexpr int ATT_WARPS = 4;
 constexpr int ATT_NT = 32 * ATT_WARPS;
 constexpr int ATT_MAX_SPLIT = 16;
+constexpr int ATT_STAGES = 3;
+#ifndef LODA_ATTN_CTAS_PER_SM
+#define LODA_ATTN_CTAS_PER_SM 1
+#endif
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_ptr) {
   const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_ptr);
@@ -68,16 +72,15 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
   constexpr int KSTR = D + 8, VSTR = DV + 8;   // padded rows: conflict-free ldmatrix
   constexpr int KSTEPS = D / 16, NTV = DV / 8;
   extern __shared__ __align__(16) unsigned char smem[];
-  bf16* Ks = (bf16*)smem;                          // [TILE][KSTR]
-  bf16* Vs = Ks + ATT_TILE * KSTR;                 // [TILE][VSTR]
-  int* slot_s = (int*)(Vs + ATT_TILE * VSTR);      // [TILE]
-  float* wm = (float*)(slot_s + ATT_TILE);         // [WARPS][16]
+  bf16* Ks = (bf16*)smem;                                   // [STAGES][TILE][KSTR]
+  bf16* Vs = Ks + ATT_STAGES * ATT_TILE * KSTR;             // [STAGES][TILE][VSTR]
+  int* slot_s = (int*)(Vs + ATT_STAGES * ATT_TILE * VSTR);  // [STAGES][TILE] physical slot of each staged token
+  float* wm = (float*)(slot_s + ATT_STAGES * ATT_TILE);     // [WARPS][16]
   float* wz = wm + ATT_WARPS * 16;                 // [WARPS][16]
   int* sh = (int*)(wz + ATT_WARPS * 16);           // 4
   float* fm = (float*)(sh + 4);                    // [16] merged max of this CTA
   float* fz = fm + 16;                             // [16] merged sum of this CTA
-  long long* rowoff = (long long*)(fz + 16);       // [TILE] pool row of each staged token
-  float* wo = (float*)(rowoff + ATT_TILE);         // [WARPS][G][DV]
+  float* wo = (float*)Vs;                          // [WARPS][G][DV], after the last tile (V stages consumed)
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int split = blockIdx.x, kv = blockIdx.y, t = blockIdx.z;
@@ -86,7 +89,9 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
   const int cta_id = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
   LODA_PHASE(attn, cta_id, 0);
   pdl_wait();
+#if LODA_PDL_TRIGGER == 0
   pdl_launch_dependents();
+#endif
   LODA_PHASE(attn, cta_id, 1);
   const int req = query_to_req[t];
   int n = 0;
@@ -116,34 +121,64 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
   for (int i = 0; i < NTV; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.0f; }
   float m_run[2] = {-INFINITY, -INFINITY}, z_run[2] = {0.0f, 0.0f};   // rows lane/4 and lane/4 + 8
 
-  for (int base = c0; base < c1; base += ATT_TILE) {
-    const int ntok = min(ATT_TILE, c1 - base);
-    __syncthreads();   // previous tile fully consumed
-    if (tid < ATT_TILE) {
-      int s = tid < ntok ? list[base + tid] : -1;
-      if (s >= g.num_pages * g.page) s = -1;
-      slot_s[tid] = s;
-      // page is a power of two: slot -> pool row without a division
-      rowoff[tid] = s >= 0 ? ((long long)(s >> page_log2) * g.num_kv_heads + kv) * g.page + (s & (g.page - 1)) : 0;
+  // Staging: 16-byte chunk (row kr + k * RPI, column kc) of every tile belongs to this
+  // thread, so it reads the gather-list entries of its own rows into registers and needs
+  // no shared slot table to issue the copies.  ATT_STAGES tiles are in flight: all the
+  // lists of the first tiles are fetched in one round of loads, then all their copies are
+  // issued; after the math of tile i its stage is refilled with tile i + ATT_STAGES, whose
+  // list entries were fetched one iteration earlier.
+  constexpr int KCH = D / 8, VCH = DV / 8;
+  static_assert(KCH == VCH, "K and V rows are staged by the same threads");
+  constexpr int RPI = ATT_NT / KCH, NIT = ATT_TILE / RPI;
+  static_assert(ATT_NT % KCH == 0 && ATT_TILE % RPI == 0, "tile shape");
+  const int kr = tid / KCH, kc = tid % KCH;
+  const int slot_end = g.num_pages * g.page;
+  const int ntiles = (c1 - c0 + ATT_TILE - 1) / ATT_TILE;
+  auto fetch_slots = [&](int (&sl)[NIT], int tile) {
+    const int base = c0 + tile * ATT_TILE;
+#pragma unroll
+    for (int k = 0; k < NIT; ++k) {
+      const int idx = base + kr + k * RPI;
+      const int s = (tile < ntiles && idx < c1) ? __ldg(list + idx) : -1;
+      sl[k] = s >= slot_end ? -1 : s;
     }
+  };
+  auto issue = [&](int stage, const int (&sl)[NIT], int tile) {
+    if (tile < ntiles) {
+      bf16* Kb = Ks + stage * ATT_TILE * KSTR;
+      bf16* Vb = Vs + stage * ATT_TILE * VSTR;
+      int* sb = slot_s + stage * ATT_TILE;
+#pragma unroll
+      for (int k = 0; k < NIT; ++k) {
+        const int r = kr + k * RPI, s = sl[k];
+        // page is a power of two: slot -> pool row without a division
+        const long long off = s >= 0 ? ((long long)(s >> page_log2) * g.num_kv_heads + kv) * g.page + (s & (g.page - 1)) : 0;
+        cp_async16(Kb + r * KSTR + kc * 8, (const bf16*)L.pool_k + off * D + kc * 8, s >= 0);
+        cp_async16(Vb + r * VSTR + kc * 8, (const bf16*)L.pool_v + off * DV + kc * 8, s >= 0);
+        if (kc == 0) sb[r] = s;
+      }
+    }
+    cp_async_commit();     // one group per tile index, empty past the last tile
+  };
+  int nxt[NIT];
+  {
+    int sl[ATT_STAGES][NIT];
+#pragma unroll
+    for (int s = 0; s < ATT_STAGES; ++s) fetch_slots(sl[s], s);
+#pragma unroll
+    for (int s = 0; s < ATT_STAGES; ++s) issue(s, sl[s], s);
+  }
+  fetch_slots(nxt, ATT_STAGES);
+  LODA_PHASE(attn, cta_id, 3);
+  int stage = 0;
+  for (int it = 0; it < ntiles; ++it) {
+    const int ntok = min(ATT_TILE, c1 - c0 - it * ATT_TILE);
+    cp_async_wait<ATT_STAGES - 1>();
     __syncthreads();
-    // stage K and V rows: 16 lanes per 256-byte row
-    constexpr int KCH = D / 8, VCH = DV / 8;
-#pragma unroll 4
-    for (int c = tid; c < ATT_TILE * KCH; c += ATT_NT) {
-      const int r = c / KCH, cc = c % KCH;
-      cp_async16(Ks + r * KSTR + cc * 8, (const bf16*)L.pool_k + rowoff[r] * D + cc * 8, slot_s[r] >= 0);
-    }
-#pragma unroll 4
-    for (int c = tid; c < ATT_TILE * VCH; c += ATT_NT) {
-      const int r = c / VCH, cc = c % VCH;
-      cp_async16(Vs + r * VSTR + cc * 8, (const bf16*)L.pool_v + rowoff[r] * DV + cc * 8, slot_s[r] >= 0);
-    }
-    cp_async_commit();
-    LODA_PHASE(attn, cta_id, 3);
-    cp_async_wait<0>();
-    __syncthreads();
-    LODA_PHASE(attn, cta_id, 4);
+    if (it == 0) { LODA_PHASE(attn, cta_id, 4); }
+    const bf16* Kt = Ks + stage * ATT_TILE * KSTR;
+    const bf16* Vt = Vs + stage * ATT_TILE * VSTR;
+    const int* slot_t = slot_s + stage * ATT_TILE;
 
     const int tok0 = warp * 16;
     if (tok0 < ntok) {
@@ -153,7 +188,7 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
       for (int ks = 0; ks < KSTEPS; ++ks) {
         uint32_t kb[4];
         const int mi = lane >> 3, r = lane & 7;
-        ldmatrix_x4(kb, Ks + (tok0 + (mi >> 1) * 8 + r) * KSTR + ks * 16 + (mi & 1) * 8);
+        ldmatrix_x4(kb, Kt + (tok0 + (mi >> 1) * 8 + r) * KSTR + ks * 16 + (mi & 1) * 8);
         mma_bf16(sacc[0], qa[ks], kb[0], kb[1]);
         mma_bf16(sacc[1], qa[ks], kb[2], kb[3]);
       }
@@ -164,7 +199,7 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int tk = tok0 + j * 8 + (lane & 3) * 2 + (e & 1);
-          const bool ok = tk < ntok && slot_s[tk] >= 0;
+          const bool ok = tk < ntok && slot_t[tk] >= 0;
           const float v = ok ? sacc[j][e] * scale_log2 : -INFINITY;
           sacc[j][e] = v;
           mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -215,15 +250,22 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
       for (int i = 0; i < NTV; i += 2) {
         uint32_t vb[4];
         const int mi = lane >> 3, r = lane & 7;
-        ldmatrix_x4_trans(vb, Vs + (tok0 + (mi & 1) * 8 + r) * VSTR + i * 8 + (mi >> 1) * 8);
+        ldmatrix_x4_trans(vb, Vt + (tok0 + (mi & 1) * 8 + r) * VSTR + i * 8 + (mi >> 1) * 8);
         mma_bf16(oacc[i], pa, vb[0], vb[1]);
         mma_bf16(oacc[i + 1], pa, vb[2], vb[3]);
       }
     }
+    __syncthreads();   // the stage is free: refill it
+    issue(stage, nxt, it + ATT_STAGES);
+    fetch_slots(nxt, it + ATT_STAGES + 1);
+    stage = stage + 1 == ATT_STAGES ? 0 : stage + 1;
   }
+  cp_async_wait<0>();
 
   // ---- merge the warps of this CTA (fixed order) -------------------------------
-  __syncthreads();
+#if LODA_PDL_TRIGGER == 1 || LODA_PDL_TRIGGER == 3
+  pdl_launch_dependents();
+#endif
   LODA_PHASE(attn, cta_id, 5);
   {
     const int r0 = lane >> 2;
@@ -380,20 +422,20 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
 }
 
 size_t attn_smem_bytes(const loda_geometry& g) {
-  const int G = g.num_q_heads / g.num_kv_heads;
-  const size_t wo = (size_t)ATT_WARPS * G * g.head_dim_v;
-  return (size_t)ATT_TILE * (g.head_dim + 8) * 2 + (size_t)ATT_TILE * (g.head_dim_v + 8) * 2 + ATT_TILE * 4 +
-         2 * ATT_WARPS * 16 * 4 + 16 + 2 * 16 * 4 + ATT_TILE * 8 + sizeof(float) * (wo > 1024 ? wo : 1024);
+  // the per-warp partial outputs [WARPS][G][DV] fp32 reuse the V stages (G <= 16 fits)
+  return ATT_STAGES * ((size_t)ATT_TILE * (g.head_dim + 8) * 2 + (size_t)ATT_TILE * (g.head_dim_v + 8) * 2 + ATT_TILE * 4) +
+         2 * ATT_WARPS * 16 * 4 + 16 + 2 * 16 * 4;
 }
 
-// power-of-two split count: enough CTAs to cover the GPU about twice, at least
-// one 64-token tile per split, at most ATT_MAX_SPLIT (the largest cluster)
+// power-of-two split count: no more splits than it takes to give every SM a CTA (a split
+// costs a prologue and a merge, about as much as streaming 300 tokens), at least one
+// 64-token tile per split, at most ATT_MAX_SPLIT (the largest cluster)
 int attn_nsplit(const loda_geometry& g, int n_query) {
   const int pairs = n_query * g.num_kv_heads;
-  const int want = (2 * 148 + pairs - 1) / pairs;
+  const int want = (LODA_ATTN_CTAS_PER_SM * 148 + pairs - 1) / pairs;
   const int by_len = (g.max_visible + ATT_TILE - 1) / ATT_TILE;
   int ns = 1;
-  while (ns * 2 <= want && ns * 2 <= by_len && ns * 2 <= ATT_MAX_SPLIT) ns *= 2;
+  while (ns < want && ns * 2 <= by_len && ns * 2 <= ATT_MAX_SPLIT) ns *= 2;
   return ns;
 }
 
@@ -410,7 +452,7 @@ static cudaError_t launch_attn_dims(const loda_geometry& g, const loda_layer& L,
   cudaError_t e;
   if (allow_cluster && cluster_ok && nsplit > 1) {
     auto kernel = attn_kernel<D, DV, true>;
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = set_kernel_smem(kernel, smem);
     if (e == cudaSuccess && nsplit > 8)
       e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e == cudaSuccess) {
@@ -439,7 +481,7 @@ static cudaError_t launch_attn_dims(const loda_geometry& g, const loda_layer& L,
     cluster_ok = false;
   }
   auto kernel = attn_kernel<D, DV, false>;
-  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  e = set_kernel_smem(kernel, smem);
   if (e != cudaSuccess) return e;
   return launch_pdl(kernel, grid, dim3(ATT_NT), smem, st, g, L, (const bf16*)q, gather, visible_lens, query_to_req,
                     n_req_rows, scale_log2, (bf16*)out, lse, ws, nsplit);

@@ -20,7 +20,6 @@ cudaError_t launch_l2(const loda_geometry&, const loda_layer&, const loda_batch&
 int l1_score_stride(const loda_geometry&);
 cudaError_t launch_attn(const loda_geometry&, const loda_layer&, const void*, const int32_t*, const int32_t*,
                         const int32_t*, int, int, float, void*, float*, const AttnWorkspace&, bool, cudaStream_t);
-int l1_nsplit(const loda_geometry&);
 size_t l1_smem_bytes(const loda_geometry&);
 size_t l2_smem_bytes(const loda_geometry&);
 int attn_nsplit(const loda_geometry&, int);
@@ -114,7 +113,7 @@ static int check_geometry(const loda_geometry* g) {
     return fail(LODA_ERR_UNSUPPORTED, "more than 32768 L2 candidate slots per row");
   if (g->page < 8 && g->k_far + g->k_near > 0)
     return fail(LODA_ERR_UNSUPPORTED, "the selector needs pages of at least 8 tokens");
-  if (g->pool_near_len / g->page + 1 > 512)
+  if (g->pool_near_len / g->page + 8 > 512)
     return fail(LODA_ERR_UNSUPPORTED, "near pool wider than 512 pages");
   if (g->level2_topk < g->sink + g->swa) return fail(LODA_ERR_ARGUMENT, "level2_topk < sink + swa");
   if (g->max_visible < g->level2_topk) return fail(LODA_ERR_ARGUMENT, "max_visible < level2_topk");

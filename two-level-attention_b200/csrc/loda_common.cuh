@@ -265,11 +265,94 @@ __device__ __forceinline__ int block_rank_topk_small(const uint16_t* sc, int n, 
   return total;
 }
 
+// (1b) NT < n <= 2 NT scores: the same with two elements per thread (tid, tid + NT).
+// keys: 2 NT words (16-byte aligned); wtot: 64 ints.
+template <int NT>
+__device__ __forceinline__ int block_rank_topk_pair(const uint16_t* sc, int n, int k, int* out, uint32_t* keys,
+                                                    int* wtot) {
+  const int tid = threadIdx.x, hi = tid + NT;
+  const uint32_t k0 = tid < n ? rank_key(sc[tid], tid) : 0u;
+  const uint32_t k1 = hi < n ? rank_key(sc[hi], hi) : 0u;
+  keys[tid] = k0;
+  keys[hi] = k1;
+  __syncthreads();
+  int a0 = 0, a1 = 0, b0 = 0, b1 = 0;
+  const int n4 = (n + 3) >> 2;
+#pragma unroll 4
+  for (int j = 0; j < n4; ++j) {
+    const uint4 o = ((const uint4*)keys)[j];
+    a0 += (o.x > k0) + (o.y > k0); a1 += (o.z > k0) + (o.w > k0);
+    b0 += (o.x > k1) + (o.y > k1); b1 += (o.z > k1) + (o.w > k1);
+  }
+  const bool s0 = k0 != 0 && a0 + a1 < k, s1 = k1 != 0 && b0 + b1 < k;
+  int t0, t1;
+  const int p0 = block_flag_scan<NT>(s0, wtot, 0, &t0);
+  const int p1 = block_flag_scan<NT>(s1, wtot, 1, &t1);
+  if (s0) out[p0] = tid;
+  if (s1) out[t0 + p1] = hi;
+  __syncthreads();
+  return t0 + t1;
+}
+
+// Shared last step of the threshold selections: keep, in index order, the scores
+// strictly above `thr` and the first `rem` scores equal to it (`all`: every scored
+// element).  Blocked layout (ept consecutive scores per thread), one shuffle scan.
+// wtot: 32 ints.  Returns all ? nvalid : k.
+template <int NT>
+__device__ __forceinline__ int block_compact_threshold(const uint16_t* sc, int n, int k, uint32_t thr, int rem, bool all,
+                                                       int nvalid, int* out, int* wtot) {
+  constexpr int NW = NT / 32;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ept = (((n + NT - 1) / NT) + 7) & ~7;
+  const int base = tid * ept;
+  const int nch = base < n ? min(ept, ((n - base + 7) & ~7)) >> 3 : 0;
+  const uint4* blk = (const uint4*)(sc + base);
+  int gt = 0, tie = 0;
+  for (int ch = 0; ch < nch; ++ch) {
+    uint32_t v[8];
+    unpack_u16x8(blk[ch], v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { gt += all ? v[j] != 0 : v[j] > thr; tie += (!all) && v[j] == thr; }
+  }
+  // exclusive scan of (gt | tie << 16): shuffles inside the warp, columns across warps
+  int incl = gt | (tie << 16);
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int nb = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += nb;
+  }
+  __syncthreads();                             // the columns may still be read by slower warps
+  if (lane == 31) wtot[warp] = incl;
+  __syncthreads();
+  int before = 0;
+#pragma unroll
+  for (int w = 0; w < NW; ++w) before += w < warp ? wtot[w] : 0;
+  const int excl = before + incl - (gt | (tie << 16));
+  int tb = excl >> 16;
+  int pos = (excl & 0xFFFF) + min(tb, rem);
+  for (int ch = 0; ch < nch; ++ch) {
+    uint32_t v[8];
+    unpack_u16x8(blk[ch], v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = base + ch * 8 + j;
+      if (all ? v[j] != 0 : v[j] > thr) out[pos++] = i;
+      else if (!all && v[j] == thr) { if (tb < rem) out[pos++] = i; ++tb; }
+    }
+  }
+  __syncthreads();
+  return all ? nvalid : k;
+}
+
 // (2) any n < 65536, any k: bisection over the 16 score bits, two bits per round.
-// The row is cut into chunks of 8 scores dealt round-robin to the threads; per
-// round every thread counts its scores at or above three candidate thresholds
-// (independent chains), one barrier publishes the block sums.  The compaction
-// runs over the same chunks, one flag scan per score position.
+// The row is cut into chunks of 8 scores dealt round-robin to the threads (kept in
+// registers); a last partial round of chunks that holds at most NT scores is dealt
+// one score per thread instead, so that no thread pays for a whole chunk slot that
+// only a few threads fill.  A first pass finds the number of scored elements and
+// their minimum and maximum: the bits above the highest bit in which the two differ
+// are those of the k-th largest score too, and their rounds are skipped.  Per round
+// every thread counts its scores at or above three candidate thresholds (independent
+// chains), one barrier publishes the block sums.
 // wtot: 6 x 32 ints (16-byte aligned).
 template <int NT>
 __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int k, int* out, int* wtot) {
@@ -277,19 +360,23 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
   constexpr int MAXC = 4;                        // chunks a thread keeps in registers
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nchunks = (n + 7) >> 3;
-  const bool in_regs = nchunks <= NT * MAXC;
+  const int full = nchunks / NT, remc = nchunks - full * NT;     // whole rounds of chunks, chunks left
+  const bool single = remc > 0 && remc * 8 <= NT;                // the rest as one score per thread
+  const int nslots = full + ((remc > 0 && !single) ? 1 : 0);
+  const bool in_regs = nslots <= MAXC;
   uint4 mine[MAXC];
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
     const int ch = tid + c * NT;
-    mine[c] = (in_regs && ch < nchunks) ? ((const uint4*)sc)[ch] : make_uint4(0, 0, 0, 0);
+    mine[c] = (in_regs && c < nslots && ch < nchunks) ? ((const uint4*)sc)[ch] : make_uint4(0, 0, 0, 0);
   }
+  const uint32_t xtra = (in_regs && single && tid < remc * 8) ? sc[full * NT * 8 + tid] : 0u;
   auto count3 = [&](uint32_t t1, uint32_t t2, uint32_t t3, int& c1, int& c2, int& c3) {
-    c1 = c2 = c3 = 0;
+    c1 = xtra >= t1; c2 = xtra >= t2; c3 = xtra >= t3;           // thresholds are >= 1
     if (in_regs) {
 #pragma unroll
       for (int c = 0; c < MAXC; ++c) {
-        if (c * NT < nchunks) {                  // uniform: skip register slots no thread uses
+        if (c < nslots) {                        // uniform: skip register slots no thread uses
           uint32_t v[8];
           unpack_u16x8(mine[c], v);
 #pragma unroll
@@ -330,67 +417,135 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
   };
   for (int i = tid; i < 6 * 32; i += NT) wtot[i] = 0;      // columns of absent warps stay 0
   __syncthreads();
-  int nv, d1, d2;
-  count3(1u, 0x10000u, 0x10000u, nv, d1, d2);
-  sum3(0, nv, d1, d2);
-  const int nvalid = nv;
+  // scored elements, their maximum, and 0xFFFF - their minimum (so that empty columns, 0, are neutral)
+  int nvalid;
+  uint32_t smax, smin;
+  {
+    int nz = xtra != 0u;
+    uint32_t mx = xtra, mi = xtra ? 0xFFFFu - xtra : 0u;
+    auto visit = [&](const uint4& u) {
+      uint32_t v[8];
+      unpack_u16x8(u, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        nz += v[j] != 0u;
+        mx = max(mx, v[j]);
+        mi = max(mi, v[j] ? 0xFFFFu - v[j] : 0u);
+      }
+    };
+    if (in_regs) {
+#pragma unroll
+      for (int c = 0; c < MAXC; ++c)
+        if (c < nslots) visit(mine[c]);
+    } else {
+      for (int ch = tid; ch < nchunks; ch += NT) visit(((const uint4*)sc)[ch]);
+    }
+    nz = __reduce_add_sync(0xffffffffu, nz);
+    mx = __reduce_max_sync(0xffffffffu, mx);
+    mi = __reduce_max_sync(0xffffffffu, mi);
+    if (lane == 0) {
+      wtot[0 * 32 + warp] = nz;
+      wtot[1 * 32 + warp] = (int)mx;
+      wtot[2 * 32 + warp] = (int)mi;
+    }
+    __syncthreads();
+    int a = 0, b = 0, c = 0;
+#pragma unroll
+    for (int w4 = 0; w4 < (NW + 3) / 4; ++w4) {
+      const int4 x = ((const int4*)(wtot + 0 * 32))[w4];
+      const int4 y = ((const int4*)(wtot + 1 * 32))[w4];
+      const int4 z = ((const int4*)(wtot + 2 * 32))[w4];
+      a += (x.x + x.y) + (x.z + x.w);
+      b = max(max(b, max(y.x, y.y)), max(y.z, y.w));
+      c = max(max(c, max(z.x, z.y)), max(z.z, z.w));
+    }
+    nvalid = a;
+    smax = (uint32_t)b;
+    smin = 0xFFFFu - (uint32_t)c;
+  }
   if (k <= 0 || nvalid == 0) { __syncthreads(); return 0; }
   const bool all = nvalid <= k;
   uint32_t thr = 1u;     // keep v >= thr ...
   int rem = 0;           // ... but of those equal to thr only the first `rem` (all == true: everything scored)
   if (!all) {
-    thr = 0;
+    // rounds whose two bits lie above the highest bit in which minimum and maximum differ are decided
+    const uint32_t diff = smax ^ smin;
+    int first_round = 8;
+    int buf = 1;           // the first pass used the columns of buffer 0; the buffers alternate from here
+    thr = smax;
+    if (diff != 0u) {
+      const int shift0 = (31 - __clz(diff)) & ~1;
+      first_round = (14 - shift0) >> 1;
+      thr = smax & ~((4u << shift0) - 1u);
+    }
 #pragma unroll 1
-    for (int round = 0; round < 8; ++round) {
+    for (int round = first_round; round < 8; ++round) {
       const int shift = 14 - 2 * round;
       int c1, c2, c3;
       count3(thr | (1u << shift), thr | (2u << shift), thr | (3u << shift), c1, c2, c3);
-      sum3((round + 1) & 1, c1, c2, c3);
+      sum3(buf, c1, c2, c3);
+      buf ^= 1;
       thr |= (c3 >= k ? 3u : c2 >= k ? 2u : c1 >= k ? 1u : 0u) << shift;   // largest candidate with >= k at or above
     }
     int gt, e1, e2;
     count3(thr + 1u, 0x10000u, 0x10000u, gt, e1, e2);
-    sum3(1, gt, e1, e2);
+    sum3(buf, gt, e1, e2);
     rem = k - gt;
   }
-  // compaction in index order over a blocked layout (ept consecutive scores per
-  // thread): strictly above the threshold, then the first `rem` ties
-  const int ept = (((n + NT - 1) / NT) + 7) & ~7;
-  const int base = tid * ept;
-  const int nch = base < n ? min(ept, ((n - base + 7) & ~7)) >> 3 : 0;
-  const uint4* blk = (const uint4*)(sc + base);
-  int gt = 0, tie = 0;
-  for (int ch = 0; ch < nch; ++ch) {
-    uint32_t v[8];
-    unpack_u16x8(blk[ch], v);
+  if (!in_regs) return block_compact_threshold<NT>(sc, n, k, thr, rem, all, nvalid, out, wtot);
+  // Compaction from the registers, in index order: consecutive threads hold consecutive
+  // chunks of a slot, so one scan over the threads per slot places its survivors (strictly
+  // above the threshold, then the first `rem` scores equal to it).
+  int base_gt = 0, base_tie = 0, cbuf = 0;
+  auto place = [&](const uint32_t (&v)[8], int idx0) {
+    int gt = 0, tie = 0;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { gt += all ? v[j] != 0 : v[j] > thr; tie += (!all) && v[j] == thr; }
-  }
-  // exclusive scan of (gt | tie << 16): shuffles inside the warp, columns across warps
-  int incl = gt | (tie << 16);
+    for (int j = 0; j < 8; ++j) { gt += all ? v[j] != 0u : v[j] > thr; tie += (!all) && v[j] == thr; }
+    const int own = gt | (tie << 16);
+    int incl = own;
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int nb = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += nb;
-  }
-  __syncthreads();                             // the columns may still be read by slower warps
-  if (lane == 31) wtot[warp] = incl;
-  __syncthreads();
-  int before = 0;
-#pragma unroll
-  for (int w = 0; w < NW; ++w) before += w < warp ? wtot[w] : 0;
-  const int excl = before + incl - (gt | (tie << 16));
-  int tb = excl >> 16;
-  int pos = (excl & 0xFFFF) + min(tb, rem);
-  for (int ch = 0; ch < nch; ++ch) {
-    uint32_t v[8];
-    unpack_u16x8(blk[ch], v);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int i = base + ch * 8 + j;
-      if (all ? v[j] != 0 : v[j] > thr) out[pos++] = i;
-      else if (!all && v[j] == thr) { if (tb < rem) out[pos++] = i; ++tb; }
+    for (int o = 1; o < 32; o <<= 1) {
+      const int nb = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += nb;
     }
+    if (lane == 31) wtot[cbuf * 32 + warp] = incl;
+    __syncthreads();
+    int before = 0, tot = 0;
+#pragma unroll
+    for (int w4 = 0; w4 < (NW + 3) / 4; ++w4) {
+      const int4 x = ((const int4*)(wtot + cbuf * 32))[w4];
+      tot += (x.x + x.y) + (x.z + x.w);
+      before += (w4 * 4 + 0 < warp ? x.x : 0) + (w4 * 4 + 1 < warp ? x.y : 0) + (w4 * 4 + 2 < warp ? x.z : 0) +
+                (w4 * 4 + 3 < warp ? x.w : 0);
+    }
+    cbuf ^= 1;
+    const int excl = before + incl - own;
+    int tb = base_tie + (excl >> 16);
+    int pos = base_gt + (excl & 0xFFFF) + min(tb, rem);
+    if (own != 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (all ? v[j] != 0u : v[j] > thr) out[pos++] = idx0 + j;
+        else if (!all && v[j] == thr) { if (tb < rem) out[pos++] = idx0 + j; ++tb; }
+      }
+    }
+    base_gt += tot & 0xFFFF;
+    base_tie += tot >> 16;
+  };
+  __syncthreads();                               // the columns may still be read by slower warps
+  if (tid < 64) wtot[tid] = 0;                   // two rows of per-warp totals; absent warps stay 0
+  __syncthreads();
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    if (c < nslots) {
+      uint32_t v[8];
+      unpack_u16x8(mine[c], v);
+      place(v, (tid + c * NT) * 8);
+    }
+  }
+  if (single) {
+    const uint32_t v[8] = {xtra, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    place(v, full * NT * 8 + tid);
   }
   __syncthreads();
   return all ? nvalid : k;
@@ -510,7 +665,16 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // its predecessor in the stream still runs; it must not touch memory before
 // pdl_wait(), which returns once the predecessor has completed and flushed.
 // Both are no-ops for a kernel launched without the attribute.
+// LODA_PDL_TRIGGER chooses where a kernel releases its dependent launch: 1 (default) =
+// when its long phase is over (after the row's selection, after the attention tiles), so
+// that the dependent's launch latency and prologue hide behind the closing phase only;
+// 0 = at once.  Released at once, the dependent's CTAs sit on the SMs waiting while the
+// single selecting CTA of a row still works, and slow it down: measured 4.4 us per
+// layer-step (of 48.7) at batch 1.
 // ---------------------------------------------------------------------------
+#ifndef LODA_PDL_TRIGGER
+#define LODA_PDL_TRIGGER 1
+#endif
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -542,19 +706,49 @@ struct AppendArgs {
 };
 
 // ---------------------------------------------------------------------------
+// Shared-memory carve-out asked for every kernel of the chain (percent of the maximum).
+// All kernels ask for the same one: an SM has to drain before its L1/shared split can
+// change, which would keep a dependent launch from starting beside its predecessor.
+#ifndef LODA_CARVEOUT
+#define LODA_CARVEOUT 100
+#endif
+template <typename K>
+inline cudaError_t set_kernel_smem(K kernel, size_t smem) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == cudaSuccess && LODA_CARVEOUT >= 0)
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, LODA_CARVEOUT);
+  return e;
+}
+
 // optional phase timestamps (compile with -DLODA_PHASES): thread 0 of each CTA
 // records clock64() at numbered points; LODA_PHASE_STORAGE defines the per-file
 // array and a C reader.  Compiled out of the shipped library.
 // ---------------------------------------------------------------------------
 #ifdef LODA_PHASES
+#define LODA_PHASE_CTAS 2048
 #define LODA_PHASE_STORAGE(name)                                                        \
-  static __device__ long long g_phase_##name[512][16];                                  \
+  static __device__ long long g_phase_##name[LODA_PHASE_CTAS][16];                      \
   extern "C" int loda_phase_read_##name(long long* host) {                              \
-    return (int)cudaMemcpyFromSymbol(host, g_phase_##name, sizeof(long long) * 512 * 16); \
+    return (int)cudaMemcpyFromSymbol(host, g_phase_##name, sizeof(long long) * LODA_PHASE_CTAS * 16); \
   }
+// phase 0 also stores the global timer (ns) in slot 15 and the SM id in slot 14; slot 13
+// holds the global timer of the latest phase >= 8 (the kernels' closing phases)
 #define LODA_PHASE(name, cta, i)                                                        \
   do {                                                                                  \
-    if (threadIdx.x == 0 && (cta) < 512) g_phase_##name[(cta)][(i)] = clock64();        \
+    if (threadIdx.x == 0 && (cta) < LODA_PHASE_CTAS) {                                  \
+      g_phase_##name[(cta)][(i)] = clock64();                                           \
+      if ((i) == 0 || (i) >= 8) {                                                       \
+        unsigned long long gt_;                                                         \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));                         \
+        if ((i) == 0) {                                                                 \
+          unsigned sm_;                                                                 \
+          asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_));                              \
+          g_phase_##name[(cta)][15] = (long long)gt_;                                   \
+          g_phase_##name[(cta)][14] = sm_;                                              \
+        }                                                                               \
+        g_phase_##name[(cta)][13] = (long long)gt_;                                     \
+      }                                                                                 \
+    }                                                                                   \
   } while (0)
 #else
 #define LODA_PHASE_STORAGE(name)

@@ -68,6 +68,7 @@ LODA_PHASE_STORAGE(l1)
 // the selecting CTA reuses the staging area: 40 KB for the far pool's scores (2 bytes per page)
 // and 1 KB for the near pool's
 constexpr size_t L1_TAIL_BYTES = 41 * 1024;
+constexpr int L1_NEAR_CAP = 512;     // scores of the near row (1 KB behind the 40 KB far row)
 
 // Rank the n kept pages of one pool best-first (score descending, lower id
 // first) and append fillers (lowest page ids not kept): the page-id lists the
@@ -112,8 +113,8 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   float* qlow = qhat + G * DSUB;
   float* qhigh = qlow + G * DSUB;
   int* kept = (int*)(qhigh + G * DSUB);                          // k_far + k_near + 2
-  uint32_t* keys = (uint32_t*)(((uintptr_t)(kept + (g.k_far + g.k_near + 2)) + 15) & ~(uintptr_t)15);   // P + 8
-  int* wtot = (int*)(keys + P + 8);                              // 6 x 32
+  uint32_t* keys = (uint32_t*)(((uintptr_t)(kept + (g.k_far + g.k_near + 2)) + 15) & ~(uintptr_t)15);   // 2 P + 8
+  int* wtot = (int*)(keys + 2 * P + 8);                              // 6 x 32
   int* sh = wtot + 192;                                          // 8
 
   const int tid = threadIdx.x;
@@ -122,7 +123,9 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   const int cta_id = blockIdx.y * gridDim.x + blockIdx.x;
   LODA_PHASE(l1, cta_id, 0);
   pdl_wait();
+#if LODA_PDL_TRIGGER == 0
   pdl_launch_dependents();
+#endif
   LODA_PHASE(l1, cta_id, 1);
   if (split == nsplit) {
     // extra CTA of the row: the decode append.  It touches only the newest token
@@ -136,17 +139,18 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   const int req = (int)B.valid_req_ids[b];
   const int length = act >= 0 ? len_raw : 0;
   const Regions rg = make_regions(g, length);
-  // this CTA's tiles of P pages; tiles past the request's last page are neither read nor written
+  // this CTA's tiles of P pages: split, split + nsplit, ... (interleaved, so that the tiles a
+  // short request really has are spread over the CTAs of its row); tiles past the request's
+  // last page are neither read nor written, and a CTA without tiles only takes its ticket
   const size_t pg0 = ((size_t)req * g.num_kv_heads + kv) * g.max_blocks;
   const unsigned char* mm_base = (const unsigned char*)L.page_mm + pg0 * (4 * DSUB);
   const unsigned char* sum_base = (const unsigned char*)L.page_sum + pg0 * (2 * DSUB);
   uint16_t* row_scores = ws.l1_scores + (size_t)row * ws.score_stride;
   const int page_end = min(rg.kt_eff, g.max_blocks);
-  const int tile0 = split * tiles_per_cta;
-  for (int tile = tile0; tile < tile0 + tiles_per_cta; ++tile) {
-    const int p0 = tile * P;
-    if (p0 >= page_end && tile > tile0) break;           // the first tile always runs (it prepares nothing else)
-    if (tile > tile0) __syncthreads();                   // the staging rows are reused
+  for (int it = 0; it < tiles_per_cta; ++it) {
+    const int p0 = (split + it * nsplit) * P;
+    if (p0 >= page_end) break;
+    if (it > 0) __syncthreads();                         // the staging rows are reused
     // stage the metadata rows of the tile (issued first: the longest latency)
     for (int c = tid; c < P * CPR; c += P) {
       const int pl = c / CPR, cc = c % CPR;
@@ -158,7 +162,7 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
       }
     }
     cp_async_commit();
-    if (tile == tile0) {
+    if (it == 0) {
       // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
       for (int i = tid; i < G * DSUB; i += P) {
         const int j = i / DSUB, d = i % DSUB;
@@ -206,7 +210,7 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
       ord = ord16(bf16r(__fdiv_rn(acc, gf)));
     }
     if (ord == ORD16_NEG_INF) ord = 0;   // a -inf score never competes (it equals "not in the pool")
-    if (p0 < page_end) row_scores[page] = (uint16_t)ord;   // the selecting CTA reads pages below page_end (rounded up to 8)
+    row_scores[page] = (uint16_t)ord;     // the selecting CTA reads pages below page_end (rounded up to 8)
   }
   LODA_PHASE(l1, cta_id, 4);
 
@@ -224,9 +228,10 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   const int far_lo = rg.far_lo, far_hi = max(rg.far_hi, rg.far_lo);
   const int near_lo = rg.near_blks, near_lo8 = near_lo & ~7;
   const int n_far = far_hi;                                                   // far row: pages [0, far_hi)
-  const int n_near = near_hi > near_lo ? min(near_hi - near_lo8, P) : 0;      // near row: pages [near_lo8, ...)
+  static_assert(2 * P >= L1_NEAR_CAP, "the near row is ranked with at most two scores per thread");
+  const int n_near = near_hi > near_lo ? min(near_hi - near_lo8, L1_NEAR_CAP) : 0;   // near row: pages [near_lo8, ...)
   uint16_t* scf = (uint16_t*)rows;                       // up to 40 KB
-  uint16_t* scn = (uint16_t*)(rows + 40 * 1024);         // P scores
+  uint16_t* scn = (uint16_t*)(rows + 40 * 1024);         // L1_NEAR_CAP scores
   {
     const uint4* src = (const uint4*)row_scores;         // 8 scores per load; unscored pages hold 0
     for (int c = tid; c < (n_far + 7) / 8; c += P) {
@@ -245,6 +250,9 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
     }
   }
   __syncthreads();
+#if LODA_PDL_TRIGGER == 3
+  pdl_launch_dependents();
+#endif
   LODA_PHASE(l1, cta_id, 6);
   int np = 0;
   const bool want_lists = out.i_far != nullptr;
@@ -261,10 +269,14 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
       }
     }
     if (n_near > 0) {
-      n_n = block_rank_topk_small<P>(scn, n_near, g.k_near, kept_near, keys, wtot);
+      n_n = n_near <= P ? block_rank_topk_small<P>(scn, n_near, g.k_near, kept_near, keys, wtot)
+                        : block_rank_topk_pair<P>(scn, n_near, g.k_near, kept_near, keys, wtot);
       for (int i = tid; i < n_n; i += P) kept_near[i] += near_lo8;
       __syncthreads();
     }
+#if LODA_PDL_TRIGGER == 1
+    pdl_launch_dependents();
+#endif
     LODA_PHASE(l1, cta_id, 7);
     if (want_lists) {
       // best-first lists need the scores by page id: near scores go back beside the far ones
@@ -277,9 +289,11 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
     }
     if (rg.quota > 0) {
       // ascending list: [sink bypass] far... near... [window bypass]
-      const int v = tid < n_n ? kept_near[tid] : 0;      // k_near <= P
+      const int v0 = tid < n_n ? kept_near[tid] : 0;     // k_near <= 2 P
+      const int v1 = tid + P < n_n ? kept_near[tid + P] : 0;
       __syncthreads();
-      if (tid < n_n) kept[np + n_f + tid] = v;
+      if (tid < n_n) kept[np + n_f + tid] = v0;
+      if (tid + P < n_n) kept[np + n_f + tid + P] = v1;
       np += n_f + n_n;
       if (rg.swa_byp) { if (tid == 0) kept[np] = rg.swa_byp_blk; ++np; }
     }
@@ -303,42 +317,59 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   LODA_PHASE(l1, cta_id, 9);
 }
 
-constexpr int L1_P = 512;
+// Two tile shapes.  512 pages per 512-thread CTA: one CTA per SM (128 registers), the
+// fewest tickets and the shortest path for a grid that fits the GPU in one round (batch 1
+// at 128K tokens: 8 rows x 16 tiles).  256 pages per 256-thread CTA: two CTAs per SM, so
+// that one CTA's copies overlap the other's arithmetic, for every larger grid.
+constexpr int L1_P_WIDE = 512, L1_P_NARROW = 256;
 
-size_t l1_smem_bytes(const loda_geometry& g) {
+static size_t l1_smem_bytes_p(const loda_geometry& g, int P) {
   const int G = g.num_q_heads / g.num_kv_heads;
-  const size_t rows = (size_t)L1_P * (4 * g.sub_dims + 16);
+  const size_t rows = (size_t)P * (4 * g.sub_dims + 16);
   return (rows > L1_TAIL_BYTES ? rows : L1_TAIL_BYTES) + (size_t)3 * G * g.sub_dims * 4 +
-         (size_t)(g.k_far + g.k_near + 2) * 4 + (size_t)(L1_P + 8) * 4 + (192 + 8) * 4 + 32;
+         (size_t)(g.k_far + g.k_near + 2) * 4 + (size_t)(2 * P + 8) * 4 + (192 + 8) * 4 + 32;
 }
 
-int l1_nsplit(const loda_geometry& g) { return (g.max_blocks + L1_P - 1) / L1_P; }
+size_t l1_smem_bytes(const loda_geometry& g) { return l1_smem_bytes_p(g, L1_P_WIDE); }
 
-int l1_score_stride(const loda_geometry& g) { return l1_nsplit(g) * L1_P; }
+// scores per row in the workspace: whole tiles of either shape
+int l1_score_stride(const loda_geometry& g) { return (g.max_blocks + L1_P_WIDE - 1) / L1_P_WIDE * L1_P_WIDE; }
 
-// CTAs per row: one tile of 512 pages each while the grid is small (batch 1: latency), several
-// tiles per CTA once rows x tiles exceeds about four waves (fewer prologues, tickets and waves)
-void l1_split(const loda_geometry& g, int rows, int* ctas_per_row, int* tiles_per_cta) {
-  const int ntiles = l1_nsplit(g);
-  int tpc = (rows * ntiles + 4 * 148 - 1) / (4 * 148);
+static bool l1_wide(const loda_geometry& g, int rows) {
+  return rows * ((g.max_blocks + L1_P_WIDE - 1) / L1_P_WIDE + 1) <= 148;
+}
+
+// CTAs per row: one tile each while the grid is small (batch 1: latency), several
+// interleaved tiles per CTA once rows x tiles exceeds about eight CTAs per SM
+static void l1_split(const loda_geometry& g, int rows, int P, int* ctas_per_row, int* tiles_per_cta) {
+  const int ntiles = (g.max_blocks + P - 1) / P;
+  int tpc = (rows * ntiles + 8 * 148 - 1) / (8 * 148);
   tpc = tpc < 1 ? 1 : tpc > ntiles ? ntiles : tpc;
   *tiles_per_cta = tpc;
   *ctas_per_row = (ntiles + tpc - 1) / tpc;
+}
+
+template <int DS, int P>
+static cudaError_t launch_l1_p(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
+                               float scale, const loda_selection& out, const SelectWorkspace& ws,
+                               const AppendArgs& ap, cudaStream_t st) {
+  const int rows = B.batch * g.num_kv_heads;
+  int nsplit, tpc;
+  l1_split(g, rows, P, &nsplit, &tpc);
+  const dim3 grid(nsplit + (ap.enabled ? 1 : 0), rows);
+  const size_t smem = l1_smem_bytes_p(g, P);
+  cudaError_t e = set_kernel_smem(l1_kernel<DS, P>, smem);
+  if (e != cudaSuccess) return e;
+  return launch_pdl(l1_kernel<DS, P>, grid, dim3(P), smem, st, g, L, B, (const bf16*)q, scale, out, ws, nsplit, tpc,
+                    ap);
 }
 
 template <int DS>
 static cudaError_t launch_l1_d(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                float scale, const loda_selection& out, const SelectWorkspace& ws,
                                const AppendArgs& ap, cudaStream_t st) {
-  const int rows = B.batch * g.num_kv_heads;
-  int nsplit, tpc;
-  l1_split(g, rows, &nsplit, &tpc);
-  const dim3 grid(nsplit + (ap.enabled ? 1 : 0), rows);
-  const size_t smem = l1_smem_bytes(g);
-  cudaError_t e = cudaFuncSetAttribute(l1_kernel<DS, L1_P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return e;
-  return launch_pdl(l1_kernel<DS, L1_P>, grid, dim3(L1_P), smem, st, g, L, B, (const bf16*)q, scale, out, ws,
-                    nsplit, tpc, ap);
+  return l1_wide(g, B.batch * g.num_kv_heads) ? launch_l1_p<DS, L1_P_WIDE>(g, L, B, q, scale, out, ws, ap, st)
+                                              : launch_l1_p<DS, L1_P_NARROW>(g, L, B, q, scale, out, ws, ap, st);
 }
 
 cudaError_t launch_l1(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,

@@ -54,13 +54,20 @@ __device__ __forceinline__ float l2_logit(const uint8_t* __restrict__ codes, flo
   return bf16r(acc);
 }
 
+#ifndef LODA_L2_MINB
+#define LODA_L2_MINB 1     // resident CTAs per SM the register budget must allow (4 costs spills)
+#endif
+#ifndef LODA_L2_CTAS_PER_SM
+#define LODA_L2_CTAS_PER_SM 1
+#endif
+
 LODA_PHASE_STORAGE(l2)
 
 constexpr int L2_SPLIT = 8;
 constexpr int L2_NT = 256;
 
 template <int DSUB, int NT>
-__global__ void __launch_bounds__(NT) l2_kernel(loda_geometry g, loda_layer L, loda_batch B,
+__global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, loda_layer L, loda_batch B,
                                                  const bf16* __restrict__ q, float scale,
                                                  loda_selection S, SelectWorkspace ws, uint32_t* status,
                                                  int nsplit) {
@@ -109,7 +116,9 @@ __global__ void __launch_bounds__(NT) l2_kernel(loda_geometry g, loda_layer L, l
   // produced by the preceding L1 launch
   LODA_PHASE(l2, cta_id, 1);
   pdl_wait();
+#if LODA_PDL_TRIGGER == 0
   pdl_launch_dependents();
+#endif
   LODA_PHASE(l2, cta_id, 2);
 
   const int np = min(__ldcg(ws.np + row), np_max);
@@ -152,10 +161,16 @@ __global__ void __launch_bounds__(NT) l2_kernel(loda_geometry g, loda_layer L, l
     physs[i] = __ldcg(ws.phys + (size_t)row * np_max + i);
   }
   __syncthreads();
+#if LODA_PDL_TRIGGER == 3
+  pdl_launch_dependents();
+#endif
   LODA_PHASE(l2, cta_id, 5);
   const int quota = rg.quota;
   int* slots_sel = mid_b;      // ascending candidate slots kept by the select
   const int take = block_bisect_topk<NT>(sc, nitems, min(quota, K2), slots_sel, wtot);
+#if LODA_PDL_TRIGGER == 1
+  pdl_launch_dependents();
+#endif
   LODA_PHASE(l2, cta_id, 6);
   if (take == quota) {
     // Common case: the quota is filled by scored candidates (all of them >= sink, no holes).
@@ -295,13 +310,14 @@ template <int DS>
 static cudaError_t launch_l2_d(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                float scale, const loda_selection& S, const SelectWorkspace& ws, uint32_t* status,
                                cudaStream_t st) {
-  // scoring CTAs per row: 8 at batch 1 (latency), fewer once the rows alone fill the GPU
+  // scoring CTAs per row: 8 at batch 1 (latency), one once the rows alone give every SM a CTA
+  // (every CTA of a row pays the ticket; the row's selection runs in one CTA either way)
   const int rows = B.batch * g.num_kv_heads;
-  int nsplit = (2 * 148 + rows - 1) / rows;
+  int nsplit = (LODA_L2_CTAS_PER_SM * 148 + rows - 1) / rows;
   nsplit = nsplit < 1 ? 1 : nsplit > L2_SPLIT ? L2_SPLIT : nsplit;
   const dim3 grid(nsplit, rows);
   const size_t smem = l2_smem_bytes(g);
-  cudaError_t e = cudaFuncSetAttribute(l2_kernel<DS, L2_NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = set_kernel_smem(l2_kernel<DS, L2_NT>, smem);
   if (e != cudaSuccess) return e;
   return launch_pdl(l2_kernel<DS, L2_NT>, grid, dim3(L2_NT), smem, st, g, L, B, (const bf16*)q, scale, S, ws, status,
                     nsplit);
