@@ -8,6 +8,18 @@
 
 #include "loda_b200.h"
 
+// optional sub-phase timestamps inside the block routines (compile with -DLODA_PHASES):
+// thread 0 of the CTAs with blockIdx.y == 0 records clock64() at numbered points
+#ifdef LODA_PHASES
+static __device__ long long g_subphase[32];
+#define LODA_SUB(i) do { if (threadIdx.x == 0 && blockIdx.y == 0) g_subphase[(i)] = clock64(); } while (0)
+#define LODA_SUB_READER(name) extern "C" int loda_phase_read_sub_##name(long long* host) { \
+    return (int)cudaMemcpyFromSymbol(host, g_subphase, sizeof(long long) * 32); }
+#else
+#define LODA_SUB(i)
+#define LODA_SUB_READER(name)
+#endif
+
 namespace loda {
 
 // ---------------------------------------------------------------------------
@@ -415,8 +427,10 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
     }
     c1 = s[0]; c2 = s[1]; c3 = s[2];
   };
+  LODA_SUB(0);
   for (int i = tid; i < 6 * 32; i += NT) wtot[i] = 0;      // columns of absent warps stay 0
   __syncthreads();
+  LODA_SUB(1);
   // scored elements, their maximum, and 0xFFFF - their minimum (so that empty columns, 0, are neutral)
   int nvalid;
   uint32_t smax, smin;
@@ -463,6 +477,7 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
     smax = (uint32_t)b;
     smin = 0xFFFFu - (uint32_t)c;
   }
+  LODA_SUB(2);
   if (k <= 0 || nvalid == 0) { __syncthreads(); return 0; }
   const bool all = nvalid <= k;
   uint32_t thr = 1u;     // keep v >= thr ...
@@ -486,11 +501,13 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
       sum3(buf, c1, c2, c3);
       buf ^= 1;
       thr |= (c3 >= k ? 3u : c2 >= k ? 2u : c1 >= k ? 1u : 0u) << shift;   // largest candidate with >= k at or above
+      LODA_SUB(3 + round);
     }
     int gt, e1, e2;
     count3(thr + 1u, 0x10000u, 0x10000u, gt, e1, e2);
     sum3(buf, gt, e1, e2);
     rem = k - gt;
+    LODA_SUB(11);
   }
   if (!in_regs) return block_compact_threshold<NT>(sc, n, k, thr, rem, all, nvalid, out, wtot);
   // Compaction from the registers, in index order: consecutive threads hold consecutive
@@ -498,10 +515,14 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
   // above the threshold, then the first `rem` scores equal to it).
   int base_gt = 0, base_tie = 0, cbuf = 0;
   auto place = [&](const uint32_t (&v)[8], int idx0) {
-    int gt = 0, tie = 0;
+    // bit j of gm / tm: score j is above / equal to the threshold
+    uint32_t gm = 0, tm = 0;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { gt += all ? v[j] != 0u : v[j] > thr; tie += (!all) && v[j] == thr; }
-    const int own = gt | (tie << 16);
+    for (int j = 0; j < 8; ++j) {
+      gm |= (uint32_t)(all ? v[j] != 0u : v[j] > thr) << j;
+      tm |= (uint32_t)((!all) && v[j] == thr) << j;
+    }
+    const int own = __popc(gm) | (__popc(tm) << 16);
     int incl = own;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -520,14 +541,19 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
     }
     cbuf ^= 1;
     const int excl = before + incl - own;
-    int tb = base_tie + (excl >> 16);
-    int pos = base_gt + (excl & 0xFFFF) + min(tb, rem);
-    if (own != 0) {
+    const int tb = base_tie + (excl >> 16);              // ties before this thread's scores
+    const int pos = base_gt + (excl & 0xFFFF) + min(tb, rem);
+    // of this thread's ties only the first rem - tb survive; every survivor's place follows
+    // from the bits below it, so the eight stores are independent and predicated
+    const int allowed = max(rem - tb, 0);
+    uint32_t m = gm;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (all ? v[j] != 0u : v[j] > thr) out[pos++] = idx0 + j;
-        else if (!all && v[j] == thr) { if (tb < rem) out[pos++] = idx0 + j; ++tb; }
-      }
+    for (int j = 0; j < 8; ++j) {
+      if ((tm >> j) & 1u) m |= (uint32_t)(__popc(tm & ((1u << j) - 1u)) < allowed) << j;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if ((m >> j) & 1u) out[pos + __popc(m & ((1u << j) - 1u))] = idx0 + j;
     }
     base_gt += tot & 0xFFFF;
     base_tie += tot >> 16;
@@ -543,11 +569,13 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
       place(v, (tid + c * NT) * 8);
     }
   }
+  LODA_SUB(12);
   if (single) {
     const uint32_t v[8] = {xtra, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
     place(v, full * NT * 8 + tid);
   }
   __syncthreads();
+  LODA_SUB(13);
   return all ? nvalid : k;
 }
 

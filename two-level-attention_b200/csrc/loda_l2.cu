@@ -62,6 +62,7 @@ __device__ __forceinline__ float l2_logit(const uint8_t* __restrict__ codes, flo
 #endif
 
 LODA_PHASE_STORAGE(l2)
+LODA_SUB_READER(l2)
 
 constexpr int L2_SPLIT = 8;
 constexpr int L2_NT = 256;
