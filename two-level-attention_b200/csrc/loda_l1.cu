@@ -113,7 +113,9 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   float* qlow = qhat + G * DSUB;
   float* qhigh = qlow + G * DSUB;
   int* kept = (int*)(qhigh + G * DSUB);                          // k_far + k_near + 2
-  uint32_t* keys = (uint32_t*)(((uintptr_t)(kept + (g.k_far + g.k_near + 2)) + 15) & ~(uintptr_t)15);   // 2 P + 8
+  // (an offset, not pointer arithmetic through an integer: the compiler must keep seeing shared memory)
+  const size_t keys_off = (ROWS_BYTES + (size_t)3 * G * DSUB * 4 + (size_t)(g.k_far + g.k_near + 2) * 4 + 15) & ~(size_t)15;
+  uint32_t* keys = (uint32_t*)(smem + keys_off);                 // 2 P + 8
   int* wtot = (int*)(keys + 2 * P + 8);                              // 6 x 32
   int* sh = wtot + 192;                                          // 8
 

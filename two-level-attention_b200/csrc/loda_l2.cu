@@ -76,18 +76,19 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
   const int np_max = g.k_far + g.k_near + 2;
   const int K2 = g.level2_topk;
   // shared memory: scores (u16) | qf | pages | mid | mid2 | hist | scan | sh | win
+  // (offsets, not pointer arithmetic through integers: the compiler must keep seeing shared memory)
   uint16_t* sc = (uint16_t*)smem;
-  unsigned char* p = smem + (((size_t)np_max * g.page * 2 + 15) & ~(size_t)15);
-  float* qf = (float*)p; p += DSUB * 4;
-  int* pages = (int*)p; p += np_max * 4;
-  int* physs = (int*)p; p += np_max * 4;
-  int* mid_a = (int*)p; p += K2 * 4;
-  int* mid_b = (int*)p; p += K2 * 4;
-  p = (unsigned char*)(((uintptr_t)p + 15) & ~(uintptr_t)15);
-  int* wtot = (int*)p; p += 192 * 4;
-  int* scan = (int*)p; p += 40 * 4;
-  int* sh = (int*)p; p += 16 * 4;
-  uint8_t* win = (uint8_t*)p;
+  size_t off = ((size_t)np_max * g.page * 2 + 15) & ~(size_t)15;
+  float* qf = (float*)(smem + off); off += DSUB * 4;
+  int* pages = (int*)(smem + off); off += (size_t)np_max * 4;
+  int* physs = (int*)(smem + off); off += (size_t)np_max * 4;
+  int* mid_a = (int*)(smem + off); off += (size_t)K2 * 4;
+  int* mid_b = (int*)(smem + off); off += (size_t)K2 * 4;
+  off = (off + 15) & ~(size_t)15;
+  int* wtot = (int*)(smem + off); off += 192 * 4;
+  int* scan = (int*)(smem + off); off += 40 * 4;
+  int* sh = (int*)(smem + off); off += 16 * 4;
+  uint8_t* win = (uint8_t*)(smem + off);
 
   const int tid = threadIdx.x;
   const int split = blockIdx.x, row = blockIdx.y;
