@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
     loda_geometry g, loda_layer L, const bf16* __restrict__ q, const int32_t* __restrict__ gather,
     const int32_t* __restrict__ visible_lens, const int32_t* __restrict__ query_to_req,
     int n_req_rows, float scale_log2, bf16* __restrict__ out, float* __restrict__ lse, AttnWorkspace ws,
-    int nsplit) {
+    int nsplit, int chained) {
   constexpr int KSTR = D + 8, VSTR = DV + 8;   // padded rows: conflict-free ldmatrix
   constexpr int KSTEPS = D / 16, NTV = DV / 8;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -88,21 +88,12 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
   const int page_log2 = 31 - __clz(g.page);
   const int cta_id = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
   LODA_PHASE(attn, cta_id, 0);
-  pdl_wait();
-#if LODA_PDL_TRIGGER == 0
-  pdl_launch_dependents();
-#endif
-  LODA_PHASE(attn, cta_id, 1);
-  const int req = query_to_req[t];
-  int n = 0;
-  if (req >= 0 && req < n_req_rows) n = min(max(visible_lens[(size_t)req * g.num_kv_heads + kv], 0), g.max_visible);
-  const int c0 = (int)(((long long)split * n) / nsplit);
-  const int c1 = (int)(((long long)(split + 1) * n) / nsplit);
-  const int32_t* list = gather + ((size_t)max(req, 0) * g.num_kv_heads + kv) * g.max_visible;
-
-  // Q fragments: A operand, rows = heads of the group (zero beyond G)
+  // Q fragments: A operand, rows = heads of the group (zero beyond G).  When this launch is
+  // chained behind the selector launches of the same step (which read the query too, after
+  // their own wait), the query was complete before they could release this launch, and it is
+  // read before the wait; a launch that stands alone reads it after.
   uint32_t qa[KSTEPS][4];
-  {
+  auto load_q = [&]() {
     const int r0 = lane >> 2, r1 = r0 + 8, kc = (lane & 3) * 2;
     const bf16* q0 = q + ((size_t)t * g.num_q_heads + kv * G + r0) * D;
     const bf16* q1 = q + ((size_t)t * g.num_q_heads + kv * G + r1) * D;
@@ -113,7 +104,20 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
       qa[ks][2] = r0 < G ? *(const uint32_t*)(q0 + ks * 16 + kc + 8) : 0u;
       qa[ks][3] = r1 < G ? *(const uint32_t*)(q1 + ks * 16 + kc + 8) : 0u;
     }
-  }
+  };
+  if (chained) load_q();
+  pdl_wait();
+#if LODA_PDL_TRIGGER == 0
+  pdl_launch_dependents();
+#endif
+  if (!chained) load_q();
+  LODA_PHASE(attn, cta_id, 1);
+  const int req = query_to_req[t];
+  int n = 0;
+  if (req >= 0 && req < n_req_rows) n = min(max(visible_lens[(size_t)req * g.num_kv_heads + kv], 0), g.max_visible);
+  const int c0 = (int)(((long long)split * n) / nsplit);
+  const int c1 = (int)(((long long)(split + 1) * n) / nsplit);
+  const int32_t* list = gather + ((size_t)max(req, 0) * g.num_kv_heads + kv) * g.max_visible;
 
   LODA_PHASE(attn, cta_id, 2);
   float oacc[NTV][4];
@@ -444,7 +448,7 @@ static cudaError_t launch_attn_dims(const loda_geometry& g, const loda_layer& L,
                                     const int32_t* gather, const int32_t* visible_lens,
                                     const int32_t* query_to_req, int n_query, int n_req_rows, float scale_log2,
                                     void* out, float* lse, const AttnWorkspace& ws, bool allow_cluster,
-                                    cudaStream_t st) {
+                                    bool chained, cudaStream_t st) {
   const int nsplit = attn_nsplit(g, n_query);
   const dim3 grid(nsplit, g.num_kv_heads, n_query);
   const size_t smem = attn_smem_bytes(g);
@@ -471,7 +475,7 @@ static cudaError_t launch_attn_dims(const loda_geometry& g, const loda_layer& L,
       cfg.attrs = attr;
       cfg.numAttrs = 2;
       e = cudaLaunchKernelEx(&cfg, kernel, g, L, (const bf16*)q, gather, visible_lens, query_to_req, n_req_rows,
-                             scale_log2, (bf16*)out, lse, ws, nsplit);
+                             scale_log2, (bf16*)out, lse, ws, nsplit, (int)chained);
     }
     if (e == cudaSuccess) return cudaSuccess;
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
@@ -484,21 +488,21 @@ static cudaError_t launch_attn_dims(const loda_geometry& g, const loda_layer& L,
   e = set_kernel_smem(kernel, smem);
   if (e != cudaSuccess) return e;
   return launch_pdl(kernel, grid, dim3(ATT_NT), smem, st, g, L, (const bf16*)q, gather, visible_lens, query_to_req,
-                    n_req_rows, scale_log2, (bf16*)out, lse, ws, nsplit);
+                    n_req_rows, scale_log2, (bf16*)out, lse, ws, nsplit, (int)chained);
 }
 
 cudaError_t launch_attn(const loda_geometry& g, const loda_layer& L, const void* q, const int32_t* gather,
                         const int32_t* visible_lens, const int32_t* query_to_req, int n_query,
                         int n_req_rows, float scale, void* out, float* lse, const AttnWorkspace& ws,
-                        bool allow_cluster, cudaStream_t st) {
+                        bool allow_cluster, bool chained, cudaStream_t st) {
   if (n_query <= 0) return cudaSuccess;
   const float scale_log2 = scale * 1.4426950408889634f;
   if (g.head_dim == 128 && g.head_dim_v == 128)
     return launch_attn_dims<128, 128>(g, L, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale_log2,
-                                      out, lse, ws, allow_cluster, st);
+                                      out, lse, ws, allow_cluster, chained, st);
   if (g.head_dim == 64 && g.head_dim_v == 64)
     return launch_attn_dims<64, 64>(g, L, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale_log2,
-                                    out, lse, ws, allow_cluster, st);
+                                    out, lse, ws, allow_cluster, chained, st);
   return cudaErrorInvalidValue;
 }
 
@@ -580,7 +584,7 @@ extern "C" int loda_gather_attend_static(const loda_geometry* g, const loda_laye
   cudaError_t e = cudaMemsetAsync(ws.ticket, 0, ATT_STATIC_TICKET_BYTES, (cudaStream_t)stream);
   if (e == cudaSuccess)
     e = launch_attn(*g, *layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale, out, nullptr, ws,
-                    /*allow_cluster=*/false, (cudaStream_t)stream);   // this entry point exists for the scratch path
+                    /*allow_cluster=*/false, /*chained=*/false, (cudaStream_t)stream);   // this entry point exists for the scratch path
   if (e != cudaSuccess) {
     char msg[160];
     snprintf(msg, sizeof(msg), "gather_attend_static: %s", cudaGetErrorString(e));

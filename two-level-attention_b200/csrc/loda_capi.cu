@@ -16,10 +16,10 @@ cudaError_t launch_write_prefill(const loda_geometry&, const loda_layer&, const 
 cudaError_t launch_l1(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
                       const loda_selection&, const SelectWorkspace&, const AppendArgs&, cudaStream_t);
 cudaError_t launch_l2(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
-                      const loda_selection&, const SelectWorkspace&, uint32_t*, cudaStream_t);
+                      const loda_selection&, const SelectWorkspace&, uint32_t*, bool, cudaStream_t);
 int l1_score_stride(const loda_geometry&);
 cudaError_t launch_attn(const loda_geometry&, const loda_layer&, const void*, const int32_t*, const int32_t*,
-                        const int32_t*, int, int, float, void*, float*, const AttnWorkspace&, bool, cudaStream_t);
+                        const int32_t*, int, int, float, void*, float*, const AttnWorkspace&, bool, bool, cudaStream_t);
 size_t l1_smem_bytes(const loda_geometry&);
 size_t l2_smem_bytes(const loda_geometry&);
 int attn_nsplit(const loda_geometry&, int);
@@ -251,7 +251,8 @@ int loda_select_step(const loda_geometry* g, const loda_layer* layer, const loda
   const SelectWorkspace ws = select_ws(*g, workspace);
   const AppendArgs ap{(const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, slots, status, 1};
   LODA_TRY(check_cuda(launch_l1(*g, *layer, *b, q, scale, *sel, ws, ap, (cudaStream_t)stream), "select_step/l1"));
-  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, ws, status, (cudaStream_t)stream), "select_step/l2");
+  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, ws, status, /*chained=*/true, (cudaStream_t)stream),
+                    "select_step/l2");
 }
 
 int loda_select_l2(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
@@ -264,14 +265,16 @@ int loda_select_l2(const loda_geometry* g, const loda_layer* layer, const loda_b
     return fail(LODA_ERR_ARGUMENT, "L2 needs q, gather, visible_lens and the workspace L1 ran on");
   if ((sel->middle == nullptr) != (sel->middle_counts == nullptr))
     return fail(LODA_ERR_ARGUMENT, "middle and middle_counts must be given together");
-  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, select_ws(*g, workspace), status, (cudaStream_t)stream),
+  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, select_ws(*g, workspace), status, /*chained=*/false,
+                              (cudaStream_t)stream),
                     "select_l2");
 }
 
-int loda_gather_attend_lse(const loda_geometry* g, const loda_layer* layer, const void* q, const int32_t* gather,
-                           const int32_t* visible_lens, const int32_t* query_to_req, int32_t n_query,
-                           int32_t n_req_rows, float scale, void* out, float* lse, void* workspace,
-                           void* stream) {
+// chained: the launch directly follows the selector launches of the same call
+static int gather_attend_impl(const loda_geometry* g, const loda_layer* layer, const void* q, const int32_t* gather,
+                              const int32_t* visible_lens, const int32_t* query_to_req, int32_t n_query,
+                              int32_t n_req_rows, float scale, void* out, float* lse, void* workspace,
+                              bool chained, void* stream) {
   LODA_TRY(check_gather_attend_args(g, layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, out));
   if (n_query == 0) return LODA_OK;
   if (!workspace) return fail(LODA_ERR_ARGUMENT, "gather attention needs a workspace");
@@ -280,15 +283,23 @@ int loda_gather_attend_lse(const loda_geometry* g, const loda_layer* layer, cons
   const AttnWorkspace ws{(int*)(base + w.at_ticket), (float*)(base + w.at_m), (float*)(base + w.at_z),
                          (float*)(base + w.at_o)};
   return check_cuda(launch_attn(*g, *layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale,
-                                out, lse, ws, /*allow_cluster=*/true, (cudaStream_t)stream),
+                                out, lse, ws, /*allow_cluster=*/true, chained, (cudaStream_t)stream),
                     "gather_attend");
+}
+
+int loda_gather_attend_lse(const loda_geometry* g, const loda_layer* layer, const void* q, const int32_t* gather,
+                           const int32_t* visible_lens, const int32_t* query_to_req, int32_t n_query,
+                           int32_t n_req_rows, float scale, void* out, float* lse, void* workspace,
+                           void* stream) {
+  return gather_attend_impl(g, layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale, out, lse,
+                            workspace, /*chained=*/false, stream);
 }
 
 int loda_gather_attend(const loda_geometry* g, const loda_layer* layer, const void* q, const int32_t* gather,
                        const int32_t* visible_lens, const int32_t* query_to_req, int32_t n_query,
                        int32_t n_req_rows, float scale, void* out, void* workspace, void* stream) {
-  return loda_gather_attend_lse(g, layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale, out,
-                                nullptr, workspace, stream);
+  return gather_attend_impl(g, layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale, out,
+                            nullptr, workspace, /*chained=*/false, stream);
 }
 
 int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
@@ -296,8 +307,9 @@ int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda
                      const loda_selection* sel, const int32_t* query_to_req, void* out, uint32_t* status,
                      void* workspace, void* stream) {
   LODA_TRY(loda_select_step(g, layer, b, q, k_new, v_new, slots, scale, sel, status, workspace, stream));
-  return loda_gather_attend(g, layer, q, sel->gather, sel->visible_lens, query_to_req, b->batch,
-                            g->max_requests, scale, out, workspace, stream);
+  if (b->batch == 0) return LODA_OK;
+  return gather_attend_impl(g, layer, q, sel->gather, sel->visible_lens, query_to_req, b->batch, g->max_requests,
+                            scale, out, nullptr, workspace, /*chained=*/true, stream);
 }
 
 }  // extern "C"

@@ -136,6 +136,12 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
     if (tid < 32) append_row<DSUB>(g, L, B, ap.k_new, ap.v_new, ap.slots, ap.status, b, kv, tid);
     return;
   }
+  // this thread's first query element is requested before anything that depends on the
+  // request's length, so that the two global round trips overlap
+  const int nq = G * DSUB;
+  float q_first = 0.0f;
+  if (tid < nq)
+    q_first = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + tid / DSUB) * g.head_dim + sub_dim(g, tid % DSUB)]);
   const long long act = B.active_req_ids[b];
   const int len_raw = B.lengths[b];
   const int req = (int)B.valid_req_ids[b];
@@ -166,9 +172,10 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
     cp_async_commit();
     if (it == 0) {
       // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
-      for (int i = tid; i < G * DSUB; i += P) {
+      for (int i = tid; i < nq; i += P) {
         const int j = i / DSUB, d = i % DSUB;
-        const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, d)]);
+        const float qv = i == tid ? q_first
+                                  : __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, d)]);
         const float qh = bf16r(__fmul_rn(qv, scale));
         qhat[i] = qh;
         qlow[i] = fminf(qh, 0.0f);
@@ -235,20 +242,36 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   uint16_t* scf = (uint16_t*)rows;                       // up to 40 KB
   uint16_t* scn = (uint16_t*)(rows + 40 * 1024);         // L1_NEAR_CAP scores
   {
+    // all the loads of a batch are issued before the first is used (one round trip, not one per load)
     const uint4* src = (const uint4*)row_scores;         // 8 scores per load; unscored pages hold 0
-    for (int c = tid; c < (n_far + 7) / 8; c += P) {
-      uint32_t v[8];
-      unpack_u16x8(__ldcg(src + c), v);
+    const int nc_far = (n_far + 7) / 8, nc_near = (n_near + 7) / 8;          // nc_near <= L1_NEAR_CAP / 8 <= P
+    uint4 nreg = make_uint4(0u, 0u, 0u, 0u);
+    if (tid < nc_near) nreg = __ldcg(src + near_lo8 / 8 + tid);
+    for (int c0 = 0; c0 < nc_far; c0 += 4 * P) {
+      uint4 f[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { const int i = c * 8 + j; v[j] = (i >= far_lo && i < far_hi) ? v[j] : 0u; }
-      ((uint4*)scf)[c] = make_uint4(v[0] | v[1] << 16, v[2] | v[3] << 16, v[4] | v[5] << 16, v[6] | v[7] << 16);
+      for (int k = 0; k < 4; ++k) {
+        const int c = c0 + k * P + tid;
+        f[k] = c < nc_far ? __ldcg(src + c) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = c0 + k * P + tid;
+        if (c < nc_far) {
+          uint32_t v[8];
+          unpack_u16x8(f[k], v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { const int i = c * 8 + j; v[j] = (i >= far_lo && i < far_hi) ? v[j] : 0u; }
+          ((uint4*)scf)[c] = make_uint4(v[0] | v[1] << 16, v[2] | v[3] << 16, v[4] | v[5] << 16, v[6] | v[7] << 16);
+        }
+      }
     }
-    for (int c = tid; c < (n_near + 7) / 8; c += P) {
+    if (tid < nc_near) {
       uint32_t v[8];
-      unpack_u16x8(__ldcg(src + near_lo8 / 8 + c), v);
+      unpack_u16x8(nreg, v);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { const int i = near_lo8 + c * 8 + j; v[j] = (i >= near_lo && i < near_hi) ? v[j] : 0u; }
-      ((uint4*)scn)[c] = make_uint4(v[0] | v[1] << 16, v[2] | v[3] << 16, v[4] | v[5] << 16, v[6] | v[7] << 16);
+      for (int j = 0; j < 8; ++j) { const int i = near_lo8 + tid * 8 + j; v[j] = (i >= near_lo && i < near_hi) ? v[j] : 0u; }
+      ((uint4*)scn)[tid] = make_uint4(v[0] | v[1] << 16, v[2] | v[3] << 16, v[4] | v[5] << 16, v[6] | v[7] << 16);
     }
   }
   __syncthreads();

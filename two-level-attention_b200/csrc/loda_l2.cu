@@ -71,7 +71,7 @@ template <int DSUB, int NT>
 __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, loda_layer L, loda_batch B,
                                                  const bf16* __restrict__ q, float scale,
                                                  loda_selection S, SelectWorkspace ws, uint32_t* status,
-                                                 int nsplit) {
+                                                 int nsplit, int chained) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int np_max = g.k_far + g.k_near + 2;
   const int K2 = g.level2_topk;
@@ -104,23 +104,27 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
   const int32_t* table = L.block_table + (size_t)req * g.max_blocks;
 
   // ---- grouped query on the subspace ---------------------------------------
-  if (tid < DSUB) {
-    float acc = 0.0f;
-    for (int j = 0; j < G; ++j) {
-      const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, tid)]);
-      acc = __fadd_rn(acc, bf16r(__fmul_rn(qv, scale)));
+  // It depends only on inputs of the step.  Chained behind the L1 launch of the same call
+  // (which reads the query after its own wait) it is computed before this launch's wait;
+  // a launch that stands alone computes it after.
+  auto group_query = [&]() {
+    if (tid < DSUB) {
+      float acc = 0.0f;
+      for (int j = 0; j < G; ++j) {
+        const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, tid)]);
+        acc = __fadd_rn(acc, bf16r(__fmul_rn(qv, scale)));
+      }
+      qf[tid] = acc;
     }
-    qf[tid] = acc;
-  }
-  __syncthreads();
-
-  // everything above depends only on inputs of the step; the page list below is
-  // produced by the preceding L1 launch
+  };
+  if (chained) group_query();
   LODA_PHASE(l2, cta_id, 1);
   pdl_wait();
 #if LODA_PDL_TRIGGER == 0
   pdl_launch_dependents();
 #endif
+  if (!chained) group_query();
+  __syncthreads();
   LODA_PHASE(l2, cta_id, 2);
 
   const int np = min(__ldcg(ws.np + row), np_max);
@@ -311,7 +315,7 @@ size_t l2_smem_bytes(const loda_geometry& g) {
 template <int DS>
 static cudaError_t launch_l2_d(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                float scale, const loda_selection& S, const SelectWorkspace& ws, uint32_t* status,
-                               cudaStream_t st) {
+                               bool chained, cudaStream_t st) {
   // scoring CTAs per row: 8 at batch 1 (latency), one once the rows alone give every SM a CTA
   // (every CTA of a row pays the ticket; the row's selection runs in one CTA either way)
   const int rows = B.batch * g.num_kv_heads;
@@ -322,16 +326,16 @@ static cudaError_t launch_l2_d(const loda_geometry& g, const loda_layer& L, cons
   cudaError_t e = set_kernel_smem(l2_kernel<DS, L2_NT>, smem);
   if (e != cudaSuccess) return e;
   return launch_pdl(l2_kernel<DS, L2_NT>, grid, dim3(L2_NT), smem, st, g, L, B, (const bf16*)q, scale, S, ws, status,
-                    nsplit);
+                    nsplit, (int)chained);
 }
 
 cudaError_t launch_l2(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                       float scale, const loda_selection& S, const SelectWorkspace& ws, uint32_t* status,
-                      cudaStream_t st) {
+                      bool chained, cudaStream_t st) {
   switch (g.sub_dims) {
-    case 16: return launch_l2_d<16>(g, L, B, q, scale, S, ws, status, st);
-    case 32: return launch_l2_d<32>(g, L, B, q, scale, S, ws, status, st);
-    case 64: return launch_l2_d<64>(g, L, B, q, scale, S, ws, status, st);
+    case 16: return launch_l2_d<16>(g, L, B, q, scale, S, ws, status, chained, st);
+    case 32: return launch_l2_d<32>(g, L, B, q, scale, S, ws, status, chained, st);
+    case 64: return launch_l2_d<64>(g, L, B, q, scale, S, ws, status, chained, st);
     default: return cudaErrorInvalidValue;
   }
 }
