@@ -345,6 +345,65 @@ def batched_arm(torch, capi, lib, dev, seed, barrier):
             "chain_hbm_frac_of_8TBs": tot_bytes / (us_layer * 1e-6) / 8e12}
 
 
+def tls_chain_arm(torch, dev, warm=10, iters=100):
+    """The prototype chain on a contiguous cache at the shape of the reference's own micro-benchmark
+    (benchmark/efficiency/benchmark_mha_kernel.py:21-37): batch 4, 4 query heads on 1 KV head, D 128,
+    131 072 tokens, 64-token blocks, cmp ratio 4, level-1 top 128 blocks, level-2 top 1 024 tokens, 3
+    sliding blocks; level 1 -> level 2 -> sparse attention timed together (each feeds the next), and
+    the dense attention over the whole cache beside it.  Random bf16 tensors as in that script."""
+    ops = mod("tls_attn.ops")
+    batch, hq, hkv, d, s, block, cmp, k1, k2, sliding = 4, 4, 1, 128, 131072, 64, 4, 128, 1024, 3
+    g = torch.Generator(device=dev).manual_seed(0)
+    rn = lambda *shape: torch.randn(*shape, dtype=torch.bfloat16, device=dev, generator=g)
+    q, k, v = rn(batch, 1, hq, d), rn(batch, s, hkv, d), rn(batch, s, hkv, d)
+    lengths = torch.full((batch,), s, dtype=torch.int32, device=dev)
+    l1q, kmin, kmax = rn(batch, 1, hq, d), rn(batch, s // block, hkv, d), rn(batch, s // block, hkv, d)
+    l1_scores = torch.full((batch, hkv, s // block), float("-inf"), dtype=torch.float32, device=dev)
+    l1_ts = torch.zeros((batch, hkv, k1), dtype=torch.float32, device=dev)
+    l1_ti = torch.zeros((batch, hkv, k1), dtype=torch.int32, device=dev)
+    l1_len = lengths // block
+    l2q, l2k = rn(batch, 1, hq, d // cmp), rn(batch, s, hkv, d // cmp)
+    l2_scores = torch.full((batch, hkv, k1 * block), float("-inf"), dtype=torch.float32, device=dev)
+    l2_idx = torch.full((batch, hkv, k1 * block), -1, dtype=torch.int32, device=dev)
+    l2_cm = torch.full((batch, hkv, k1 * block), float("-inf"), dtype=torch.float32, device=dev)
+    l2_ts = torch.zeros((batch, hkv, k2), dtype=torch.float32, device=dev)
+    l2_ti = torch.zeros((batch, hkv, k2), dtype=torch.int32, device=dev)
+    o = torch.zeros(batch, 1, hq, d, dtype=torch.bfloat16, device=dev)
+    lvl1 = ops.MHAIndexerLevel1Interface(hq, hkv, d, k1, sliding)
+    lvl2 = ops.MHAIndexerLevel2Interface(hq, hkv, d // cmp, k1, k2, block, sliding)
+    sparse = ops.SparseMHAInterface(hq, hkv, d, d, k2)
+    dense = ops.MHAInterface(hq, hkv, d, d)
+
+    def chain():
+        lvl1.forward_with_buffer(l1q, kmin, kmax, l1_len, l1_scores, l1_ts, l1_ti)
+        lvl2.forward_with_buffer(l2q, l2k, l1_ti, lengths, l2_scores, l2_idx, l2_cm, l2_ts, l2_ti)
+        sparse.forward_with_buffer(q, k, v, l2_ti, o)
+
+    def timed(fn):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    out = {"workload": "tls_attn chain: batch 4, 4q/1kv heads, d128, 131072 tokens, block 64, cmp 4, K1 128, K2 1024, "
+                       "3 sliding blocks (the reference micro-benchmark's shape)",
+           "sparse_chain_ms": timed(chain),
+           "level1_ms": timed(lambda: lvl1.forward_with_buffer(l1q, kmin, kmax, l1_len, l1_scores, l1_ts, l1_ti)),
+           "level2_ms": timed(lambda: lvl2.forward_with_buffer(l2q, l2k, l1_ti, lengths, l2_scores, l2_idx, l2_cm,
+                                                               l2_ts, l2_ti)),
+           "sparse_mha_ms": timed(lambda: sparse.forward_with_buffer(q, k, v, l2_ti, o)),
+           "dense_mha_ms": timed(lambda: dense.forward_with_buffer(q, k, v, lengths, o)),
+           "iters": iters, "warmup": warm}
+    torch.cuda.synchronize()
+    return out
+
+
 def cpu_baseline(sample_steps=3, threads=1):
     """One layer of the workload on the host cores with the CPU oracle (index
     prebuilt, as the reference maintains its page statistics incrementally)."""
@@ -411,6 +470,7 @@ def main():
     ap.add_argument("--skip-dense", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-batched", action="store_true")
+    ap.add_argument("--skip-tls", action="store_true")
     ap.add_argument("--shard", default="request", choices=("request", "kvhead"),
                     help="multi-GPU partition: one independent request shard per GPU (weak scaling, default) "
                          "or the KV-head groups of ONE request split over the GPUs (strong scaling)")
@@ -535,6 +595,9 @@ def main():
             line["batched"] = batched_arm(torch, capi, lib, dev, 5, lambda: torch.cuda.synchronize())
         if kvhead:
             line.pop("batched", None)
+        if not args.skip_tls and not kvhead and world == 1:
+            torch.cuda.empty_cache()
+            line["tls_chain"] = tls_chain_arm(torch, dev)
         if not args.skip_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(sample_steps=3)
         print(json.dumps(line), flush=True)

@@ -259,6 +259,58 @@ int loda_tia_scores(const void* q, const void* kmin, const void* kmax, const voi
                     void* coarse, void* fine, int32_t Hq, int32_t Hkv, int32_t D, int32_t T,
                     int32_t S, float scale, int32_t dtype, void* stream);
 
+/* ---- the prototype chain on a contiguous KV cache (tls_attn/ops) ---------------
+ * All tensors bf16 unless stated, caches [max_batch, max_seqlen, Hkv, D] token-major
+ * as in the reference; scores fp32; indices int32. */
+
+/* decode = 0: cache[b, s] = x[b, offsets[b] + s] for s < seqlen - offsets[b], for
+ * k [batch, seqlen, Hkv, dim_k] and v [.., dim_v]; decode = 1: x is [batch, 1, Hkv, D]
+ * and lands at cache[b, lengths[b] - 1].  Replaces MHAStoreKVInterface.prefill_forward /
+ * decode_forward (tls_attn/ops/mha_store_kv.py:123-141). */
+int loda_tls_store_kv(const void* k, const void* v, const int32_t* offsets_or_lengths,
+                      void* k_cache, void* v_cache, int32_t batch, int32_t seqlen,
+                      int32_t max_seqlen, int32_t num_kv_heads, int32_t dim_k, int32_t dim_v,
+                      int32_t decode, void* stream);
+
+/* Index of the keys: per block of `block` tokens the min and max over the tokens of the
+ * full key (l1_min, l1_max [max_batch, l1_len, Hkv, dim_k]; a ragged last block is padded
+ * with zeros) and per token the tail sub-dimensions [D/2 - c, D/2) ++ [D - c, D),
+ * c = D / 2 / cmp_ratio (l2_k [max_batch, l2_len, Hkv, 2c]).  decode = 0: k is
+ * [batch, src_len, Hkv, dim_k], tokens from offsets[b] on are indexed at positions 0..;
+ * decode = 1: k is the cache [max_batch, src_len, Hkv, dim_k], the token lengths[b] - 1
+ * is indexed (its block's min / max only when it completes the block).  Replaces
+ * MHAStoreKIndexInterface.prefill_forward / decode_forward
+ * (tls_attn/ops/mha_store_k_index.py:167-185). */
+int loda_tls_store_k_index(const void* k, const int32_t* offsets_or_lengths, void* l1_min,
+                           void* l1_max, void* l2_k, int32_t batch, int32_t src_len,
+                           int32_t num_kv_heads, int32_t dim_k, int32_t block, int32_t cmp_ratio,
+                           int32_t l1_len, int32_t l2_len, int32_t decode, void* stream);
+
+/* scores [batch, Hkv, max_length] = sum over the group's heads of max(q s, 0) . k_max +
+ * min(q s, 0) . k_min per block (q [batch, 1, Hq, dim_k]; q s rounded to bf16; lengths in
+ * blocks), -inf from lengths[b] - sliding_blocks on; then the topk best blocks, sorted
+ * (score descending, lower block first), missing entries (-inf, -1).  Replaces
+ * MHAIndexerLevel1Interface.forward_with_buffer (tls_attn/ops/mha_indexer_level1.py:237-249). */
+int loda_tls_level1(const void* q, const void* k_min, const void* k_max, const int32_t* lengths,
+                    float* scores, float* topk_scores, int32_t* topk_indices, int32_t batch,
+                    int32_t num_heads, int32_t num_kv_heads, int32_t dim_k, int32_t l1_len,
+                    int32_t max_length, int32_t topk, int32_t sliding_blocks, float scaling,
+                    void* stream);
+
+/* For every token of the blocks block_indices [batch, Hkv, level1_topk] (-1 = hole):
+ * scores = sum over the group's heads of exp(s_g - M), s_g = (q_g s) . k_token on the
+ * sub-dimensions (k [max_batch, k_len, Hkv, dim_k]), M the maximum over the row; indices =
+ * token ids (-1 for holes); cummax_scores (may be NULL) is filled with M.  Then the
+ * level2_topk best tokens, the tokens of the last sliding_blocks blocks of the sequence
+ * (lengths in tokens) first with score +inf.  Replaces
+ * MHAIndexerLevel2Interface.forward_with_buffer (tls_attn/ops/mha_indexer_level2.py:277-290). */
+int loda_tls_level2(const void* q, const void* k, const int32_t* block_indices,
+                    const int32_t* lengths, float* scores, float* cummax_scores, int32_t* indices,
+                    float* topk_scores, int32_t* topk_indices, int32_t batch, int32_t num_heads,
+                    int32_t num_kv_heads, int32_t dim_k, int32_t k_len, int32_t level1_topk,
+                    int32_t level2_topk, int32_t block, int32_t sliding_blocks, float scaling,
+                    void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -52,7 +52,8 @@ class Selection(C.Structure):
 EXPORTS = ("loda_version", "loda_last_error", "loda_workspace_bytes", "loda_append_decode",
            "loda_write_prefill", "loda_build_index", "loda_select_l1", "loda_select_l2",
            "loda_gather_attend", "loda_decode_step", "loda_gather_attend_static",
-           "loda_select_step", "loda_tia_quant4", "loda_tia_block_minmax", "loda_tia_scores", "loda_gather_attend_lse")
+           "loda_select_step", "loda_tia_quant4", "loda_tia_block_minmax", "loda_tia_scores", "loda_gather_attend_lse",
+           "loda_tls_store_kv", "loda_tls_store_k_index", "loda_tls_level1", "loda_tls_level2")
 
 _lib = None
 
@@ -87,6 +88,10 @@ def lib():
     L.loda_tia_block_minmax.argtypes = [P, P, P, I, I, I, I, I, V]
     L.loda_tia_scores.argtypes = [P, P, P, P, P, P, I, I, I, I, I, F, I, V]
     L.loda_decode_step.argtypes = [G, LY, B, P, P, P, P, F, S, P, P, P, P, V]
+    L.loda_tls_store_kv.argtypes = [P, P, P, P, P, I, I, I, I, I, I, I, V]
+    L.loda_tls_store_k_index.argtypes = [P, P, P, P, P, I, I, I, I, I, I, I, I, I, V]
+    L.loda_tls_level1.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, V]
+    L.loda_tls_level2.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, V]
     for name in EXPORTS[3:]:
         getattr(L, name).restype = C.c_int
     _lib = L

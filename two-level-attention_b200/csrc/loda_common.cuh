@@ -98,13 +98,21 @@ __device__ __forceinline__ bool in_near_pool(const Regions& r, int t) {
   return true;
 }
 
+// Barrier of a thread group: BAR = 0 is the whole CTA (__syncthreads); BAR > 0 is the named
+// barrier BAR over the CTA's first NT threads, for routines that run on a part of a larger CTA.
+template <int NT, int BAR>
+__device__ __forceinline__ void group_sync() {
+  if constexpr (BAR == 0) __syncthreads();
+  else asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(NT) : "memory");
+}
+
 // ---------------------------------------------------------------------------
-// block-wide primitives (NT threads, all must call)
+// block-wide primitives (NT threads, all must call; BAR as in group_sync)
 // ---------------------------------------------------------------------------
 
 // Exclusive prefix sum of one int per thread; *total gets the block sum.
 // scratch: 33 ints of shared memory.
-template <int NT>
+template <int NT, int BAR = 0>
 __device__ __forceinline__ int block_exclusive_scan(int v, int* scratch, int* total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int incl = v;
@@ -113,9 +121,9 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* scratch, int* to
     int n = __shfl_up_sync(0xffffffffu, incl, o);
     if (lane >= o) incl += n;
   }
-  __syncthreads();
+  group_sync<NT, BAR>();
   if (lane == 31) scratch[warp] = incl;
-  __syncthreads();
+  group_sync<NT, BAR>();
   if (warp == 0) {
     int w = lane < NT / 32 ? scratch[lane] : 0;
     int wi = w;
@@ -127,7 +135,7 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* scratch, int* to
     scratch[lane] = wi - w;
     if (lane == 31) scratch[32] = wi;
   }
-  __syncthreads();
+  group_sync<NT, BAR>();
   *total = scratch[32];
   return scratch[warp] + incl - v;
 }
@@ -219,13 +227,13 @@ __device__ __forceinline__ int count_greater(const uint32_t* keys, int n4, uint3
 // exclusive scan of one flag per thread: ballot inside the warp, per-warp totals
 // through shared memory, one barrier.  wtot: 2 x 32 ints (16-byte aligned), the
 // caller alternates `buf` between back-to-back calls.
-template <int NT>
+template <int NT, int BAR = 0>
 __device__ __forceinline__ int block_flag_scan(bool flag, int* wtot, int buf, int* total) {
   constexpr int NW = NT / 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const unsigned bal = __ballot_sync(0xffffffffu, flag);
   if (lane == 0) wtot[buf * 32 + warp] = __popc(bal);
-  __syncthreads();
+  group_sync<NT, BAR>();
   int before = 0, all = 0;
 #pragma unroll
   for (int w = 0; w < NW; ++w) {
@@ -238,12 +246,12 @@ __device__ __forceinline__ int block_flag_scan(bool flag, int* wtot, int buf, in
 }
 
 // sum of one int per thread: redux, per-warp column, one barrier (same buffers)
-template <int NT>
+template <int NT, int BAR = 0>
 __device__ __forceinline__ int block_sum_cols(int v, int* wtot, int buf) {
   constexpr int NW = NT / 32;
   const int r = __reduce_add_sync(0xffffffffu, v);
   if ((threadIdx.x & 31) == 0) wtot[buf * 32 + (threadIdx.x >> 5)] = r;
-  __syncthreads();
+  group_sync<NT, BAR>();
   const int4* col = (const int4*)(wtot + buf * 32);
   int s = 0;
 #pragma unroll
@@ -310,7 +318,7 @@ __device__ __forceinline__ int block_rank_topk_pair(const uint16_t* sc, int n, i
 // strictly above `thr` and the first `rem` scores equal to it (`all`: every scored
 // element).  Blocked layout (ept consecutive scores per thread), one shuffle scan.
 // wtot: 32 ints.  Returns all ? nvalid : k.
-template <int NT>
+template <int NT, int BAR = 0>
 __device__ __forceinline__ int block_compact_threshold(const uint16_t* sc, int n, int k, uint32_t thr, int rem, bool all,
                                                        int nvalid, int* out, int* wtot) {
   constexpr int NW = NT / 32;
@@ -333,9 +341,9 @@ __device__ __forceinline__ int block_compact_threshold(const uint16_t* sc, int n
     const int nb = __shfl_up_sync(0xffffffffu, incl, o);
     if (lane >= o) incl += nb;
   }
-  __syncthreads();                             // the columns may still be read by slower warps
+  group_sync<NT, BAR>();                             // the columns may still be read by slower warps
   if (lane == 31) wtot[warp] = incl;
-  __syncthreads();
+  group_sync<NT, BAR>();
   int before = 0;
 #pragma unroll
   for (int w = 0; w < NW; ++w) before += w < warp ? wtot[w] : 0;
@@ -352,7 +360,7 @@ __device__ __forceinline__ int block_compact_threshold(const uint16_t* sc, int n
       else if (!all && v[j] == thr) { if (tb < rem) out[pos++] = i; ++tb; }
     }
   }
-  __syncthreads();
+  group_sync<NT, BAR>();
   return all ? nvalid : k;
 }
 
@@ -366,7 +374,7 @@ __device__ __forceinline__ int block_compact_threshold(const uint16_t* sc, int n
 // every thread counts its scores at or above three candidate thresholds (independent
 // chains), one barrier publishes the block sums.
 // wtot: 6 x 32 ints (16-byte aligned).
-template <int NT>
+template <int NT, int BAR = 0>
 __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int k, int* out, int* wtot) {
   constexpr int NW = NT / 32;
   constexpr int MAXC = 4;                        // chunks a thread keeps in registers
@@ -414,7 +422,7 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
       wtot[(buf * 3 + 1) * 32 + warp] = c2;
       wtot[(buf * 3 + 2) * 32 + warp] = c3;
     }
-    __syncthreads();
+    group_sync<NT, BAR>();
     int s[3] = {0, 0, 0};
 #pragma unroll
     for (int q = 0; q < 3; ++q) {
@@ -429,7 +437,7 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
   };
   LODA_SUB(0);
   for (int i = tid; i < 6 * 32; i += NT) wtot[i] = 0;      // columns of absent warps stay 0
-  __syncthreads();
+  group_sync<NT, BAR>();
   LODA_SUB(1);
   // scored elements, their maximum, and 0xFFFF - their minimum (so that empty columns, 0, are neutral)
   int nvalid;
@@ -462,7 +470,7 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
       wtot[1 * 32 + warp] = (int)mx;
       wtot[2 * 32 + warp] = (int)mi;
     }
-    __syncthreads();
+    group_sync<NT, BAR>();
     int a = 0, b = 0, c = 0;
 #pragma unroll
     for (int w4 = 0; w4 < (NW + 3) / 4; ++w4) {
@@ -478,7 +486,7 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
     smin = 0xFFFFu - (uint32_t)c;
   }
   LODA_SUB(2);
-  if (k <= 0 || nvalid == 0) { __syncthreads(); return 0; }
+  if (k <= 0 || nvalid == 0) { group_sync<NT, BAR>(); return 0; }
   const bool all = nvalid <= k;
   uint32_t thr = 1u;     // keep v >= thr ...
   int rem = 0;           // ... but of those equal to thr only the first `rem` (all == true: everything scored)
@@ -509,7 +517,7 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
     rem = k - gt;
     LODA_SUB(11);
   }
-  if (!in_regs) return block_compact_threshold<NT>(sc, n, k, thr, rem, all, nvalid, out, wtot);
+  if (!in_regs) return block_compact_threshold<NT, BAR>(sc, n, k, thr, rem, all, nvalid, out, wtot);
   // Compaction from the registers, in index order: consecutive threads hold consecutive
   // chunks of a slot, so one scan over the threads per slot places its survivors (strictly
   // above the threshold, then the first `rem` scores equal to it).
@@ -530,7 +538,7 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
       if (lane >= o) incl += nb;
     }
     if (lane == 31) wtot[cbuf * 32 + warp] = incl;
-    __syncthreads();
+    group_sync<NT, BAR>();
     int before = 0, tot = 0;
 #pragma unroll
     for (int w4 = 0; w4 < (NW + 3) / 4; ++w4) {
@@ -558,9 +566,9 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
     base_gt += tot & 0xFFFF;
     base_tie += tot >> 16;
   };
-  __syncthreads();                               // the columns may still be read by slower warps
+  group_sync<NT, BAR>();                               // the columns may still be read by slower warps
   if (tid < 64) wtot[tid] = 0;                   // two rows of per-warp totals; absent warps stay 0
-  __syncthreads();
+  group_sync<NT, BAR>();
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
     if (c < nslots) {
@@ -574,7 +582,7 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
     const uint32_t v[8] = {xtra, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
     place(v, full * NT * 8 + tid);
   }
-  __syncthreads();
+  group_sync<NT, BAR>();
   LODA_SUB(13);
   return all ? nvalid : k;
 }

@@ -23,79 +23,11 @@
 // head order, divided by G and rounded to bf16.  bf16 x bf16 products are exact
 // in fp32, so fmaf equals a separate multiply and add here.
 #include "loda_append.cuh"
+#include "loda_select.cuh"
 
 namespace loda {
 
-__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
-  f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xFFFF0000u);
-  f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xFFFF0000u);
-  f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xFFFF0000u);
-  f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xFFFF0000u);
-}
-
-// tree over NC chunk sums (NC a power of two), adjacent pairs first
-template <int NC>
-__device__ __forceinline__ float chunk_tree(float (&p)[NC]) {
-#pragma unroll
-  for (int w = 1; w < NC; w <<= 1) {
-#pragma unroll
-    for (int i = 0; i + w < NC; i += 2 * w) p[i] = __fadd_rn(p[i], p[i + w]);
-  }
-  return p[0];
-}
-
-// canonical dot of DSUB register values with DSUB floats in shared memory
-template <int DSUB>
-__device__ __forceinline__ float dot_chunks(const float (&k)[DSUB], const float* qv) {
-  constexpr int NC = DSUB / 8;
-  float p[NC];
-#pragma unroll
-  for (int c = 0; c < NC; ++c) {
-    const float4 q0 = *(const float4*)(qv + c * 8);
-    const float4 q1 = *(const float4*)(qv + c * 8 + 4);
-    float a = 0.0f;
-    a = fmaf(k[8 * c + 0], q0.x, a); a = fmaf(k[8 * c + 1], q0.y, a);
-    a = fmaf(k[8 * c + 2], q0.z, a); a = fmaf(k[8 * c + 3], q0.w, a);
-    a = fmaf(k[8 * c + 4], q1.x, a); a = fmaf(k[8 * c + 5], q1.y, a);
-    a = fmaf(k[8 * c + 6], q1.z, a); a = fmaf(k[8 * c + 7], q1.w, a);
-    p[c] = a;
-  }
-  return chunk_tree<NC>(p);
-}
-
 LODA_PHASE_STORAGE(l1)
-
-// the selecting CTA reuses the staging area: 40 KB for the far pool's scores (2 bytes per page)
-// and 1 KB for the near pool's
-constexpr size_t L1_TAIL_BYTES = 41 * 1024;
-constexpr int L1_NEAR_CAP = 512;     // scores of the near row (1 KB behind the 40 KB far row)
-
-// Rank the n kept pages of one pool best-first (score descending, lower id
-// first) and append fillers (lowest page ids not kept): the page-id lists the
-// reference selector exposes.  Optional output, used by parity checks.
-template <int NT>
-__device__ void emit_best_first(const int* kept, int n, int k, const uint16_t* sc, int32_t* out_ids,
-                                int32_t* out_n, int max_blocks) {
-  const int tid = threadIdx.x;
-  for (int i = tid; i < n; i += NT) {
-    const int id = kept[i];
-    const uint32_t key = ((uint32_t)sc[id] << 16) | (uint32_t)(0xFFFF - id);
-    int rank = 0;
-    for (int j = 0; j < n; ++j) {
-      const int idj = kept[j];
-      rank += (((uint32_t)sc[idj] << 16) | (uint32_t)(0xFFFF - idj)) > key;
-    }
-    out_ids[rank] = id;
-  }
-  for (int j = tid; j < k - n; j += NT) {   // kept[] is ascending: j-th smallest id not kept
-    int c = j;
-    for (int i = 0; i < n; ++i) {
-      if (kept[i] <= c) ++c; else break;
-    }
-    out_ids[n + j] = min(c, max_blocks - 1);
-  }
-  if (tid == 0) *out_n = n;
-}
 
 template <int DSUB, int P>
 __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, loda_batch B,
@@ -189,36 +121,8 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
 
     // one page per thread
     const int page = p0 + tid;
-    uint32_t ord = 0;
     const unsigned char* myrow = rows + (size_t)tid * ROWB;
-    const float gf = (float)G;
-    if (in_far_pool(rg, page)) {
-      float kmin[DSUB], kmax[DSUB];
-#pragma unroll
-      for (int c = 0; c < NC; ++c) {
-        unpack8(*(const uint4*)(myrow + c * 16), *(float(*)[8])(kmin + 8 * c));
-        unpack8(*(const uint4*)(myrow + (NC + c) * 16), *(float(*)[8])(kmax + 8 * c));
-      }
-      float acc = 0.0f;
-#pragma unroll 1
-      for (int j = 0; j < G; ++j) {
-        const float mm = __fadd_rn(dot_chunks<DSUB>(kmin, qlow + j * DSUB), dot_chunks<DSUB>(kmax, qhigh + j * DSUB));
-        acc = __fadd_rn(acc, bf16r(mm));
-      }
-      ord = ord16(bf16r(__fdiv_rn(acc, gf)));
-    } else if (in_near_pool(rg, page)) {
-      float kavg[DSUB];
-      const float bsf = (float)g.page;
-#pragma unroll
-      for (int c = 0; c < NC; ++c) unpack8(*(const uint4*)(myrow + c * 16), *(float(*)[8])(kavg + 8 * c));
-#pragma unroll
-      for (int i = 0; i < DSUB; ++i) kavg[i] = bf16r(__fdiv_rn(kavg[i], bsf));
-      float acc = 0.0f;
-#pragma unroll 1
-      for (int j = 0; j < G; ++j) acc = __fadd_rn(acc, bf16r(dot_chunks<DSUB>(kavg, qhat + j * DSUB)));
-      ord = ord16(bf16r(__fdiv_rn(acc, gf)));
-    }
-    if (ord == ORD16_NEG_INF) ord = 0;   // a -inf score never competes (it equals "not in the pool")
+    const uint32_t ord = l1_page_score<DSUB>(g, rg, page, myrow, qhat, qlow, qhigh, G);
     row_scores[page] = (uint16_t)ord;     // the selecting CTA reads pages below page_end (rounded up to 8)
   }
   LODA_PHASE(l1, cta_id, 4);
@@ -279,52 +183,9 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   pdl_launch_dependents();
 #endif
   LODA_PHASE(l1, cta_id, 6);
-  int np = 0;
-  const bool want_lists = out.i_far != nullptr;
-  if (rg.quota > 0 || want_lists) {
-    if (rg.quota > 0 && rg.sink_byp && rg.spl < rg.kt_eff) { if (tid == 0) kept[0] = rg.spl; np = 1; }
-    int* kept_near = kept + np + g.k_far;                // compacted below
-    int n_f = 0, n_n = 0;
-    if (n_far > far_lo) {
-      if (n_far <= P) {
-        n_f = block_rank_topk_small<P>(scf, n_far, g.k_far, kept + np, keys, wtot);
-      } else {
-        n_f = g.k_far <= 128 ? block_prefilter_topk<P>(scf, n_far, g.k_far, kept + np, keys, wtot, sh) : -1;
-        if (n_f < 0) n_f = block_bisect_topk<P>(scf, n_far, g.k_far, kept + np, wtot);   // heavily tied scores
-      }
-    }
-    if (n_near > 0) {
-      n_n = n_near <= P ? block_rank_topk_small<P>(scn, n_near, g.k_near, kept_near, keys, wtot)
-                        : block_rank_topk_pair<P>(scn, n_near, g.k_near, kept_near, keys, wtot);
-      for (int i = tid; i < n_n; i += P) kept_near[i] += near_lo8;
-      __syncthreads();
-    }
-#if LODA_PDL_TRIGGER == 1
-    pdl_launch_dependents();
-#endif
-    LODA_PHASE(l1, cta_id, 7);
-    if (want_lists) {
-      // best-first lists need the scores by page id: near scores go back beside the far ones
-      for (int i = near_lo + tid; i < near_hi; i += P) scf[i] = scn[i - near_lo8];
-      __syncthreads();
-      emit_best_first<P>(kept + np, n_f, g.k_far, scf, out.i_far + (size_t)row * g.k_far, out.n_far + row, g.max_blocks);
-      emit_best_first<P>(kept_near, n_n, g.k_near, scf, out.i_near + (size_t)row * g.k_near, out.n_near + row,
-                         g.max_blocks);
-      __syncthreads();
-    }
-    if (rg.quota > 0) {
-      // ascending list: [sink bypass] far... near... [window bypass]
-      const int v0 = tid < n_n ? kept_near[tid] : 0;     // k_near <= 2 P
-      const int v1 = tid + P < n_n ? kept_near[tid + P] : 0;
-      __syncthreads();
-      if (tid < n_n) kept[np + n_f + tid] = v0;
-      if (tid + P < n_n) kept[np + n_f + tid + P] = v1;
-      np += n_f + n_n;
-      if (rg.swa_byp) { if (tid == 0) kept[np] = rg.swa_byp_blk; ++np; }
-    }
-    __syncthreads();
-    LODA_PHASE(l1, cta_id, 8);
-  }
+  const int np = l1_select_pages<P, LODA_PDL_TRIGGER == 1>(g, rg, out, row, scf, scn, n_far, far_lo, n_near, near_lo,
+                                                           near_lo8, near_hi, kept, keys, wtot, sh);
+  LODA_PHASE(l1, cta_id, 8);
   // hand the ascending page list and its physical pages to the L2 launch
   const int np_max = g.k_far + g.k_near + 2;
   const int32_t* table = L.block_table + (size_t)req * g.max_blocks;

@@ -17,42 +17,9 @@
 // q_fine[d] is the fp32 sum over the GQA group (head order) of the bf16-rounded
 // scaled query; the logit is one left-to-right fp32 chain of separate multiplies
 // and adds over the d' dims, rounded to bf16.
-#include "loda_common.cuh"
+#include "loda_select.cuh"
 
 namespace loda {
-
-using bf16 = __nv_bfloat16;
-
-template <int DSUB>
-__device__ __forceinline__ float l2_logit(const uint8_t* __restrict__ codes, float scale, float zero,
-                                          const float* __restrict__ qf) {
-  constexpr int WORDS = DSUB / 8;   // 32-bit words of packed codes
-  uint32_t w[WORDS];
-  if constexpr (WORDS == 4) {
-    const uint4 u = *(const uint4*)codes;
-    w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
-  } else if constexpr (WORDS == 2) {
-    const uint2 u = *(const uint2*)codes;
-    w[0] = u.x; w[1] = u.y;
-  } else {
-#pragma unroll
-    for (int i = 0; i < WORDS; i += 4) {
-      const uint4 u = *(const uint4*)(codes + 4 * i);
-      w[i] = u.x; w[i + 1] = u.y; w[i + 2] = u.z; w[i + 3] = u.w;
-    }
-  }
-  float acc = 0.0f;
-#pragma unroll
-  for (int i = 0; i < WORDS; ++i) {
-#pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      const float c = (float)((w[i] >> (4 * n)) & 15u);
-      const float x = bf16r(__fsub_rn(bf16r(__fmul_rn(c, scale)), zero));
-      acc = __fadd_rn(acc, __fmul_rn(x, qf[8 * i + n]));
-    }
-  }
-  return bf16r(acc);
-}
 
 #ifndef LODA_L2_MINB
 #define LODA_L2_MINB 1     // resident CTAs per SM the register budget must allow (4 costs spills)
@@ -171,138 +138,9 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
   pdl_launch_dependents();
 #endif
   LODA_PHASE(l2, cta_id, 5);
-  const int quota = rg.quota;
-  int* slots_sel = mid_b;      // ascending candidate slots kept by the select
-  const int take = block_bisect_topk<NT>(sc, nitems, min(quota, K2), slots_sel, wtot);
-#if LODA_PDL_TRIGGER == 1
-  pdl_launch_dependents();
-#endif
-  LODA_PHASE(l2, cta_id, 6);
-  if (take == quota) {
-    // Common case: the quota is filled by scored candidates (all of them >= sink, no holes).
-    // The survivors' physical pages came with the page list, so only the sink and window ids
-    // need a block-table lookup: sink ++ middle ++ window, one pass.
-    const int cap = g.max_blocks * g.page;
-    const int sk = min(length, g.sink);
-    const int count_s = min(length, g.sink + g.swa) - sk;
-    const int s_lo = max(max(length - g.swa, 0), sk);
-    const int s_hi = min(length - g.swa + count_s, cap);
-    const int n_s = max(s_hi - s_lo, 0);
-    const int total = sk + take + n_s;
-    const int n_out = min(total, g.max_visible);
-    int32_t* gout = S.gather + ((size_t)b * g.num_kv_heads + kv) * g.max_visible;
-    for (int i = tid; i < n_out; i += NT) {
-      int slot;
-      if (i >= sk && i < sk + take) {
-        const int sl = slots_sel[i - sk];
-        slot = physs[sl / g.page] * g.page + sl % g.page;
-        if (S.middle != nullptr) S.middle[(size_t)row * K2 + (i - sk)] = pages[sl / g.page] * g.page + sl % g.page;
-      } else {
-        const int id = i < sk ? i : s_lo + (i - sk - take);
-        const int lp = id / g.page;
-        int ph = lp < g.max_blocks ? table[lp] : -1;
-        if (ph < 0 || ph >= g.num_pages) {
-          if (status) atomicOr(status, LODA_STATUS_BAD_PAGE);
-          ph = g.num_pages - 1;
-        }
-        slot = ph * g.page + id % g.page;
-      }
-      gout[i] = slot;
-    }
-    if (tid == 0) {
-      if (S.middle != nullptr) S.middle_counts[row] = take;
-      S.visible_lens[(size_t)b * g.num_kv_heads + kv] = n_out;
-      if (total > g.max_visible && status) atomicOr(status, LODA_STATUS_TRUNCATED);
-      ws.l2_ticket[row] = 0;
-    }
-    LODA_PHASE(l2, cta_id, 9);
-    return;
-  }
-  for (int i = tid; i < take; i += NT) {
-    const int sl = slots_sel[i];
-    mid_a[i] = pages[sl / g.page] * g.page + sl % g.page;
-  }
-  __syncthreads();
-  LODA_PHASE(l2, cta_id, 7);
-  int count = take;
-  int* mid = mid_a;
-
-  // ---- hole fill (nfa_layer_batch_selector.py:545-566) -------------------------
-  if (take < quota) {
-    const int need = quota - take;
-    // the holes are among the first `quota` ids of [lower, upper)
-    for (int i = tid; i < quota; i += NT) win[i] = 0;
-    __syncthreads();
-    int in_win = 0;
-    for (int i = tid; i < take; i += NT) {
-      const int w = mid_a[i] - rg.lower;
-      if (w < quota) { win[w] = 1; ++in_win; }
-    }
-    int cw;
-    block_exclusive_scan<NT>(in_win, scan, &cw);
-    const int ipt = (quota + NT - 1) / NT;
-    const int lo = min(tid * ipt, quota), hi = min(lo + ipt, quota);
-    int zeros = 0;
-    for (int w = lo; w < hi; ++w) zeros += win[w] == 0;
-    int ztotal;
-    int zrank = block_exclusive_scan<NT>(zeros, scan, &ztotal);
-    int keep = 0;
-    for (int w = lo; w < hi; ++w) {
-      if (win[w] == 0) { if (zrank < need) win[w] = 2; ++zrank; }
-      keep += win[w] != 0;
-    }
-    int ktotal;
-    int pos = block_exclusive_scan<NT>(keep, scan, &ktotal);
-    for (int w = lo; w < hi; ++w) {
-      if (win[w] != 0) mid_b[pos++] = rg.lower + w;
-    }
-    // chosen tokens beyond the window follow all holes
-    for (int i = cw + tid; i < take; i += NT) mid_b[ktotal + (i - cw)] = mid_a[i];
-    __syncthreads();
-    count = ktotal + (take - cw);
-    mid = mid_b;
-  }
-
-  // ---- drop ids below the sink (only holes can be there), ascending already ----
-  int below = 0;
-  for (int i = tid; i < min(count, g.sink); i += NT) below += mid[i] < g.sink;
-  int d0;
-  block_exclusive_scan<NT>(below, scan, &d0);
-  const int count_m = count - d0;
-  if (S.middle != nullptr) {
-    for (int i = tid; i < count_m; i += NT) S.middle[(size_t)row * K2 + i] = mid[d0 + i];
-    if (tid == 0) S.middle_counts[row] = count_m;
-  }
-
-  LODA_PHASE(l2, cta_id, 8);
-  // ---- union with sink and window ids (nfa_layer_batch_selector.py:1348-1437) --
-  const int cap = g.max_blocks * g.page;
-  const int sk = min(length, g.sink);
-  const int count_s = min(length, g.sink + g.swa) - sk;
-  const int s_lo = max(max(length - g.swa, 0), sk);
-  const int s_hi = min(length - g.swa + count_s, cap);
-  const int n_s = max(s_hi - s_lo, 0);
-  const int total = sk + count_m + n_s;
-  const int n_out = min(total, g.max_visible);
-  int32_t* gout = S.gather + ((size_t)b * g.num_kv_heads + kv) * g.max_visible;
-  for (int i = tid; i < n_out; i += NT) {
-    int id;
-    if (i < sk) id = i;
-    else if (i < sk + count_m) id = mid[d0 + i - sk];
-    else id = s_lo + (i - sk - count_m);
-    const int lp = id / g.page;
-    int ph = lp < g.max_blocks ? table[lp] : -1;
-    if (ph < 0 || ph >= g.num_pages) {
-      if (status) atomicOr(status, LODA_STATUS_BAD_PAGE);
-      ph = g.num_pages - 1;   // PAD page: zeros, never out of bounds
-    }
-    gout[i] = ph * g.page + id % g.page;
-  }
-  if (tid == 0) {
-    S.visible_lens[(size_t)b * g.num_kv_heads + kv] = n_out;
-    if (total > g.max_visible && status) atomicOr(status, LODA_STATUS_TRUNCATED);
-    ws.l2_ticket[row] = 0;
-  }
+  const L2Shared shm{sc, pages, physs, mid_a, mid_b, wtot, scan, win};
+  l2_select_and_write<NT, 0, LODA_PDL_TRIGGER == 1>(g, rg, S, status, table, b, kv, row, length, nitems, shm,
+                                                    ws.l2_ticket + row);
   LODA_PHASE(l2, cta_id, 9);
 }
 

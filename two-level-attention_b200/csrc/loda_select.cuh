@@ -1,0 +1,352 @@
+// Device pieces shared by the selector kernels: the canonical L1 page score, the L1 page
+// selection of the selecting CTA, the L2 logit on the packed 4-bit tail keys.
+#pragma once
+
+#include "loda_common.cuh"
+
+namespace loda {
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xFFFF0000u);
+  f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xFFFF0000u);
+  f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xFFFF0000u);
+  f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xFFFF0000u);
+}
+
+// tree over NC chunk sums (NC a power of two), adjacent pairs first
+template <int NC>
+__device__ __forceinline__ float chunk_tree(float (&p)[NC]) {
+#pragma unroll
+  for (int w = 1; w < NC; w <<= 1) {
+#pragma unroll
+    for (int i = 0; i + w < NC; i += 2 * w) p[i] = __fadd_rn(p[i], p[i + w]);
+  }
+  return p[0];
+}
+
+// canonical dot of DSUB register values with DSUB floats in shared memory
+template <int DSUB>
+__device__ __forceinline__ float dot_chunks(const float (&k)[DSUB], const float* qv) {
+  constexpr int NC = DSUB / 8;
+  float p[NC];
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const float4 q0 = *(const float4*)(qv + c * 8);
+    const float4 q1 = *(const float4*)(qv + c * 8 + 4);
+    float a = 0.0f;
+    a = fmaf(k[8 * c + 0], q0.x, a); a = fmaf(k[8 * c + 1], q0.y, a);
+    a = fmaf(k[8 * c + 2], q0.z, a); a = fmaf(k[8 * c + 3], q0.w, a);
+    a = fmaf(k[8 * c + 4], q1.x, a); a = fmaf(k[8 * c + 5], q1.y, a);
+    a = fmaf(k[8 * c + 6], q1.z, a); a = fmaf(k[8 * c + 7], q1.w, a);
+    p[c] = a;
+  }
+  return chunk_tree<NC>(p);
+}
+
+// Ordered 16-bit score of one logical page from its staged metadata row (min then max, or the
+// sum in the first half); 0 = the page is in neither pool or scores -inf.
+template <int DSUB>
+__device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const Regions& rg, int page,
+                                                  const unsigned char* myrow, const float* qhat, const float* qlow,
+                                                  const float* qhigh, int G) {
+  constexpr int NC = DSUB / 8;
+  uint32_t ord = 0;
+  const float gf = (float)G;
+  if (in_far_pool(rg, page)) {
+    float kmin[DSUB], kmax[DSUB];
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      unpack8(*(const uint4*)(myrow + c * 16), *(float(*)[8])(kmin + 8 * c));
+      unpack8(*(const uint4*)(myrow + (NC + c) * 16), *(float(*)[8])(kmax + 8 * c));
+    }
+    float acc = 0.0f;
+#pragma unroll 1
+    for (int j = 0; j < G; ++j) {
+      const float mm = __fadd_rn(dot_chunks<DSUB>(kmin, qlow + j * DSUB), dot_chunks<DSUB>(kmax, qhigh + j * DSUB));
+      acc = __fadd_rn(acc, bf16r(mm));
+    }
+    ord = ord16(bf16r(__fdiv_rn(acc, gf)));
+  } else if (in_near_pool(rg, page)) {
+    float kavg[DSUB];
+    const float bsf = (float)g.page;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) unpack8(*(const uint4*)(myrow + c * 16), *(float(*)[8])(kavg + 8 * c));
+#pragma unroll
+    for (int i = 0; i < DSUB; ++i) kavg[i] = bf16r(__fdiv_rn(kavg[i], bsf));
+    float acc = 0.0f;
+#pragma unroll 1
+    for (int j = 0; j < G; ++j) acc = __fadd_rn(acc, bf16r(dot_chunks<DSUB>(kavg, qhat + j * DSUB)));
+    ord = ord16(bf16r(__fdiv_rn(acc, gf)));
+  }
+  return ord == ORD16_NEG_INF ? 0u : ord;   // a -inf score never competes (it equals "not in the pool")
+}
+
+// the selecting CTA reuses the staging area: 40 KB for the far pool's scores (2 bytes per page)
+// and 1 KB for the near pool's
+constexpr size_t L1_TAIL_BYTES = 41 * 1024;
+constexpr int L1_NEAR_CAP = 512;     // scores of the near row (1 KB behind the 40 KB far row)
+
+// Rank the n kept pages of one pool best-first (score descending, lower id
+// first) and append fillers (lowest page ids not kept): the page-id lists the
+// reference selector exposes.  Optional output, used by parity checks.
+template <int NT>
+__device__ void emit_best_first(const int* kept, int n, int k, const uint16_t* sc, int32_t* out_ids,
+                                int32_t* out_n, int max_blocks) {
+  const int tid = threadIdx.x;
+  for (int i = tid; i < n; i += NT) {
+    const int id = kept[i];
+    const uint32_t key = ((uint32_t)sc[id] << 16) | (uint32_t)(0xFFFF - id);
+    int rank = 0;
+    for (int j = 0; j < n; ++j) {
+      const int idj = kept[j];
+      rank += (((uint32_t)sc[idj] << 16) | (uint32_t)(0xFFFF - idj)) > key;
+    }
+    out_ids[rank] = id;
+  }
+  for (int j = tid; j < k - n; j += NT) {   // kept[] is ascending: j-th smallest id not kept
+    int c = j;
+    for (int i = 0; i < n; ++i) {
+      if (kept[i] <= c) ++c; else break;
+    }
+    out_ids[n + j] = min(c, max_blocks - 1);
+  }
+  if (tid == 0) *out_n = n;
+}
+
+// The selecting CTA's work once the row's scores sit in shared memory, far pool in scf (pages
+// [0, n_far), zero outside the pool) and near pool in scn (pages [near_lo8, near_lo8 + n_near)):
+// exact top-k of each pool, the optional best-first lists, and the ascending page list
+// kept[0, np) = [sink bypass] far... near... [window bypass].  Returns np.  All P threads call.
+// TRIGGER: release the dependent launch after the two selections.
+template <int P, bool TRIGGER>
+__device__ __forceinline__ int l1_select_pages(const loda_geometry& g, const Regions& rg, const loda_selection& out,
+                                               int row, uint16_t* scf, uint16_t* scn, int n_far, int far_lo, int n_near,
+                                               int near_lo, int near_lo8, int near_hi, int* kept, uint32_t* keys,
+                                               int* wtot, int* sh) {
+  const int tid = threadIdx.x;
+  int np = 0;
+  const bool want_lists = out.i_far != nullptr;
+  if (rg.quota > 0 || want_lists) {
+    if (rg.quota > 0 && rg.sink_byp && rg.spl < rg.kt_eff) { if (tid == 0) kept[0] = rg.spl; np = 1; }
+    int* kept_near = kept + np + g.k_far;                // compacted below
+    int n_f = 0, n_n = 0;
+    if (n_far > far_lo) {
+      if (n_far <= P) {
+        n_f = block_rank_topk_small<P>(scf, n_far, g.k_far, kept + np, keys, wtot);
+      } else {
+        n_f = g.k_far <= 128 ? block_prefilter_topk<P>(scf, n_far, g.k_far, kept + np, keys, wtot, sh) : -1;
+        if (n_f < 0) n_f = block_bisect_topk<P>(scf, n_far, g.k_far, kept + np, wtot);   // heavily tied scores
+      }
+    }
+    if (n_near > 0) {
+      n_n = n_near <= P ? block_rank_topk_small<P>(scn, n_near, g.k_near, kept_near, keys, wtot)
+                        : block_rank_topk_pair<P>(scn, n_near, g.k_near, kept_near, keys, wtot);
+      for (int i = tid; i < n_n; i += P) kept_near[i] += near_lo8;
+      __syncthreads();
+    }
+    if (TRIGGER) pdl_launch_dependents();
+    if (want_lists) {
+      // best-first lists need the scores by page id: near scores go back beside the far ones
+      for (int i = near_lo + tid; i < near_hi; i += P) scf[i] = scn[i - near_lo8];
+      __syncthreads();
+      emit_best_first<P>(kept + np, n_f, g.k_far, scf, out.i_far + (size_t)row * g.k_far, out.n_far + row, g.max_blocks);
+      emit_best_first<P>(kept_near, n_n, g.k_near, scf, out.i_near + (size_t)row * g.k_near, out.n_near + row,
+                         g.max_blocks);
+      __syncthreads();
+    }
+    if (rg.quota > 0) {
+      // ascending list: [sink bypass] far... near... [window bypass]
+      const int v0 = tid < n_n ? kept_near[tid] : 0;     // k_near <= 2 P
+      const int v1 = tid + P < n_n ? kept_near[tid + P] : 0;
+      __syncthreads();
+      if (tid < n_n) kept[np + n_f + tid] = v0;
+      if (tid + P < n_n) kept[np + n_f + tid + P] = v1;
+      np += n_f + n_n;
+      if (rg.swa_byp) { if (tid == 0) kept[np] = rg.swa_byp_blk; ++np; }
+    }
+    __syncthreads();
+  }
+  return np;
+}
+
+template <int DSUB>
+__device__ __forceinline__ float l2_logit(const uint8_t* __restrict__ codes, float scale, float zero,
+                                          const float* __restrict__ qf) {
+  constexpr int WORDS = DSUB / 8;   // 32-bit words of packed codes
+  uint32_t w[WORDS];
+  if constexpr (WORDS == 4) {
+    const uint4 u = *(const uint4*)codes;
+    w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
+  } else if constexpr (WORDS == 2) {
+    const uint2 u = *(const uint2*)codes;
+    w[0] = u.x; w[1] = u.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < WORDS; i += 4) {
+      const uint4 u = *(const uint4*)(codes + 4 * i);
+      w[i] = u.x; w[i + 1] = u.y; w[i + 2] = u.z; w[i + 3] = u.w;
+    }
+  }
+  float acc = 0.0f;
+#pragma unroll
+  for (int i = 0; i < WORDS; ++i) {
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const float c = (float)((w[i] >> (4 * n)) & 15u);
+      const float x = bf16r(__fsub_rn(bf16r(__fmul_rn(c, scale)), zero));
+      acc = __fadd_rn(acc, __fmul_rn(x, qf[8 * i + n]));
+    }
+  }
+  return bf16r(acc);
+}
+
+// The selecting CTA's work once the row's candidate scores sit in shared memory (sc, nitems
+// slots; slot i * page + o is token pages[i] * page + o, physical page physs[i]): keep the
+// quota best by bisection, fill holes, drop ids below the sink, and write
+// sink ++ middle ++ window as physical slots.  Runs on the first NT threads of the CTA
+// (BAR as in group_sync).  TRIGGER: release the dependent launch after the selection.
+struct L2Shared {
+  uint16_t* sc;
+  int *pages, *physs, *mid_a, *mid_b, *wtot, *scan;
+  uint8_t* win;
+};
+
+template <int NT, int BAR, bool TRIGGER>
+__device__ __forceinline__ void l2_select_and_write(const loda_geometry& g, const Regions& rg, const loda_selection& S,
+                                                    uint32_t* status, const int32_t* table, int b, int kv, int row,
+                                                    int length, int nitems, const L2Shared& sm, int* ticket) {
+  const int tid = threadIdx.x;
+  const int K2 = g.level2_topk;
+  uint16_t* sc = sm.sc;
+  int *pages = sm.pages, *physs = sm.physs, *mid_a = sm.mid_a, *mid_b = sm.mid_b, *wtot = sm.wtot, *scan = sm.scan;
+  uint8_t* win = sm.win;
+  const int quota = rg.quota;
+  int* slots_sel = mid_b;      // ascending candidate slots kept by the select
+  const int take = block_bisect_topk<NT, BAR>(sc, nitems, min(quota, K2), slots_sel, wtot);
+  if (TRIGGER) pdl_launch_dependents();
+  if (take == quota) {
+    // Common case: the quota is filled by scored candidates (all of them >= sink, no holes).
+    // The survivors' physical pages came with the page list, so only the sink and window ids
+    // need a block-table lookup: sink ++ middle ++ window, one pass.
+    const int cap = g.max_blocks * g.page;
+    const int sk = min(length, g.sink);
+    const int count_s = min(length, g.sink + g.swa) - sk;
+    const int s_lo = max(max(length - g.swa, 0), sk);
+    const int s_hi = min(length - g.swa + count_s, cap);
+    const int n_s = max(s_hi - s_lo, 0);
+    const int total = sk + take + n_s;
+    const int n_out = min(total, g.max_visible);
+    int32_t* gout = S.gather + ((size_t)b * g.num_kv_heads + kv) * g.max_visible;
+    for (int i = tid; i < n_out; i += NT) {
+      int slot;
+      if (i >= sk && i < sk + take) {
+        const int sl = slots_sel[i - sk];
+        slot = physs[sl / g.page] * g.page + sl % g.page;
+        if (S.middle != nullptr) S.middle[(size_t)row * K2 + (i - sk)] = pages[sl / g.page] * g.page + sl % g.page;
+      } else {
+        const int id = i < sk ? i : s_lo + (i - sk - take);
+        const int lp = id / g.page;
+        int ph = lp < g.max_blocks ? table[lp] : -1;
+        if (ph < 0 || ph >= g.num_pages) {
+          if (status) atomicOr(status, LODA_STATUS_BAD_PAGE);
+          ph = g.num_pages - 1;
+        }
+        slot = ph * g.page + id % g.page;
+      }
+      gout[i] = slot;
+    }
+    if (tid == 0) {
+      if (S.middle != nullptr) S.middle_counts[row] = take;
+      S.visible_lens[(size_t)b * g.num_kv_heads + kv] = n_out;
+      if (total > g.max_visible && status) atomicOr(status, LODA_STATUS_TRUNCATED);
+      if (ticket) *ticket = 0;
+    }
+    return;
+  }
+  for (int i = tid; i < take; i += NT) {
+    const int sl = slots_sel[i];
+    mid_a[i] = pages[sl / g.page] * g.page + sl % g.page;
+  }
+  group_sync<NT, BAR>();
+  int count = take;
+  int* mid = mid_a;
+
+  // ---- hole fill (nfa_layer_batch_selector.py:545-566) -------------------------
+  if (take < quota) {
+    const int need = quota - take;
+    // the holes are among the first `quota` ids of [lower, upper)
+    for (int i = tid; i < quota; i += NT) win[i] = 0;
+    group_sync<NT, BAR>();
+    int in_win = 0;
+    for (int i = tid; i < take; i += NT) {
+      const int w = mid_a[i] - rg.lower;
+      if (w < quota) { win[w] = 1; ++in_win; }
+    }
+    int cw;
+    block_exclusive_scan<NT, BAR>(in_win, scan, &cw);
+    const int ipt = (quota + NT - 1) / NT;
+    const int lo = min(tid * ipt, quota), hi = min(lo + ipt, quota);
+    int zeros = 0;
+    for (int w = lo; w < hi; ++w) zeros += win[w] == 0;
+    int ztotal;
+    int zrank = block_exclusive_scan<NT, BAR>(zeros, scan, &ztotal);
+    int keep = 0;
+    for (int w = lo; w < hi; ++w) {
+      if (win[w] == 0) { if (zrank < need) win[w] = 2; ++zrank; }
+      keep += win[w] != 0;
+    }
+    int ktotal;
+    int pos = block_exclusive_scan<NT, BAR>(keep, scan, &ktotal);
+    for (int w = lo; w < hi; ++w) {
+      if (win[w] != 0) mid_b[pos++] = rg.lower + w;
+    }
+    // chosen tokens beyond the window follow all holes
+    for (int i = cw + tid; i < take; i += NT) mid_b[ktotal + (i - cw)] = mid_a[i];
+    group_sync<NT, BAR>();
+    count = ktotal + (take - cw);
+    mid = mid_b;
+  }
+
+  // ---- drop ids below the sink (only holes can be there), ascending already ----
+  int below = 0;
+  for (int i = tid; i < min(count, g.sink); i += NT) below += mid[i] < g.sink;
+  int d0;
+  block_exclusive_scan<NT, BAR>(below, scan, &d0);
+  const int count_m = count - d0;
+  if (S.middle != nullptr) {
+    for (int i = tid; i < count_m; i += NT) S.middle[(size_t)row * K2 + i] = mid[d0 + i];
+    if (tid == 0) S.middle_counts[row] = count_m;
+  }
+  // ---- union with sink and window ids (nfa_layer_batch_selector.py:1348-1437) --
+  const int cap = g.max_blocks * g.page;
+  const int sk = min(length, g.sink);
+  const int count_s = min(length, g.sink + g.swa) - sk;
+  const int s_lo = max(max(length - g.swa, 0), sk);
+  const int s_hi = min(length - g.swa + count_s, cap);
+  const int n_s = max(s_hi - s_lo, 0);
+  const int total = sk + count_m + n_s;
+  const int n_out = min(total, g.max_visible);
+  int32_t* gout = S.gather + ((size_t)b * g.num_kv_heads + kv) * g.max_visible;
+  for (int i = tid; i < n_out; i += NT) {
+    int id;
+    if (i < sk) id = i;
+    else if (i < sk + count_m) id = mid[d0 + i - sk];
+    else id = s_lo + (i - sk - count_m);
+    const int lp = id / g.page;
+    int ph = lp < g.max_blocks ? table[lp] : -1;
+    if (ph < 0 || ph >= g.num_pages) {
+      if (status) atomicOr(status, LODA_STATUS_BAD_PAGE);
+      ph = g.num_pages - 1;   // PAD page: zeros, never out of bounds
+    }
+    gout[i] = ph * g.page + id % g.page;
+  }
+  if (tid == 0) {
+    S.visible_lens[(size_t)b * g.num_kv_heads + kv] = n_out;
+    if (total > g.max_visible && status) atomicOr(status, LODA_STATUS_TRUNCATED);
+    if (ticket) *ticket = 0;
+  }
+}
+
+}  // namespace loda

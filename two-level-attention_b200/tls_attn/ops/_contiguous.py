@@ -32,7 +32,7 @@ def runtime(q, k, v, num_heads, num_kv_heads, max_visible):
         dtype=_capi.LODA_DTYPE_BF16, num_q_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=d,
         head_dim_v=v.shape[-1], sub_dims=32, sub_lo0=0, sub_lo1=16, page=1, num_pages=max_b * s + 1,
         max_blocks=16, max_requests=batch, max_query_tokens=batch, max_visible=max_visible, k_far=0, k_near=0,
-        level2_topk=max_visible, sink=0, swa=1, near_len=1, pool_near_len=1)
+        level2_topk=1, sink=0, swa=1, near_len=1, pool_near_len=1)      # the selector is not used: smallest legal budgets
     nbytes = _capi.lib().loda_workspace_bytes(C.byref(g))
     if nbytes == 0:
         raise _capi.FallbackRequired(_capi.lib().loda_last_error().decode())
