@@ -110,13 +110,13 @@ def test_separate_write_then_select_matches_fused_write():
     _check_against_oracle(b, out_b)
 
 
-def test_incremental_append_equals_bulk_rebuild_over_many_steps():
+@pytest.mark.parametrize("base", [[5000, 777], [5000]], ids=["two_requests", "one_request_one_launch_selector"])
+def test_incremental_append_equals_bulk_rebuild_over_many_steps(base):
     """Decode 40 tokens (crossing page boundaries) with the append kernel, then
     compare the index with a bulk rebuild and the selection with the oracle."""
     from helpers import make_setup, mod
     sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
     synth = mod("synth")
-    base = [5000, 777]
     steps = 40
     setup = make_setup(base, seed=3, extra_blocks=8)
     cache = setup.cache
@@ -127,7 +127,7 @@ def test_incremental_append_equals_bulk_rebuild_over_many_steps():
         k_new = torch.stack([c.k[l - 1 + s] for c, l in zip(full, base)])[:, :, None].to(setup.dev)
         v_new = torch.stack([c.v[l - 1 + s] for c, l in zip(full, base)])[:, :, None].to(setup.dev)
         cache.plan_common(setup.req_ids)
-        slots = cache.slot_mapping_for_layer(0)[:2]
+        slots = cache.slot_mapping_for_layer(0)[:len(base)]
         sel_mod.select_topk_for_layer_batched(cache, 0, setup.req_ids, setup.q, attention=setup.attention,
                                               decode_write=(k_new, v_new, slots))
         cache.commit_step()
@@ -143,6 +143,25 @@ def test_incremental_append_equals_bulk_rebuild_over_many_steps():
     out = nfa.decode_graph_ready(setup.attention, setup.q, cache)
     torch.cuda.synchronize()
     _check_against_oracle(setup, out)
+
+
+@pytest.mark.parametrize("length", [1, 17, 131, 4241, 20000, 40000])
+def test_single_request_one_launch_selector_matches_oracle_and_the_two_launch_chain(length, monkeypatch):
+    """A single request (8 rows) is served by the one-launch selector (a cluster per row); the
+    same inputs through the two-launch chain (LODA_B200_SELECT_PATH=split) must give the same
+    integers and the same attention bits, and both must match the oracle."""
+    from helpers import make_setup
+    a = make_setup([length], seed=7)
+    out_a = _run_step(a)
+    _check_against_oracle(a, out_a)
+    monkeypatch.setenv("LODA_B200_SELECT_PATH", "split")
+    b = make_setup([length], seed=7)
+    out_b = _run_step(b)
+    _check_against_oracle(b, out_b)
+    n = int(a.cache.visible_lens_for_layer(0).max())
+    assert torch.equal(a.cache.visible_lens_for_layer(0), b.cache.visible_lens_for_layer(0))
+    assert torch.equal(a.cache.gather_indices_for_layer(0)[..., :n], b.cache.gather_indices_for_layer(0)[..., :n])
+    assert torch.equal(out_a, out_b)
 
 
 def test_padding_rows_and_noncontiguous_request_slots():

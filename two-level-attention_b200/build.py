@@ -11,7 +11,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-SOURCES = ["loda_append.cu", "loda_l1.cu", "loda_l2.cu", "loda_attn.cu", "loda_tia.cu", "loda_tls.cu", "loda_capi.cu"]
+SOURCES = ["loda_append.cu", "loda_l1.cu", "loda_l2.cu", "loda_select_fused.cu", "loda_attn.cu", "loda_tia.cu", "loda_tls.cu", "loda_capi.cu"]
 LIB = os.path.join(HERE, "libloda_b200.so")
 
 

@@ -18,6 +18,10 @@ cudaError_t launch_l1(const loda_geometry&, const loda_layer&, const loda_batch&
 cudaError_t launch_l2(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
                       const loda_selection&, const SelectWorkspace&, uint32_t*, bool, cudaStream_t);
 int l1_score_stride(const loda_geometry&);
+bool select_fused_applicable(const loda_geometry&, int);
+void select_fused_refuse(int);
+cudaError_t launch_select_fused(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
+                                const loda_selection&, uint32_t*, const AppendArgs&, cudaStream_t);
 cudaError_t launch_attn(const loda_geometry&, const loda_layer&, const void*, const int32_t*, const int32_t*,
                         const int32_t*, int, int, float, void*, float*, const AttnWorkspace&, bool, bool, cudaStream_t);
 size_t l1_smem_bytes(const loda_geometry&);
@@ -250,6 +254,18 @@ int loda_select_step(const loda_geometry* g, const loda_layer* layer, const loda
     return fail(LODA_ERR_ARGUMENT, "k_new, v_new and slots go together (all NULL = refresh the index only)");
   const SelectWorkspace ws = select_ws(*g, workspace);
   const AppendArgs ap{(const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, slots, status, 1};
+  if (select_fused_applicable(*g, b->batch * g->num_kv_heads)) {
+    // one launch for both levels (a cluster per row); refused shapes fall through to the two-launch chain
+    const cudaError_t e = launch_select_fused(*g, *layer, *b, q, scale, *sel, status, ap, (cudaStream_t)stream);
+    if (e == cudaSuccess) return LODA_OK;
+    if (e != cudaErrorNotSupported) {                    // NotSupported: nothing was launched, the GPU cannot hold the clusters
+      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+      cudaStreamIsCapturing((cudaStream_t)stream, &cap);
+      if (cap != cudaStreamCaptureStatusNone) return check_cuda(e, "select_step/fused");   // cannot retry inside a capture
+      (void)cudaGetLastError();
+      select_fused_refuse(g->sub_dims);
+    }
+  }
   LODA_TRY(check_cuda(launch_l1(*g, *layer, *b, q, scale, *sel, ws, ap, (cudaStream_t)stream), "select_step/l1"));
   return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, ws, status, /*chained=*/true, (cudaStream_t)stream),
                     "select_step/l2");

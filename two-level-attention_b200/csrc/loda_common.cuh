@@ -107,14 +107,14 @@ __device__ __forceinline__ void group_sync() {
 }
 
 // ---------------------------------------------------------------------------
-// block-wide primitives (NT threads, all must call; BAR as in group_sync)
+// block-wide primitives (NT threads, all must call; BAR as in group_sync; TBASE = first thread of the group)
 // ---------------------------------------------------------------------------
 
 // Exclusive prefix sum of one int per thread; *total gets the block sum.
 // scratch: 33 ints of shared memory.
-template <int NT, int BAR = 0>
+template <int NT, int BAR = 0, int TBASE = 0>
 __device__ __forceinline__ int block_exclusive_scan(int v, int* scratch, int* total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lane = ((int)threadIdx.x - TBASE) & 31, warp = ((int)threadIdx.x - TBASE) >> 5;
   int incl = v;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -227,10 +227,10 @@ __device__ __forceinline__ int count_greater(const uint32_t* keys, int n4, uint3
 // exclusive scan of one flag per thread: ballot inside the warp, per-warp totals
 // through shared memory, one barrier.  wtot: 2 x 32 ints (16-byte aligned), the
 // caller alternates `buf` between back-to-back calls.
-template <int NT, int BAR = 0>
+template <int NT, int BAR = 0, int TBASE = 0>
 __device__ __forceinline__ int block_flag_scan(bool flag, int* wtot, int buf, int* total) {
   constexpr int NW = NT / 32;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lane = ((int)threadIdx.x - TBASE) & 31, warp = ((int)threadIdx.x - TBASE) >> 5;
   const unsigned bal = __ballot_sync(0xffffffffu, flag);
   if (lane == 0) wtot[buf * 32 + warp] = __popc(bal);
   group_sync<NT, BAR>();
@@ -246,11 +246,11 @@ __device__ __forceinline__ int block_flag_scan(bool flag, int* wtot, int buf, in
 }
 
 // sum of one int per thread: redux, per-warp column, one barrier (same buffers)
-template <int NT, int BAR = 0>
+template <int NT, int BAR = 0, int TBASE = 0>
 __device__ __forceinline__ int block_sum_cols(int v, int* wtot, int buf) {
   constexpr int NW = NT / 32;
   const int r = __reduce_add_sync(0xffffffffu, v);
-  if ((threadIdx.x & 31) == 0) wtot[buf * 32 + (threadIdx.x >> 5)] = r;
+  if ((((int)threadIdx.x - TBASE) & 31) == 0) wtot[buf * 32 + (((int)threadIdx.x - TBASE) >> 5)] = r;
   group_sync<NT, BAR>();
   const int4* col = (const int4*)(wtot + buf * 32);
   int s = 0;
@@ -269,33 +269,33 @@ __device__ __forceinline__ void unpack_u16x8(const uint4& u, uint32_t (&v)[8]) {
 
 // (1) n <= NT scores: every thread ranks its own element against all others.
 // keys: NT words (16-byte aligned); wtot: 64 ints.
-template <int NT>
+template <int NT, int BAR = 0, int TBASE = 0>
 __device__ __forceinline__ int block_rank_topk_small(const uint16_t* sc, int n, int k, int* out, uint32_t* keys,
                                                      int* wtot) {
-  const int tid = threadIdx.x;
+  const int tid = ((int)threadIdx.x - TBASE);
   const uint32_t key = tid < n ? rank_key(sc[tid], tid) : 0u;
   keys[tid] = key;
-  __syncthreads();
+  group_sync<NT, BAR>();
   const int rank = key ? count_greater(keys, (n + 3) >> 2, key) : 0;
   const bool sel = key != 0 && rank < k;
   int total;
-  const int pos = block_flag_scan<NT>(sel, wtot, 0, &total);
+  const int pos = block_flag_scan<NT, BAR, TBASE>(sel, wtot, 0, &total);
   if (sel) out[pos] = tid;
-  __syncthreads();
+  group_sync<NT, BAR>();
   return total;
 }
 
 // (1b) NT < n <= 2 NT scores: the same with two elements per thread (tid, tid + NT).
 // keys: 2 NT words (16-byte aligned); wtot: 64 ints.
-template <int NT>
+template <int NT, int BAR = 0, int TBASE = 0>
 __device__ __forceinline__ int block_rank_topk_pair(const uint16_t* sc, int n, int k, int* out, uint32_t* keys,
                                                     int* wtot) {
-  const int tid = threadIdx.x, hi = tid + NT;
+  const int tid = ((int)threadIdx.x - TBASE), hi = tid + NT;
   const uint32_t k0 = tid < n ? rank_key(sc[tid], tid) : 0u;
   const uint32_t k1 = hi < n ? rank_key(sc[hi], hi) : 0u;
   keys[tid] = k0;
   keys[hi] = k1;
-  __syncthreads();
+  group_sync<NT, BAR>();
   int a0 = 0, a1 = 0, b0 = 0, b1 = 0;
   const int n4 = (n + 3) >> 2;
 #pragma unroll 4
@@ -306,11 +306,11 @@ __device__ __forceinline__ int block_rank_topk_pair(const uint16_t* sc, int n, i
   }
   const bool s0 = k0 != 0 && a0 + a1 < k, s1 = k1 != 0 && b0 + b1 < k;
   int t0, t1;
-  const int p0 = block_flag_scan<NT>(s0, wtot, 0, &t0);
-  const int p1 = block_flag_scan<NT>(s1, wtot, 1, &t1);
+  const int p0 = block_flag_scan<NT, BAR, TBASE>(s0, wtot, 0, &t0);
+  const int p1 = block_flag_scan<NT, BAR, TBASE>(s1, wtot, 1, &t1);
   if (s0) out[p0] = tid;
   if (s1) out[t0 + p1] = hi;
-  __syncthreads();
+  group_sync<NT, BAR>();
   return t0 + t1;
 }
 
@@ -318,11 +318,11 @@ __device__ __forceinline__ int block_rank_topk_pair(const uint16_t* sc, int n, i
 // strictly above `thr` and the first `rem` scores equal to it (`all`: every scored
 // element).  Blocked layout (ept consecutive scores per thread), one shuffle scan.
 // wtot: 32 ints.  Returns all ? nvalid : k.
-template <int NT, int BAR = 0>
+template <int NT, int BAR = 0, int TBASE = 0>
 __device__ __forceinline__ int block_compact_threshold(const uint16_t* sc, int n, int k, uint32_t thr, int rem, bool all,
                                                        int nvalid, int* out, int* wtot) {
   constexpr int NW = NT / 32;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = ((int)threadIdx.x - TBASE), lane = tid & 31, warp = tid >> 5;
   const int ept = (((n + NT - 1) / NT) + 7) & ~7;
   const int base = tid * ept;
   const int nch = base < n ? min(ept, ((n - base + 7) & ~7)) >> 3 : 0;
@@ -374,11 +374,11 @@ __device__ __forceinline__ int block_compact_threshold(const uint16_t* sc, int n
 // every thread counts its scores at or above three candidate thresholds (independent
 // chains), one barrier publishes the block sums.
 // wtot: 6 x 32 ints (16-byte aligned).
-template <int NT, int BAR = 0>
+template <int NT, int BAR = 0, int TBASE = 0>
 __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int k, int* out, int* wtot) {
   constexpr int NW = NT / 32;
   constexpr int MAXC = 4;                        // chunks a thread keeps in registers
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = ((int)threadIdx.x - TBASE), lane = tid & 31, warp = tid >> 5;
   const int nchunks = (n + 7) >> 3;
   const int full = nchunks / NT, remc = nchunks - full * NT;     // whole rounds of chunks, chunks left
   const bool single = remc > 0 && remc * 8 <= NT;                // the rest as one score per thread
@@ -517,7 +517,7 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
     rem = k - gt;
     LODA_SUB(11);
   }
-  if (!in_regs) return block_compact_threshold<NT, BAR>(sc, n, k, thr, rem, all, nvalid, out, wtot);
+  if (!in_regs) return block_compact_threshold<NT, BAR, TBASE>(sc, n, k, thr, rem, all, nvalid, out, wtot);
   // Compaction from the registers, in index order: consecutive threads hold consecutive
   // chunks of a slot, so one scan over the threads per slot places its survivors (strictly
   // above the threshold, then the first `rem` scores equal to it).
@@ -594,15 +594,15 @@ __device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int 
 // score (k groups each hold a score at or above it).  Scores at or above the
 // bound (about 1.5-2 k of them for unclustered scores) are compacted in index
 // order and ranked against each other.  Returns -1 without writing anything
-// when more than NT survive (heavily tied or sorted scores): the caller then
-// bisects.  keys: NT + 8 words (16-byte aligned); wtot: 64 ints; sh: 2 ints.
-template <int NT>
+// when more than 2 NT survive (heavily tied or sorted scores): the caller then
+// bisects.  keys: 2 NT + 8 words (16-byte aligned); wtot: 64 ints; sh: 2 ints.
+template <int NT, int BAR = 0, int TBASE = 0>
 __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, int k, int* out, uint32_t* keys,
                                                     int* wtot, int* sh) {
   static_assert(NT % 128 == 0 && NT / 128 <= 32, "group layout");
   constexpr int GS = NT / 128;                   // threads per group
   constexpr int NW = NT / 32;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = ((int)threadIdx.x - TBASE), lane = tid & 31, warp = tid >> 5;
   const int nchunks = (n + 7) >> 3;
   // thread maximum (two independent chains)
   uint32_t m0 = 0, m1 = 0;
@@ -616,7 +616,8 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
 #pragma unroll
   for (int o = 1; o < GS; o <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
   if ((tid & (GS - 1)) == 0) keys[tid / GS] = rank_key(m, tid / GS);
-  __syncthreads();
+  if (tid == 0) sh[1] = 0;
+  group_sync<NT, BAR>();
   int is_kth = 0;
   uint32_t gkey = 0;
   if (tid < 128) {
@@ -625,8 +626,9 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
     if (is_kth) sh[0] = (int)(gkey >> 16);
   }
   // fewer than k non-empty groups: nothing can be discarded
-  const int found = __syncthreads_or(is_kth);
-  const uint32_t bound = found ? (uint32_t)sh[0] : 1u;
+  if (is_kth) sh[1] = 1;                         // sh[1] was cleared before the barrier above
+  group_sync<NT, BAR>();
+  const uint32_t bound = sh[1] ? (uint32_t)sh[0] : 1u;
   // survivors, counted per thread then placed in index order round by round
   int total = 0;
   {
@@ -637,9 +639,9 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
 #pragma unroll
       for (int j = 0; j < 8; ++j) cnt += v[j] >= bound;
     }
-    total = block_sum_cols<NT>(cnt, wtot, 0);
+    total = block_sum_cols<NT, BAR, TBASE>(cnt, wtot, 0);
   }
-  if (total > NT) return -1;
+  if (total > 2 * NT) return -1;
   int base_out = 0, buf = 1;
   for (int c0 = 0; c0 < nchunks; c0 += NT) {
     const int ch = c0 + tid;
@@ -655,7 +657,7 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
       if (lane >= o) incl += nb;
     }
     if (lane == 31) wtot[buf * 32 + warp] = incl;
-    __syncthreads();
+    group_sync<NT, BAR>();
     int before = 0, tot = 0;
 #pragma unroll
     for (int w = 0; w < NW; ++w) {
@@ -672,16 +674,23 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
     base_out += tot;
   }
   if (tid < 4) keys[total + tid] = 0;            // pad the last vector of keys
-  __syncthreads();
-  // exact ranking of the survivors (already in ascending index order)
-  const uint32_t key = tid < total ? keys[tid] : 0u;
-  const int rank = key ? count_greater(keys, (total + 3) >> 2, key) : 0;
-  const bool sel = key != 0 && rank < k;
-  int kept;
-  const int opos = block_flag_scan<NT>(sel, wtot, buf, &kept);
-  if (sel) out[opos] = 0xFFFF - (int)(key & 0xFFFFu);
-  __syncthreads();
-  return kept;
+  group_sync<NT, BAR>();
+  // exact ranking of the survivors (already in ascending index order), up to two per thread
+  const int n4 = (total + 3) >> 2;
+  const uint32_t key0 = tid < total ? keys[tid] : 0u;
+  const bool sel0 = key0 != 0 && count_greater(keys, n4, key0) < k;
+  int kept0;
+  const int pos0 = block_flag_scan<NT, BAR, TBASE>(sel0, wtot, buf, &kept0);
+  if (sel0) out[pos0] = 0xFFFF - (int)(key0 & 0xFFFFu);
+  int kept1 = 0;
+  if (total > NT) {                              // uniform
+    const uint32_t key1 = tid + NT < total ? keys[tid + NT] : 0u;
+    const bool sel1 = key1 != 0 && count_greater(keys, n4, key1) < k;
+    const int pos1 = block_flag_scan<NT, BAR, TBASE>(sel1, wtot, buf ^ 1, &kept1);
+    if (sel1) out[kept0 + pos1] = 0xFFFF - (int)(key1 & 0xFFFFu);
+  }
+  group_sync<NT, BAR>();
+  return kept0 + kept1;
 }
 
 // ---------------------------------------------------------------------------

@@ -48,8 +48,8 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   // (an offset, not pointer arithmetic through an integer: the compiler must keep seeing shared memory)
   const size_t keys_off = (ROWS_BYTES + (size_t)3 * G * DSUB * 4 + (size_t)(g.k_far + g.k_near + 2) * 4 + 15) & ~(size_t)15;
   uint32_t* keys = (uint32_t*)(smem + keys_off);                 // 2 P + 8
-  int* wtot = (int*)(keys + 2 * P + 8);                              // 6 x 32
-  int* sh = wtot + 192;                                          // 8
+  int* wtot = (int*)(keys + 2 * P + 8);                          // 8 x 32
+  int* sh = wtot + 256;                                          // 8
 
   const int tid = threadIdx.x;
   const int split = blockIdx.x, row = blockIdx.y;
@@ -213,7 +213,7 @@ static size_t l1_smem_bytes_p(const loda_geometry& g, int P) {
   const int G = g.num_q_heads / g.num_kv_heads;
   const size_t rows = (size_t)P * (4 * g.sub_dims + 16);
   return (rows > L1_TAIL_BYTES ? rows : L1_TAIL_BYTES) + (size_t)3 * G * g.sub_dims * 4 +
-         (size_t)(g.k_far + g.k_near + 2) * 4 + (size_t)(2 * P + 8) * 4 + (192 + 8) * 4 + 32;
+         (size_t)(g.k_far + g.k_near + 2) * 4 + (size_t)(2 * P + 8) * 4 + (256 + 8) * 4 + 32;
 }
 
 size_t l1_smem_bytes(const loda_geometry& g) { return l1_smem_bytes_p(g, L1_P_WIDE); }

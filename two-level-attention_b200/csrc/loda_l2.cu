@@ -105,16 +105,7 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
       const int i = idx / g.page, o = idx % g.page;
       const int pg = __ldcg(ws.pages + (size_t)row * np_max + i);
       const int ph = __ldcg(ws.phys + (size_t)row * np_max + i);
-      const int tok = pg * g.page + o;
-      uint32_t ord = 0;
-      if (ph >= 0 && tok >= g.sink && tok < rg.swa_lo_tok && tok < length && tok >= rg.lower && tok < rg.upper) {
-        const size_t trow = ((size_t)ph * g.num_kv_heads + kv) * g.page + o;
-        const __nv_bfloat162 sz = *(const __nv_bfloat162*)((const bf16*)L.tail_sz + trow * 2);
-        const float lg = l2_logit<DSUB>(L.tail_code + trow * (DSUB / 2), __low2float(sz), __high2float(sz), qf);
-        if (lg == lg && lg != -INFINITY) ord = ord16(lg);
-      } else if (ph < 0 && status) {
-        atomicOr(status, LODA_STATUS_BAD_PAGE);
-      }
+      const uint32_t ord = l2_slot_score<DSUB>(g, L, rg, length, kv, pg, ph, o, qf, status);
       row_scores[idx] = (uint16_t)ord;
     }
   }

@@ -119,6 +119,7 @@ __device__ void emit_best_first(const int* kept, int n, int k, const uint16_t* s
 // [0, n_far), zero outside the pool) and near pool in scn (pages [near_lo8, near_lo8 + n_near)):
 // exact top-k of each pool, the optional best-first lists, and the ascending page list
 // kept[0, np) = [sink bypass] far... near... [window bypass].  Returns np.  All P threads call.
+// keys: 2 P + 8 words; wtot: 256 ints; sh: 8 ints.
 // TRIGGER: release the dependent launch after the two selections.
 template <int P, bool TRIGGER>
 __device__ __forceinline__ int l1_select_pages(const loda_geometry& g, const Regions& rg, const loda_selection& out,
@@ -132,19 +133,50 @@ __device__ __forceinline__ int l1_select_pages(const loda_geometry& g, const Reg
     if (rg.quota > 0 && rg.sink_byp && rg.spl < rg.kt_eff) { if (tid == 0) kept[0] = rg.spl; np = 1; }
     int* kept_near = kept + np + g.k_far;                // compacted below
     int n_f = 0, n_n = 0;
-    if (n_far > far_lo) {
-      if (n_far <= P) {
-        n_f = block_rank_topk_small<P>(scf, n_far, g.k_far, kept + np, keys, wtot);
+    if constexpr (P == 512) {
+      // the two pools are selected at the same time: far by the first 256 threads, near by the
+      // other 256, each group on its own named barrier, key buffer and sum columns
+      constexpr int H = 256;
+      if (tid < H) {
+        int r = 0;
+        if (n_far > far_lo) {
+          if (n_far <= H) {
+            r = block_rank_topk_small<H, 1, 0>(scf, n_far, g.k_far, kept + np, keys, wtot);
+          } else if (n_far <= 2 * H) {
+            r = block_rank_topk_pair<H, 1, 0>(scf, n_far, g.k_far, kept + np, keys, wtot);
+          } else {
+            r = g.k_far <= 128 ? block_prefilter_topk<H, 1, 0>(scf, n_far, g.k_far, kept + np, keys, wtot, sh) : -1;
+            if (r < 0) r = block_bisect_topk<H, 1, 0>(scf, n_far, g.k_far, kept + np, wtot);   // heavily tied scores
+          }
+        }
+        if (tid == 0) sh[2] = r;
       } else {
-        n_f = g.k_far <= 128 ? block_prefilter_topk<P>(scf, n_far, g.k_far, kept + np, keys, wtot, sh) : -1;
-        if (n_f < 0) n_f = block_bisect_topk<P>(scf, n_far, g.k_far, kept + np, wtot);   // heavily tied scores
+        int r = 0;
+        if (n_near > 0) {
+          r = n_near <= H ? block_rank_topk_small<H, 2, H>(scn, n_near, g.k_near, kept_near, keys + 2 * H + 8, wtot + 192)
+                          : block_rank_topk_pair<H, 2, H>(scn, n_near, g.k_near, kept_near, keys + 2 * H + 8, wtot + 192);
+          for (int i = tid - H; i < r; i += H) kept_near[i] += near_lo8;
+        }
+        if (tid == H) sh[3] = r;
       }
-    }
-    if (n_near > 0) {
-      n_n = n_near <= P ? block_rank_topk_small<P>(scn, n_near, g.k_near, kept_near, keys, wtot)
-                        : block_rank_topk_pair<P>(scn, n_near, g.k_near, kept_near, keys, wtot);
-      for (int i = tid; i < n_n; i += P) kept_near[i] += near_lo8;
       __syncthreads();
+      n_f = sh[2];
+      n_n = sh[3];
+    } else {
+      if (n_far > far_lo) {
+        if (n_far <= P) {
+          n_f = block_rank_topk_small<P>(scf, n_far, g.k_far, kept + np, keys, wtot);
+        } else {
+          n_f = g.k_far <= 128 ? block_prefilter_topk<P>(scf, n_far, g.k_far, kept + np, keys, wtot, sh) : -1;
+          if (n_f < 0) n_f = block_bisect_topk<P>(scf, n_far, g.k_far, kept + np, wtot);   // heavily tied scores
+        }
+      }
+      if (n_near > 0) {
+        n_n = n_near <= P ? block_rank_topk_small<P>(scn, n_near, g.k_near, kept_near, keys, wtot)
+                          : block_rank_topk_pair<P>(scn, n_near, g.k_near, kept_near, keys, wtot);
+        for (int i = tid; i < n_n; i += P) kept_near[i] += near_lo8;
+        __syncthreads();
+      }
     }
     if (TRIGGER) pdl_launch_dependents();
     if (want_lists) {
@@ -200,6 +232,25 @@ __device__ __forceinline__ float l2_logit(const uint8_t* __restrict__ codes, flo
     }
   }
   return bf16r(acc);
+}
+
+// Ordered 16-bit logit of candidate slot (logical page pg, physical page ph, offset o); 0 = the
+// token is not a candidate (outside the scored window, NaN or -inf logit, invalid page).
+template <int DSUB>
+__device__ __forceinline__ uint32_t l2_slot_score(const loda_geometry& g, const loda_layer& L, const Regions& rg,
+                                                  int length, int kv, int pg, int ph, int o, const float* qf,
+                                                  uint32_t* status) {
+  const int tok = pg * g.page + o;
+  uint32_t ord = 0;
+  if (ph >= 0 && tok >= g.sink && tok < rg.swa_lo_tok && tok < length && tok >= rg.lower && tok < rg.upper) {
+    const size_t trow = ((size_t)ph * g.num_kv_heads + kv) * g.page + o;
+    const __nv_bfloat162 sz = *(const __nv_bfloat162*)((const bf16*)L.tail_sz + trow * 2);
+    const float lg = l2_logit<DSUB>((const uint8_t*)L.tail_code + trow * (DSUB / 2), __low2float(sz), __high2float(sz), qf);
+    if (lg == lg && lg != -INFINITY) ord = ord16(lg);
+  } else if (ph < 0 && status) {
+    atomicOr(status, LODA_STATUS_BAD_PAGE);
+  }
+  return ord;
 }
 
 // The selecting CTA's work once the row's candidate scores sit in shared memory (sc, nitems

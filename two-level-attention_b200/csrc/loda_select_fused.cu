@@ -1,0 +1,345 @@
+// The two selector levels of one decode step in ONE launch, for grids that fit the GPU in a
+// single round (batch 1 at long context): a thread-block cluster of 16 CTAs per (request, kv
+// head) row keeps everything the two levels exchange in shared memory.
+//
+//   1. every CTA stages and scores its tiles of 512 pages (as l1_kernel does) and stores the
+//      16-bit page scores straight into the row leader's shared memory (DSMEM);
+//   2. cluster barrier; the leader (rank 0) selects the far and near pages and looks up their
+//      physical pages, while rank 1 performs the decode append of the row;
+//   3. cluster barrier; every CTA scores its share of the candidate slots on the packed 4-bit
+//      tail keys, reading the page list from the leader's shared memory and storing the 16-bit
+//      logits there;
+//   4. cluster barrier; the peers exit, the leader's first 256 threads select the quota, fill
+//      holes and write the gather list (the routines of l2_kernel on a named barrier).
+//
+// Against the two-launch chain this removes one launch boundary, the global round trip of the
+// page scores and of the candidate logits with their fences and tickets, and the second
+// kernel's prologue.  Same device routines, same arithmetic, same results.
+// Restates the same reference code as loda_l1.cu and loda_l2.cu
+// (nfa_layer_batch_selector.py:174-354, 422-605, 1194-1251, 1336-1437, 1473-1793).
+//
+// The cluster barriers are hardware barriers (no spinning in this code); every CTA of a
+// cluster executes all four of them on every path.
+#include <cooperative_groups.h>
+
+#include <cstdlib>
+#include <cstring>
+
+#include "loda_append.cuh"
+#include "loda_select.cuh"
+
+namespace loda {
+
+namespace cg = cooperative_groups;
+
+LODA_PHASE_STORAGE(sel)
+LODA_SUB_READER(sel)
+
+constexpr int SF_P = 512;          // threads per CTA = pages per tile
+constexpr int SF_CLUSTER_MAX = 16; // CTAs per row: 16, or 8 when the GPU cannot hold a 16-CTA cluster for every row
+constexpr int SF_L2_NT = 256;      // threads of the leader that run the level-2 selection
+
+struct FusedLayout {
+  size_t rows_bytes, qv, kept, physk, keys, wtot, scan, sh, scall, total;
+};
+
+__host__ __device__ inline FusedLayout fused_layout(const loda_geometry& g, int tiles_per_cta, int cluster_size) {
+  const int G = g.num_q_heads / g.num_kv_heads;
+  const int np_max = g.k_far + g.k_near + 2;
+  FusedLayout f;
+  const size_t rows = (size_t)SF_P * (4 * g.sub_dims + 16);
+  f.rows_bytes = rows > L1_TAIL_BYTES ? rows : L1_TAIL_BYTES;
+  size_t off = f.rows_bytes * (tiles_per_cta > 1 ? 2 : 1);      // two staging buffers when a CTA has several tiles
+  f.qv = off; off += (size_t)(3 * G + 1) * g.sub_dims * 4;             // qhat, qlow, qhigh [G][d'], qf [d']
+  f.kept = off; off += (size_t)np_max * 4;
+  f.physk = off; off += (size_t)np_max * 4;
+  off = (off + 15) & ~(size_t)15;
+  f.keys = off; off += (size_t)(2 * SF_P + 8) * 4;
+  f.wtot = off; off += 256 * 4;
+  f.scan = off; off += 40 * 4;
+  f.sh = off; off += 8 * 4;
+  off = (off + 15) & ~(size_t)15;
+  f.scall = off; off += (size_t)tiles_per_cta * cluster_size * SF_P * 2 + 16;   // every page score of the row
+  f.total = off;
+  return f;
+}
+
+// bytes of the level-2 arrays the leader lays over the staging rows
+__host__ __device__ inline size_t fused_l2_bytes(const loda_geometry& g) {
+  const size_t np_max = g.k_far + g.k_near + 2;
+  return ((np_max * g.page * 2 + 15) & ~(size_t)15) + 2 * (size_t)g.level2_topk * 4 + g.level2_topk + 32;
+}
+
+template <int DSUB>
+__global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, loda_layer L, loda_batch B,
+                                                            const bf16* __restrict__ q, float scale, loda_selection S,
+                                                            uint32_t* status, AppendArgs ap, int tiles_per_cta) {
+  constexpr int P = SF_P;
+  constexpr int NC = DSUB / 8, CPR = 2 * NC, ROWB = 4 * DSUB + 16;
+  extern __shared__ __align__(16) unsigned char smem[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int CS = (int)cluster.num_blocks();
+  const FusedLayout lay = fused_layout(g, tiles_per_cta, CS);
+  const int G = g.num_q_heads / g.num_kv_heads;
+  unsigned char* rows = smem;
+  float* qhat = (float*)(smem + lay.qv);
+  float* qlow = qhat + G * DSUB;
+  float* qhigh = qlow + G * DSUB;
+  float* qf = qhigh + G * DSUB;
+  int* kept = (int*)(smem + lay.kept);
+  int* physk = (int*)(smem + lay.physk);
+  uint32_t* keys = (uint32_t*)(smem + lay.keys);
+  int* wtot = (int*)(smem + lay.wtot);
+  int* scan = (int*)(smem + lay.scan);
+  int* sh = (int*)(smem + lay.sh);
+  uint16_t* scall = (uint16_t*)(smem + lay.scall);
+
+  const int tid = threadIdx.x;
+  const int rank = (int)cluster.block_rank();        // = blockIdx.x: the cluster spans the grid's x
+  const int row = blockIdx.y;
+  const int b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
+  const int cta_id = blockIdx.y * gridDim.x + blockIdx.x;
+  // the leader's copies of what the cluster shares
+  uint16_t* l_scall = cluster.map_shared_rank(scall, 0);
+  int* l_kept = cluster.map_shared_rank(kept, 0);
+  int* l_physk = cluster.map_shared_rank(physk, 0);
+  int* l_sh = cluster.map_shared_rank(sh, 0);
+  uint16_t* l_sc2 = (uint16_t*)cluster.map_shared_rank(rows, 0);       // level-2 scores, over the leader's rows
+
+  LODA_PHASE(sel, cta_id, 0);
+  pdl_wait();
+  // this thread's first query element is requested before anything that depends on the
+  // request's length, so that the two global round trips overlap
+  const int nq = G * DSUB;
+  float q_first = 0.0f;
+  if (tid < nq)
+    q_first = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + tid / DSUB) * g.head_dim + sub_dim(g, tid % DSUB)]);
+  const long long act = B.active_req_ids[b];
+  const int len_raw = B.lengths[b];
+  const int req = (int)B.valid_req_ids[b];
+  const int length = act >= 0 ? len_raw : 0;
+  const Regions rg = make_regions(g, length);
+  const size_t pg0 = ((size_t)req * g.num_kv_heads + kv) * g.max_blocks;
+  const unsigned char* mm_base = (const unsigned char*)L.page_mm + pg0 * (4 * DSUB);
+  const unsigned char* sum_base = (const unsigned char*)L.page_sum + pg0 * (2 * DSUB);
+  const int page_end = min(rg.kt_eff, g.max_blocks);
+
+  // ---- level 1: score this CTA's tiles (rank, rank + CS, ...), two staging buffers ------------
+  auto stage = [&](int it) {
+    const int p0 = (rank + it * CS) * P;
+    unsigned char* dst = rows + (size_t)(it & 1) * lay.rows_bytes;
+    if (it < tiles_per_cta && p0 < page_end) {
+      for (int c = tid; c < P * CPR; c += P) {
+        const int pl = c / CPR, cc = c % CPR;
+        const int page = p0 + pl;
+        if (in_far_pool(rg, page)) {
+          cp_async16(dst + (size_t)pl * ROWB + cc * 16, mm_base + (size_t)page * (4 * DSUB) + cc * 16, true);
+        } else if (cc < NC && in_near_pool(rg, page)) {
+          cp_async16(dst + (size_t)pl * ROWB + cc * 16, sum_base + (size_t)page * (2 * DSUB) + cc * 16, true);
+        }
+      }
+    }
+    cp_async_commit();                                   // one group per tile index, empty when there is no tile
+  };
+  stage(0);
+  stage(1);
+  // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
+  for (int i = tid; i < nq; i += P) {
+    const int j = i / DSUB, d = i % DSUB;
+    const float qv = i == tid ? q_first
+                              : __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, d)]);
+    const float qh = bf16r(__fmul_rn(qv, scale));
+    qhat[i] = qh;
+    qlow[i] = fminf(qh, 0.0f);
+    qhigh[i] = fmaxf(qh, 0.0f);
+  }
+  // grouped query of level 2 (head order, fp32): needed by every CTA, with or without tiles
+  if (tid < DSUB) {
+    float acc = 0.0f;
+    for (int j = 0; j < G; ++j) {
+      const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, tid)]);
+      acc = __fadd_rn(acc, bf16r(__fmul_rn(qv, scale)));
+    }
+    qf[tid] = acc;
+  }
+  cluster.sync();       // (0) every CTA of the cluster runs: its shared memory may be addressed from now on
+  for (int it = 0; it < tiles_per_cta; ++it) {
+    const int p0 = (rank + it * CS) * P;
+    if (p0 >= page_end) break;
+    cp_async_wait<1>();                                  // tile it has landed (tile it + 1 may be in flight)
+    __syncthreads();
+    const int page = p0 + tid;
+    const unsigned char* src = rows + (size_t)(it & 1) * lay.rows_bytes;
+    const uint32_t ord = l1_page_score<DSUB>(g, rg, page, src + (size_t)tid * ROWB, qhat, qlow, qhigh, G);
+    l_scall[page] = (uint16_t)ord;                       // into the leader's shared memory
+    __syncthreads();                                     // the buffer is free
+    stage(it + 2);
+  }
+  cp_async_wait<0>();
+  LODA_PHASE(sel, cta_id, 1);
+  cluster.sync();                                        // (1) all page scores are in the leader
+  LODA_PHASE(sel, cta_id, 2);
+
+  if (rank == 1 && ap.enabled && tid < 32) {
+    // The decode append of the row.  It touches only the newest token and its page, which lie
+    // in the sliding window and are read by neither level of this step; the attention kernel
+    // runs after this launch completes.
+    append_row<DSUB>(g, L, B, ap.k_new, ap.v_new, ap.slots, ap.status, b, kv, tid);
+  }
+  const int32_t* table = L.block_table + (size_t)req * g.max_blocks;
+  if (rank == 0) {
+    // far row = the row's scores in place (zero outside the far pool), near row copied out first
+    const int near_hi = min(min(rg.swa_lo_blk, rg.kt_eff), g.max_blocks);
+    const int far_lo = rg.far_lo, far_hi = max(rg.far_hi, rg.far_lo);
+    const int near_lo = rg.near_blks, near_lo8 = near_lo & ~7;
+    const int n_far = far_hi;
+    const int n_near = near_hi > near_lo ? min(near_hi - near_lo8, L1_NEAR_CAP) : 0;
+    uint16_t* scf = scall;
+    uint16_t* scn = (uint16_t*)(rows + 40 * 1024);
+    for (int i = tid; i < ((n_near + 7) & ~7); i += P) {
+      const int pgi = near_lo8 + i;
+      scn[i] = (pgi >= near_lo && pgi < near_hi) ? scall[pgi] : (uint16_t)0;
+    }
+    __syncthreads();
+    for (int i = tid; i < far_lo; i += P) scf[i] = 0;
+    for (int i = far_hi + tid; i < ((n_far + 7) & ~7); i += P) scf[i] = 0;
+    __syncthreads();
+    LODA_PHASE(sel, cta_id, 3);
+    const int np = l1_select_pages<P, false>(g, rg, S, row, scf, scn, n_far, far_lo, n_near, near_lo, near_lo8, near_hi,
+                                             kept, keys, wtot, sh);
+    for (int i = tid; i < np; i += P) {
+      const int pg = kept[i];
+      int ph = (pg >= 0 && pg < g.max_blocks) ? table[pg] : -1;
+      if (ph < 0 || ph >= g.num_pages) ph = -1;
+      physk[i] = ph;
+    }
+    if (tid == 0) sh[4] = np;
+    LODA_PHASE(sel, cta_id, 4);
+  }
+  cluster.sync();                                        // (2) page list and physical pages are in the leader
+  LODA_PHASE(sel, cta_id, 5);
+
+  // ---- level 2: score this CTA's share of the candidate slots ---------------------------------
+  const int np_max = g.k_far + g.k_near + 2;
+  const int np = min(l_sh[4], np_max);
+  const int nitems = np * g.page;
+  {
+    const int per = ((nitems + CS - 1) / CS + 7) & ~7;
+    const int lo = min(rank * per, nitems), hi = min(lo + per, nitems);
+    for (int idx = lo + tid; idx < hi; idx += P) {
+      const int i = idx / g.page, o = idx % g.page;
+      const int pg = l_kept[i], ph = l_physk[i];
+      l_sc2[idx] = (uint16_t)l2_slot_score<DSUB>(g, L, rg, length, kv, pg, ph, o, qf, status);
+    }
+  }
+  LODA_PHASE(sel, cta_id, 6);
+  cluster.sync();                                        // (3) all candidate scores are in the leader
+  if (rank != 0 || tid >= SF_L2_NT) return;
+  LODA_PHASE(sel, cta_id, 7);
+
+  // ---- leader, first 256 threads: quota selection, hole fill, union, gather list --------------
+  {
+    const int K2 = g.level2_topk;
+    size_t off = ((size_t)np_max * g.page * 2 + 15) & ~(size_t)15;     // behind the scores
+    L2Shared shm;
+    shm.sc = (uint16_t*)rows;
+    shm.pages = kept;
+    shm.physs = physk;
+    shm.mid_a = (int*)(rows + off); off += (size_t)K2 * 4;
+    shm.mid_b = (int*)(rows + off); off += (size_t)K2 * 4;
+    shm.win = (uint8_t*)(rows + off);
+    shm.wtot = wtot;
+    shm.scan = scan;
+    l2_select_and_write<SF_L2_NT, 1, true>(g, rg, S, status, table, b, kv, row, length, nitems, shm, nullptr);
+  }
+  LODA_PHASE(sel, cta_id, 9);
+}
+
+static bool g_fused_refused[3] = {false, false, false};    // per sub-space width: a launch failed, stay on the chain
+
+static int fused_slot(int sub_dims) { return sub_dims == 16 ? 0 : sub_dims == 32 ? 1 : 2; }
+
+static int fused_tiles_per_cta(const loda_geometry& g, int cs) {
+  const int ntiles = (g.max_blocks + SF_P - 1) / SF_P;
+  return (ntiles + cs - 1) / cs;
+}
+
+static bool fused_shape_ok(const loda_geometry& g, int cs) {
+  const FusedLayout lay = fused_layout(g, fused_tiles_per_cta(g, cs), cs);
+  return lay.total <= 220 * 1024 && fused_l2_bytes(g) <= lay.rows_bytes;     // the level-2 arrays overlay the rows
+}
+
+// whether the fused launch may serve this geometry and batch (the launch itself still asks the
+// GPU how many clusters of the shape it can hold)
+bool select_fused_applicable(const loda_geometry& g, int rows) {
+  // LODA_B200_SELECT_PATH=split forces the two-launch chain (A/B measurements, tests of both paths)
+  const char* path = getenv("LODA_B200_SELECT_PATH");
+  if (path && strcmp(path, "split") == 0) return false;
+  if (g.sub_dims != 16 && g.sub_dims != 32 && g.sub_dims != 64) return false;
+  if (g_fused_refused[fused_slot(g.sub_dims)]) return false;
+  if (rows < 1 || rows * 8 > 148) return false;                              // one round of clusters of 8 at least
+  if ((size_t)g.max_blocks * 2 + 16 > 40 * 1024) return false;
+  return fused_shape_ok(g, 16) || fused_shape_ok(g, 8);
+}
+
+template <int DS>
+static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
+                                  float scale, const loda_selection& S, uint32_t* status, const AppendArgs& ap,
+                                  cudaStream_t st) {
+  const int rows = B.batch * g.num_kv_heads;
+  auto kernel = select_fused_kernel<DS>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (e != cudaSuccess) return e;
+  // clusters of 16 CTAs when the GPU holds one for every row at once, else clusters of 8 (two tiles
+  // per CTA at 128K tokens); the answers are remembered per shape
+  struct Memo { size_t smem; int rows_ok; };
+  static Memo memo[3][2] = {};
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  cfg.blockDim = dim3(SF_P);
+  cfg.stream = st;
+  for (int which = 0; which < 2; ++which) {
+    const int cs = which == 0 ? 16 : 8;
+    if (!fused_shape_ok(g, cs) || rows * cs > 148) continue;
+    const int tpc = fused_tiles_per_cta(g, cs);
+    const size_t smem = fused_layout(g, tpc, cs).total;
+    e = set_kernel_smem(kernel, smem);
+    if (e != cudaSuccess) return e;
+    cfg.gridDim = dim3(cs, rows);
+    cfg.dynamicSmemBytes = smem;
+    attr[1].val.clusterDim.x = cs;
+    Memo& m = memo[fused_slot(DS)][which];
+    if (m.smem != smem) {
+      int nclusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&nclusters, kernel, &cfg) != cudaSuccess) { (void)cudaGetLastError(); nclusters = 0; }
+      m.smem = smem;
+      m.rows_ok = nclusters;
+    }
+    if (rows > m.rows_ok) continue;                      // the clusters of all rows must run at once
+    return cudaLaunchKernelEx(&cfg, kernel, g, L, B, (const bf16*)q, scale, S, status, ap, tpc);
+  }
+  return cudaErrorNotSupported;
+}
+
+void select_fused_refuse(int sub_dims) { g_fused_refused[fused_slot(sub_dims)] = true; }
+
+// cudaErrorNotSupported = the caller launches the two-kernel chain instead
+cudaError_t launch_select_fused(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
+                                float scale, const loda_selection& S, uint32_t* status, const AppendArgs& ap,
+                                cudaStream_t st) {
+  switch (g.sub_dims) {
+    case 16: return launch_fused_d<16>(g, L, B, q, scale, S, status, ap, st);
+    case 32: return launch_fused_d<32>(g, L, B, q, scale, S, status, ap, st);
+    case 64: return launch_fused_d<64>(g, L, B, q, scale, S, status, ap, st);
+    default: return cudaErrorNotSupported;
+  }
+}
+
+}  // namespace loda
