@@ -589,12 +589,14 @@ def main():
                          "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                          # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel on
                          # this workload (profiles/fused_chain_cfg2_128k_batch1.md); not measured live
-                         "traffic": None},
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the selector launch on
+                         # this workload (profiles/fused_chain_cfg2_128k_batch1.md); not measured live
+                         "traffic": 8821504 if dominant == "select" else None},
             "dense_decode": {"us_per_layer": dense_us, "note": dense_note,
                              "ours_over_dense": (us_layer / dense_us) if dense_us else None},
             "e2e": {"value": (1 if kvhead else world) * 1e3 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": K * N_LAYERS * 3, "device_status": status, "clocks": clocks,
+            "gpu_launches": K * N_LAYERS * 2,      # selector (one launch at this batch) + attention per layer-step "device_status": status, "clocks": clocks,
         }
         if not args.skip_batched and not kvhead:
             del wl, runner, cache

@@ -98,6 +98,10 @@ __device__ __forceinline__ bool in_near_pool(const Regions& r, int t) {
   return true;
 }
 
+#ifndef LODA_BISECT_INLINE
+#define LODA_BISECT_INLINE __forceinline__
+#endif
+
 // Barrier of a thread group: BAR = 0 is the whole CTA (__syncthreads); BAR > 0 is the named
 // barrier BAR over the CTA's first NT threads, for routines that run on a part of a larger CTA.
 template <int NT, int BAR>
@@ -375,7 +379,7 @@ __device__ __forceinline__ int block_compact_threshold(const uint16_t* sc, int n
 // chains), one barrier publishes the block sums.
 // wtot: 6 x 32 ints (16-byte aligned).
 template <int NT, int BAR = 0, int TBASE = 0>
-__device__ __forceinline__ int block_bisect_topk(const uint16_t* sc, int n, int k, int* out, int* wtot) {
+__device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, int k, int* out, int* wtot) {
   constexpr int NW = NT / 32;
   constexpr int MAXC = 4;                        // chunks a thread keeps in registers
   const int tid = ((int)threadIdx.x - TBASE), lane = tid & 31, warp = tid >> 5;
