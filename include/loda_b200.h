@@ -69,6 +69,8 @@ typedef struct loda_geometry {
   int32_t swa;            /* sliding window, a multiple of `page` */
   int32_t near_len;       /* region geometry `near` */
   int32_t pool_near_len;  /* near candidate-pool span in tokens */
+  int32_t shard_rank;     /* sequence sharding: this GPU owns the logical pages p with        */
+  int32_t shard_count;    /* p % shard_count == shard_rank; 0 or 1 = not sharded              */
 } loda_geometry;
 
 /* Per-layer device buffers.
@@ -235,6 +237,37 @@ int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda
                      const void* q, const void* k_new, const void* v_new, const int32_t* slots,
                      float scale, const loda_selection* sel, const int32_t* query_to_req,
                      void* out, uint32_t* status, void* workspace, void* stream);
+
+/* ---- sequence sharding (batch-1 long context over several GPUs) ---------------
+ * No counterpart in the reference's code; the mode is described by the task's
+ * specification: logical page p belongs to GPU p % shard_count (geometry.shard_rank /
+ * shard_count), whose block table holds -1 for the pages of the others.  The selector
+ * runs in four stages; between the stages the caller combines the score rows of the
+ * GPUs with a bitwise OR (every page / slot is scored by exactly one GPU, the others
+ * hold 0), e.g. an all-gather over NCCL.  With identical combined scores every GPU
+ * selects the same pages and tokens as a single GPU would; its gather list holds -1
+ * for tokens on pages it does not own, its attention (loda_gather_attend_lse) covers
+ * its own tokens, and the partial outputs merge by log-sum-exp. */
+
+/* out[0], out[1] = byte offset and size of the level-1 score rows in the workspace,
+ * out[2], out[3] = of the level-2 score rows (both uint16, 0 = not scored here). */
+int loda_shard_workspace_regions(const loda_geometry* g, int64_t* out);
+
+/* level 1: scores of this GPU's pages -> workspace | selection on the combined scores */
+int loda_shard_l1_scores(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
+                         const void* q, float scale, const loda_selection* sel, void* workspace,
+                         void* stream);
+int loda_shard_l1_select(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
+                         const void* q, float scale, const loda_selection* sel, void* workspace,
+                         void* stream);
+/* level 2: logits of the candidate slots on this GPU's pages -> workspace | quota
+ * selection, hole fill and union on the combined logits -> gather, visible_lens */
+int loda_shard_l2_scores(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
+                         const void* q, float scale, const loda_selection* sel, uint32_t* status,
+                         void* workspace, void* stream);
+int loda_shard_l2_select(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
+                         const void* q, float scale, const loda_selection* sel, uint32_t* status,
+                         void* workspace, void* stream);
 
 /* ---- kernels under the TIA indexer's method surface -------------------------
  * (sparse_attn/indexer/tia_indexer.py; tensors bf16 or fp32, dtype = LODA_DTYPE_*) */

@@ -350,3 +350,67 @@ def test_other_geometries_match_oracle(page, overrides, lengths):
     setup = make_setup(lengths, seed=8, page=page, selector_overrides=overrides, max_visible=mv)
     out = _run_step(setup)
     _check_against_oracle(setup, out)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sequence_sharded_selector_and_attention_equal_the_single_gpu_path(world):
+    """Sequence sharding emulated on one GPU: `world` views of the same cache, each owning the
+    logical pages p % world == rank, run the staged selector in lockstep; the score rows are
+    combined with the OR the all-gather path uses.  Every view must select exactly the single-GPU
+    token list (with -1 at the other views' tokens), and the log-sum-exp merge of the partial
+    attentions must equal the single-GPU attention."""
+    from helpers import make_setup, mod
+    sharding = mod("sharding")
+    setup = make_setup([9000, 300, 20000], seed=11)
+    ref_out = _run_step(setup)                      # single-GPU path; also appends the step's token
+    cache = setup.cache
+    ref_gather = cache.gather_indices_for_layer(0).clone()
+    ref_lens = cache.visible_lens_for_layer(0).clone()
+    b = len(setup.req_ids)
+    q, scale = setup.q.contiguous(), float(setup.attention.scaling)
+    views = [sharding.SequenceShard(cache, setup.indexer, r, world) for r in range(world)]
+
+    def combine(rows):
+        out = rows[0].clone()
+        for r in rows[1:]:
+            out |= r
+        return out
+
+    for v in views:
+        v.l1_scores_stage(0, b, q, scale)
+    both = combine([v.l1_scores for v in views])
+    for v in views:
+        v.l1_scores.copy_(both)
+        v.l1_select_stage(0, b, q, scale)
+        v.l2_scores_stage(0, b, q, scale)
+    both = combine([v.l2_scores for v in views])
+    outs, lses = [], []
+    for v in views:
+        v.l2_scores.copy_(both)
+        v.l2_select_stage(0, b, q, scale)
+        o, l = v.attend_stage(0, b, q, scale)
+        outs.append(o.float())
+        lses.append(l)
+    torch.cuda.synchronize()
+    assert cache.read_status() == 0
+    page = setup.page
+    table = cache.block_table_buf[0]
+    for v in views:
+        assert torch.equal(v.visible_lens[:b], ref_lens[:b])
+    n = int(ref_lens[:b].max())
+    stacked = torch.stack([v.gather[:b, :, :n] for v in views])           # [world, B, Hkv, n]
+    valid = torch.arange(n, device=stacked.device)[None, None, :] < ref_lens[:b, :, None]
+    owned = (stacked >= 0) & valid
+    assert int(owned.sum(0).max()) == 1 and bool((owned.sum(0) == 1)[valid].all())   # every token on exactly one view
+    merged_list = stacked.clamp_min(-1).max(0).values
+    assert torch.equal(merged_list[valid], ref_gather[:b, :, :n][valid])
+    # ownership follows the logical page of the token: slot -> physical page -> logical page
+    for r, v in enumerate(views):
+        for bi, rid in enumerate(setup.req_ids):
+            slots = v.gather[bi, :, :n][owned[r, bi]]
+            phys = (slots // page).cpu()
+            logical = {int(p): i for i, p in enumerate(table[rid].cpu().tolist()) if p >= 0}
+            assert all(logical[int(p)] % world == r for p in phys.tolist())
+    lse = torch.stack(lses)
+    merged = sharding.lse_merge(torch.stack(outs), lse[..., 0], lse[..., 1])
+    torch.testing.assert_close(merged, ref_out.float(), atol=ATOL, rtol=RTOL)

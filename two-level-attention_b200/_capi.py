@@ -31,7 +31,7 @@ class Geometry(C.Structure):
         "dtype", "num_q_heads", "num_kv_heads", "head_dim", "head_dim_v", "sub_dims",
         "sub_lo0", "sub_lo1", "page", "num_pages", "max_blocks", "max_requests",
         "max_query_tokens", "max_visible", "k_far", "k_near", "level2_topk", "sink", "swa",
-        "near_len", "pool_near_len")]
+        "near_len", "pool_near_len", "shard_rank", "shard_count")]
 
 
 class Layer(C.Structure):
@@ -53,7 +53,9 @@ EXPORTS = ("loda_version", "loda_last_error", "loda_workspace_bytes", "loda_appe
            "loda_write_prefill", "loda_build_index", "loda_select_l1", "loda_select_l2",
            "loda_gather_attend", "loda_decode_step", "loda_gather_attend_static",
            "loda_select_step", "loda_tia_quant4", "loda_tia_block_minmax", "loda_tia_scores", "loda_gather_attend_lse",
-           "loda_tls_store_kv", "loda_tls_store_k_index", "loda_tls_level1", "loda_tls_level2")
+           "loda_tls_store_kv", "loda_tls_store_k_index", "loda_tls_level1", "loda_tls_level2",
+           "loda_shard_workspace_regions", "loda_shard_l1_scores", "loda_shard_l1_select", "loda_shard_l2_scores",
+           "loda_shard_l2_select")
 
 _lib = None
 
@@ -92,6 +94,11 @@ def lib():
     L.loda_tls_store_k_index.argtypes = [P, P, P, P, P, I, I, I, I, I, I, I, I, I, V]
     L.loda_tls_level1.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, V]
     L.loda_tls_level2.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, V]
+    L.loda_shard_workspace_regions.argtypes = [G, P]
+    L.loda_shard_l1_scores.argtypes = [G, LY, B, P, F, S, P, V]
+    L.loda_shard_l1_select.argtypes = [G, LY, B, P, F, S, P, V]
+    L.loda_shard_l2_scores.argtypes = [G, LY, B, P, F, S, P, P, V]
+    L.loda_shard_l2_select.argtypes = [G, LY, B, P, F, S, P, P, V]
     for name in EXPORTS[3:]:
         getattr(L, name).restype = C.c_int
     _lib = L

@@ -14,9 +14,9 @@ cudaError_t launch_build_index(const loda_geometry&, const loda_layer&, int, int
 cudaError_t launch_write_prefill(const loda_geometry&, const loda_layer&, const void*, const void*,
                                  const int32_t*, int, cudaStream_t);
 cudaError_t launch_l1(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
-                      const loda_selection&, const SelectWorkspace&, const AppendArgs&, cudaStream_t);
+                      const loda_selection&, const SelectWorkspace&, const AppendArgs&, int, cudaStream_t);
 cudaError_t launch_l2(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
-                      const loda_selection&, const SelectWorkspace&, uint32_t*, bool, cudaStream_t);
+                      const loda_selection&, const SelectWorkspace&, uint32_t*, bool, int, cudaStream_t);
 int l1_score_stride(const loda_geometry&);
 bool select_fused_applicable(const loda_geometry&, int);
 void select_fused_refuse(int);
@@ -93,6 +93,8 @@ static int check_geometry(const loda_geometry* g) {
   if (!g) return fail(LODA_ERR_ARGUMENT, "geometry is NULL");
   if (g->dtype != LODA_DTYPE_BF16)
     return fail(LODA_ERR_UNSUPPORTED, "only bf16 KV pools are implemented (dtype=%d)", g->dtype);
+  if (g->shard_count < 0 || (g->shard_count > 1 && (g->shard_rank < 0 || g->shard_rank >= g->shard_count)))
+    return fail(LODA_ERR_ARGUMENT, "shard_rank must be in [0, shard_count)");
   if (g->num_kv_heads < 1 || g->num_q_heads % g->num_kv_heads)
     return fail(LODA_ERR_ARGUMENT, "GQA requires num_q_heads %% num_kv_heads == 0");
   const int G = g->num_q_heads / g->num_kv_heads;
@@ -233,7 +235,7 @@ int loda_select_l1(const loda_geometry* g, const loda_layer* layer, const loda_b
   if (out->i_far && (!out->i_near || !out->n_far || !out->n_near))
     return fail(LODA_ERR_ARGUMENT, "i_far, n_far, i_near, n_near are given together or not at all");
   const AppendArgs none{nullptr, nullptr, nullptr, nullptr, 0};
-  return check_cuda(launch_l1(*g, *layer, *b, q, scale, *out, select_ws(*g, workspace), none, (cudaStream_t)stream),
+  return check_cuda(launch_l1(*g, *layer, *b, q, scale, *out, select_ws(*g, workspace), none, 0, (cudaStream_t)stream),
                     "select_l1");
 }
 
@@ -254,6 +256,8 @@ int loda_select_step(const loda_geometry* g, const loda_layer* layer, const loda
     return fail(LODA_ERR_ARGUMENT, "k_new, v_new and slots go together (all NULL = refresh the index only)");
   const SelectWorkspace ws = select_ws(*g, workspace);
   const AppendArgs ap{(const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, slots, status, 1};
+  if (g->shard_count > 1)
+    return fail(LODA_ERR_ARGUMENT, "sequence-sharded geometries use the staged selector (loda_shard_*)");
   if (select_fused_applicable(*g, b->batch * g->num_kv_heads)) {
     // one launch for both levels (a cluster per row); refused shapes fall through to the two-launch chain
     const cudaError_t e = launch_select_fused(*g, *layer, *b, q, scale, *sel, status, ap, (cudaStream_t)stream);
@@ -266,8 +270,8 @@ int loda_select_step(const loda_geometry* g, const loda_layer* layer, const loda
       select_fused_refuse(g->sub_dims);
     }
   }
-  LODA_TRY(check_cuda(launch_l1(*g, *layer, *b, q, scale, *sel, ws, ap, (cudaStream_t)stream), "select_step/l1"));
-  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, ws, status, /*chained=*/true, (cudaStream_t)stream),
+  LODA_TRY(check_cuda(launch_l1(*g, *layer, *b, q, scale, *sel, ws, ap, 0, (cudaStream_t)stream), "select_step/l1"));
+  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, ws, status, /*chained=*/true, 0, (cudaStream_t)stream),
                     "select_step/l2");
 }
 
@@ -281,7 +285,7 @@ int loda_select_l2(const loda_geometry* g, const loda_layer* layer, const loda_b
     return fail(LODA_ERR_ARGUMENT, "L2 needs q, gather, visible_lens and the workspace L1 ran on");
   if ((sel->middle == nullptr) != (sel->middle_counts == nullptr))
     return fail(LODA_ERR_ARGUMENT, "middle and middle_counts must be given together");
-  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, select_ws(*g, workspace), status, /*chained=*/false,
+  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, select_ws(*g, workspace), status, /*chained=*/false, 0,
                               (cudaStream_t)stream),
                     "select_l2");
 }
@@ -316,6 +320,59 @@ int loda_gather_attend(const loda_geometry* g, const loda_layer* layer, const vo
                        int32_t n_req_rows, float scale, void* out, void* workspace, void* stream) {
   return gather_attend_impl(g, layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale, out,
                             nullptr, workspace, /*chained=*/false, stream);
+}
+
+// ---- sequence sharding: the selector in four stages, the caller combines the score rows of the
+// ---- GPUs (bitwise OR: every page and every slot is scored by exactly one of them) in between
+int loda_shard_workspace_regions(const loda_geometry* g, int64_t* out) {
+  LODA_TRY(check_geometry(g));
+  if (!out) return fail(LODA_ERR_ARGUMENT, "out is NULL");
+  const WsLayout w = ws_layout(*g);
+  const size_t rows = (size_t)g->max_query_tokens * g->num_kv_heads;
+  out[0] = (int64_t)w.l1_scores;
+  out[1] = (int64_t)(rows * (size_t)l1_score_stride(*g) * 2);
+  out[2] = (int64_t)w.l2_scores;
+  out[3] = (int64_t)(rows * (size_t)(g->k_far + g->k_near + 2) * g->page * 2);
+  return LODA_OK;
+}
+
+static int shard_stage(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q, float scale,
+                       const loda_selection* sel, uint32_t* status, void* workspace, void* stream, int level,
+                       int phase) {
+  LODA_TRY(check_geometry(g));
+  LODA_TRY(check_layer(layer));
+  LODA_TRY(check_batch(g, b));
+  if (g->shard_count < 2) return fail(LODA_ERR_ARGUMENT, "the staged selector is for shard_count >= 2");
+  if (b->batch == 0) return LODA_OK;
+  if (!q || !sel || !workspace) return fail(LODA_ERR_ARGUMENT, "staged selector needs q, a selection struct and a workspace");
+  if (level == 2 && phase == 2 && (!sel->gather || !sel->visible_lens))
+    return fail(LODA_ERR_ARGUMENT, "the level-2 selection needs gather and visible_lens");
+  const SelectWorkspace ws = select_ws(*g, workspace);
+  if (level == 1) {
+    const AppendArgs none{nullptr, nullptr, nullptr, nullptr, 0};
+    loda_selection no_lists = *sel;
+    no_lists.i_far = nullptr;                            // the best-first lists are not produced in this mode
+    return check_cuda(launch_l1(*g, *layer, *b, q, scale, no_lists, ws, none, phase, (cudaStream_t)stream), "shard/l1");
+  }
+  return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, ws, status, /*chained=*/false, phase, (cudaStream_t)stream),
+                    "shard/l2");
+}
+
+int loda_shard_l1_scores(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
+                         float scale, const loda_selection* sel, void* workspace, void* stream) {
+  return shard_stage(g, layer, b, q, scale, sel, nullptr, workspace, stream, 1, 1);
+}
+int loda_shard_l1_select(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
+                         float scale, const loda_selection* sel, void* workspace, void* stream) {
+  return shard_stage(g, layer, b, q, scale, sel, nullptr, workspace, stream, 1, 2);
+}
+int loda_shard_l2_scores(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
+                         float scale, const loda_selection* sel, uint32_t* status, void* workspace, void* stream) {
+  return shard_stage(g, layer, b, q, scale, sel, status, workspace, stream, 2, 1);
+}
+int loda_shard_l2_select(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
+                         float scale, const loda_selection* sel, uint32_t* status, void* workspace, void* stream) {
+  return shard_stage(g, layer, b, q, scale, sel, status, workspace, stream, 2, 2);
 }
 
 int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,

@@ -60,6 +60,7 @@ struct Regions {
   int swa_lo_blk, swa_lo_tok, swa_byp_blk;
   bool swa_byp, sink_byp;
   int lower, upper, quota, kt_cap;
+  int shard_rank, shard_count;   // sequence sharding: logical page p is scored here iff p % count == rank
 };
 
 __device__ __forceinline__ int cdiv_trunc(int a, int b) { return a / b; }  // C division truncates
@@ -84,18 +85,25 @@ __device__ __forceinline__ Regions make_regions(const loda_geometry& g, int leng
   r.upper = max(r.lower, r.swa_lo_tok);
   int q = max(min(length, g.level2_topk) - g.sink - (length - r.swa_lo_tok), 0);
   r.quota = min(q, r.upper - r.lower);
+  r.shard_rank = g.shard_rank;
+  r.shard_count = g.shard_count;
   return r;
 }
 
+__device__ __forceinline__ bool page_owned(const Regions& r, int t) {
+  return r.shard_count <= 1 || t % r.shard_count == r.shard_rank;
+}
+
+// (pool membership as this GPU scores it: under sequence sharding only the pages it owns)
 __device__ __forceinline__ bool in_far_pool(const Regions& r, int t) {
-  return t >= r.far_lo && t < r.far_hi;
+  return t >= r.far_lo && t < r.far_hi && page_owned(r, t);
 }
 
 __device__ __forceinline__ bool in_near_pool(const Regions& r, int t) {
   if (t < r.near_blks || t >= r.swa_lo_blk || t >= r.kt_eff || t >= r.kt_cap) return false;
   if (r.swa_byp && t == r.swa_byp_blk) return false;
   if (r.sink_byp && t == r.spl) return false;
-  return true;
+  return page_owned(r, t);
 }
 
 #ifndef LODA_BISECT_INLINE

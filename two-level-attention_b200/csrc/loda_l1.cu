@@ -33,7 +33,7 @@ template <int DSUB, int P>
 __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, loda_batch B,
                                                 const bf16* __restrict__ q, float scale,
                                                 loda_selection out, SelectWorkspace ws, int nsplit,
-                                                int tiles_per_cta, AppendArgs ap) {
+                                                int tiles_per_cta, AppendArgs ap, int phase) {
   constexpr int NC = DSUB / 8;            // 8-dim chunks per statistic
   constexpr int CPR = 2 * NC;             // 16-byte chunks per min/max row
   constexpr int ROWB = 4 * DSUB + 16;     // padded row: conflict-free 16-byte reads
@@ -127,14 +127,18 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   }
   LODA_PHASE(l1, cta_id, 4);
 
-  // last CTA of the row selects
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) sh[0] = (atomicAdd(ws.l1_ticket + row, 1) == nsplit - 1);
-  __syncthreads();
-  LODA_PHASE(l1, cta_id, 5);
-  if (!sh[0]) return;
-  __threadfence();
+  // last CTA of the row selects.  phase 1 = scores only (the caller combines the score rows of
+  // several GPUs before the selection), phase 2 = selection only (one CTA per row, no tiles)
+  if (phase == 1) return;
+  if (phase == 0) {
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) sh[0] = (atomicAdd(ws.l1_ticket + row, 1) == nsplit - 1);
+    __syncthreads();
+    LODA_PHASE(l1, cta_id, 5);
+    if (!sh[0]) return;
+    __threadfence();
+  }
   // the staging rows are consumed: the row's scores are copied into two rows of
   // shared memory, one per pool, each holding 0 outside its pool
   const int near_hi = min(min(rg.swa_lo_blk, rg.kt_eff), g.max_blocks);
@@ -238,33 +242,39 @@ static void l1_split(const loda_geometry& g, int rows, int P, int* ctas_per_row,
 template <int DS, int P>
 static cudaError_t launch_l1_p(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                float scale, const loda_selection& out, const SelectWorkspace& ws,
-                               const AppendArgs& ap, cudaStream_t st) {
+                               const AppendArgs& ap, int phase, cudaStream_t st) {
   const int rows = B.batch * g.num_kv_heads;
   int nsplit, tpc;
   l1_split(g, rows, P, &nsplit, &tpc);
-  const dim3 grid(nsplit + (ap.enabled ? 1 : 0), rows);
+  dim3 grid(nsplit + (ap.enabled ? 1 : 0), rows);
+  if (phase == 2) {                 // selection only: one CTA per row and no tiles
+    grid = dim3(1, rows);
+    tpc = 0;
+  }
   const size_t smem = l1_smem_bytes_p(g, P);
   cudaError_t e = set_kernel_smem(l1_kernel<DS, P>, smem);
   if (e != cudaSuccess) return e;
   return launch_pdl(l1_kernel<DS, P>, grid, dim3(P), smem, st, g, L, B, (const bf16*)q, scale, out, ws, nsplit, tpc,
-                    ap);
+                    ap, phase);
 }
 
 template <int DS>
 static cudaError_t launch_l1_d(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                float scale, const loda_selection& out, const SelectWorkspace& ws,
-                               const AppendArgs& ap, cudaStream_t st) {
-  return l1_wide(g, B.batch * g.num_kv_heads) ? launch_l1_p<DS, L1_P_WIDE>(g, L, B, q, scale, out, ws, ap, st)
-                                              : launch_l1_p<DS, L1_P_NARROW>(g, L, B, q, scale, out, ws, ap, st);
+                               const AppendArgs& ap, int phase, cudaStream_t st) {
+  return l1_wide(g, B.batch * g.num_kv_heads)
+             ? launch_l1_p<DS, L1_P_WIDE>(g, L, B, q, scale, out, ws, ap, phase, st)
+             : launch_l1_p<DS, L1_P_NARROW>(g, L, B, q, scale, out, ws, ap, phase, st);
 }
 
+// phase 0: scores and selection; 1: scores only; 2: selection only (of the scores in the workspace)
 cudaError_t launch_l1(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                       float scale, const loda_selection& out, const SelectWorkspace& ws, const AppendArgs& ap,
-                      cudaStream_t st) {
+                      int phase, cudaStream_t st) {
   switch (g.sub_dims) {
-    case 16: return launch_l1_d<16>(g, L, B, q, scale, out, ws, ap, st);
-    case 32: return launch_l1_d<32>(g, L, B, q, scale, out, ws, ap, st);
-    case 64: return launch_l1_d<64>(g, L, B, q, scale, out, ws, ap, st);
+    case 16: return launch_l1_d<16>(g, L, B, q, scale, out, ws, ap, phase, st);
+    case 32: return launch_l1_d<32>(g, L, B, q, scale, out, ws, ap, phase, st);
+    case 64: return launch_l1_d<64>(g, L, B, q, scale, out, ws, ap, phase, st);
     default: return cudaErrorInvalidValue;
   }
 }

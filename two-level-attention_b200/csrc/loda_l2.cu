@@ -38,7 +38,7 @@ template <int DSUB, int NT>
 __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, loda_layer L, loda_batch B,
                                                  const bf16* __restrict__ q, float scale,
                                                  loda_selection S, SelectWorkspace ws, uint32_t* status,
-                                                 int nsplit, int chained) {
+                                                 int nsplit, int chained, int phase) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int np_max = g.k_far + g.k_near + 2;
   const int K2 = g.level2_topk;
@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
   // ---- score this CTA's share of the candidate slots ---------------------------
   {
     const int per = ((nitems + nsplit - 1) / nsplit + 7) & ~7;         // multiple of 8 slots
-    const int lo = min(split * per, nitems), hi = min(lo + per, nitems);
+    const int lo = min(split * per, nitems), hi = phase == 2 ? lo : min(lo + per, nitems);
     for (int idx = lo + tid; idx < hi; idx += NT) {
       const int i = idx / g.page, o = idx % g.page;
       const int pg = __ldcg(ws.pages + (size_t)row * np_max + i);
@@ -112,13 +112,18 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
   LODA_PHASE(l2, cta_id, 3);
 
   // ---- last CTA of the row selects ----------------------------------------------
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) sh[0] = (atomicAdd(ws.l2_ticket + row, 1) == nsplit - 1);
-  __syncthreads();
-  LODA_PHASE(l2, cta_id, 4);
-  if (!sh[0]) return;
-  __threadfence();
+  // phase 1 = scores only (the caller combines the score rows of several GPUs before the
+  // selection), phase 2 = selection only (one CTA per row, which scored nothing above)
+  if (phase == 1) return;
+  if (phase == 0) {
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) sh[0] = (atomicAdd(ws.l2_ticket + row, 1) == nsplit - 1);
+    __syncthreads();
+    LODA_PHASE(l2, cta_id, 4);
+    if (!sh[0]) return;
+    __threadfence();
+  }
   for (int i = tid; i < (nitems + 7) / 8; i += NT) ((uint4*)sc)[i] = __ldcg((const uint4*)row_scores + i);
   for (int i = tid; i < np; i += NT) {
     pages[i] = __ldcg(ws.pages + (size_t)row * np_max + i);
@@ -144,27 +149,27 @@ size_t l2_smem_bytes(const loda_geometry& g) {
 template <int DS>
 static cudaError_t launch_l2_d(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                float scale, const loda_selection& S, const SelectWorkspace& ws, uint32_t* status,
-                               bool chained, cudaStream_t st) {
+                               bool chained, int phase, cudaStream_t st) {
   // scoring CTAs per row: 8 at batch 1 (latency), one once the rows alone give every SM a CTA
   // (every CTA of a row pays the ticket; the row's selection runs in one CTA either way)
   const int rows = B.batch * g.num_kv_heads;
   int nsplit = (LODA_L2_CTAS_PER_SM * 148 + rows - 1) / rows;
   nsplit = nsplit < 1 ? 1 : nsplit > L2_SPLIT ? L2_SPLIT : nsplit;
-  const dim3 grid(nsplit, rows);
+  const dim3 grid(phase == 2 ? 1 : nsplit, rows);      // selection only: one CTA per row
   const size_t smem = l2_smem_bytes(g);
   cudaError_t e = set_kernel_smem(l2_kernel<DS, L2_NT>, smem);
   if (e != cudaSuccess) return e;
   return launch_pdl(l2_kernel<DS, L2_NT>, grid, dim3(L2_NT), smem, st, g, L, B, (const bf16*)q, scale, S, ws, status,
-                    nsplit, (int)chained);
+                    nsplit, (int)chained, phase);
 }
 
 cudaError_t launch_l2(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                       float scale, const loda_selection& S, const SelectWorkspace& ws, uint32_t* status,
-                      bool chained, cudaStream_t st) {
+                      bool chained, int phase, cudaStream_t st) {
   switch (g.sub_dims) {
-    case 16: return launch_l2_d<16>(g, L, B, q, scale, S, ws, status, chained, st);
-    case 32: return launch_l2_d<32>(g, L, B, q, scale, S, ws, status, chained, st);
-    case 64: return launch_l2_d<64>(g, L, B, q, scale, S, ws, status, chained, st);
+    case 16: return launch_l2_d<16>(g, L, B, q, scale, S, ws, status, chained, phase, st);
+    case 32: return launch_l2_d<32>(g, L, B, q, scale, S, ws, status, chained, phase, st);
+    case 64: return launch_l2_d<64>(g, L, B, q, scale, S, ws, status, chained, phase, st);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -247,7 +247,7 @@ __device__ __forceinline__ uint32_t l2_slot_score(const loda_geometry& g, const 
     const __nv_bfloat162 sz = *(const __nv_bfloat162*)((const bf16*)L.tail_sz + trow * 2);
     const float lg = l2_logit<DSUB>((const uint8_t*)L.tail_code + trow * (DSUB / 2), __low2float(sz), __high2float(sz), qf);
     if (lg == lg && lg != -INFINITY) ord = ord16(lg);
-  } else if (ph < 0 && status) {
+  } else if (ph < 0 && status && rg.shard_count <= 1) {     // under sequence sharding a missing page is another GPU's
     atomicOr(status, LODA_STATUS_BAD_PAGE);
   }
   return ord;
@@ -294,17 +294,22 @@ __device__ __forceinline__ void l2_select_and_write(const loda_geometry& g, cons
       int slot;
       if (i >= sk && i < sk + take) {
         const int sl = slots_sel[i - sk];
-        slot = physs[sl / g.page] * g.page + sl % g.page;
+        const int ph = physs[sl / g.page];                 // -1: the page lives on another GPU (sequence sharding)
+        slot = ph >= 0 ? ph * g.page + sl % g.page : -1;
         if (S.middle != nullptr) S.middle[(size_t)row * K2 + (i - sk)] = pages[sl / g.page] * g.page + sl % g.page;
       } else {
         const int id = i < sk ? i : s_lo + (i - sk - take);
         const int lp = id / g.page;
         int ph = lp < g.max_blocks ? table[lp] : -1;
         if (ph < 0 || ph >= g.num_pages) {
-          if (status) atomicOr(status, LODA_STATUS_BAD_PAGE);
-          ph = g.num_pages - 1;
+          if (rg.shard_count > 1) {
+            ph = -1;                                         // another GPU's page: skipped by the attention
+          } else {
+            if (status) atomicOr(status, LODA_STATUS_BAD_PAGE);
+            ph = g.num_pages - 1;
+          }
         }
-        slot = ph * g.page + id % g.page;
+        slot = ph >= 0 ? ph * g.page + id % g.page : -1;
       }
       gout[i] = slot;
     }
@@ -388,10 +393,14 @@ __device__ __forceinline__ void l2_select_and_write(const loda_geometry& g, cons
     const int lp = id / g.page;
     int ph = lp < g.max_blocks ? table[lp] : -1;
     if (ph < 0 || ph >= g.num_pages) {
-      if (status) atomicOr(status, LODA_STATUS_BAD_PAGE);
-      ph = g.num_pages - 1;   // PAD page: zeros, never out of bounds
+      if (rg.shard_count > 1) {
+        ph = -1;              // another GPU's page: skipped by the attention
+      } else {
+        if (status) atomicOr(status, LODA_STATUS_BAD_PAGE);
+        ph = g.num_pages - 1;   // PAD page: zeros, never out of bounds
+      }
     }
-    gout[i] = ph * g.page + id % g.page;
+    gout[i] = ph >= 0 ? ph * g.page + id % g.page : -1;
   }
   if (tid == 0) {
     S.visible_lens[(size_t)b * g.num_kv_heads + kv] = n_out;

@@ -251,6 +251,10 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     shm.wtot = wtot;
     shm.scan = scan;
     l2_select_and_write<SF_L2_NT, 1, true>(g, rg, S, status, table, b, kv, row, length, nitems, shm, nullptr);
+#ifdef LODA_TWICE
+    LODA_PHASE(sel, cta_id, 8);
+    l2_select_and_write<SF_L2_NT, 1, false>(g, rg, S, status, table, b, kv, row, length, nitems, shm, nullptr);
+#endif
   }
   LODA_PHASE(sel, cta_id, 9);
 }

@@ -93,3 +93,142 @@ def lse_merge(outs, ms, zs):
         z = z + w[r]
         o = o + outs[r].float() * w[r].unsqueeze(-1)
     return torch.where(z.unsqueeze(-1) > 0, o / z.unsqueeze(-1).clamp_min(1e-38), torch.zeros_like(o))
+
+
+# ---------------------------------------------------------------------------
+# sequence sharding of one long request over the GPUs (batch-1 long context)
+# ---------------------------------------------------------------------------
+def combine_disjoint_scores(local, group=None):
+    """All-gather of the ranks' uint16 score rows followed by a bitwise OR.  Every page (level 1)
+    and every candidate slot (level 2) is scored by exactly one rank and is 0 on the others, so
+    the OR is the single-GPU score row, identical on every rank.  The rows travel as bytes (NCCL
+    has no 16-bit integer type; a bitwise OR does not care)."""
+    world = dist.get_world_size(group)
+    mine = local.contiguous().view(torch.uint8)
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine, group=group)
+    out = parts[0]
+    for r in range(1, world):
+        out = torch.bitwise_or(out, parts[r])
+    return out.view(local.dtype).view(local.shape)
+
+
+class SequenceShard:
+    """One GPU's view of a paged cache under sequence sharding: logical page p belongs to rank
+    p % world.  The view owns a copy of the block tables in which the other ranks' pages are -1
+    (a deployment would simply never allocate them), a geometry carrying (rank, world), its own
+    selector workspace and its own gather list; the pools and the page statistics are the
+    cache's.  The selector runs in four stages (methods below); between them the score rows of
+    the ranks are combined (`combine_disjoint_scores`)."""
+
+    def __init__(self, cache, indexer, rank, world):
+        import ctypes as C
+
+        from . import _capi
+        if world < 2 or not 0 <= rank < world:
+            raise ValueError("sequence sharding needs world >= 2 and 0 <= rank < world")
+        self.cache, self.rank, self.world = cache, rank, world
+        rt = cache.ensure_index(indexer)
+        self.rt = rt
+        g = _capi.Geometry()
+        C.memmove(C.byref(g), C.byref(rt.geometry), C.sizeof(g))
+        g.shard_rank, g.shard_count = rank, world
+        self.geometry = g
+        regions = (C.c_int64 * 4)()
+        _capi.check(_capi.lib().loda_shard_workspace_regions(C.byref(g), regions))
+        self.workspace = torch.zeros_like(rt.workspace)
+        ws = self.workspace
+        self.l1_scores = ws[regions[0]:regions[0] + regions[1]].view(torch.int16)
+        self.l2_scores = ws[regions[2]:regions[2] + regions[3]].view(torch.int16)
+        self.gather = torch.full_like(cache.gather_indices_for_layer(0), -1)
+        self.visible_lens = torch.zeros_like(cache.visible_lens_for_layer(0))
+        self.block_tables = torch.empty_like(cache.block_table_buf)
+        self.layers = []
+        for li, st in enumerate(rt.layer_structs):
+            layer = _capi.Layer()
+            C.memmove(C.byref(layer), C.byref(st), C.sizeof(layer))
+            layer.block_table = self.block_tables[li].data_ptr()
+            self.layers.append(layer)
+        self.refresh_block_tables()
+
+    def refresh_block_tables(self):
+        """Mask the other ranks' pages out of a fresh copy of the cache's block tables."""
+        bt = self.cache.block_table_buf
+        page_ids = torch.arange(bt.shape[-1], device=bt.device)
+        mine = (page_ids % self.world) == self.rank
+        self.block_tables.copy_(torch.where(mine, bt, torch.full_like(bt, -1)))
+
+    def owns_token(self, position):
+        return (position // self.cache.geometry.page) % self.world == self.rank
+
+    def _call(self, fn, layer_idx, batch, q, scale, with_status):
+        import ctypes as C
+
+        from . import _capi
+        rt, cache = self.rt, self.cache
+        sel = rt.selection_struct(self.gather, self.visible_lens, with_middle=False, with_page_lists=False)
+        args = [C.byref(self.geometry), C.byref(self.layers[layer_idx]), C.byref(rt.batch_struct(batch)),
+                _capi.ptr(q), float(scale), C.byref(sel)]
+        if with_status:
+            args.append(C.c_void_p(cache.status_buf.data_ptr()))
+        args += [_capi.ptr(self.workspace), _capi.current_stream()]
+        _capi.check(fn(*args))
+
+    def l1_scores_stage(self, layer_idx, batch, q, scale):
+        from . import _capi
+        self._call(_capi.lib().loda_shard_l1_scores, layer_idx, batch, q, scale, False)
+
+    def l1_select_stage(self, layer_idx, batch, q, scale):
+        from . import _capi
+        self._call(_capi.lib().loda_shard_l1_select, layer_idx, batch, q, scale, False)
+
+    def l2_scores_stage(self, layer_idx, batch, q, scale):
+        from . import _capi
+        self._call(_capi.lib().loda_shard_l2_scores, layer_idx, batch, q, scale, True)
+
+    def l2_select_stage(self, layer_idx, batch, q, scale):
+        from . import _capi
+        self._call(_capi.lib().loda_shard_l2_select, layer_idx, batch, q, scale, True)
+
+    def attend_stage(self, layer_idx, batch, q, scale):
+        """Attention over this rank's tokens of the selection: (out [B, Hq, Dv] bf16, lse [B, Hq, 2])."""
+        import ctypes as C
+
+        from . import _capi
+        cache = self.cache
+        hq, dv = cache.num_query_heads, cache.layers[layer_idx].head_dim_v
+        out = q.new_empty((batch, hq, dv))
+        lse = torch.empty((batch, hq, 2), dtype=torch.float32, device=q.device)
+        _capi.check(_capi.lib().loda_gather_attend_lse(
+            C.byref(self.geometry), C.byref(self.layers[layer_idx]), _capi.ptr(q), _capi.ptr(self.gather),
+            _capi.ptr(self.visible_lens), _capi.ptr(cache.query_to_req_buf), batch, cache.max_requests, float(scale),
+            _capi.ptr(out), _capi.ptr(lse), _capi.ptr(self.workspace), _capi.current_stream()))
+        return out, lse
+
+
+def sequence_sharded_decode_step(shard, layer_idx, req_ids, query_states, attention, group=None):
+    """Selector and attention of one layer with the request's pages dealt round robin over the
+    ranks: level-1 scores of the own pages, all-gather + OR, page selection (identical on every
+    rank); level-2 logits of the own pages' candidates, all-gather + OR, token selection
+    (identical); attention over the own tokens; all-gather of (out, max, sum) and a fixed-order
+    log-sum-exp merge.  Returns (out [B, Hq, Dv] fp32, gather, visible_lens); the index lists are
+    those of the single-GPU path with -1 at the other ranks' tokens.  The cache must have been
+    planned for the step (plan_common) and hold the step's token (the owner of its page appends)."""
+    b = len(req_ids)
+    q = query_states.contiguous()
+    scale = float(attention.scaling)
+    shard.l1_scores_stage(layer_idx, b, q, scale)
+    shard.l1_scores.copy_(combine_disjoint_scores(shard.l1_scores, group))
+    shard.l1_select_stage(layer_idx, b, q, scale)
+    shard.l2_scores_stage(layer_idx, b, q, scale)
+    shard.l2_scores.copy_(combine_disjoint_scores(shard.l2_scores, group))
+    shard.l2_select_stage(layer_idx, b, q, scale)
+    out, lse = shard.attend_stage(layer_idx, b, q, scale)
+    dv = out.shape[-1]
+    world = dist.get_world_size(group)
+    packed = torch.cat((out.float(), lse), dim=-1).contiguous()            # [B, Hq, Dv + 2]
+    parts = [torch.empty_like(packed) for _ in range(world)]
+    dist.all_gather(parts, packed, group=group)
+    allp = torch.stack(parts)                                              # rank order = merge order
+    merged = lse_merge(allp[..., :dv], allp[..., dv], allp[..., dv + 1])
+    return merged, shard.gather, shard.visible_lens
