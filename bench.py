@@ -409,6 +409,95 @@ def tls_chain_arm(torch, dev, warm=10, iters=100):
     return out
 
 
+def run_sequence_sharded(torch, dist, capi, lib, dev, local, rank, world, K, W, barrier):
+    """Strong scaling of ONE 131 072-token request: logical page p lives on rank p % world; per layer
+    the staged selector with two all-gathers of 16-bit score rows, the attention over the rank's own
+    tokens and an all-gather + log-sum-exp merge of the partial outputs (NCCL).  Every rank holds the
+    whole synthetic cache here and masks the other ranks' pages out of its block table; the owner of
+    the new token's page appends it (the other ranks pass slot -1, the pad slot).  Timed twice: eager
+    launches, and the whole step over all layers (kernels and collectives) replayed as one CUDA graph."""
+    sharding = mod("sharding")
+    total = 2 * (W + K) + 4
+    wl = build_workload(torch, dev, total, seed=11)              # the same request on every rank
+    cache = wl.cache
+    sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
+    lengths, slots = preplan(torch, wl, total - 2)
+    for li in range(wl.n_layers):
+        sel_mod._ensure_index_built(cache, wl.rt, li, wl.rids, has_current_token_in_pool=True)
+    shard = sharding.SequenceShard(cache, wl.indexer, rank, world)
+    g = C.byref(wl.rt.geometry)
+    status = C.c_void_p(cache.status_buf.data_ptr())
+    host_len = [int(x) for x in lengths[:, 0].cpu().tolist()]
+    own = torch.tensor([shard.owns_token(n - 1) for n in host_len], device=dev)
+    my_slots = torch.where(own[:, None, None], slots, torch.full_like(slots, -1))
+    # fixed-address inputs of a step (a captured graph reads them)
+    q_in, k_in, v_in = wl.q[0].clone(), wl.k[0].clone(), wl.v[0].clone()
+    slot_in = my_slots[0].clone()
+    batch = capi.Batch(batch=1, lengths=cache.planned_lengths_buf.data_ptr(),
+                       valid_req_ids=cache.valid_req_ids_buf.data_ptr(),
+                       active_req_ids=cache.active_req_ids_buf.data_ptr())
+
+    def load(s):
+        cache.planned_lengths_buf[:1].copy_(lengths[s])
+        q_in.copy_(wl.q[s]); k_in.copy_(wl.k[s]); v_in.copy_(wl.v[s]); slot_in.copy_(my_slots[s])
+
+    def body():
+        outs = None
+        for li in range(wl.n_layers):
+            capi.check(lib.loda_append_decode(g, C.byref(wl.rt.layer_structs[li]), C.byref(batch), capi.ptr(k_in[li]),
+                                              capi.ptr(v_in[li]), capi.ptr(slot_in[li]), status,
+                                              capi.current_stream()))
+            outs, _, _ = sharding.sequence_sharded_decode_step(shard, li, wl.rids, q_in[li], wl.attention)
+        return outs
+
+    def timed(run, first):
+        for s in range(first, first + W):
+            load(s); run()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in range(first + W, first + W + K):
+            load(s); run()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / K
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    eager_ms = timed(body, 0)
+    graph_ms, graph_note = None, None
+    try:
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        load(W + K)
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graph, stream=stream):
+                body()
+        torch.cuda.current_stream().wait_stream(stream)
+        graph_ms = timed(graph.replay, W + K)
+    except Exception as exc:            # capture of the collectives refused: the eager figure stands
+        graph_note = f"graph capture failed: {type(exc).__name__}"
+    clocks = sampler.stop()
+    ms_per_step = graph_ms if graph_ms is not None else eager_ms
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": 1e3 / ms_per_step, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "cfg2-qwen3-8b-128k", "layers": N_LAYERS, "context": CONTEXT, "batch": 1,
+                       "page": PAGE, "sharding": f"sequence: pages round robin over {world} GPUs, all-gather of "
+                                                 "16-bit score rows after each selector level, LSE merge of the "
+                                                 "partial attentions (NCCL)"},
+            "us_per_decode_step_per_layer": ms_per_step * 1e3 / N_LAYERS,
+            "eager_us_per_layer": eager_ms * 1e3 / N_LAYERS,
+            "graph_us_per_layer": None if graph_ms is None else graph_ms * 1e3 / N_LAYERS, "graph_note": graph_note,
+            "gpu_launches": K * N_LAYERS * 6, "device_status": cache.read_status(), "clocks": clocks,
+            "roofline": None, "e2e": None}), flush=True)
+
+
 def cpu_baseline(sample_steps=3, threads=1):
     """One layer of the workload on the host cores with the CPU oracle (index
     prebuilt, as the reference maintains its page statistics incrementally)."""
@@ -476,9 +565,10 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-batched", action="store_true")
     ap.add_argument("--skip-tls", action="store_true")
-    ap.add_argument("--shard", default="request", choices=("request", "kvhead"),
-                    help="multi-GPU partition: one independent request shard per GPU (weak scaling, default) "
-                         "or the KV-head groups of ONE request split over the GPUs (strong scaling)")
+    ap.add_argument("--shard", default="request", choices=("request", "kvhead", "sequence"),
+                    help="multi-GPU partition: one independent request shard per GPU (weak scaling, default), "
+                         "the KV-head groups of ONE request split over the GPUs, or the pages of ONE request "
+                         "dealt round robin over the GPUs with NCCL all-gathers between the stages (strong scaling)")
     ap.add_argument("--layers", type=int, default=N_LAYERS,
                     help="profiling aid: fewer layers than the 36 of the named workload (not a bench line)")
     args = ap.parse_args()
@@ -511,6 +601,11 @@ def main():
         torch.cuda.synchronize()
 
     K, W = args.steps, args.warmup
+    if args.shard == "sequence" and world > 1:
+        run_sequence_sharded(torch, dist, capi, lib, dev, local, rank, world, K, W, barrier)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     e2e_steps = K
     total = W + K + W + e2e_steps + 8
     wl = build_workload(torch, dev, total, seed=11 + (0 if kvhead else rank))

@@ -81,3 +81,36 @@ def test_lse_merge_of_disjoint_token_sets_equals_full_attention():
         outs.append(((p @ v[idx]) / z[:, None]).float()); ms.append(m.float()); zs.append(z.float())
     merged = sh.lse_merge(torch.stack(outs), torch.stack(ms), torch.stack(zs))
     np.testing.assert_allclose(merged.numpy(), full.float().numpy(), rtol=2e-5, atol=2e-5)
+
+
+def _combine_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        sh = load_pkg("sharding")
+        gen = torch.Generator().manual_seed(5)
+        full = torch.randint(1, 65536, (4, 1000), generator=gen).to(torch.int32)     # the single-GPU score rows
+        pages = torch.arange(1000)
+        mine = torch.where(pages % world == rank, full, torch.zeros_like(full))      # this rank scored its pages only
+        as_u16 = mine.to(torch.int16)                                                # same bits as uint16 (wraps)
+        got = sh.combine_disjoint_scores(as_u16)
+        q.put((rank, torch.equal(got, full.to(torch.int16)), got.dtype == torch.int16, tuple(got.shape)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_score_rows_of_disjoint_owners_combine_to_the_full_row_world2():
+    """Sequence sharding: every page is scored by one rank (0 elsewhere); the all-gather + OR of
+    the ranks' rows is the full row on every rank."""
+    world, port = 2, 31000 + os.getpid() % 2000
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_combine_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(r[1] and r[2] and r[3] == (4, 1000) for r in res)
