@@ -118,7 +118,9 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   const int len_raw = B.lengths[b];
   const int req = (int)B.valid_req_ids[b];
   const int length = act >= 0 ? len_raw : 0;
-  const Regions rg = make_regions(g, length);
+  Regions rg = make_regions(g, length);
+  rg.shard_rank = 0;          // this launch never serves a sequence-sharded geometry: the ownership
+  rg.shard_count = 0;         // tests fold away
   const size_t pg0 = ((size_t)req * g.num_kv_heads + kv) * g.max_blocks;
   const unsigned char* mm_base = (const unsigned char*)L.page_mm + pg0 * (4 * DSUB);
   const unsigned char* sum_base = (const unsigned char*)L.page_sum + pg0 * (2 * DSUB);
