@@ -187,8 +187,8 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   pdl_launch_dependents();
 #endif
   LODA_PHASE(l1, cta_id, 6);
-  const int np = l1_select_pages<P, LODA_PDL_TRIGGER == 1>(g, rg, out, row, scf, scn, n_far, far_lo, n_near, near_lo,
-                                                           near_lo8, near_hi, kept, keys, wtot, sh);
+  const int np = l1_select_pages<P>(g, rg, out, row, scf, scn, n_far, far_lo, n_near, near_lo, near_lo8, near_hi, kept,
+                                    keys, wtot, sh, LODA_PDL_TRIGGER == 1);
   LODA_PHASE(l1, cta_id, 8);
   // hand the ascending page list and its physical pages to the L2 launch
   const int np_max = g.k_far + g.k_near + 2;

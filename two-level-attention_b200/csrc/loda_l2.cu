@@ -135,8 +135,8 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
 #endif
   LODA_PHASE(l2, cta_id, 5);
   const L2Shared shm{sc, pages, physs, mid_a, mid_b, wtot, scan, win};
-  l2_select_and_write<NT, 0, LODA_PDL_TRIGGER == 1>(g, rg, S, status, table, b, kv, row, length, nitems, shm,
-                                                    ws.l2_ticket + row);
+  l2_select_and_write<NT, 0>(g, rg, S, status, table, b, kv, row, length, nitems, shm, ws.l2_ticket + row,
+                             LODA_PDL_TRIGGER == 1);
   LODA_PHASE(l2, cta_id, 9);
 }
 

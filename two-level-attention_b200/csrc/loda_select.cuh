@@ -120,12 +120,12 @@ __device__ void emit_best_first(const int* kept, int n, int k, const uint16_t* s
 // exact top-k of each pool, the optional best-first lists, and the ascending page list
 // kept[0, np) = [sink bypass] far... near... [window bypass].  Returns np.  All P threads call.
 // keys: 2 P + 8 words; wtot: 256 ints; sh: 8 ints.
-// TRIGGER: release the dependent launch after the two selections.
-template <int P, bool TRIGGER>
+// trigger: release the dependent launch after the two selections.
+template <int P>
 __device__ __forceinline__ int l1_select_pages(const loda_geometry& g, const Regions& rg, const loda_selection& out,
                                                int row, uint16_t* scf, uint16_t* scn, int n_far, int far_lo, int n_near,
                                                int near_lo, int near_lo8, int near_hi, int* kept, uint32_t* keys,
-                                               int* wtot, int* sh) {
+                                               int* wtot, int* sh, bool trigger) {
   const int tid = threadIdx.x;
   int np = 0;
   const bool want_lists = out.i_far != nullptr;
@@ -178,7 +178,7 @@ __device__ __forceinline__ int l1_select_pages(const loda_geometry& g, const Reg
         __syncthreads();
       }
     }
-    if (TRIGGER) pdl_launch_dependents();
+    if (trigger) pdl_launch_dependents();
     if (want_lists) {
       // best-first lists need the scores by page id: near scores go back beside the far ones
       for (int i = near_lo + tid; i < near_hi; i += P) scf[i] = scn[i - near_lo8];
@@ -257,17 +257,21 @@ __device__ __forceinline__ uint32_t l2_slot_score(const loda_geometry& g, const 
 // slots; slot i * page + o is token pages[i] * page + o, physical page physs[i]): keep the
 // quota best by bisection, fill holes, drop ids below the sink, and write
 // sink ++ middle ++ window as physical slots.  Runs on the first NT threads of the CTA
-// (BAR as in group_sync).  TRIGGER: release the dependent launch after the selection.
+// (BAR as in group_sync).  trigger: release the dependent launch after the selection.
 struct L2Shared {
   uint16_t* sc;
   int *pages, *physs, *mid_a, *mid_b, *wtot, *scan;
   uint8_t* win;
 };
 
-template <int NT, int BAR, bool TRIGGER>
-__device__ __forceinline__ void l2_select_and_write(const loda_geometry& g, const Regions& rg, const loda_selection& S,
+#ifndef LODA_L2TAIL_INLINE
+#define LODA_L2TAIL_INLINE __forceinline__
+#endif
+template <int NT, int BAR>
+__device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, const Regions& rg, const loda_selection& S,
                                                     uint32_t* status, const int32_t* table, int b, int kv, int row,
-                                                    int length, int nitems, const L2Shared& sm, int* ticket) {
+                                                    int length, int nitems, const L2Shared& sm, int* ticket,
+                                                    bool trigger) {
   const int tid = threadIdx.x;
   const int K2 = g.level2_topk;
   uint16_t* sc = sm.sc;
@@ -276,7 +280,7 @@ __device__ __forceinline__ void l2_select_and_write(const loda_geometry& g, cons
   const int quota = rg.quota;
   int* slots_sel = mid_b;      // ascending candidate slots kept by the select
   const int take = block_bisect_topk<NT, BAR>(sc, nitems, min(quota, K2), slots_sel, wtot);
-  if (TRIGGER) pdl_launch_dependents();
+  if (trigger) pdl_launch_dependents();
   if (take == quota) {
     // Common case: the quota is filled by scored candidates (all of them >= sink, no holes).
     // The survivors' physical pages came with the page list, so only the sink and window ids

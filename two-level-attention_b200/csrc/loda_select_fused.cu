@@ -207,8 +207,8 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     for (int i = far_hi + tid; i < ((n_far + 7) & ~7); i += P) scf[i] = 0;
     __syncthreads();
     LODA_PHASE(sel, cta_id, 3);
-    const int np = l1_select_pages<P, false>(g, rg, S, row, scf, scn, n_far, far_lo, n_near, near_lo, near_lo8, near_hi,
-                                             kept, keys, wtot, sh);
+    const int np = l1_select_pages<P>(g, rg, S, row, scf, scn, n_far, far_lo, n_near, near_lo, near_lo8, near_hi, kept,
+                                      keys, wtot, sh, false);
     for (int i = tid; i < np; i += P) {
       const int pg = kept[i];
       int ph = (pg >= 0 && pg < g.max_blocks) ? table[pg] : -1;
@@ -252,11 +252,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     shm.win = (uint8_t*)(rows + off);
     shm.wtot = wtot;
     shm.scan = scan;
-    l2_select_and_write<SF_L2_NT, 1, true>(g, rg, S, status, table, b, kv, row, length, nitems, shm, nullptr);
-#ifdef LODA_TWICE
-    LODA_PHASE(sel, cta_id, 8);
-    l2_select_and_write<SF_L2_NT, 1, false>(g, rg, S, status, table, b, kv, row, length, nitems, shm, nullptr);
-#endif
+    l2_select_and_write<SF_L2_NT, 1>(g, rg, S, status, table, b, kv, row, length, nitems, shm, nullptr, true);
   }
   LODA_PHASE(sel, cta_id, 9);
 }
