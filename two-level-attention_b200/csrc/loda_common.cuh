@@ -386,10 +386,9 @@ __device__ __forceinline__ int block_compact_threshold(const uint16_t* sc, int n
 // every thread counts its scores at or above three candidate thresholds (independent
 // chains), one barrier publishes the block sums.
 // wtot: 6 x 32 ints (16-byte aligned).
-template <int NT, int BAR = 0, int TBASE = 0>
+template <int NT, int BAR = 0, int TBASE = 0, int MAXC = 4>     // MAXC: chunks a thread keeps in registers
 __device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, int k, int* out, int* wtot) {
   constexpr int NW = NT / 32;
-  constexpr int MAXC = 4;                        // chunks a thread keeps in registers
   const int tid = ((int)threadIdx.x - TBASE), lane = tid & 31, warp = tid >> 5;
   const int nchunks = (n + 7) >> 3;
   const int full = nchunks / NT, remc = nchunks - full * NT;     // whole rounds of chunks, chunks left

@@ -279,7 +279,11 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
   uint8_t* win = sm.win;
   const int quota = rg.quota;
   int* slots_sel = mid_b;      // ascending candidate slots kept by the select
-  const int take = block_bisect_topk<NT, BAR>(sc, nitems, min(quota, K2), slots_sel, wtot);
+  // two instantiations: rows of at most 9 NT slots (one chunk and one single score per thread: the
+  // 2 080 slots of the default budgets) run a much shorter instruction stream, and executed once,
+  // cold, a selection costs about as much in instruction fetch as in arithmetic
+  const int take = nitems <= 9 * NT ? block_bisect_topk<NT, BAR, 0, 1>(sc, nitems, min(quota, K2), slots_sel, wtot)
+                                    : block_bisect_topk<NT, BAR, 0, 4>(sc, nitems, min(quota, K2), slots_sel, wtot);
   if (trigger) pdl_launch_dependents();
   if (take == quota) {
     // Common case: the quota is filled by scored candidates (all of them >= sink, no holes).
