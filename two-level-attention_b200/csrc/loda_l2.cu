@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
     const int per = ((nitems + nsplit - 1) / nsplit + 7) & ~7;         // multiple of 8 slots
     const int lo = min(split * per, nitems), hi = phase == 2 ? lo : min(lo + per, nitems);
     for (int idx = lo + tid; idx < hi; idx += NT) {
-      const int i = idx / g.page, o = idx % g.page;
+      const int i = idx >> (31 - __clz(g.page)), o = idx & (g.page - 1);      // page is a power of two
       const int pg = __ldcg(ws.pages + (size_t)row * np_max + i);
       const int ph = __ldcg(ws.phys + (size_t)row * np_max + i);
       const uint32_t ord = l2_slot_score<DSUB>(g, L, rg, length, kv, pg, ph, o, qf, status);

@@ -274,6 +274,7 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
                                                     bool trigger) {
   const int tid = threadIdx.x;
   const int K2 = g.level2_topk;
+  const int pl2 = 31 - __clz(g.page), pmask = g.page - 1;      // page is a power of two
   uint16_t* sc = sm.sc;
   int *pages = sm.pages, *physs = sm.physs, *mid_a = sm.mid_a, *mid_b = sm.mid_b, *wtot = sm.wtot, *scan = sm.scan;
   uint8_t* win = sm.win;
@@ -302,12 +303,12 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
       int slot;
       if (i >= sk && i < sk + take) {
         const int sl = slots_sel[i - sk];
-        const int ph = physs[sl / g.page];                 // -1: the page lives on another GPU (sequence sharding)
-        slot = ph >= 0 ? ph * g.page + sl % g.page : -1;
-        if (S.middle != nullptr) S.middle[(size_t)row * K2 + (i - sk)] = pages[sl / g.page] * g.page + sl % g.page;
+        const int ph = physs[(sl >> pl2)];                 // -1: the page lives on another GPU (sequence sharding)
+        slot = ph >= 0 ? ph * g.page + (sl & pmask) : -1;
+        if (S.middle != nullptr) S.middle[(size_t)row * K2 + (i - sk)] = pages[(sl >> pl2)] * g.page + (sl & pmask);
       } else {
         const int id = i < sk ? i : s_lo + (i - sk - take);
-        const int lp = id / g.page;
+        const int lp = (id >> pl2);
         int ph = lp < g.max_blocks ? table[lp] : -1;
         if (ph < 0 || ph >= g.num_pages) {
           if (rg.shard_count > 1) {
@@ -317,7 +318,7 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
             ph = g.num_pages - 1;
           }
         }
-        slot = ph >= 0 ? ph * g.page + id % g.page : -1;
+        slot = ph >= 0 ? ph * g.page + (id & pmask) : -1;
       }
       gout[i] = slot;
     }
@@ -331,7 +332,7 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
   }
   for (int i = tid; i < take; i += NT) {
     const int sl = slots_sel[i];
-    mid_a[i] = pages[sl / g.page] * g.page + sl % g.page;
+    mid_a[i] = pages[(sl >> pl2)] * g.page + (sl & pmask);
   }
   group_sync<NT, BAR>();
   int count = take;
@@ -398,7 +399,7 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
     if (i < sk) id = i;
     else if (i < sk + count_m) id = mid[d0 + i - sk];
     else id = s_lo + (i - sk - count_m);
-    const int lp = id / g.page;
+    const int lp = (id >> pl2);
     int ph = lp < g.max_blocks ? table[lp] : -1;
     if (ph < 0 || ph >= g.num_pages) {
       if (rg.shard_count > 1) {
@@ -408,7 +409,7 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
         ph = g.num_pages - 1;   // PAD page: zeros, never out of bounds
       }
     }
-    gout[i] = ph >= 0 ? ph * g.page + id % g.page : -1;
+    gout[i] = ph >= 0 ? ph * g.page + (id & pmask) : -1;
   }
   if (tid == 0) {
     S.visible_lens[(size_t)b * g.num_kv_heads + kv] = n_out;

@@ -155,16 +155,14 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     qlow[i] = fminf(qh, 0.0f);
     qhigh[i] = fmaxf(qh, 0.0f);
   }
-  // grouped query of level 2 (head order, fp32): needed by every CTA, with or without tiles
+  cluster.sync();       // (0) every CTA of the cluster runs: its shared memory may be addressed from now on
+  // grouped query of level 2: the fp32 sum over the group, in head order, of the bf16-rounded scaled
+  // query elements — exactly the values just stored in qhat (the barrier above orders them)
   if (tid < DSUB) {
     float acc = 0.0f;
-    for (int j = 0; j < G; ++j) {
-      const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, tid)]);
-      acc = __fadd_rn(acc, bf16r(__fmul_rn(qv, scale)));
-    }
+    for (int j = 0; j < G; ++j) acc = __fadd_rn(acc, qhat[j * DSUB + tid]);
     qf[tid] = acc;
   }
-  cluster.sync();       // (0) every CTA of the cluster runs: its shared memory may be addressed from now on
   for (int it = 0; it < tiles_per_cta; ++it) {
     const int p0 = (rank + it * CS) * P;
     if (p0 >= page_end) break;
@@ -229,7 +227,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     const int per = ((nitems + CS - 1) / CS + 7) & ~7;
     const int lo = min(rank * per, nitems), hi = min(lo + per, nitems);
     for (int idx = lo + tid; idx < hi; idx += P) {
-      const int i = idx / g.page, o = idx % g.page;
+      const int i = idx >> (31 - __clz(g.page)), o = idx & (g.page - 1);      // page is a power of two
       const int pg = l_kept[i], ph = l_physk[i];
       l_sc2[idx] = (uint16_t)l2_slot_score<DSUB>(g, L, rg, length, kv, pg, ph, o, qf, status);
     }
