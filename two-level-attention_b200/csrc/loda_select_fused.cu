@@ -107,6 +107,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   uint16_t* l_sc2 = (uint16_t*)cluster.map_shared_rank(rows, 0);       // level-2 scores, over the leader's rows
 
   LODA_PHASE(sel, cta_id, 0);
+  cluster.barrier_arrive();   // (0) "this CTA runs": waited for just before the first store into a peer
   pdl_wait();
   // this thread's first query element is requested before anything that depends on the
   // request's length, so that the two global round trips overlap
@@ -155,7 +156,8 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     qlow[i] = fminf(qh, 0.0f);
     qhigh[i] = fmaxf(qh, 0.0f);
   }
-  cluster.sync();       // (0) every CTA of the cluster runs: its shared memory may be addressed from now on
+  cluster.barrier_wait();     // (0) every CTA of the cluster runs: its shared memory may be addressed from now on
+  __syncthreads();            // (and qhat is complete)
   // grouped query of level 2: the fp32 sum over the group, in head order, of the bf16-rounded scaled
   // query elements — exactly the values just stored in qhat (the barrier above orders them)
   if (tid < DSUB) {
