@@ -640,50 +640,45 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
   if (is_kth) sh[1] = 1;                         // sh[1] was cleared before the barrier above
   group_sync<NT, BAR>();
   const uint32_t bound = sh[1] ? (uint32_t)sh[0] : 1u;
-  // survivors, counted per thread then placed in index order round by round
-  int total = 0;
+  // survivors: every thread owns `cpt` consecutive chunks, so one scan over the thread counts places
+  // them in index order (and yields the total)
+  const int cpt = (nchunks + NT - 1) / NT;
+  const int ch0 = tid * cpt, ch1 = min(ch0 + cpt, nchunks);
+  int cnt = 0;
+  for (int ch = ch0; ch < ch1; ++ch) {
+    uint32_t v[8];
+    unpack_u16x8(((const uint4*)sc)[ch], v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cnt += v[j] >= bound;
+  }
+  int incl = cnt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int nb = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += nb;
+  }
+  if (lane == 31) wtot[warp] = incl;
+  group_sync<NT, BAR>();
+  int before = 0, total = 0;
+#pragma unroll
+  for (int w = 0; w < NW; ++w) {
+    const int x = wtot[w];
+    total += x;
+    before += w < warp ? x : 0;
+  }
+  if (total > 2 * NT) return -1;
   {
-    int cnt = 0;
-    for (int ch = tid; ch < nchunks; ch += NT) {
+    int pos = before + incl - cnt;
+    for (int ch = ch0; ch < ch1 && cnt > 0; ++ch) {
       uint32_t v[8];
       unpack_u16x8(((const uint4*)sc)[ch], v);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) cnt += v[j] >= bound;
+      for (int j = 0; j < 8; ++j) {
+        if (v[j] >= bound) keys[pos++] = rank_key(v[j], ch * 8 + j);
+      }
     }
-    total = block_sum_cols<NT, BAR, TBASE>(cnt, wtot, 0);
   }
-  if (total > 2 * NT) return -1;
-  int base_out = 0, buf = 1;
-  for (int c0 = 0; c0 < nchunks; c0 += NT) {
-    const int ch = c0 + tid;
-    uint32_t v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (ch < nchunks) unpack_u16x8(((const uint4*)sc)[ch], v);
-    int cnt = 0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) cnt += v[j] >= bound;
-    int incl = cnt;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int nb = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += nb;
-    }
-    if (lane == 31) wtot[buf * 32 + warp] = incl;
-    group_sync<NT, BAR>();
-    int before = 0, tot = 0;
-#pragma unroll
-    for (int w = 0; w < NW; ++w) {
-      const int x = wtot[buf * 32 + w];
-      tot += x;
-      before += w < warp ? x : 0;
-    }
-    buf ^= 1;
-    int pos = base_out + before + incl - cnt;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (v[j] >= bound) keys[pos++] = rank_key(v[j], ch * 8 + j);
-    }
-    base_out += tot;
-  }
+  int buf = 1;
   if (tid < 4) keys[total + tid] = 0;            // pad the last vector of keys
   group_sync<NT, BAR>();
   // exact ranking of the survivors (already in ascending index order), up to two per thread
