@@ -121,6 +121,10 @@ typedef struct loda_selection {
   int32_t* visible_lens;
   int32_t* middle;
   int32_t* middle_counts;
+  int32_t middle_only;    /* 1: gather / visible_lens receive the level-2 survivors only, without the sink
+                           * and window tokens (select_topk_for_layer_batched(middle_only=True),
+                           * nfa_layer_batch_selector.py:2649-2671) */
+  int32_t reserved;
 } loda_selection;
 
 const char* loda_version(void);
@@ -237,6 +241,14 @@ int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda
                      const void* q, const void* k_new, const void* v_new, const int32_t* slots,
                      float scale, const loda_selection* sel, const int32_t* query_to_req,
                      void* out, uint32_t* status, void* workspace, void* stream);
+
+/* gather / visible_lens = the protected tokens only: sink ++ sliding window as physical
+ * slots, per (batch row, kv head).  Replaces build_protected_gather
+ * (sparse_attn/ops/paged_region_kernels_nfa.py:84-119).  With loda_selection.middle_only
+ * and loda_gather_attend_lse on the two lists, the partial attentions merge by
+ * log-sum-exp (the reference's "disjoint protected / middle" operator mode). */
+int loda_protected_gather(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
+                          int32_t* gather, int32_t* visible_lens, uint32_t* status, void* stream);
 
 /* ---- sequence sharding (batch-1 long context over several GPUs) ---------------
  * No counterpart in the reference's code; the mode is described by the task's

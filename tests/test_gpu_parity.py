@@ -343,7 +343,10 @@ def test_partial_attentions_merge_by_lse_to_the_full_attention():
     (16, {"tia_level2_cmp_ratio": 8}, [9000, 3000]),                      # 16-dim subspace
     (16, {"tia_level1_topk": 64, "nfa_near_pages": 16, "tia_level2_topk": 512, "nfa_sink_tokens": 16,
           "nfa_swa_size": 64, "nfa_near_len": 2048}, [7000, 1200, 40]),    # other budgets, page-aligned sink
-], ids=["page64", "sub64", "sub16", "small-budgets"])
+    (16, {"tia_level2_topk": 2048, "tia_level1_topk": 192}, [30000, 2500]),       # visible-length bucket 2048
+    (16, {"tia_level2_topk": 4096, "tia_level1_topk": 320, "nfa_near_pages": 64}, [40000]),   # bucket 4096, one-launch selector
+    (16, {"tia_level2_topk": 512, "tia_level1_topk": 64, "nfa_near_pages": 16}, [20000, 600]),  # bucket 512
+], ids=["page64", "sub64", "sub16", "small-budgets", "visible2048", "visible4096", "visible512"])
 def test_other_geometries_match_oracle(page, overrides, lengths):
     from helpers import make_setup
     mv = int(overrides.get("tia_level2_topk", 1024))
@@ -414,3 +417,41 @@ def test_sequence_sharded_selector_and_attention_equal_the_single_gpu_path(world
     lse = torch.stack(lses)
     merged = sharding.lse_merge(torch.stack(outs), lse[..., 0], lse[..., 1])
     torch.testing.assert_close(merged, ref_out.float(), atol=ATOL, rtol=RTOL)
+
+
+def test_disjoint_protected_and_middle_arms_equal_the_single_list_path():
+    """The "disjoint protected / middle" operator mode: the protected list (sink ++ window) and the
+    middle-only selection are disjoint, their concatenation in logical order is the single list of
+    the default path, and the merge of the two partial attentions equals its attention."""
+    from helpers import make_setup, mod
+    sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
+    nfa = mod("sparse_attn.ops.paged_region_kernels_nfa")
+    ops = mod("sparse_attn.ops.paged_region_kernels")
+    for lengths in ([20000], [9000, 131, 3, 4400]):          # one-launch selector, then the two-launch chain
+        setup = make_setup(lengths, seed=13)
+        ref_out = _run_step(setup)
+        cache, b = setup.cache, len(lengths)
+        ref_gather = cache.gather_indices_for_layer(0)[:b].clone()
+        ref_lens = cache.visible_lens_for_layer(0)[:b].clone()
+        pg, pl, mg, ml = nfa.split_gather_buffers(cache, 0, b)
+        nfa.build_protected_gather(cache, 0, setup.indexer, pg, pl)
+        sel_mod.select_topk_for_layer_batched(cache, 0, setup.req_ids, setup.q, attention=setup.attention,
+                                              middle_only=True, selection_output=(mg, ml))
+        layer, q2r = cache.layers[0], cache.query_to_req_buf
+        prot = ops.sparse_paged_attention_gather_partial(layer, setup.q, pg, pl, q2r, scale=setup.attention.scaling,
+                                                         workspace=None, name="protected", nsplit=1)
+        mid = ops.sparse_paged_attention_gather_partial(layer, setup.q, mg, ml, q2r, scale=setup.attention.scaling,
+                                                        workspace=None, name="middle", nsplit=4)
+        out = ops.sparse_paged_attention_regions_combine(setup.q, prot, mid)
+        torch.cuda.synchronize()
+        assert cache.read_status() == 0
+        sink = setup.indexer.sink_tokens
+        for bi in range(b):
+            for kv in range(cache.num_kv_heads):
+                n, npr, nm = int(ref_lens[bi, kv]), int(pl[bi, kv]), int(ml[bi, kv])
+                assert npr + nm == n
+                sk = min(sink, lengths[bi])
+                want = ref_gather[bi, kv, :n]
+                got = torch.cat((pg[bi, kv, :sk], mg[bi, kv, :nm], pg[bi, kv, sk:npr]))
+                assert torch.equal(got, want)
+        torch.testing.assert_close(out.float(), ref_out.float(), atol=ATOL, rtol=RTOL)

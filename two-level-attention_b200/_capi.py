@@ -46,7 +46,8 @@ class Batch(C.Structure):
 
 class Selection(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
-        "i_far", "n_far", "i_near", "n_near", "gather", "visible_lens", "middle", "middle_counts")]
+        "i_far", "n_far", "i_near", "n_near", "gather", "visible_lens", "middle", "middle_counts")] + [
+        ("middle_only", C.c_int32), ("reserved", C.c_int32)]
 
 
 EXPORTS = ("loda_version", "loda_last_error", "loda_workspace_bytes", "loda_append_decode",
@@ -55,7 +56,7 @@ EXPORTS = ("loda_version", "loda_last_error", "loda_workspace_bytes", "loda_appe
            "loda_select_step", "loda_tia_quant4", "loda_tia_block_minmax", "loda_tia_scores", "loda_gather_attend_lse",
            "loda_tls_store_kv", "loda_tls_store_k_index", "loda_tls_level1", "loda_tls_level2",
            "loda_shard_workspace_regions", "loda_shard_l1_scores", "loda_shard_l1_select", "loda_shard_l2_scores",
-           "loda_shard_l2_select")
+           "loda_shard_l2_select", "loda_protected_gather")
 
 _lib = None
 
@@ -94,6 +95,7 @@ def lib():
     L.loda_tls_store_k_index.argtypes = [P, P, P, P, P, I, I, I, I, I, I, I, I, I, V]
     L.loda_tls_level1.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, V]
     L.loda_tls_level2.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, V]
+    L.loda_protected_gather.argtypes = [G, LY, B, P, P, P, V]
     L.loda_shard_workspace_regions.argtypes = [G, P]
     L.loda_shard_l1_scores.argtypes = [G, LY, B, P, F, S, P, V]
     L.loda_shard_l1_select.argtypes = [G, LY, B, P, F, S, P, V]

@@ -18,6 +18,8 @@ cudaError_t launch_l1(const loda_geometry&, const loda_layer&, const loda_batch&
 cudaError_t launch_l2(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
                       const loda_selection&, const SelectWorkspace&, uint32_t*, bool, int, cudaStream_t);
 int l1_score_stride(const loda_geometry&);
+cudaError_t launch_protected_gather(const loda_geometry&, const loda_layer&, const loda_batch&, int32_t*, int32_t*,
+                                    uint32_t*, cudaStream_t);
 bool select_fused_applicable(const loda_geometry&, int);
 void select_fused_refuse(int);
 cudaError_t launch_select_fused(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
@@ -320,6 +322,18 @@ int loda_gather_attend(const loda_geometry* g, const loda_layer* layer, const vo
                        int32_t n_req_rows, float scale, void* out, void* workspace, void* stream) {
   return gather_attend_impl(g, layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale, out,
                             nullptr, workspace, /*chained=*/false, stream);
+}
+
+int loda_protected_gather(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, int32_t* gather,
+                          int32_t* visible_lens, uint32_t* status, void* stream) {
+  LODA_TRY(check_geometry(g));
+  LODA_TRY(check_layer(layer));
+  LODA_TRY(check_batch(g, b));
+  if (b->batch == 0) return LODA_OK;
+  if (!gather || !visible_lens) return fail(LODA_ERR_ARGUMENT, "protected_gather needs gather and visible_lens");
+  if (g->sink + g->swa > g->max_visible) return fail(LODA_ERR_ARGUMENT, "max_visible < sink + swa");
+  return check_cuda(launch_protected_gather(*g, *layer, *b, gather, visible_lens, status, (cudaStream_t)stream),
+                    "protected_gather");
 }
 
 // ---- sequence sharding: the selector in four stages, the caller combines the score rows of the

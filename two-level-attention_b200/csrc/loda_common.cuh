@@ -577,19 +577,74 @@ __device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, i
     base_gt += tot & 0xFFFF;
     base_tie += tot >> 16;
   };
+  // the last chunk slot and the single scores behind it in one scan (two counters per thread,
+  // one barrier): the single scores follow every chunk in index order
+  auto place_with_single = [&](const uint32_t (&v)[8], int idx0) {
+    uint32_t gm = 0, tm = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      gm |= (uint32_t)(all ? v[j] != 0u : v[j] > thr) << j;
+      tm |= (uint32_t)((!all) && v[j] == thr) << j;
+    }
+    const bool xg = all ? xtra != 0u : xtra > thr, xt = (!all) && xtra == thr;
+    const int own = __popc(gm) | (__popc(tm) << 16), ownx = (int)xg | ((int)xt << 16);
+    int incl = own, inclx = ownx;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int nb = __shfl_up_sync(0xffffffffu, incl, o), nx = __shfl_up_sync(0xffffffffu, inclx, o);
+      if (lane >= o) { incl += nb; inclx += nx; }
+    }
+    if (lane == 31) { wtot[cbuf * 32 + warp] = incl; wtot[64 + cbuf * 32 + warp] = inclx; }
+    group_sync<NT, BAR>();
+    int before = 0, tot = 0, beforex = 0, totx = 0;
+#pragma unroll
+    for (int w4 = 0; w4 < (NW + 3) / 4; ++w4) {
+      const int4 x = ((const int4*)(wtot + cbuf * 32))[w4];
+      const int4 y = ((const int4*)(wtot + 64 + cbuf * 32))[w4];
+      tot += (x.x + x.y) + (x.z + x.w);
+      totx += (y.x + y.y) + (y.z + y.w);
+      before += (w4 * 4 + 0 < warp ? x.x : 0) + (w4 * 4 + 1 < warp ? x.y : 0) + (w4 * 4 + 2 < warp ? x.z : 0) +
+                (w4 * 4 + 3 < warp ? x.w : 0);
+      beforex += (w4 * 4 + 0 < warp ? y.x : 0) + (w4 * 4 + 1 < warp ? y.y : 0) + (w4 * 4 + 2 < warp ? y.z : 0) +
+                 (w4 * 4 + 3 < warp ? y.w : 0);
+    }
+    cbuf ^= 1;
+    const int excl = before + incl - own;
+    const int tb = base_tie + (excl >> 16);
+    const int pos = base_gt + (excl & 0xFFFF) + min(tb, rem);
+    const int allowed = max(rem - tb, 0);
+    uint32_t m = gm;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if ((tm >> j) & 1u) m |= (uint32_t)(__popc(tm & ((1u << j) - 1u)) < allowed) << j;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if ((m >> j) & 1u) out[pos + __popc(m & ((1u << j) - 1u))] = idx0 + j;
+    }
+    base_gt += tot & 0xFFFF;
+    base_tie += tot >> 16;
+    const int exclx = beforex + inclx - ownx;
+    const int tbx = base_tie + (exclx >> 16);
+    const int posx = base_gt + (exclx & 0xFFFF) + min(tbx, rem);
+    if (xg || (xt && tbx < rem)) out[posx] = full * NT * 8 + tid;
+    base_gt += totx & 0xFFFF;
+    base_tie += totx >> 16;
+  };
   group_sync<NT, BAR>();                               // the columns may still be read by slower warps
-  if (tid < 64) wtot[tid] = 0;                   // two rows of per-warp totals; absent warps stay 0
+  if (tid < 128) wtot[tid] = 0;                  // rows of per-warp totals; absent warps stay 0
   group_sync<NT, BAR>();
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
     if (c < nslots) {
       uint32_t v[8];
       unpack_u16x8(mine[c], v);
-      place(v, (tid + c * NT) * 8);
+      if (single && c == nslots - 1) place_with_single(v, (tid + c * NT) * 8);
+      else place(v, (tid + c * NT) * 8);
     }
   }
   LODA_SUB(12);
-  if (single) {
+  if (single && nslots == 0) {
     const uint32_t v[8] = {xtra, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
     place(v, full * NT * 8 + tid);
   }

@@ -140,6 +140,54 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
   LODA_PHASE(l2, cta_id, 9);
 }
 
+// sink ++ window of every (batch row, kv head) as physical slots: the union of l2_select_and_write
+// with an empty middle (the reference builds its protected list the same way,
+// paged_region_kernels_nfa.py:84-119)
+__global__ void __launch_bounds__(128) protected_gather_kernel(loda_geometry g, loda_layer L, loda_batch B,
+                                                               int32_t* __restrict__ gather,
+                                                               int32_t* __restrict__ visible_lens, uint32_t* status) {
+  const int row = blockIdx.x, b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
+  pdl_wait();
+  const int length = B.active_req_ids[b] >= 0 ? B.lengths[b] : 0;
+  const int req = (int)B.valid_req_ids[b];
+  const int32_t* table = L.block_table + (size_t)req * g.max_blocks;
+  const int pl2 = 31 - __clz(g.page), pmask = g.page - 1;
+  const int cap = g.max_blocks * g.page;
+  const int sk = min(length, g.sink);
+  const int count_s = min(length, g.sink + g.swa) - sk;
+  const int s_lo = max(max(length - g.swa, 0), sk);
+  const int s_hi = min(length - g.swa + count_s, cap);
+  const int n_s = max(s_hi - s_lo, 0);
+  const int total = sk + n_s;
+  const int n_out = min(total, g.max_visible);
+  int32_t* gout = gather + ((size_t)b * g.num_kv_heads + kv) * g.max_visible;
+  for (int i = threadIdx.x; i < n_out; i += blockDim.x) {
+    const int id = i < sk ? i : s_lo + (i - sk);
+    const int lp = id >> pl2;
+    int ph = lp < g.max_blocks ? table[lp] : -1;
+    if (ph < 0 || ph >= g.num_pages) {
+      if (g.shard_count > 1) {
+        ph = -1;
+      } else {
+        if (status) atomicOr(status, LODA_STATUS_BAD_PAGE);
+        ph = g.num_pages - 1;
+      }
+    }
+    gout[i] = ph >= 0 ? ph * g.page + (id & pmask) : -1;
+  }
+  if (threadIdx.x == 0) {
+    visible_lens[(size_t)b * g.num_kv_heads + kv] = n_out;
+    if (total > g.max_visible && status) atomicOr(status, LODA_STATUS_TRUNCATED);
+  }
+}
+
+cudaError_t launch_protected_gather(const loda_geometry& g, const loda_layer& L, const loda_batch& B, int32_t* gather,
+                                    int32_t* visible_lens, uint32_t* status, cudaStream_t st) {
+  const int rows = B.batch * g.num_kv_heads;
+  if (rows <= 0) return cudaSuccess;
+  return launch_pdl(protected_gather_kernel, dim3(rows), dim3(128), 0, st, g, L, B, gather, visible_lens, status);
+}
+
 size_t l2_smem_bytes(const loda_geometry& g) {
   const size_t np_max = g.k_far + g.k_near + 2;
   return ((np_max * g.page * 2 + 15) & ~(size_t)15) + g.sub_dims * 4 + 2 * np_max * 4 +

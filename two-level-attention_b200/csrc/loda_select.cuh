@@ -291,11 +291,12 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
     // The survivors' physical pages came with the page list, so only the sink and window ids
     // need a block-table lookup: sink ++ middle ++ window, one pass.
     const int cap = g.max_blocks * g.page;
-    const int sk = min(length, g.sink);
-    const int count_s = min(length, g.sink + g.swa) - sk;
-    const int s_lo = max(max(length - g.swa, 0), sk);
+    const int sk_all = min(length, g.sink);
+    const int count_s = min(length, g.sink + g.swa) - sk_all;
+    const int s_lo = max(max(length - g.swa, 0), sk_all);
     const int s_hi = min(length - g.swa + count_s, cap);
-    const int n_s = max(s_hi - s_lo, 0);
+    const int sk = S.middle_only ? 0 : sk_all;                     // middle only: no sink, no window
+    const int n_s = S.middle_only ? 0 : max(s_hi - s_lo, 0);
     const int total = sk + take + n_s;
     const int n_out = min(total, g.max_visible);
     int32_t* gout = S.gather + ((size_t)b * g.num_kv_heads + kv) * g.max_visible;
@@ -386,11 +387,12 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
   }
   // ---- union with sink and window ids (nfa_layer_batch_selector.py:1348-1437) --
   const int cap = g.max_blocks * g.page;
-  const int sk = min(length, g.sink);
-  const int count_s = min(length, g.sink + g.swa) - sk;
-  const int s_lo = max(max(length - g.swa, 0), sk);
+  const int sk_all = min(length, g.sink);
+  const int count_s = min(length, g.sink + g.swa) - sk_all;
+  const int s_lo = max(max(length - g.swa, 0), sk_all);
   const int s_hi = min(length - g.swa + count_s, cap);
-  const int n_s = max(s_hi - s_lo, 0);
+  const int sk = S.middle_only ? 0 : sk_all;                       // middle only: no sink, no window
+  const int n_s = S.middle_only ? 0 : max(s_hi - s_lo, 0);
   const int total = sk + count_m + n_s;
   const int n_out = min(total, g.max_visible);
   int32_t* gout = S.gather + ((size_t)b * g.num_kv_heads + kv) * g.max_visible;

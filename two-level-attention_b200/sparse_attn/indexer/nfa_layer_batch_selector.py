@@ -59,8 +59,7 @@ def select_topk_for_layer_batched(cache, layer_idx, req_ids, query_states, atten
     if middle_only:
         if selection_output is None or len(selection_output) != 2:
             raise ValueError("middle-only selection requires gather/lens output")
-        raise FallbackRequired("middle-only (disjoint protected/middle) mode is not implemented")
-    if selection_output is not None:
+    elif selection_output is not None:
         raise ValueError("custom selection output requires middle_only=True")
     b = len(req_ids)
     if b == 0:
@@ -100,10 +99,20 @@ def select_topk_for_layer_batched(cache, layer_idx, req_ids, query_states, atten
         kp, vp, sp = _capi.ptr(k), _capi.ptr(v), _capi.ptr(slots)
     else:
         kp = vp = sp = None      # K/V already in the pool: refresh the index of the newest token
-    gather = cache.gather_indices_for_layer(layer_idx)
-    lens = cache.visible_lens_for_layer(layer_idx)
+    if middle_only:
+        # the L2 survivors alone (no sink, no window) into the caller's buffers: the middle arm of
+        # the disjoint protected / middle operator mode (nfa_layer_batch_selector.py:2649-2671)
+        gather, lens = selection_output
+        if gather.dtype != torch.int32 or lens.dtype != torch.int32 or not gather.is_contiguous():
+            raise ValueError("selection_output must be contiguous int32 (gather, lens)")
+        if gather.shape[-1] != cache.max_visible_len or tuple(gather.shape[:2]) != (b, cache.num_kv_heads):
+            raise ValueError("selection_output gather must be [B, Hkv, max_visible]")
+    else:
+        gather = cache.gather_indices_for_layer(layer_idx)
+        lens = cache.visible_lens_for_layer(layer_idx)
     diag = bool(getattr(cache, "selector_diagnostics", False))
     sel = rt.selection_struct(gather, lens, with_middle=diag, with_page_lists=diag)
+    sel.middle_only = 1 if middle_only else 0
     _capi.check(lib.loda_select_step(g, layer, C.byref(batch), _capi.ptr(q), kp, vp, sp, scale, C.byref(sel),
                                      status, _capi.ptr(rt.workspace), stream))
 

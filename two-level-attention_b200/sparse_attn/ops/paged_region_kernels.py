@@ -149,3 +149,25 @@ def sparse_paged_attention_gather(cache_layer, q, gather_indices, visible_lens, 
         total_q, gather_indices.shape[0], float(scale), _capi.ptr(out), _capi.ptr(lse),
         _capi.ptr(rt["workspace"]), _capi.current_stream()))
     return (out, lse) if return_lse else out
+
+
+def sparse_paged_attention_gather_partial(cache_layer, q, gather_indices, visible_lens, query_to_req, *,
+                                          scale, workspace=None, name="", nsplit=1):
+    """Attention over one region's token list as a partial state that can be merged with
+    another region's (reference: sparse_attn/ops/paged_region_kernels.py:727-780).  Returns
+    (acc [1, T, HQ, DV] fp32, m [1, T, HQ], z [1, T, HQ]): the partial output normalised by its own
+    sum, the row maximum (exp2 domain) and the sum.  `nsplit` and `name` are accepted for signature
+    compatibility: the kernel chooses its own split and merges it inside the launch."""
+    out, lse = sparse_paged_attention_gather(cache_layer, q, gather_indices, visible_lens, query_to_req,
+                                             scale=scale, workspace=workspace, return_lse=True)
+    return out.float()[None], lse[None, ..., 0], lse[None, ..., 1]
+
+
+def sparse_paged_attention_regions_combine(q, protected_parts, middle_parts, *, workspace=None):
+    """Fixed-order log-sum-exp merge of the protected and the middle partial attentions
+    (reference: sparse_attn/ops/paged_region_kernels.py:783-797); [T, HQ, DV] in q's dtype."""
+    from ...sharding import lse_merge
+    acc = torch.cat((protected_parts[0], middle_parts[0]))
+    m = torch.cat((protected_parts[1], middle_parts[1]))
+    z = torch.cat((protected_parts[2], middle_parts[2]))
+    return lse_merge(acc, m, z).to(q.dtype)

@@ -46,3 +46,38 @@ def decode_graph_ready(module, q, cache, *, gather_indices=None, visible_lens=No
     return sparse_paged_attention_gather(
         layer, q, gather_indices, visible_lens, query_to_req, scale=scale,
         workspace=cache.selector_workspace())
+
+
+def split_gather_buffers(cache, layer_idx, batch):
+    """Fixed-address (protected gather, protected lens, middle gather, middle lens) buffers of one
+    layer for the disjoint protected / middle operator mode
+    (reference: sparse_attn/ops/paged_region_kernels_nfa.py:60-81)."""
+    import torch
+    store = cache.__dict__.setdefault("_split_gather_buffers", {})
+    key = (layer_idx, batch)
+    buffers = store.get(key)
+    if buffers is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("split gather buffers must be warmed before capture")
+        shape = (batch, cache.num_kv_heads, cache.max_visible_len)
+        buffers = (torch.full((2,) + shape, -1, dtype=torch.int32, device=cache.device),
+                   torch.zeros((2, batch, cache.num_kv_heads), dtype=torch.int32, device=cache.device))
+        store[key] = buffers
+    return buffers[0][0], buffers[1][0], buffers[0][1], buffers[1][1]
+
+
+def build_protected_gather(cache, layer_idx, indexer, gather_out, vis_out):
+    """sink ++ sliding window of every planned request row as physical slots into
+    (gather_out [B, Hkv, max_visible], vis_out [B, Hkv])
+    (reference: sparse_attn/ops/paged_region_kernels_nfa.py:84-119)."""
+    import ctypes as C
+
+    from ... import _capi
+    rt = cache.ensure_index(indexer)
+    batch = gather_out.shape[0]
+    if tuple(gather_out.shape[1:]) != (cache.num_kv_heads, cache.max_visible_len) or tuple(vis_out.shape) != (
+            batch, cache.num_kv_heads):
+        raise ValueError("protected gather buffers must be [B, Hkv, max_visible] and [B, Hkv]")
+    _capi.check(_capi.lib().loda_protected_gather(
+        C.byref(rt.geometry), C.byref(rt.layer_structs[layer_idx]), C.byref(rt.batch_struct(batch)),
+        _capi.ptr(gather_out), _capi.ptr(vis_out), C.c_void_p(cache.status_buf.data_ptr()), _capi.current_stream()))
