@@ -70,11 +70,13 @@ __device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const 
     ord = ord16(bf16r(__fdiv_rn(acc, gf)));
   } else if (in_near_pool(rg, page)) {
     float kavg[DSUB];
-    const float bsf = (float)g.page;
+    // mean = sum / page: the page size is a power of two, so the division is an exact scaling and
+    // the multiplication by 1 / page gives the same bits at a fraction of the instructions
+    const float inv_bs = 1.0f / (float)g.page;
 #pragma unroll
     for (int c = 0; c < NC; ++c) unpack8(*(const uint4*)(myrow + c * 16), *(float(*)[8])(kavg + 8 * c));
 #pragma unroll
-    for (int i = 0; i < DSUB; ++i) kavg[i] = bf16r(__fdiv_rn(kavg[i], bsf));
+    for (int i = 0; i < DSUB; ++i) kavg[i] = bf16r(__fmul_rn(kavg[i], inv_bs));
     float acc = 0.0f;
 #pragma unroll 1
     for (int j = 0; j < G; ++j) acc = __fadd_rn(acc, bf16r(dot_chunks<DSUB>(kavg, qhat + j * DSUB)));
