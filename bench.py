@@ -691,7 +691,8 @@ def main():
                              "ours_over_dense": (us_layer / dense_us) if dense_us else None},
             "e2e": {"value": (1 if kvhead else world) * 1e3 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": K * N_LAYERS * 2,      # selector (one launch at this batch) + attention per layer-step "device_status": status, "clocks": clocks,
+            # selector (one launch at this batch) + attention per layer-step
+            "gpu_launches": K * N_LAYERS * 2, "device_status": status, "clocks": clocks,
         }
         if not args.skip_batched and not kvhead:
             del wl, runner, cache
