@@ -682,15 +682,14 @@ def main():
             "chain_hbm_frac_of_8TBs": ab["total"] / (us_layer * 1e-6) / 8e12,
             "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel on
-                         # this workload (profiles/fused_chain_cfg2_128k_batch1.md); not measured live
                          # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the selector launch on
                          # this workload (profiles/fused_chain_cfg2_128k_batch1.md); not measured live
                          "traffic": 8821504 if dominant == "select" else None},
             "dense_decode": {"us_per_layer": dense_us, "note": dense_note,
                              "ours_over_dense": (us_layer / dense_us) if dense_us else None},
-            "e2e": {"value": (1 if kvhead else world) * 1e3 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e": None if args.skip_e2e else {
+                "value": (1 if kvhead else world) * 1e3 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             # selector (one launch at this batch) + attention per layer-step
             "gpu_launches": K * N_LAYERS * 2, "device_status": status, "clocks": clocks,
         }

@@ -376,6 +376,60 @@ __device__ __forceinline__ int block_compact_threshold(const uint16_t* sc, int n
   return all ? nvalid : k;
 }
 
+// Bin of the k-th largest element in a histogram over the top 12 bits of 16-bit scores: 4096
+// counters of 16 bits, two per word (bin b in word b >> 1, half b & 1; at most 65535 elements).
+// Thread t covers the words [2048 - (t + 1) W, 2048 - t W), so the running sum over the threads
+// counts from the largest bin down.  *nvalid receives the number of elements; the result is
+// meaningful only when *nvalid > k > 0.  wtot: 64 ints, zero in the columns of absent warps.
+template <int NT, int BAR = 0, int TBASE = 0>
+__device__ __forceinline__ uint32_t block_hist_kth_bin(const uint32_t* hist, int k, int* wtot, int* nvalid) {
+  static_assert(2048 % NT == 0 && (2048 / NT) % 4 == 0, "whole 16-byte vectors per thread");
+  constexpr int NW = NT / 32, WPT = 2048 / NT;
+  const int tid = ((int)threadIdx.x - TBASE), lane = tid & 31, warp = tid >> 5;
+  const int w0 = 2048 - (tid + 1) * WPT;
+  uint32_t w[WPT];
+#pragma unroll
+  for (int i = 0; i < WPT; i += 4) {
+    const uint4 u = *(const uint4*)(hist + w0 + i);
+    w[i] = u.x; w[i + 1] = u.y; w[i + 2] = u.z; w[i + 3] = u.w;
+  }
+  int own = 0;                         // elements in this thread's bins
+#pragma unroll
+  for (int i = 0; i < WPT; ++i) own += (int)((w[i] & 0xFFFFu) + (w[i] >> 16));
+  int incl = own;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int nb = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += nb;
+  }
+  if (lane == 31) wtot[warp] = incl;
+  group_sync<NT, BAR>();
+  int before = 0, tot = 0;
+#pragma unroll
+  for (int w4 = 0; w4 < (NW + 3) / 4; ++w4) {
+    const int4 x = ((const int4*)wtot)[w4];
+    tot += (x.x + x.y) + (x.z + x.w);
+    before += (w4 * 4 + 0 < warp ? x.x : 0) + (w4 * 4 + 1 < warp ? x.y : 0) + (w4 * 4 + 2 < warp ? x.z : 0) +
+              (w4 * 4 + 3 < warp ? x.w : 0);
+  }
+  int c = before + incl - own;         // elements in bins above this thread's
+  if (c < k && k <= c + own) {         // exactly one thread when tot >= k > 0
+    int bin = 0;
+#pragma unroll
+    for (int i = WPT - 1; i >= 0; --i) {
+      const int hi = (int)(w[i] >> 16), lo = (int)(w[i] & 0xFFFFu);
+      if (c < k && k <= c + hi) bin = 2 * (w0 + i) + 1;
+      c += hi;
+      if (c < k && k <= c + lo) bin = 2 * (w0 + i);
+      c += lo;
+    }
+    wtot[32] = bin;
+  }
+  group_sync<NT, BAR>();
+  *nvalid = tot;
+  return (uint32_t)wtot[32];
+}
+
 // (2) any n < 65536, any k: bisection over the 16 score bits, two bits per round.
 // The row is cut into chunks of 8 scores dealt round-robin to the threads (kept in
 // registers); a last partial round of chunks that holds at most NT scores is dealt
@@ -386,15 +440,19 @@ __device__ __forceinline__ int block_compact_threshold(const uint16_t* sc, int n
 // every thread counts its scores at or above three candidate thresholds (independent
 // chains), one barrier publishes the block sums.
 // wtot: 6 x 32 ints (16-byte aligned).
-template <int NT, int BAR = 0, int TBASE = 0, int MAXC = 4>     // MAXC: chunks a thread keeps in registers
-__device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, int k, int* out, int* wtot) {
+// With HIST the caller hands in a histogram of the scored elements by the top 12 bits of their
+// score (block_hist_kth_bin): it replaces the first pass and the six rounds above the last four bits.
+template <int NT, int BAR = 0, int TBASE = 0, int MAXC = 4, bool HIST = false>   // MAXC: chunks a thread keeps in registers
+__device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, int k, int* out, int* wtot,
+                                                    const uint32_t* hist = nullptr) {
   constexpr int NW = NT / 32;
   const int tid = ((int)threadIdx.x - TBASE), lane = tid & 31, warp = tid >> 5;
   const int nchunks = (n + 7) >> 3;
   const int full = nchunks / NT, remc = nchunks - full * NT;     // whole rounds of chunks, chunks left
   const bool single = remc > 0 && remc * 8 <= NT;                // the rest as one score per thread
   const int nslots = full + ((remc > 0 && !single) ? 1 : 0);
-  const bool in_regs = nslots <= MAXC;
+  // MAXC == 1: the caller guarantees n <= 9 NT (one chunk and one single score per thread at most)
+  const bool in_regs = MAXC == 1 || nslots <= MAXC;
   uint4 mine[MAXC];
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
@@ -452,8 +510,10 @@ __device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, i
   LODA_SUB(1);
   // scored elements, their maximum, and 0xFFFF - their minimum (so that empty columns, 0, are neutral)
   int nvalid;
-  uint32_t smax, smin;
-  {
+  uint32_t smax = 0, smin = 0, hist_bin = 0;
+  if constexpr (HIST) {
+    hist_bin = block_hist_kth_bin<NT, BAR, TBASE>(hist, k, wtot, &nvalid);
+  } else {
     int nz = xtra != 0u;
     uint32_t mx = xtra, mi = xtra ? 0xFFFFu - xtra : 0u;
     auto visit = [&](const uint4& u) {
@@ -507,33 +567,41 @@ __device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, i
     int first_round = 8;
     int buf = 1;           // the first pass used the columns of buffer 0; the buffers alternate from here
     thr = smax;
-    if (diff != 0u) {
+    if constexpr (HIST) {
+      first_round = 6;     // the histogram decided the top 12 bits
+      thr = hist_bin << 4;
+    } else if (diff != 0u) {
       const int shift0 = (31 - __clz(diff)) & ~1;
       first_round = (14 - shift0) >> 1;
       thr = smax & ~((4u << shift0) - 1u);
     }
+    // rounds 0..7 decide two bits each; the closing round counts the scores strictly above the
+    // threshold (one loop body for both: this code runs once per launch, and fetching it costs
+    // as much as executing it)
 #pragma unroll 1
-    for (int round = first_round; round < 8; ++round) {
-      const int shift = 14 - 2 * round;
+    for (int round = first_round; round <= 8; ++round) {
+      const bool closing = round == 8;
+      const int shift = closing ? 0 : 14 - 2 * round;
       int c1, c2, c3;
-      count3(thr | (1u << shift), thr | (2u << shift), thr | (3u << shift), c1, c2, c3);
+      count3(closing ? thr + 1u : thr | (1u << shift), closing ? 0x10000u : thr | (2u << shift),
+             closing ? 0x10000u : thr | (3u << shift), c1, c2, c3);
       sum3(buf, c1, c2, c3);
       buf ^= 1;
-      thr |= (c3 >= k ? 3u : c2 >= k ? 2u : c1 >= k ? 1u : 0u) << shift;   // largest candidate with >= k at or above
+      if (closing) rem = k - c1;
+      else thr |= (c3 >= k ? 3u : c2 >= k ? 2u : c1 >= k ? 1u : 0u) << shift;   // largest candidate with >= k at or above
       LODA_SUB(3 + round);
     }
-    int gt, e1, e2;
-    count3(thr + 1u, 0x10000u, 0x10000u, gt, e1, e2);
-    sum3(buf, gt, e1, e2);
-    rem = k - gt;
-    LODA_SUB(11);
   }
-  if (!in_regs) return block_compact_threshold<NT, BAR, TBASE>(sc, n, k, thr, rem, all, nvalid, out, wtot);
+  if constexpr (MAXC > 1) {
+    if (!in_regs) return block_compact_threshold<NT, BAR, TBASE>(sc, n, k, thr, rem, all, nvalid, out, wtot);
+  }
   // Compaction from the registers, in index order: consecutive threads hold consecutive
   // chunks of a slot, so one scan over the threads per slot places its survivors (strictly
-  // above the threshold, then the first `rem` scores equal to it).
+  // above the threshold, then the first `rem` scores equal to it).  The single scores follow
+  // every chunk in index order: they ride with the last slot's scan (two counters per thread,
+  // one barrier), x is the thread's single score there and 0 in the slots before.
   int base_gt = 0, base_tie = 0, cbuf = 0;
-  auto place = [&](const uint32_t (&v)[8], int idx0) {
+  auto place = [&](const uint32_t (&v)[8], int idx0, uint32_t x) {
     // bit j of gm / tm: score j is above / equal to the threshold
     uint32_t gm = 0, tm = 0;
 #pragma unroll
@@ -541,52 +609,7 @@ __device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, i
       gm |= (uint32_t)(all ? v[j] != 0u : v[j] > thr) << j;
       tm |= (uint32_t)((!all) && v[j] == thr) << j;
     }
-    const int own = __popc(gm) | (__popc(tm) << 16);
-    int incl = own;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int nb = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += nb;
-    }
-    if (lane == 31) wtot[cbuf * 32 + warp] = incl;
-    group_sync<NT, BAR>();
-    int before = 0, tot = 0;
-#pragma unroll
-    for (int w4 = 0; w4 < (NW + 3) / 4; ++w4) {
-      const int4 x = ((const int4*)(wtot + cbuf * 32))[w4];
-      tot += (x.x + x.y) + (x.z + x.w);
-      before += (w4 * 4 + 0 < warp ? x.x : 0) + (w4 * 4 + 1 < warp ? x.y : 0) + (w4 * 4 + 2 < warp ? x.z : 0) +
-                (w4 * 4 + 3 < warp ? x.w : 0);
-    }
-    cbuf ^= 1;
-    const int excl = before + incl - own;
-    const int tb = base_tie + (excl >> 16);              // ties before this thread's scores
-    const int pos = base_gt + (excl & 0xFFFF) + min(tb, rem);
-    // of this thread's ties only the first rem - tb survive; every survivor's place follows
-    // from the bits below it, so the eight stores are independent and predicated
-    const int allowed = max(rem - tb, 0);
-    uint32_t m = gm;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if ((tm >> j) & 1u) m |= (uint32_t)(__popc(tm & ((1u << j) - 1u)) < allowed) << j;
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if ((m >> j) & 1u) out[pos + __popc(m & ((1u << j) - 1u))] = idx0 + j;
-    }
-    base_gt += tot & 0xFFFF;
-    base_tie += tot >> 16;
-  };
-  // the last chunk slot and the single scores behind it in one scan (two counters per thread,
-  // one barrier): the single scores follow every chunk in index order
-  auto place_with_single = [&](const uint32_t (&v)[8], int idx0) {
-    uint32_t gm = 0, tm = 0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      gm |= (uint32_t)(all ? v[j] != 0u : v[j] > thr) << j;
-      tm |= (uint32_t)((!all) && v[j] == thr) << j;
-    }
-    const bool xg = all ? xtra != 0u : xtra > thr, xt = (!all) && xtra == thr;
+    const bool xg = all ? x != 0u : x > thr, xt = (!all) && x == thr;
     const int own = __popc(gm) | (__popc(tm) << 16), ownx = (int)xg | ((int)xt << 16);
     int incl = own, inclx = ownx;
 #pragma unroll
@@ -599,19 +622,21 @@ __device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, i
     int before = 0, tot = 0, beforex = 0, totx = 0;
 #pragma unroll
     for (int w4 = 0; w4 < (NW + 3) / 4; ++w4) {
-      const int4 x = ((const int4*)(wtot + cbuf * 32))[w4];
-      const int4 y = ((const int4*)(wtot + 64 + cbuf * 32))[w4];
-      tot += (x.x + x.y) + (x.z + x.w);
-      totx += (y.x + y.y) + (y.z + y.w);
-      before += (w4 * 4 + 0 < warp ? x.x : 0) + (w4 * 4 + 1 < warp ? x.y : 0) + (w4 * 4 + 2 < warp ? x.z : 0) +
-                (w4 * 4 + 3 < warp ? x.w : 0);
-      beforex += (w4 * 4 + 0 < warp ? y.x : 0) + (w4 * 4 + 1 < warp ? y.y : 0) + (w4 * 4 + 2 < warp ? y.z : 0) +
-                 (w4 * 4 + 3 < warp ? y.w : 0);
+      const int4 x4 = ((const int4*)(wtot + cbuf * 32))[w4];
+      const int4 y4 = ((const int4*)(wtot + 64 + cbuf * 32))[w4];
+      tot += (x4.x + x4.y) + (x4.z + x4.w);
+      totx += (y4.x + y4.y) + (y4.z + y4.w);
+      before += (w4 * 4 + 0 < warp ? x4.x : 0) + (w4 * 4 + 1 < warp ? x4.y : 0) + (w4 * 4 + 2 < warp ? x4.z : 0) +
+                (w4 * 4 + 3 < warp ? x4.w : 0);
+      beforex += (w4 * 4 + 0 < warp ? y4.x : 0) + (w4 * 4 + 1 < warp ? y4.y : 0) + (w4 * 4 + 2 < warp ? y4.z : 0) +
+                 (w4 * 4 + 3 < warp ? y4.w : 0);
     }
     cbuf ^= 1;
     const int excl = before + incl - own;
-    const int tb = base_tie + (excl >> 16);
+    const int tb = base_tie + (excl >> 16);              // ties before this thread's scores
     const int pos = base_gt + (excl & 0xFFFF) + min(tb, rem);
+    // of this thread's ties only the first rem - tb survive; every survivor's place follows
+    // from the bits below it, so the eight stores are independent and predicated
     const int allowed = max(rem - tb, 0);
     uint32_t m = gm;
 #pragma unroll
@@ -634,20 +659,17 @@ __device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, i
   group_sync<NT, BAR>();                               // the columns may still be read by slower warps
   if (tid < 128) wtot[tid] = 0;                  // rows of per-warp totals; absent warps stay 0
   group_sync<NT, BAR>();
+  // one loop body for all slots (the registers rotate); a row of single scores alone takes one pass
+  const int ns = min(nslots, MAXC);
+#pragma unroll 1
+  for (int c = 0; c < max(ns, 1); ++c) {
+    uint32_t v[8];
+    unpack_u16x8(c < ns ? mine[0] : make_uint4(0, 0, 0, 0), v);
+    place(v, (tid + c * NT) * 8, c >= ns - 1 ? xtra : 0u);
 #pragma unroll
-  for (int c = 0; c < MAXC; ++c) {
-    if (c < nslots) {
-      uint32_t v[8];
-      unpack_u16x8(mine[c], v);
-      if (single && c == nslots - 1) place_with_single(v, (tid + c * NT) * 8);
-      else place(v, (tid + c * NT) * 8);
-    }
+    for (int r = 0; r + 1 < MAXC; ++r) mine[r] = mine[r + 1];
   }
   LODA_SUB(12);
-  if (single && nslots == 0) {
-    const uint32_t v[8] = {xtra, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-    place(v, full * NT * 8 + tid);
-  }
   group_sync<NT, BAR>();
   LODA_SUB(13);
   return all ? nvalid : k;
@@ -662,39 +684,53 @@ __device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, i
 // order and ranked against each other.  Returns -1 without writing anything
 // when more than 2 NT survive (heavily tied or sorted scores): the caller then
 // bisects.  keys: 2 NT + 8 words (16-byte aligned); wtot: 64 ints; sh: 2 ints.
-template <int NT, int BAR = 0, int TBASE = 0>
+// With HIST the caller hands in a histogram of the row's scored elements by the top 12 bits of
+// their score (block_hist_kth_bin): the bin of the k-th largest is the bound, and the survivors
+// are the k best and the scores that share its bin.
+template <int NT, int BAR = 0, int TBASE = 0, bool HIST = false>
 __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, int k, int* out, uint32_t* keys,
-                                                    int* wtot, int* sh) {
+                                                    int* wtot, int* sh, const uint32_t* hist = nullptr) {
   static_assert(NT % 128 == 0 && NT / 128 <= 32, "group layout");
   constexpr int GS = NT / 128;                   // threads per group
   constexpr int NW = NT / 32;
   const int tid = ((int)threadIdx.x - TBASE), lane = tid & 31, warp = tid >> 5;
   const int nchunks = (n + 7) >> 3;
-  // thread maximum (two independent chains)
-  uint32_t m0 = 0, m1 = 0;
-  for (int ch = tid; ch < nchunks; ch += NT) {
-    uint32_t v[8];
-    unpack_u16x8(((const uint4*)sc)[ch], v);
-    m0 = max(max(m0, max(v[0], v[1])), max(v[2], v[3]));
-    m1 = max(max(m1, max(v[4], v[5])), max(v[6], v[7]));
-  }
-  uint32_t m = max(m0, m1);
+  LODA_SUB(16);
+  uint32_t bound;
+  if constexpr (HIST) {
+    static_assert(NW % 4 == 0, "every column of the histogram scan is written");
+    int nvalid;
+    const uint32_t bin = block_hist_kth_bin<NT, BAR, TBASE>(hist, k, wtot, &nvalid);
+    bound = nvalid > k ? max(bin << 4, 1u) : 1u;
+  } else {
+    // thread maximum (two independent chains)
+    uint32_t m0 = 0, m1 = 0;
+    for (int ch = tid; ch < nchunks; ch += NT) {
+      uint32_t v[8];
+      unpack_u16x8(((const uint4*)sc)[ch], v);
+      m0 = max(max(m0, max(v[0], v[1])), max(v[2], v[3]));
+      m1 = max(max(m1, max(v[4], v[5])), max(v[6], v[7]));
+    }
+    uint32_t m = max(m0, m1);
 #pragma unroll
-  for (int o = 1; o < GS; o <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if ((tid & (GS - 1)) == 0) keys[tid / GS] = rank_key(m, tid / GS);
-  if (tid == 0) sh[1] = 0;
-  group_sync<NT, BAR>();
-  int is_kth = 0;
-  uint32_t gkey = 0;
-  if (tid < 128) {
-    gkey = keys[tid];
-    is_kth = gkey != 0 && count_greater(keys, 32, gkey) == k - 1;
-    if (is_kth) sh[0] = (int)(gkey >> 16);
+    for (int o = 1; o < GS; o <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((tid & (GS - 1)) == 0) keys[tid / GS] = rank_key(m, tid / GS);
+    if (tid == 0) sh[1] = 0;
+    group_sync<NT, BAR>();
+    LODA_SUB(17);
+    int is_kth = 0;
+    uint32_t gkey = 0;
+    if (tid < 128) {
+      gkey = keys[tid];
+      is_kth = gkey != 0 && count_greater(keys, 32, gkey) == k - 1;
+      if (is_kth) sh[0] = (int)(gkey >> 16);
+    }
+    // fewer than k non-empty groups: nothing can be discarded
+    if (is_kth) sh[1] = 1;                         // sh[1] was cleared before the barrier above
+    group_sync<NT, BAR>();
+    bound = sh[1] ? (uint32_t)sh[0] : 1u;
   }
-  // fewer than k non-empty groups: nothing can be discarded
-  if (is_kth) sh[1] = 1;                         // sh[1] was cleared before the barrier above
-  group_sync<NT, BAR>();
-  const uint32_t bound = sh[1] ? (uint32_t)sh[0] : 1u;
+  LODA_SUB(18);
   // survivors: every thread owns `cpt` consecutive chunks, so one scan over the thread counts places
   // them in index order (and yields the total)
   const int cpt = (nchunks + NT - 1) / NT;
@@ -722,6 +758,7 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
     before += w < warp ? x : 0;
   }
   if (total > 2 * NT) return -1;
+  LODA_SUB(19);
   {
     int pos = before + incl - cnt;
     for (int ch = ch0; ch < ch1 && cnt > 0; ++ch) {
@@ -736,6 +773,7 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
   int buf = 1;
   if (tid < 4) keys[total + tid] = 0;            // pad the last vector of keys
   group_sync<NT, BAR>();
+  LODA_SUB(20);
   // exact ranking of the survivors (already in ascending index order), up to two per thread
   const int n4 = (total + 3) >> 2;
   const uint32_t key0 = tid < total ? keys[tid] : 0u;
@@ -751,6 +789,7 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
     if (sel1) out[kept0 + pos1] = 0xFFFF - (int)(key1 & 0xFFFFu);
   }
   group_sync<NT, BAR>();
+  LODA_SUB(21);
   return kept0 + kept1;
 }
 

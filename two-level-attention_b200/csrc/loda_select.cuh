@@ -123,11 +123,13 @@ __device__ void emit_best_first(const int* kept, int n, int k, const uint16_t* s
 // kept[0, np) = [sink bypass] far... near... [window bypass].  Returns np.  All P threads call.
 // keys: 2 P + 8 words; wtot: 256 ints; sh: 8 ints.
 // trigger: release the dependent launch after the two selections.
-template <int P>
+// HIST (P == 512): hist holds the far pool's scores counted by their top 12 bits (block_hist_kth_bin).
+template <int P, bool HIST = false>
 __device__ __forceinline__ int l1_select_pages(const loda_geometry& g, const Regions& rg, const loda_selection& out,
                                                int row, uint16_t* scf, uint16_t* scn, int n_far, int far_lo, int n_near,
                                                int near_lo, int near_lo8, int near_hi, int* kept, uint32_t* keys,
-                                               int* wtot, int* sh, bool trigger) {
+                                               int* wtot, int* sh, bool trigger, const uint32_t* hist = nullptr) {
+  static_assert(!HIST || P == 512, "the histogram serves the two-group selection");
   const int tid = threadIdx.x;
   int np = 0;
   const bool want_lists = out.i_far != nullptr;
@@ -147,8 +149,9 @@ __device__ __forceinline__ int l1_select_pages(const loda_geometry& g, const Reg
           } else if (n_far <= 2 * H) {
             r = block_rank_topk_pair<H, 1, 0>(scf, n_far, g.k_far, kept + np, keys, wtot);
           } else {
-            r = g.k_far <= 128 ? block_prefilter_topk<H, 1, 0>(scf, n_far, g.k_far, kept + np, keys, wtot, sh) : -1;
-            if (r < 0) r = block_bisect_topk<H, 1, 0>(scf, n_far, g.k_far, kept + np, wtot);   // heavily tied scores
+            r = g.k_far <= 128 ? block_prefilter_topk<H, 1, 0, HIST>(scf, n_far, g.k_far, kept + np, keys, wtot, sh, hist)
+                               : -1;
+            if (r < 0) r = block_bisect_topk<H, 1, 0, 4, HIST>(scf, n_far, g.k_far, kept + np, wtot, hist);   // heavily tied scores
           }
         }
         if (tid == 0) sh[2] = r;
@@ -161,7 +164,9 @@ __device__ __forceinline__ int l1_select_pages(const loda_geometry& g, const Reg
         }
         if (tid == H) sh[3] = r;
       }
+      LODA_SUB(22);
       __syncthreads();
+      LODA_SUB(23);
       n_f = sh[2];
       n_n = sh[3];
     } else {
@@ -190,17 +195,21 @@ __device__ __forceinline__ int l1_select_pages(const loda_geometry& g, const Reg
                          g.max_blocks);
       __syncthreads();
     }
+    LODA_SUB(25);
     if (rg.quota > 0) {
       // ascending list: [sink bypass] far... near... [window bypass]
       const int v0 = tid < n_n ? kept_near[tid] : 0;     // k_near <= 2 P
       const int v1 = tid + P < n_n ? kept_near[tid + P] : 0;
       __syncthreads();
+      LODA_SUB(26);
       if (tid < n_n) kept[np + n_f + tid] = v0;
       if (tid + P < n_n) kept[np + n_f + tid + P] = v1;
       np += n_f + n_n;
       if (rg.swa_byp) { if (tid == 0) kept[np] = rg.swa_byp_blk; ++np; }
     }
+    LODA_SUB(27);
     __syncthreads();
+    LODA_SUB(24);
   }
   return np;
 }
@@ -264,12 +273,13 @@ struct L2Shared {
   uint16_t* sc;
   int *pages, *physs, *mid_a, *mid_b, *wtot, *scan;
   uint8_t* win;
+  const uint32_t* hist = nullptr;    // HIST: 12-bit histogram of the candidate scores (block_hist_kth_bin)
 };
 
 #ifndef LODA_L2TAIL_INLINE
 #define LODA_L2TAIL_INLINE __forceinline__
 #endif
-template <int NT, int BAR>
+template <int NT, int BAR, bool HIST = false>
 __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, const Regions& rg, const loda_selection& S,
                                                     uint32_t* status, const int32_t* table, int b, int kv, int row,
                                                     int length, int nitems, const L2Shared& sm, int* ticket,
@@ -285,8 +295,9 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
   // two instantiations: rows of at most 9 NT slots (one chunk and one single score per thread: the
   // 2 080 slots of the default budgets) run a much shorter instruction stream, and executed once,
   // cold, a selection costs about as much in instruction fetch as in arithmetic
-  const int take = nitems <= 9 * NT ? block_bisect_topk<NT, BAR, 0, 1>(sc, nitems, min(quota, K2), slots_sel, wtot)
-                                    : block_bisect_topk<NT, BAR, 0, 4>(sc, nitems, min(quota, K2), slots_sel, wtot);
+  const int take = nitems <= 9 * NT
+                       ? block_bisect_topk<NT, BAR, 0, 1, HIST>(sc, nitems, min(quota, K2), slots_sel, wtot, sm.hist)
+                       : block_bisect_topk<NT, BAR, 0, 4, HIST>(sc, nitems, min(quota, K2), slots_sel, wtot, sm.hist);
   if (trigger) pdl_launch_dependents();
   if (take == quota) {
     // Common case: the quota is filled by scored candidates (all of them >= sink, no holes).

@@ -40,7 +40,7 @@ constexpr int SF_CLUSTER_MAX = 16; // CTAs per row: 16, or 8 when the GPU cannot
 constexpr int SF_L2_NT = 256;      // threads of the leader that run the level-2 selection
 
 struct FusedLayout {
-  size_t rows_bytes, qv, kept, physk, keys, wtot, scan, sh, scall, total;
+  size_t rows_bytes, qv, kept, physk, keys, wtot, scan, sh, hist2, scall, total;
 };
 
 __host__ __device__ inline FusedLayout fused_layout(const loda_geometry& g, int tiles_per_cta, int cluster_size) {
@@ -59,6 +59,7 @@ __host__ __device__ inline FusedLayout fused_layout(const loda_geometry& g, int 
   f.scan = off; off += 40 * 4;
   f.sh = off; off += 8 * 4;
   off = (off + 15) & ~(size_t)15;
+  f.hist2 = off; off += 2048 * 4;                                      // candidate scores by their top 12 bits
   f.scall = off; off += (size_t)tiles_per_cta * cluster_size * SF_P * 2 + 16;   // every page score of the row
   f.total = off;
   return f;
@@ -93,6 +94,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   int* scan = (int*)(smem + lay.scan);
   int* sh = (int*)(smem + lay.sh);
   uint16_t* scall = (uint16_t*)(smem + lay.scall);
+  uint32_t* hist2 = (uint32_t*)(smem + lay.hist2);
 
   const int tid = threadIdx.x;
   const int rank = (int)cluster.block_rank();        // = blockIdx.x: the cluster spans the grid's x
@@ -105,8 +107,10 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   int* l_physk = cluster.map_shared_rank(physk, 0);
   int* l_sh = cluster.map_shared_rank(sh, 0);
   uint16_t* l_sc2 = (uint16_t*)cluster.map_shared_rank(rows, 0);       // level-2 scores, over the leader's rows
+  uint32_t* l_hist2 = cluster.map_shared_rank(hist2, 0);
 
   LODA_PHASE(sel, cta_id, 0);
+  if (rank == 0) *(uint4*)(hist2 + 4 * tid) = make_uint4(0, 0, 0, 0);      // 2048 words; counted into after barrier (2)
   cluster.barrier_arrive();   // (0) "this CTA runs": waited for just before the first store into a peer
   pdl_wait();
   // this thread's first query element is requested before anything that depends on the
@@ -209,6 +213,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     LODA_PHASE(sel, cta_id, 3);
     const int np = l1_select_pages<P>(g, rg, S, row, scf, scn, n_far, far_lo, n_near, near_lo, near_lo8, near_hi, kept,
                                       keys, wtot, sh, false);
+    LODA_PHASE(sel, cta_id, 8);
     for (int i = tid; i < np; i += P) {
       const int pg = kept[i];
       int ph = (pg >= 0 && pg < g.max_blocks) ? table[pg] : -1;
@@ -231,7 +236,10 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     for (int idx = lo + tid; idx < hi; idx += P) {
       const int i = idx >> (31 - __clz(g.page)), o = idx & (g.page - 1);      // page is a power of two
       const int pg = l_kept[i], ph = l_physk[i];
-      l_sc2[idx] = (uint16_t)l2_slot_score<DSUB>(g, L, rg, length, kv, pg, ph, o, qf, status);
+      const uint32_t ord = l2_slot_score<DSUB>(g, L, rg, length, kv, pg, ph, o, qf, status);
+      l_sc2[idx] = (uint16_t)ord;
+      // the leader's histogram of the scores by their top 12 bits (two 16-bit counters per word)
+      if (ord != 0u) atomicAdd(l_hist2 + (ord >> 5), 1u << ((ord >> 4 & 1u) * 16));
     }
   }
   LODA_PHASE(sel, cta_id, 6);
@@ -252,7 +260,8 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     shm.win = (uint8_t*)(rows + off);
     shm.wtot = wtot;
     shm.scan = scan;
-    l2_select_and_write<SF_L2_NT, 1>(g, rg, S, status, table, b, kv, row, length, nitems, shm, nullptr, true);
+    shm.hist = hist2;
+    l2_select_and_write<SF_L2_NT, 1, true>(g, rg, S, status, table, b, kv, row, length, nitems, shm, nullptr, true);
   }
   LODA_PHASE(sel, cta_id, 9);
 }
