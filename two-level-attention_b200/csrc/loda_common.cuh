@@ -11,10 +11,10 @@
 // optional sub-phase timestamps inside the block routines (compile with -DLODA_PHASES):
 // thread 0 of the CTAs with blockIdx.y == 0 records clock64() at numbered points
 #ifdef LODA_PHASES
-static __device__ long long g_subphase[32];
+static __device__ long long g_subphase[64];
 #define LODA_SUB(i) do { if (threadIdx.x == 0 && blockIdx.y == 0) g_subphase[(i)] = clock64(); } while (0)
 #define LODA_SUB_READER(name) extern "C" int loda_phase_read_sub_##name(long long* host) { \
-    return (int)cudaMemcpyFromSymbol(host, g_subphase, sizeof(long long) * 32); }
+    return (int)cudaMemcpyFromSymbol(host, g_subphase, sizeof(long long) * 64); }
 #else
 #define LODA_SUB(i)
 #define LODA_SUB_READER(name)
@@ -691,7 +691,8 @@ template <int NT, int BAR = 0, int TBASE = 0, bool HIST = false>
 __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, int k, int* out, uint32_t* keys,
                                                     int* wtot, int* sh, const uint32_t* hist = nullptr) {
   static_assert(NT % 128 == 0 && NT / 128 <= 32, "group layout");
-  constexpr int GS = NT / 128;                   // threads per group
+  constexpr int NG = 128;                        // groups
+  constexpr int GS = NT / NG;                    // threads per group
   constexpr int NW = NT / 32;
   const int tid = ((int)threadIdx.x - TBASE), lane = tid & 31, warp = tid >> 5;
   const int nchunks = (n + 7) >> 3;
@@ -705,7 +706,8 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
   } else {
     // thread maximum (two independent chains)
     uint32_t m0 = 0, m1 = 0;
-    for (int ch = tid; ch < nchunks; ch += NT) {
+#pragma unroll 1                                 // (the loops of this routine run once per launch: fetching an
+    for (int ch = tid; ch < nchunks; ch += NT) { //  unrolled copy costs more than the loop overhead it saves)
       uint32_t v[8];
       unpack_u16x8(((const uint4*)sc)[ch], v);
       m0 = max(max(m0, max(v[0], v[1])), max(v[2], v[3]));
@@ -720,9 +722,9 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
     LODA_SUB(17);
     int is_kth = 0;
     uint32_t gkey = 0;
-    if (tid < 128) {
+    if (tid < NG) {
       gkey = keys[tid];
-      is_kth = gkey != 0 && count_greater(keys, 32, gkey) == k - 1;
+      is_kth = gkey != 0 && count_greater(keys, NG / 4, gkey) == k - 1;
       if (is_kth) sh[0] = (int)(gkey >> 16);
     }
     // fewer than k non-empty groups: nothing can be discarded
@@ -736,6 +738,7 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
   const int cpt = (nchunks + NT - 1) / NT;
   const int ch0 = tid * cpt, ch1 = min(ch0 + cpt, nchunks);
   int cnt = 0;
+#pragma unroll 1
   for (int ch = ch0; ch < ch1; ++ch) {
     uint32_t v[8];
     unpack_u16x8(((const uint4*)sc)[ch], v);
@@ -757,10 +760,14 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
     total += x;
     before += w < warp ? x : 0;
   }
+#ifdef LODA_PHASES
+  if (tid == 0 && blockIdx.y < 8) { g_subphase[32 + blockIdx.y] = total; g_subphase[40 + blockIdx.y] = bound; }
+#endif
   if (total > 2 * NT) return -1;
   LODA_SUB(19);
   {
     int pos = before + incl - cnt;
+#pragma unroll 1
     for (int ch = ch0; ch < ch1 && cnt > 0; ++ch) {
       uint32_t v[8];
       unpack_u16x8(((const uint4*)sc)[ch], v);
@@ -777,17 +784,30 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
   // exact ranking of the survivors (already in ascending index order), up to two per thread
   const int n4 = (total + 3) >> 2;
   const uint32_t key0 = tid < total ? keys[tid] : 0u;
-  const bool sel0 = key0 != 0 && count_greater(keys, n4, key0) < k;
-  int kept0;
-  const int pos0 = block_flag_scan<NT, BAR, TBASE>(sel0, wtot, buf, &kept0);
-  if (sel0) out[pos0] = 0xFFFF - (int)(key0 & 0xFFFFu);
-  int kept1 = 0;
-  if (total > NT) {                              // uniform
-    const uint32_t key1 = tid + NT < total ? keys[tid + NT] : 0u;
-    const bool sel1 = key1 != 0 && count_greater(keys, n4, key1) < k;
-    const int pos1 = block_flag_scan<NT, BAR, TBASE>(sel1, wtot, buf ^ 1, &kept1);
-    if (sel1) out[kept0 + pos1] = 0xFFFF - (int)(key1 & 0xFFFFu);
+  if (total <= NT) {                             // uniform
+    const bool sel0 = key0 != 0 && count_greater(keys, n4, key0) < k;
+    int kept0;
+    const int pos0 = block_flag_scan<NT, BAR, TBASE>(sel0, wtot, buf, &kept0);
+    if (sel0) out[pos0] = 0xFFFF - (int)(key0 & 0xFFFFu);
+    group_sync<NT, BAR>();
+    LODA_SUB(21);
+    return kept0;
   }
+  // more survivors than threads: both keys of a thread are ranked in one pass over the keys
+  const uint32_t key1 = tid + NT < total ? keys[tid + NT] : 0u;
+  int a0 = 0, a1 = 0, b0 = 0, b1 = 0;
+#pragma unroll 2
+  for (int j = 0; j < n4; ++j) {
+    const uint4 o = ((const uint4*)keys)[j];
+    a0 += (o.x > key0) + (o.y > key0); a1 += (o.z > key0) + (o.w > key0);
+    b0 += (o.x > key1) + (o.y > key1); b1 += (o.z > key1) + (o.w > key1);
+  }
+  const bool sel0 = key0 != 0 && a0 + a1 < k, sel1 = key1 != 0 && b0 + b1 < k;
+  int kept0, kept1;
+  const int pos0 = block_flag_scan<NT, BAR, TBASE>(sel0, wtot, buf, &kept0);
+  const int pos1 = block_flag_scan<NT, BAR, TBASE>(sel1, wtot, buf ^ 1, &kept1);
+  if (sel0) out[pos0] = 0xFFFF - (int)(key0 & 0xFFFFu);
+  if (sel1) out[kept0 + pos1] = 0xFFFF - (int)(key1 & 0xFFFFu);
   group_sync<NT, BAR>();
   LODA_SUB(21);
   return kept0 + kept1;

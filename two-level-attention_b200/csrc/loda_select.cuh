@@ -214,7 +214,9 @@ __device__ __forceinline__ int l1_select_pages(const loda_geometry& g, const Reg
   return np;
 }
 
-template <int DSUB>
+// ROLLED: one loop body per word of codes, for a caller that scores a single slot per thread (the
+// straight-line form costs more in instruction fetch there than its arithmetic)
+template <int DSUB, bool ROLLED = false>
 __device__ __forceinline__ float l2_logit(const uint8_t* __restrict__ codes, float scale, float zero,
                                           const float* __restrict__ qf) {
   constexpr int WORDS = DSUB / 8;   // 32-bit words of packed codes
@@ -233,13 +235,28 @@ __device__ __forceinline__ float l2_logit(const uint8_t* __restrict__ codes, flo
     }
   }
   float acc = 0.0f;
+  if constexpr (ROLLED) {
+#pragma unroll 1
+    for (int i = 0; i < WORDS; ++i) {
+      const uint32_t wi = w[0];
 #pragma unroll
-  for (int i = 0; i < WORDS; ++i) {
+      for (int r = 0; r + 1 < WORDS; ++r) w[r] = w[r + 1];       // the registers rotate
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      const float c = (float)((w[i] >> (4 * n)) & 15u);
-      const float x = bf16r(__fsub_rn(bf16r(__fmul_rn(c, scale)), zero));
-      acc = __fadd_rn(acc, __fmul_rn(x, qf[8 * i + n]));
+      for (int n = 0; n < 8; ++n) {
+        const float c = (float)((wi >> (4 * n)) & 15u);
+        const float x = bf16r(__fsub_rn(bf16r(__fmul_rn(c, scale)), zero));
+        acc = __fadd_rn(acc, __fmul_rn(x, qf[8 * i + n]));
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < WORDS; ++i) {
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const float c = (float)((w[i] >> (4 * n)) & 15u);
+        const float x = bf16r(__fsub_rn(bf16r(__fmul_rn(c, scale)), zero));
+        acc = __fadd_rn(acc, __fmul_rn(x, qf[8 * i + n]));
+      }
     }
   }
   return bf16r(acc);
@@ -247,7 +264,7 @@ __device__ __forceinline__ float l2_logit(const uint8_t* __restrict__ codes, flo
 
 // Ordered 16-bit logit of candidate slot (logical page pg, physical page ph, offset o); 0 = the
 // token is not a candidate (outside the scored window, NaN or -inf logit, invalid page).
-template <int DSUB>
+template <int DSUB, bool ROLLED = false>
 __device__ __forceinline__ uint32_t l2_slot_score(const loda_geometry& g, const loda_layer& L, const Regions& rg,
                                                   int length, int kv, int pg, int ph, int o, const float* qf,
                                                   uint32_t* status) {
@@ -256,7 +273,7 @@ __device__ __forceinline__ uint32_t l2_slot_score(const loda_geometry& g, const 
   if (ph >= 0 && tok >= g.sink && tok < rg.swa_lo_tok && tok < length && tok >= rg.lower && tok < rg.upper) {
     const size_t trow = ((size_t)ph * g.num_kv_heads + kv) * g.page + o;
     const __nv_bfloat162 sz = *(const __nv_bfloat162*)((const bf16*)L.tail_sz + trow * 2);
-    const float lg = l2_logit<DSUB>((const uint8_t*)L.tail_code + trow * (DSUB / 2), __low2float(sz), __high2float(sz), qf);
+    const float lg = l2_logit<DSUB, ROLLED>((const uint8_t*)L.tail_code + trow * (DSUB / 2), __low2float(sz), __high2float(sz), qf);
     if (lg == lg && lg != -INFINITY) ord = ord16(lg);
   } else if (ph < 0 && status && rg.shard_count <= 1) {     // under sequence sharding a missing page is another GPU's
     atomicOr(status, LODA_STATUS_BAD_PAGE);
@@ -313,6 +330,7 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
     const int total = sk + take + n_s;
     const int n_out = min(total, g.max_visible);
     int32_t* gout = S.gather + ((size_t)b * g.num_kv_heads + kv) * g.max_visible;
+#pragma unroll 1
     for (int i = tid; i < n_out; i += NT) {
       int slot;
       if (i >= sk && i < sk + take) {

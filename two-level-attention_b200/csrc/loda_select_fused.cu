@@ -202,18 +202,22 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     const int n_near = near_hi > near_lo ? min(near_hi - near_lo8, L1_NEAR_CAP) : 0;
     uint16_t* scf = scall;
     uint16_t* scn = (uint16_t*)(rows + 40 * 1024);
+#pragma unroll 1
     for (int i = tid; i < ((n_near + 7) & ~7); i += P) {
       const int pgi = near_lo8 + i;
       scn[i] = (pgi >= near_lo && pgi < near_hi) ? scall[pgi] : (uint16_t)0;
     }
     __syncthreads();
+#pragma unroll 1
     for (int i = tid; i < far_lo; i += P) scf[i] = 0;
+#pragma unroll 1
     for (int i = far_hi + tid; i < ((n_far + 7) & ~7); i += P) scf[i] = 0;
     __syncthreads();
     LODA_PHASE(sel, cta_id, 3);
     const int np = l1_select_pages<P>(g, rg, S, row, scf, scn, n_far, far_lo, n_near, near_lo, near_lo8, near_hi, kept,
                                       keys, wtot, sh, false);
     LODA_PHASE(sel, cta_id, 8);
+#pragma unroll 1
     for (int i = tid; i < np; i += P) {
       const int pg = kept[i];
       int ph = (pg >= 0 && pg < g.max_blocks) ? table[pg] : -1;
@@ -233,10 +237,11 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   {
     const int per = ((nitems + CS - 1) / CS + 7) & ~7;
     const int lo = min(rank * per, nitems), hi = min(lo + per, nitems);
+#pragma unroll 1
     for (int idx = lo + tid; idx < hi; idx += P) {
       const int i = idx >> (31 - __clz(g.page)), o = idx & (g.page - 1);      // page is a power of two
       const int pg = l_kept[i], ph = l_physk[i];
-      const uint32_t ord = l2_slot_score<DSUB>(g, L, rg, length, kv, pg, ph, o, qf, status);
+      const uint32_t ord = l2_slot_score<DSUB, true>(g, L, rg, length, kv, pg, ph, o, qf, status);
       l_sc2[idx] = (uint16_t)ord;
       // the leader's histogram of the scores by their top 12 bits (two 16-bit counters per word)
       if (ord != 0u) atomicAdd(l_hist2 + (ord >> 5), 1u << ((ord >> 4 & 1u) * 16));
