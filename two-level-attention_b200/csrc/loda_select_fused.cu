@@ -4,8 +4,10 @@
 //
 //   1. every CTA stages and scores its tiles of 512 pages (as l1_kernel does) and stores the
 //      16-bit page scores straight into the row leader's shared memory (DSMEM);
-//   2. cluster barrier; the leader (rank 0) selects the far and near pages and looks up their
-//      physical pages, while rank 1 performs the decode append of the row;
+//   2. cluster barrier; the leader (rank 0) selects the far pages, rank 1 selects the near pages
+//      (it copies their scores out of the leader's shared memory and stores its result back
+//      there; run beside the far selection on the leader's SM it slowed the longer of the two
+//      by a fifth), both look up the physical pages; rank 2 performs the decode append of the row;
 //   3. cluster barrier; every CTA scores its share of the candidate slots on the packed 4-bit
 //      tail keys, reading the page list from the leader's shared memory and storing the 16-bit
 //      logits there;
@@ -40,7 +42,7 @@ constexpr int SF_CLUSTER_MAX = 16; // CTAs per row: 16, or 8 when the GPU cannot
 constexpr int SF_L2_NT = 256;      // threads of the leader that run the level-2 selection
 
 struct FusedLayout {
-  size_t rows_bytes, qv, kept, physk, keys, wtot, scan, sh, hist2, scall, total;
+  size_t rows_bytes, qv, kept, physk, kept2, physk2, keys, wtot, scan, sh, hist2, scall, total;
 };
 
 __host__ __device__ inline FusedLayout fused_layout(const loda_geometry& g, int tiles_per_cta, int cluster_size) {
@@ -53,6 +55,8 @@ __host__ __device__ inline FusedLayout fused_layout(const loda_geometry& g, int 
   f.qv = off; off += (size_t)(3 * G + 1) * g.sub_dims * 4;             // qhat, qlow, qhigh [G][d'], qf [d']
   f.kept = off; off += (size_t)np_max * 4;
   f.physk = off; off += (size_t)np_max * 4;
+  f.kept2 = off; off += (size_t)np_max * 4;                            // the list without its gaps (leader)
+  f.physk2 = off; off += (size_t)np_max * 4;
   off = (off + 15) & ~(size_t)15;
   f.keys = off; off += (size_t)(2 * SF_P + 8) * 4;
   f.wtot = off; off += 256 * 4;
@@ -89,6 +93,8 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   float* qf = qhigh + G * DSUB;
   int* kept = (int*)(smem + lay.kept);
   int* physk = (int*)(smem + lay.physk);
+  int* kept2 = (int*)(smem + lay.kept2);
+  int* physk2 = (int*)(smem + lay.physk2);
   uint32_t* keys = (uint32_t*)(smem + lay.keys);
   int* wtot = (int*)(smem + lay.wtot);
   int* scan = (int*)(smem + lay.scan);
@@ -186,53 +192,107 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   cluster.sync();                                        // (1) all page scores are in the leader
   LODA_PHASE(sel, cta_id, 2);
 
-  if (rank == 1 && ap.enabled && tid < 32) {
+  if (rank == 2 && ap.enabled && tid < 32) {
     // The decode append of the row.  It touches only the newest token and its page, which lie
     // in the sliding window and are read by neither level of this step; the attention kernel
     // runs after this launch completes.
     append_row<DSUB>(g, L, B, ap.k_new, ap.v_new, ap.slots, ap.status, b, kv, tid);
   }
   const int32_t* table = L.block_table + (size_t)req * g.max_blocks;
+  // The page list lives in the leader in four parts at fixed places, so that the two selecting
+  // CTAs need not know each other's counts:
+  //   [0, np0) sink bypass | [np0, np0 + n_f) far | [np0 + k_far, .. + n_n) near | [np0 + k_far + k_near] window bypass
+  const bool listed = rg.quota > 0;
+  const bool want_lists = S.i_far != nullptr;
+  const int np0 = (listed && rg.sink_byp && rg.spl < rg.kt_eff) ? 1 : 0;
+  const int near_at = np0 + g.k_far, swa_at = np0 + g.k_far + g.k_near;
+  const int near_hi = min(min(rg.swa_lo_blk, rg.kt_eff), g.max_blocks);
+  const int near_lo = rg.near_blks, near_lo8 = near_lo & ~7;
+  const int n_near = near_hi > near_lo ? min(near_hi - near_lo8, L1_NEAR_CAP) : 0;
+  auto phys_of = [&](int pg) {
+    int ph = (pg >= 0 && pg < g.max_blocks) ? table[pg] : -1;
+    return (ph < 0 || ph >= g.num_pages) ? -1 : ph;
+  };
   if (rank == 0) {
-    // far row = the row's scores in place (zero outside the far pool), near row copied out first
-    const int near_hi = min(min(rg.swa_lo_blk, rg.kt_eff), g.max_blocks);
+    // far row = the row's scores in place, zero outside the far pool
     const int far_lo = rg.far_lo, far_hi = max(rg.far_hi, rg.far_lo);
-    const int near_lo = rg.near_blks, near_lo8 = near_lo & ~7;
     const int n_far = far_hi;
-    const int n_near = near_hi > near_lo ? min(near_hi - near_lo8, L1_NEAR_CAP) : 0;
     uint16_t* scf = scall;
-    uint16_t* scn = (uint16_t*)(rows + 40 * 1024);
-#pragma unroll 1
-    for (int i = tid; i < ((n_near + 7) & ~7); i += P) {
-      const int pgi = near_lo8 + i;
-      scn[i] = (pgi >= near_lo && pgi < near_hi) ? scall[pgi] : (uint16_t)0;
-    }
-    __syncthreads();
 #pragma unroll 1
     for (int i = tid; i < far_lo; i += P) scf[i] = 0;
 #pragma unroll 1
     for (int i = far_hi + tid; i < ((n_far + 7) & ~7); i += P) scf[i] = 0;
     __syncthreads();
     LODA_PHASE(sel, cta_id, 3);
-    const int np = l1_select_pages<P>(g, rg, S, row, scf, scn, n_far, far_lo, n_near, near_lo, near_lo8, near_hi, kept,
-                                      keys, wtot, sh, false);
-    LODA_PHASE(sel, cta_id, 8);
-#pragma unroll 1
-    for (int i = tid; i < np; i += P) {
-      const int pg = kept[i];
-      int ph = (pg >= 0 && pg < g.max_blocks) ? table[pg] : -1;
-      if (ph < 0 || ph >= g.num_pages) ph = -1;
-      physk[i] = ph;
+    constexpr int H = 256;             // the selection runs on the first 256 threads (named barrier 1)
+    if (tid < H) {
+      int r = 0;
+      if ((listed || want_lists) && n_far > far_lo) {
+        if (n_far <= H) {
+          r = block_rank_topk_small<H, 1, 0>(scf, n_far, g.k_far, kept + np0, keys, wtot);
+        } else if (n_far <= 2 * H) {
+          r = block_rank_topk_pair<H, 1, 0>(scf, n_far, g.k_far, kept + np0, keys, wtot);
+        } else {
+          r = g.k_far <= 128 ? block_prefilter_topk<H, 1, 0>(scf, n_far, g.k_far, kept + np0, keys, wtot, sh) : -1;
+          if (r < 0) r = block_bisect_topk<H, 1, 0>(scf, n_far, g.k_far, kept + np0, wtot);   // heavily tied scores
+        }
+      }
+      if (tid == 0) sh[2] = r;
     }
-    if (tid == 0) sh[4] = np;
+    __syncthreads();
+    const int n_f = sh[2];
+    LODA_PHASE(sel, cta_id, 8);
+    if (want_lists)
+      emit_best_first<P>(kept + np0, n_f, g.k_far, scf, S.i_far + (size_t)row * g.k_far, S.n_far + row, g.max_blocks);
+    if (listed) {
+      if (tid == 0 && np0) { kept[0] = rg.spl; physk[0] = phys_of(rg.spl); }
+      if (tid == 32 && rg.swa_byp) { kept[swa_at] = rg.swa_byp_blk; physk[swa_at] = phys_of(rg.swa_byp_blk); }
+#pragma unroll 1
+      for (int i = tid; i < n_f; i += P) physk[np0 + i] = phys_of(kept[np0 + i]);
+    }
     LODA_PHASE(sel, cta_id, 4);
+  } else if (rank == 1) {
+    // near row: the pool's scores out of the leader's row, zero outside the pool
+    uint16_t* scn = (uint16_t*)rows;
+#pragma unroll 1
+    for (int i = tid; i < ((n_near + 7) & ~7); i += P) {
+      const int pgi = near_lo8 + i;
+      scn[i] = (pgi >= near_lo && pgi < near_hi) ? l_scall[pgi] : (uint16_t)0;
+    }
+    __syncthreads();
+    int n_n = 0;
+    if ((listed || want_lists) && n_near > 0) {      // n_near <= 512 = P
+      n_n = block_rank_topk_small<P>(scn, n_near, g.k_near, kept, keys, wtot);
+    }
+    if (want_lists) {
+      for (int i = tid; i < n_n; i += P) kept[i] += near_lo8;
+      __syncthreads();
+      // scores by page id: the row starts at page near_lo8
+      emit_best_first<P>(kept, n_n, g.k_near, scn - near_lo8, S.i_near + (size_t)row * g.k_near, S.n_near + row,
+                         g.max_blocks);
+      __syncthreads();
+      for (int i = tid; i < n_n; i += P) kept[i] -= near_lo8;
+      __syncthreads();
+    }
+    if (listed) {
+#pragma unroll 1
+      for (int i = tid; i < n_n; i += P) {
+        const int pg = kept[i] + near_lo8;
+        l_kept[near_at + i] = pg;
+        l_physk[near_at + i] = phys_of(pg);
+      }
+    }
+    if (tid == 0) l_sh[3] = listed ? n_n : 0;
   }
   cluster.sync();                                        // (2) page list and physical pages are in the leader
   LODA_PHASE(sel, cta_id, 5);
 
   // ---- level 2: score this CTA's share of the candidate slots ---------------------------------
   const int np_max = g.k_far + g.k_near + 2;
-  const int np = min(l_sh[4], np_max);
+  const int n_f = listed ? l_sh[2] : 0, n_n = l_sh[3];
+  const int np = listed ? np0 + n_f + n_n + (rg.swa_byp ? 1 : 0) : 0;
+  // place of list entry i in the leader's arrays
+  auto place_of = [&](int i) { return i < np0 + n_f ? i : i < np0 + n_f + n_n ? i - n_f + g.k_far : swa_at; };
   const int nitems = np * g.page;
   {
     const int per = ((nitems + CS - 1) / CS + 7) & ~7;
@@ -240,11 +300,21 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
 #pragma unroll 1
     for (int idx = lo + tid; idx < hi; idx += P) {
       const int i = idx >> (31 - __clz(g.page)), o = idx & (g.page - 1);      // page is a power of two
-      const int pg = l_kept[i], ph = l_physk[i];
+      const int at = place_of(i);
+      const int pg = l_kept[at], ph = l_physk[at];
       const uint32_t ord = l2_slot_score<DSUB, true>(g, L, rg, length, kv, pg, ph, o, qf, status);
       l_sc2[idx] = (uint16_t)ord;
       // the leader's histogram of the scores by their top 12 bits (two 16-bit counters per word)
       if (ord != 0u) atomicAdd(l_hist2 + (ord >> 5), 1u << ((ord >> 4 & 1u) * 16));
+    }
+    // the leader closes the gaps of its list for the last phase; its highest threads have no slot to score
+    if (rank == 0) {
+#pragma unroll 1
+      for (int i = P - 1 - tid; i < np; i += P) {
+        const int at = place_of(i);
+        kept2[i] = kept[at];
+        physk2[i] = physk[at];
+      }
     }
   }
   LODA_PHASE(sel, cta_id, 6);
@@ -258,8 +328,8 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     size_t off = ((size_t)np_max * g.page * 2 + 15) & ~(size_t)15;     // behind the scores
     L2Shared shm;
     shm.sc = (uint16_t*)rows;
-    shm.pages = kept;
-    shm.physs = physk;
+    shm.pages = kept2;
+    shm.physs = physk2;
     shm.mid_a = (int*)(rows + off); off += (size_t)K2 * 4;
     shm.mid_b = (int*)(rows + off); off += (size_t)K2 * 4;
     shm.win = (uint8_t*)(rows + off);
