@@ -24,6 +24,7 @@
 
 #include <cstdio>
 
+#include "loda_attn.cuh"
 #include "loda_common.cuh"
 
 namespace loda {
@@ -39,27 +40,6 @@ constexpr int ATT_STAGES = 3;
 #ifndef LODA_ATTN_CTAS_PER_SM
 #define LODA_ATTN_CTAS_PER_SM 1
 #endif
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_ptr) {
-  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_ptr);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_ptr) {
-  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_ptr);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *(uint32_t*)&v;
-}
 
 LODA_PHASE_STORAGE(attn)
 
@@ -93,18 +73,7 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
   // their own wait), the query was complete before they could release this launch, and it is
   // read before the wait; a launch that stands alone reads it after.
   uint32_t qa[KSTEPS][4];
-  auto load_q = [&]() {
-    const int r0 = lane >> 2, r1 = r0 + 8, kc = (lane & 3) * 2;
-    const bf16* q0 = q + ((size_t)t * g.num_q_heads + kv * G + r0) * D;
-    const bf16* q1 = q + ((size_t)t * g.num_q_heads + kv * G + r1) * D;
-#pragma unroll
-    for (int ks = 0; ks < KSTEPS; ++ks) {
-      qa[ks][0] = r0 < G ? *(const uint32_t*)(q0 + ks * 16 + kc) : 0u;
-      qa[ks][1] = r1 < G ? *(const uint32_t*)(q1 + ks * 16 + kc) : 0u;
-      qa[ks][2] = r0 < G ? *(const uint32_t*)(q0 + ks * 16 + kc + 8) : 0u;
-      qa[ks][3] = r1 < G ? *(const uint32_t*)(q1 + ks * 16 + kc + 8) : 0u;
-    }
-  };
+  auto load_q = [&]() { attn_load_q<D>(qa, q + ((size_t)t * g.num_q_heads + kv * G) * D, G, lane); };
   if (chained) load_q();
   pdl_wait();
 #if LODA_PDL_TRIGGER == 0
@@ -186,78 +155,7 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
 
     const int tok0 = warp * 16;
     if (tok0 < ntok) {
-      // S = Q K^T for this warp's 16 tokens: two n-tiles of 8 tokens
-      float sacc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
-#pragma unroll
-      for (int ks = 0; ks < KSTEPS; ++ks) {
-        uint32_t kb[4];
-        const int mi = lane >> 3, r = lane & 7;
-        ldmatrix_x4(kb, Kt + (tok0 + (mi >> 1) * 8 + r) * KSTR + ks * 16 + (mi & 1) * 8);
-        mma_bf16(sacc[0], qa[ks], kb[0], kb[1]);
-        mma_bf16(sacc[1], qa[ks], kb[2], kb[3]);
-      }
-      // mask, scale (log2 domain), per-row max over this warp's tokens
-      float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int tk = tok0 + j * 8 + (lane & 3) * 2 + (e & 1);
-          const bool ok = tk < ntok && slot_t[tk] >= 0;
-          const float v = ok ? sacc[j][e] * scale_log2 : -INFINITY;
-          sacc[j][e] = v;
-          mx[e >> 1] = fmaxf(mx[e >> 1], v);
-        }
-      }
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-      }
-      float alpha[2], msafe[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const float m_new = fmaxf(m_run[h], mx[h]);
-        msafe[h] = m_new == -INFINITY ? 0.0f : m_new;
-        alpha[h] = exp2f(m_run[h] - msafe[h]);     // m_run = -inf -> 0
-        m_run[h] = m_new;
-      }
-      uint32_t pa[4];
-      float zs[2] = {0.0f, 0.0f};
-      {
-        float p[2][4];
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            p[j][e] = exp2f(sacc[j][e] - msafe[e >> 1]);
-            zs[e >> 1] += p[j][e];
-          }
-        pa[0] = pack_bf16(p[0][0], p[0][1]);   // row r,   tokens 0..7
-        pa[1] = pack_bf16(p[0][2], p[0][3]);   // row r+8, tokens 0..7
-        pa[2] = pack_bf16(p[1][0], p[1][1]);   // row r,   tokens 8..15
-        pa[3] = pack_bf16(p[1][2], p[1][3]);   // row r+8, tokens 8..15
-      }
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        zs[h] += __shfl_xor_sync(0xffffffffu, zs[h], 1);
-        zs[h] += __shfl_xor_sync(0xffffffffu, zs[h], 2);
-        z_run[h] = z_run[h] * alpha[h] + zs[h];
-      }
-#pragma unroll
-      for (int i = 0; i < NTV; ++i) {
-        oacc[i][0] *= alpha[0]; oacc[i][1] *= alpha[0];
-        oacc[i][2] *= alpha[1]; oacc[i][3] *= alpha[1];
-      }
-      // O += P V: V^T fragments by transposed ldmatrix, two dv n-tiles per load
-#pragma unroll
-      for (int i = 0; i < NTV; i += 2) {
-        uint32_t vb[4];
-        const int mi = lane >> 3, r = lane & 7;
-        ldmatrix_x4_trans(vb, Vt + (tok0 + (mi & 1) * 8 + r) * VSTR + i * 8 + (mi >> 1) * 8);
-        mma_bf16(oacc[i], pa, vb[0], vb[1]);
-        mma_bf16(oacc[i + 1], pa, vb[2], vb[3]);
-      }
+      attn_warp_step<D, DV>(Kt, Vt, slot_t, tok0, ntok, qa, scale_log2, oacc, m_run, z_run);
     }
     __syncthreads();   // the stage is free: refill it
     issue(stage, nxt, it + ATT_STAGES);

@@ -22,6 +22,8 @@ cudaError_t launch_protected_gather(const loda_geometry&, const loda_layer&, con
                                     uint32_t*, cudaStream_t);
 bool select_fused_applicable(const loda_geometry&, int);
 void select_fused_refuse(int);
+cudaError_t launch_decode_fused(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
+                                const loda_selection&, uint32_t*, const AppendArgs&, const int32_t*, void*, cudaStream_t);
 cudaError_t launch_select_fused(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
                                 const loda_selection&, uint32_t*, const AppendArgs&, cudaStream_t);
 cudaError_t launch_attn(const loda_geometry&, const loda_layer&, const void*, const int32_t*, const int32_t*,
@@ -393,6 +395,26 @@ int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda
                      const void* k_new, const void* v_new, const int32_t* slots, float scale,
                      const loda_selection* sel, const int32_t* query_to_req, void* out, uint32_t* status,
                      void* workspace, void* stream) {
+  // One launch for the whole step where a cluster per row fits the GPU (batch 1 at long context)
+  // and the head dimensions are the attention phase's; everything else, and every argument error,
+  // goes through the two entry points below, which validate their arguments themselves.
+  if (g && layer && b && sel && q && out && query_to_req && workspace && k_new && v_new && slots && sel->gather &&
+      sel->visible_lens && b->batch > 0 && check_geometry(g) == LODA_OK && check_layer(layer) == LODA_OK &&
+      check_batch(g, b) == LODA_OK && g->shard_count <= 1 && (sel->i_far == nullptr || (sel->i_near && sel->n_far && sel->n_near)) &&
+      (sel->middle == nullptr) == (sel->middle_counts == nullptr) && !sel->middle_only &&
+      select_fused_applicable(*g, b->batch * g->num_kv_heads)) {
+    const AppendArgs ap{(const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, slots, status, 1};
+    const cudaError_t e = launch_decode_fused(*g, *layer, *b, q, scale, *sel, status, ap, query_to_req, out,
+                                              (cudaStream_t)stream);
+    if (e == cudaSuccess) return LODA_OK;
+    if (e != cudaErrorNotSupported) {
+      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+      cudaStreamIsCapturing((cudaStream_t)stream, &cap);
+      if (cap != cudaStreamCaptureStatusNone) return check_cuda(e, "decode_step/fused");   // cannot retry inside a capture
+      (void)cudaGetLastError();
+      select_fused_refuse(g->sub_dims);
+    }
+  }
   LODA_TRY(loda_select_step(g, layer, b, q, k_new, v_new, slots, scale, sel, status, workspace, stream));
   if (b->batch == 0) return LODA_OK;
   return gather_attend_impl(g, layer, q, sel->gather, sel->visible_lens, query_to_req, b->batch, g->max_requests,

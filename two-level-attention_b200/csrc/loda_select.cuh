@@ -291,6 +291,8 @@ struct L2Shared {
   int *pages, *physs, *mid_a, *mid_b, *wtot, *scan;
   uint8_t* win;
   const uint32_t* hist = nullptr;    // HIST: 12-bit histogram of the candidate scores (block_hist_kth_bin)
+  int* list = nullptr;               // optional copy of the gather list in shared memory (max_visible ints) ...
+  int* list_n = nullptr;             // ... and of its length
 };
 
 #ifndef LODA_L2TAIL_INLINE
@@ -353,8 +355,10 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
         slot = ph >= 0 ? ph * g.page + (id & pmask) : -1;
       }
       gout[i] = slot;
+      if (sm.list) sm.list[i] = slot;
     }
     if (tid == 0) {
+      if (sm.list_n) *sm.list_n = n_out;
       if (S.middle != nullptr) S.middle_counts[row] = take;
       S.visible_lens[(size_t)b * g.num_kv_heads + kv] = n_out;
       if (total > g.max_visible && status) atomicOr(status, LODA_STATUS_TRUNCATED);
@@ -442,9 +446,12 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
         ph = g.num_pages - 1;   // PAD page: zeros, never out of bounds
       }
     }
-    gout[i] = ph >= 0 ? ph * g.page + (id & pmask) : -1;
+    const int slot = ph >= 0 ? ph * g.page + (id & pmask) : -1;
+    gout[i] = slot;
+    if (sm.list) sm.list[i] = slot;
   }
   if (tid == 0) {
+    if (sm.list_n) *sm.list_n = n_out;
     S.visible_lens[(size_t)b * g.num_kv_heads + kv] = n_out;
     if (total > g.max_visible && status) atomicOr(status, LODA_STATUS_TRUNCATED);
     if (ticket) *ticket = 0;

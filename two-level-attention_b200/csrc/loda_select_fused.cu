@@ -21,13 +21,14 @@
 // (nfa_layer_batch_selector.py:174-354, 422-605, 1194-1251, 1336-1437, 1473-1793).
 //
 // The cluster barriers are hardware barriers (no spinning in this code); every CTA of a
-// cluster executes all four of them on every path.
+// cluster executes all of them on every path (four, six with the attention phase).
 #include <cooperative_groups.h>
 
 #include <cstdlib>
 #include <cstring>
 
 #include "loda_append.cuh"
+#include "loda_attn.cuh"
 #include "loda_select.cuh"
 
 namespace loda {
@@ -42,7 +43,7 @@ constexpr int SF_CLUSTER_MAX = 16; // CTAs per row: 16, or 8 when the GPU cannot
 constexpr int SF_L2_NT = 256;      // threads of the leader that run the level-2 selection
 
 struct FusedLayout {
-  size_t rows_bytes, qv, kept, physk, kept2, physk2, keys, wtot, scan, sh, hist2, scall, total;
+  size_t rows_bytes, qv, kept, physk, kept2, physk2, keys, wtot, scan, sh, hist2, list, pfm, pfo, scall, total;
 };
 
 __host__ __device__ inline FusedLayout fused_layout(const loda_geometry& g, int tiles_per_cta, int cluster_size) {
@@ -64,6 +65,10 @@ __host__ __device__ inline FusedLayout fused_layout(const loda_geometry& g, int 
   f.sh = off; off += 8 * 4;
   off = (off + 15) & ~(size_t)15;
   f.hist2 = off; off += 2048 * 4;                                      // candidate scores by their top 12 bits
+  f.list = off; off += ((size_t)g.max_visible * 4 + 15) & ~(size_t)15;     // the row's gather list, for the attention phase
+  // the CTAs' attention partials, collected by the leader: max and sum [cs][2][16], output [cs][G][Dv] (fp32)
+  f.pfm = off; off += (size_t)cluster_size * 32 * 4;
+  f.pfo = off; off += (size_t)cluster_size * G * g.head_dim_v * 4;
   f.scall = off; off += (size_t)tiles_per_cta * cluster_size * SF_P * 2 + 16;   // every page score of the row
   f.total = off;
   return f;
@@ -75,10 +80,27 @@ __host__ __device__ inline size_t fused_l2_bytes(const loda_geometry& g) {
   return ((np_max * g.page * 2 + 15) & ~(size_t)15) + 2 * (size_t)g.level2_topk * 4 + g.level2_topk + 32;
 }
 
-template <int DSUB>
+// the attention phase of the launch: query_to_req [batch] (the identity, or < 0 for a row of zeros),
+// out [batch, Hq, head_dim_v]
+struct FusedAttend {
+  const int32_t* query_to_req;
+  bf16* out;
+  float scale_log2;
+};
+
+// tokens of the attention tile a CTA stages at a time: what fits the staging rows, 256 at most
+__host__ __device__ inline int fused_attend_tile(const loda_geometry& g, size_t rows_total) {
+  const size_t per_token = (size_t)(g.head_dim + 8) * 2 + (size_t)(g.head_dim_v + 8) * 2 + 4;
+  const size_t cap = rows_total / per_token;
+  return (int)(cap > 256 ? 256 : cap) & ~15;
+}
+
+// D: head dimension of the attention phase (keys and values alike), 0 = selection only
+template <int DSUB, int D>
 __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, loda_layer L, loda_batch B,
                                                             const bf16* __restrict__ q, float scale, loda_selection S,
-                                                            uint32_t* status, AppendArgs ap, int tiles_per_cta) {
+                                                            uint32_t* status, AppendArgs ap, int tiles_per_cta,
+                                                            FusedAttend at) {
   constexpr int P = SF_P;
   constexpr int NC = DSUB / 8, CPR = 2 * NC, ROWB = 4 * DSUB + 16;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -101,22 +123,34 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   int* sh = (int*)(smem + lay.sh);
   uint16_t* scall = (uint16_t*)(smem + lay.scall);
   uint32_t* hist2 = (uint32_t*)(smem + lay.hist2);
+  int* list = (int*)(smem + lay.list);
 
   const int tid = threadIdx.x;
   const int rank = (int)cluster.block_rank();        // = blockIdx.x: the cluster spans the grid's x
   const int row = blockIdx.y;
   const int b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
   const int cta_id = blockIdx.y * gridDim.x + blockIdx.x;
-  // the leader's copies of what the cluster shares
-  uint16_t* l_scall = cluster.map_shared_rank(scall, 0);
-  int* l_kept = cluster.map_shared_rank(kept, 0);
-  int* l_physk = cluster.map_shared_rank(physk, 0);
-  int* l_sh = cluster.map_shared_rank(sh, 0);
-  uint16_t* l_sc2 = (uint16_t*)cluster.map_shared_rank(rows, 0);       // level-2 scores, over the leader's rows
-  uint32_t* l_hist2 = cluster.map_shared_rank(hist2, 0);
+  // The leader's copies of what the cluster shares.  The leader itself uses its plain shared
+  // addresses: a store through the cluster window into the CTA's own shared memory is a remote
+  // store that the CTA's next barrier has to wait for (measured: the leader reached the first
+  // cluster barrier 2 000 cycles after its peers).
+#ifdef LODA_X_SELFMAP
+  const bool own = false;
+#else
+  const bool own = rank == 0;
+#endif
+  uint16_t* l_scall = own ? scall : cluster.map_shared_rank(scall, 0);
+  int* l_kept = own ? kept : cluster.map_shared_rank(kept, 0);
+  int* l_physk = own ? physk : cluster.map_shared_rank(physk, 0);
+  int* l_sh = own ? sh : cluster.map_shared_rank(sh, 0);
+  uint16_t* l_sc2 = (uint16_t*)(own ? rows : cluster.map_shared_rank(rows, 0));     // level-2 scores, over the leader's rows
+  uint32_t* l_hist2 = own ? hist2 : cluster.map_shared_rank(hist2, 0);
 
   LODA_PHASE(sel, cta_id, 0);
   if (rank == 0) *(uint4*)(hist2 + 4 * tid) = make_uint4(0, 0, 0, 0);      // 2048 words; counted into after barrier (2)
+  // rank 1 collects the near pool's scores in the same place of its own shared memory (it has no
+  // histogram): zero outside the pool, so cleared before any peer may store
+  if (rank == 1 && tid < (L1_NEAR_CAP + 8) / 2) hist2[tid] = 0;
   cluster.barrier_arrive();   // (0) "this CTA runs": waited for just before the first store into a peer
   pdl_wait();
   // this thread's first query element is requested before anything that depends on the
@@ -136,6 +170,10 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   const unsigned char* mm_base = (const unsigned char*)L.page_mm + pg0 * (4 * DSUB);
   const unsigned char* sum_base = (const unsigned char*)L.page_sum + pg0 * (2 * DSUB);
   const int page_end = min(rg.kt_eff, g.max_blocks);
+  const int near_hi = min(min(rg.swa_lo_blk, rg.kt_eff), g.max_blocks);
+  const int near_lo = rg.near_blks, near_lo8 = near_lo & ~7;
+  const int n_near = near_hi > near_lo ? min(near_hi - near_lo8, L1_NEAR_CAP) : 0;
+  uint16_t* r1_scn = (uint16_t*)(rank == 1 ? hist2 : cluster.map_shared_rank(hist2, 1));   // near row of rank 1
 
   // ---- level 1: score this CTA's tiles (rank, rank + CS, ...), two staging buffers ------------
   auto stage = [&](int it) {
@@ -184,6 +222,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     const unsigned char* src = rows + (size_t)(it & 1) * lay.rows_bytes;
     const uint32_t ord = l1_page_score<DSUB>(g, rg, page, src + (size_t)tid * ROWB, qhat, qlow, qhigh, G);
     l_scall[page] = (uint16_t)ord;                       // into the leader's shared memory
+    if (page >= near_lo && page < near_hi && page - near_lo8 < n_near) r1_scn[page - near_lo8] = (uint16_t)ord;
     __syncthreads();                                     // the buffer is free
     stage(it + 2);
   }
@@ -206,9 +245,6 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   const bool want_lists = S.i_far != nullptr;
   const int np0 = (listed && rg.sink_byp && rg.spl < rg.kt_eff) ? 1 : 0;
   const int near_at = np0 + g.k_far, swa_at = np0 + g.k_far + g.k_near;
-  const int near_hi = min(min(rg.swa_lo_blk, rg.kt_eff), g.max_blocks);
-  const int near_lo = rg.near_blks, near_lo8 = near_lo & ~7;
-  const int n_near = near_hi > near_lo ? min(near_hi - near_lo8, L1_NEAR_CAP) : 0;
   auto phys_of = [&](int pg) {
     int ph = (pg >= 0 && pg < g.max_blocks) ? table[pg] : -1;
     return (ph < 0 || ph >= g.num_pages) ? -1 : ph;
@@ -224,17 +260,23 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     for (int i = far_hi + tid; i < ((n_far + 7) & ~7); i += P) scf[i] = 0;
     __syncthreads();
     LODA_PHASE(sel, cta_id, 3);
+#ifdef LODA_X_FAR256
     constexpr int H = 256;             // the selection runs on the first 256 threads (named barrier 1)
+    constexpr int HB = 1;
+#else
+    constexpr int H = P;
+    constexpr int HB = 0;
+#endif
     if (tid < H) {
       int r = 0;
       if ((listed || want_lists) && n_far > far_lo) {
         if (n_far <= H) {
-          r = block_rank_topk_small<H, 1, 0>(scf, n_far, g.k_far, kept + np0, keys, wtot);
+          r = block_rank_topk_small<H, HB, 0>(scf, n_far, g.k_far, kept + np0, keys, wtot);
         } else if (n_far <= 2 * H) {
-          r = block_rank_topk_pair<H, 1, 0>(scf, n_far, g.k_far, kept + np0, keys, wtot);
+          r = block_rank_topk_pair<H, HB, 0>(scf, n_far, g.k_far, kept + np0, keys, wtot);
         } else {
-          r = g.k_far <= 128 ? block_prefilter_topk<H, 1, 0>(scf, n_far, g.k_far, kept + np0, keys, wtot, sh) : -1;
-          if (r < 0) r = block_bisect_topk<H, 1, 0>(scf, n_far, g.k_far, kept + np0, wtot);   // heavily tied scores
+          r = g.k_far <= 128 ? block_prefilter_topk<H, HB, 0>(scf, n_far, g.k_far, kept + np0, keys, wtot, sh) : -1;
+          if (r < 0) r = block_bisect_topk<H, HB, 0>(scf, n_far, g.k_far, kept + np0, wtot);   // heavily tied scores
         }
       }
       if (tid == 0) sh[2] = r;
@@ -252,14 +294,8 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     }
     LODA_PHASE(sel, cta_id, 4);
   } else if (rank == 1) {
-    // near row: the pool's scores out of the leader's row, zero outside the pool
-    uint16_t* scn = (uint16_t*)rows;
-#pragma unroll 1
-    for (int i = tid; i < ((n_near + 7) & ~7); i += P) {
-      const int pgi = near_lo8 + i;
-      scn[i] = (pgi >= near_lo && pgi < near_hi) ? l_scall[pgi] : (uint16_t)0;
-    }
-    __syncthreads();
+    // near row: the pool's scores as the scoring CTAs stored them, zero outside the pool
+    uint16_t* scn = (uint16_t*)hist2;
     int n_n = 0;
     if ((listed || want_lists) && n_near > 0) {      // n_near <= 512 = P
       n_n = block_rank_topk_small<P>(scn, n_near, g.k_near, kept, keys, wtot);
@@ -319,11 +355,11 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   }
   LODA_PHASE(sel, cta_id, 6);
   cluster.sync();                                        // (3) all candidate scores are in the leader
-  if (rank != 0 || tid >= SF_L2_NT) return;
+  if (D == 0 && (rank != 0 || tid >= SF_L2_NT)) return;
   LODA_PHASE(sel, cta_id, 7);
 
   // ---- leader, first 256 threads: quota selection, hole fill, union, gather list --------------
-  {
+  if (rank == 0 && tid < SF_L2_NT) {
     const int K2 = g.level2_topk;
     size_t off = ((size_t)np_max * g.page * 2 + 15) & ~(size_t)15;     // behind the scores
     L2Shared shm;
@@ -336,9 +372,146 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     shm.wtot = wtot;
     shm.scan = scan;
     shm.hist = hist2;
-    l2_select_and_write<SF_L2_NT, 1, true>(g, rg, S, status, table, b, kv, row, length, nitems, shm, nullptr, true);
+    if (D > 0) { shm.list = list; shm.list_n = sh + 5; }
+    // with an attention phase the dependent launch is released after its tiles instead
+    l2_select_and_write<SF_L2_NT, 1, true>(g, rg, S, status, table, b, kv, row, length, nitems, shm, nullptr, D == 0);
   }
   LODA_PHASE(sel, cta_id, 9);
+  if constexpr (D > 0) {
+    // ---- attention over the row's gather list, split over the CTAs of the cluster ------------
+    // Every CTA takes a balanced chunk of the list (read from the leader's shared memory),
+    // stages its K and V rows at once, each warp handles 16 tokens (attn_warp_step); warps,
+    // then CTAs, merge by log-sum-exp in a fixed order; the CTAs' partials go to the leader,
+    // which merges them and writes the output.
+    constexpr int DV = D, KSTR = D + 8, VSTR = DV + 8, NTV = DV / 8, KCH = D / 8, NW = SF_P / 32;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int q2r = at.query_to_req[b];
+    uint32_t qa[D / 16][4];
+    attn_load_q<D>(qa, q + ((size_t)b * g.num_q_heads + kv * G) * D, G, lane);
+    const int* l_list = own ? list : cluster.map_shared_rank(list, 0);
+    const int tcap = fused_attend_tile(g, lay.rows_bytes * (tiles_per_cta > 1 ? 2 : 1));
+    bf16* Ks = (bf16*)rows;                              // [tcap][KSTR]
+    bf16* Vs = Ks + (size_t)tcap * KSTR;                 // [tcap][VSTR]
+    int* slot_t = (int*)(Vs + (size_t)tcap * VSTR);      // [tcap]
+    float* wm = (float*)keys;                            // [NW][16]
+    float* wz = wm + NW * 16;                            // [NW][16]
+    float* wo = (float*)Ks;                              // [NW][G][DV], over the consumed K tile
+    float* pfm = (float*)(smem + lay.pfm);               // leader: [CS][2][16]
+    float* pfo = (float*)(smem + lay.pfo);               // leader: [CS][G][DV]
+    float* l_pfm = own ? pfm : cluster.map_shared_rank(pfm, 0);
+    float* l_pfo = own ? pfo : cluster.map_shared_rank(pfo, 0);
+    const int page_log2 = 31 - __clz(g.page);
+    const int slot_end = g.num_pages * g.page;
+    float oacc[NTV][4];
+#pragma unroll
+    for (int i = 0; i < NTV; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.0f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, z_run[2] = {0.0f, 0.0f};
+    cluster.sync();                                      // (4) the gather list is in the leader
+    const int n = q2r == b ? min(max(l_sh[5], 0), g.max_visible) : 0;
+    const int c0 = (int)(((long long)rank * n) / CS), c1 = (int)(((long long)(rank + 1) * n) / CS);
+#pragma unroll 1
+    for (int p0 = c0; p0 < c1; p0 += tcap) {
+      const int ntok = min(tcap, c1 - p0);
+      __syncthreads();                                 // the tile (or the partials) of the pass before is consumed
+      // 16-byte chunk kc of rows kr, kr + 32, ...: all their list entries in one round of remote loads,
+      // then the copies; masked rows, and rows beyond ntok up to the next multiple of 16, are zero-filled
+      constexpr int RPI = SF_P / KCH, NIT = 256 / RPI;
+      const int kr = tid / KCH, kc = tid % KCH;
+      const int nrow = (ntok + 15) & ~15;
+      int sl[NIT];
+#pragma unroll
+      for (int k = 0; k < NIT; ++k) {
+        const int r = kr + k * RPI;
+        const int s = r < ntok ? l_list[p0 + r] : -1;
+        sl[k] = s >= slot_end ? -1 : s;
+      }
+#pragma unroll
+      for (int k = 0; k < NIT; ++k) {
+        const int r = kr + k * RPI, s = sl[k];
+        if (r < nrow) {
+          const long long off = s >= 0 ? ((long long)(s >> page_log2) * g.num_kv_heads + kv) * g.page + (s & (g.page - 1)) : 0;
+          cp_async16(Ks + (size_t)r * KSTR + kc * 8, (const bf16*)L.pool_k + off * D + kc * 8, s >= 0);
+          cp_async16(Vs + (size_t)r * VSTR + kc * 8, (const bf16*)L.pool_v + off * DV + kc * 8, s >= 0);
+          if (kc == 0) slot_t[r] = s;
+        }
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncthreads();
+      if (warp * 16 < ntok) attn_warp_step<D, DV>(Ks, Vs, slot_t, warp * 16, ntok, qa, at.scale_log2, oacc, m_run, z_run);
+    }
+    pdl_launch_dependents();
+    LODA_PHASE(sel, cta_id, 10);
+    // merge the warps of this CTA (fixed order) and hand the CTA's partial to the leader
+    __syncthreads();                                   // every warp is done with the tile
+    {
+      const int r0 = lane >> 2;
+      if ((lane & 3) == 0) {
+        wm[warp * 16 + r0] = m_run[0]; wz[warp * 16 + r0] = z_run[0];
+        wm[warp * 16 + r0 + 8] = m_run[1]; wz[warp * 16 + r0 + 8] = z_run[1];
+      }
+#pragma unroll
+      for (int i = 0; i < NTV; ++i) {
+        const int col = i * 8 + (lane & 3) * 2;
+        if (r0 < G) { wo[(warp * G + r0) * DV + col] = oacc[i][0]; wo[(warp * G + r0) * DV + col + 1] = oacc[i][1]; }
+        if (r0 + 8 < G) { wo[(warp * G + r0 + 8) * DV + col] = oacc[i][2]; wo[(warp * G + r0 + 8) * DV + col + 1] = oacc[i][3]; }
+      }
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (int e = tid; e < G * DV; e += SF_P) {
+      const int gi = e / DV, dv = e % DV;
+      float pm[NW];
+#pragma unroll
+      for (int w = 0; w < NW; ++w) pm[w] = wm[w * 16 + gi];
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) M = fmaxf(M, pm[w]);
+      float z = 0.0f, o = 0.0f;
+      if (M != -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+          const float a = exp2f(pm[w] - M);
+          z += wz[w * 16 + gi] * a;
+          o += wo[(w * G + gi) * DV + dv] * a;
+        }
+      }
+      l_pfo[(size_t)rank * G * DV + e] = o;
+      if (dv == 0) { l_pfm[rank * 32 + gi] = M; l_pfm[rank * 32 + 16 + gi] = z; }
+    }
+    if (rank != 0) {
+      cluster.sync();                                    // (5) every CTA's partial is in the leader
+      return;
+    }
+    // the leader merges the CTAs' partials in rank order and writes the row's output
+    {
+      cluster.sync();                                    // (5)
+      LODA_PHASE(sel, cta_id, 11);
+#pragma unroll 1
+      for (int e = tid; e < G * DV; e += SF_P) {
+        const int gi = e / DV, dv = e % DV;
+        float pm[SF_CLUSTER_MAX];
+#pragma unroll
+        for (int s2 = 0; s2 < SF_CLUSTER_MAX; ++s2) pm[s2] = s2 < CS ? pfm[s2 * 32 + gi] : -INFINITY;
+        float M = -INFINITY;
+#pragma unroll
+        for (int s2 = 0; s2 < SF_CLUSTER_MAX; ++s2) M = fmaxf(M, pm[s2]);
+        float z = 0.0f, o = 0.0f;
+        if (M != -INFINITY) {
+#pragma unroll
+          for (int s2 = 0; s2 < SF_CLUSTER_MAX; ++s2) {
+            if (s2 < CS) {
+              const float a = exp2f(pm[s2] - M);
+              z += pfm[s2 * 32 + 16 + gi] * a;
+              o += pfo[(size_t)s2 * G * DV + e] * a;
+            }
+          }
+        }
+        at.out[((size_t)b * g.num_q_heads + kv * G + gi) * DV + dv] = __float2bfloat16_rn(z == 0.0f ? 0.0f : o / z);
+      }
+    }
+    LODA_PHASE(sel, cta_id, 12);
+  }
 }
 
 static bool g_fused_refused[3] = {false, false, false};    // per sub-space width: a launch failed, stay on the chain
@@ -368,18 +541,31 @@ bool select_fused_applicable(const loda_geometry& g, int rows) {
   return fused_shape_ok(g, 16) || fused_shape_ok(g, 8);
 }
 
-template <int DS>
+// whether the launch may also run the attention of the step on a cluster of cs CTAs
+static bool fused_attend_ok(const loda_geometry& g, int cs) {
+  // LODA_B200_DECODE_PATH=split keeps the attention in its own launch (A/B measurements, tests of both paths)
+  const char* path = getenv("LODA_B200_DECODE_PATH");
+  if (path && strcmp(path, "split") == 0) return false;
+  if (g.head_dim != 128 || g.head_dim_v != 128) return false;
+  const int G = g.num_q_heads / g.num_kv_heads;
+  const FusedLayout lay = fused_layout(g, fused_tiles_per_cta(g, cs), cs);
+  const int tcap = fused_attend_tile(g, lay.rows_bytes * (fused_tiles_per_cta(g, cs) > 1 ? 2 : 1));
+  // the warps' partial outputs and the CTA's merged one lie over the K tile
+  return tcap >= 16 && (size_t)(SF_P / 32 + 1) * G * g.head_dim_v * 4 <= (size_t)tcap * (g.head_dim + 8) * 2 && G <= 16;
+}
+
+template <int DS, int D>
 static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                   float scale, const loda_selection& S, uint32_t* status, const AppendArgs& ap,
-                                  cudaStream_t st) {
+                                  const FusedAttend& at, cudaStream_t st) {
   const int rows = B.batch * g.num_kv_heads;
-  auto kernel = select_fused_kernel<DS>;
+  auto kernel = select_fused_kernel<DS, D>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   if (e != cudaSuccess) return e;
   // clusters of 16 CTAs when the GPU holds one for every row at once, else clusters of 8 (two tiles
   // per CTA at 128K tokens); the answers are remembered per shape
   struct Memo { size_t smem; int rows_ok; };
-  static Memo memo[3][2] = {};
+  static Memo memo[3][2] = {};                           // (per instantiation of this template)
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -394,6 +580,7 @@ static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, c
   for (int which = 0; which < 2; ++which) {
     const int cs = which == 0 ? 16 : 8;
     if (!fused_shape_ok(g, cs) || rows * cs > 148) continue;
+    if (D > 0 && !fused_attend_ok(g, cs)) continue;
     const int tpc = fused_tiles_per_cta(g, cs);
     const size_t smem = fused_layout(g, tpc, cs).total;
     e = set_kernel_smem(kernel, smem);
@@ -409,7 +596,7 @@ static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, c
       m.rows_ok = nclusters;
     }
     if (rows > m.rows_ok) continue;                      // the clusters of all rows must run at once
-    return cudaLaunchKernelEx(&cfg, kernel, g, L, B, (const bf16*)q, scale, S, status, ap, tpc);
+    return cudaLaunchKernelEx(&cfg, kernel, g, L, B, (const bf16*)q, scale, S, status, ap, tpc, at);
   }
   return cudaErrorNotSupported;
 }
@@ -420,10 +607,26 @@ void select_fused_refuse(int sub_dims) { g_fused_refused[fused_slot(sub_dims)] =
 cudaError_t launch_select_fused(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                 float scale, const loda_selection& S, uint32_t* status, const AppendArgs& ap,
                                 cudaStream_t st) {
+  const FusedAttend none{nullptr, nullptr, 0.0f};
   switch (g.sub_dims) {
-    case 16: return launch_fused_d<16>(g, L, B, q, scale, S, status, ap, st);
-    case 32: return launch_fused_d<32>(g, L, B, q, scale, S, status, ap, st);
-    case 64: return launch_fused_d<64>(g, L, B, q, scale, S, status, ap, st);
+    case 16: return launch_fused_d<16, 0>(g, L, B, q, scale, S, status, ap, none, st);
+    case 32: return launch_fused_d<32, 0>(g, L, B, q, scale, S, status, ap, none, st);
+    case 64: return launch_fused_d<64, 0>(g, L, B, q, scale, S, status, ap, none, st);
+    default: return cudaErrorNotSupported;
+  }
+}
+
+// The same launch followed, inside it, by the attention of the step (out [batch, Hq, head_dim_v],
+// query_to_req the identity or < 0).  cudaErrorNotSupported = nothing was launched: the caller runs
+// the selection and the attention as separate launches.
+cudaError_t launch_decode_fused(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
+                                float scale, const loda_selection& S, uint32_t* status, const AppendArgs& ap,
+                                const int32_t* query_to_req, void* out, cudaStream_t st) {
+  const FusedAttend at{query_to_req, (bf16*)out, scale * 1.4426950408889634f};
+  switch (g.sub_dims) {
+    case 16: return launch_fused_d<16, 128>(g, L, B, q, scale, S, status, ap, at, st);
+    case 32: return launch_fused_d<32, 128>(g, L, B, q, scale, S, status, ap, at, st);
+    case 64: return launch_fused_d<64, 128>(g, L, B, q, scale, S, status, ap, at, st);
     default: return cudaErrorNotSupported;
   }
 }
