@@ -39,6 +39,9 @@ PKG = "two-level-attention_b200"
 
 N_LAYERS, HQ, HKV, D, PAGE = 36, 32, 8, 128, 16
 CONTEXT = 131072
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the one-launch decode step on this
+# workload, from one ncu capture (None until captured)
+DECODE_STEP_DRAM_BYTES = None
 SUB = 32
 METRIC = "decode tok/s at 128K ctx, two-level select+attend path over all layers"
 
@@ -656,15 +659,24 @@ def main():
     h2d = int(dq.numel() + dk.numel() + dv.numel()) * 2 + (N_LAYERS * 4 + 8 + 8 + 4 + 4)
     d2h = int(hout.numel()) * 2
 
+    # kernels per layer-step of the product path as the library last ran it: 1 = selection and attention
+    # in one launch, 2 = one-launch selection + attention, 3 = L1, L2, attention
+    launches_per_layer = int(lib.loda_last_decode_launches()) or 2
     if rank == 0:
         peak, peak_kind = peaks()
         ab = algorithmic_bytes(CONTEXT)
         # the product path launches the selector ("select": append + both levels, one launch at this
         # batch) and the attention; l1 / l2 / append are the selector's parts as stand-alone launches
-        dominant = max(("select", "attn"), key=per_kernel.get)
+        us_layer = ms_per_step * 1e3 / N_LAYERS
+        if launches_per_layer == 1:
+            # one launch per layer-step does everything: its average duration is the chain's time per layer
+            per_kernel["decode_step"] = us_layer
+            ab["decode_step"] = ab["total"]
+            dominant = "decode_step"
+        else:
+            dominant = max(("select", "attn"), key=per_kernel.get)
         achieved = ab[dominant] / (per_kernel[dominant] * 1e-6) / 1e9
         dense_us, dense_note = (None, "skipped") if args.skip_dense else dense_decode_us(torch, wl)
-        us_layer = ms_per_step * 1e3 / N_LAYERS
         line = {
             "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if kvhead else "weak",
@@ -682,16 +694,16 @@ def main():
             "chain_hbm_frac_of_8TBs": ab["total"] / (us_layer * 1e-6) / 8e12,
             "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the selector launch on
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of that launch on
                          # this workload (profiles/fused_chain_cfg2_128k_batch1.md); not measured live
-                         "traffic": 8821504 if dominant == "select" else None},
+                         "traffic": {"select": 8821504, "decode_step": DECODE_STEP_DRAM_BYTES}.get(dominant)},
             "dense_decode": {"us_per_layer": dense_us, "note": dense_note,
                              "ours_over_dense": (us_layer / dense_us) if dense_us else None},
             "e2e": None if args.skip_e2e else {
                 "value": (1 if kvhead else world) * 1e3 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            # selector (one launch at this batch) + attention per layer-step
-            "gpu_launches": K * N_LAYERS * 2, "device_status": status, "clocks": clocks,
+            "gpu_launches": K * N_LAYERS * launches_per_layer, "device_status": status, "clocks": clocks,
+            "launches_per_layer_step": launches_per_layer,
         }
         if not args.skip_batched and not kvhead:
             del wl, runner, cache

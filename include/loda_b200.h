@@ -242,6 +242,11 @@ int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda
                      float scale, const loda_selection* sel, const int32_t* query_to_req,
                      void* out, uint32_t* status, void* workspace, void* stream);
 
+/* How many kernels the latest loda_decode_step of this process launched: 1 (selection and
+ * attention in one launch: batch 1 at long context, head dimensions 128), 2 (one-launch
+ * selection, then attention) or 3 (L1, L2, attention).  For benchmarks and logs. */
+int loda_last_decode_launches(void);
+
 /* gather / visible_lens = the protected tokens only: sink ++ sliding window as physical
  * slots, per (batch row, kv head).  Replaces build_protected_gather
  * (sparse_attn/ops/paged_region_kernels_nfa.py:84-119).  With loda_selection.middle_only

@@ -164,6 +164,45 @@ def test_single_request_one_launch_selector_matches_oracle_and_the_two_launch_ch
     assert torch.equal(out_a, out_b)
 
 
+def _run_decode_step(setup):
+    """The whole step of layer 0 through the single entry point loda_decode_step."""
+    from helpers import mod
+    sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
+    capi = mod("_capi")
+    cache = setup.cache
+    cache.plan_common(setup.req_ids)
+    slots = cache.slot_mapping_for_layer(0)[:len(setup.req_ids)]
+    out = sel_mod.decode_step_fused(cache, 0, setup.req_ids, setup.q, setup.attention,
+                                    (setup.k_new, setup.v_new, slots))
+    torch.cuda.synchronize()
+    assert cache.read_status() == 0
+    return out, int(capi.lib().loda_last_decode_launches())
+
+
+@pytest.mark.parametrize("lengths", [[1], [17], [131], [4241], [20000], [40000], [9000, 2000]])
+def test_one_launch_decode_step_matches_oracle_and_the_separate_attention_launch(lengths, monkeypatch):
+    """Up to two requests are served by ONE launch for the whole step (selection, then attention
+    by the same clusters); with LODA_B200_DECODE_PATH=split the attention runs as its own launch.
+    Same integers from both, both match the oracle, the attention outputs agree within the bf16
+    tolerance of the path (2e-2: the two launches split and merge the softmax differently)."""
+    from helpers import make_setup
+    a = make_setup(lengths, seed=9)
+    out_a, launches_a = _run_decode_step(a)
+    # one request: 8 clusters of 8 CTAs always fit; two requests need 16 of them resident at once,
+    # which not every GPU grants (the library then runs L1, L2 and the attention as three launches)
+    assert launches_a == 1 if len(lengths) == 1 else launches_a in (1, 3)
+    _check_against_oracle(a, out_a)
+    monkeypatch.setenv("LODA_B200_DECODE_PATH", "split")
+    b = make_setup(lengths, seed=9)
+    out_b, launches_b = _run_decode_step(b)
+    assert launches_b == (2 if launches_a == 1 else 3)
+    _check_against_oracle(b, out_b)
+    n = int(a.cache.visible_lens_for_layer(0).max())
+    assert torch.equal(a.cache.visible_lens_for_layer(0), b.cache.visible_lens_for_layer(0))
+    assert torch.equal(a.cache.gather_indices_for_layer(0)[..., :n], b.cache.gather_indices_for_layer(0)[..., :n])
+    assert torch.allclose(out_a.float(), out_b.float(), atol=2e-2, rtol=2e-2)
+
+
 def test_padding_rows_and_noncontiguous_request_slots():
     from helpers import make_setup, mod
     sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")

@@ -23,6 +23,7 @@
 #include <cooperative_groups.h>
 
 #include <cstdio>
+#include <cstdlib>
 
 #include "loda_attn.cuh"
 #include "loda_common.cuh"
@@ -45,8 +46,8 @@ LODA_PHASE_STORAGE(attn)
 
 template <int D, int DV, bool CLUSTER>
 __global__ void __launch_bounds__(ATT_NT) attn_kernel(
-    loda_geometry g, loda_layer L, const bf16* __restrict__ q, const int32_t* __restrict__ gather,
-    const int32_t* __restrict__ visible_lens, const int32_t* __restrict__ query_to_req,
+    loda_geometry g, loda_layer L, const bf16* __restrict__ q, const int32_t* gather,
+    const int32_t* visible_lens, const int32_t* query_to_req,
     int n_req_rows, float scale_log2, bf16* __restrict__ out, float* __restrict__ lse, AttnWorkspace ws,
     int nsplit, int chained) {
   constexpr int KSTR = D + 8, VSTR = DV + 8;   // padded rows: conflict-free ldmatrix
@@ -81,9 +82,13 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
 #endif
   if (!chained) load_q();
   LODA_PHASE(attn, cta_id, 1);
-  const int req = query_to_req[t];
+  // The lists and their lengths are written by the launch this one may be chained behind: they
+  // are read with L2-coherent loads placed after the wait above, through pointers the compiler
+  // may not treat as read-only (declared const __restrict__, their loads were hoisted above
+  // the wait and saw the lists of the step before).
+  const int req = __ldcg(query_to_req + t);
   int n = 0;
-  if (req >= 0 && req < n_req_rows) n = min(max(visible_lens[(size_t)req * g.num_kv_heads + kv], 0), g.max_visible);
+  if (req >= 0 && req < n_req_rows) n = min(max(__ldcg(visible_lens + (size_t)req * g.num_kv_heads + kv), 0), g.max_visible);
   const int c0 = (int)(((long long)split * n) / nsplit);
   const int c1 = (int)(((long long)(split + 1) * n) / nsplit);
   const int32_t* list = gather + ((size_t)max(req, 0) * g.num_kv_heads + kv) * g.max_visible;
@@ -112,7 +117,7 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
 #pragma unroll
     for (int k = 0; k < NIT; ++k) {
       const int idx = base + kr + k * RPI;
-      const int s = (tile < ntiles && idx < c1) ? __ldg(list + idx) : -1;
+      const int s = (tile < ntiles && idx < c1) ? __ldcg(list + idx) : -1;
       sl[k] = s >= slot_end ? -1 : s;
     }
   };

@@ -243,6 +243,8 @@ int loda_select_l1(const loda_geometry* g, const loda_layer* layer, const loda_b
                     "select_l1");
 }
 
+static int g_last_select_launches = 0;     // kernels the latest loda_select_step launched (1 or 2)
+
 int loda_select_step(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
                      const void* k_new, const void* v_new, const int32_t* slots, float scale,
                      const loda_selection* sel, uint32_t* status, void* workspace, void* stream) {
@@ -265,7 +267,7 @@ int loda_select_step(const loda_geometry* g, const loda_layer* layer, const loda
   if (select_fused_applicable(*g, b->batch * g->num_kv_heads)) {
     // one launch for both levels (a cluster per row); refused shapes fall through to the two-launch chain
     const cudaError_t e = launch_select_fused(*g, *layer, *b, q, scale, *sel, status, ap, (cudaStream_t)stream);
-    if (e == cudaSuccess) return LODA_OK;
+    if (e == cudaSuccess) { g_last_select_launches = 1; return LODA_OK; }
     if (e != cudaErrorNotSupported) {                    // NotSupported: nothing was launched, the GPU cannot hold the clusters
       cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
       cudaStreamIsCapturing((cudaStream_t)stream, &cap);
@@ -274,6 +276,7 @@ int loda_select_step(const loda_geometry* g, const loda_layer* layer, const loda
       select_fused_refuse(g->sub_dims);
     }
   }
+  g_last_select_launches = 2;
   LODA_TRY(check_cuda(launch_l1(*g, *layer, *b, q, scale, *sel, ws, ap, 0, (cudaStream_t)stream), "select_step/l1"));
   return check_cuda(launch_l2(*g, *layer, *b, q, scale, *sel, ws, status, /*chained=*/true, 0, (cudaStream_t)stream),
                     "select_step/l2");
@@ -391,6 +394,9 @@ int loda_shard_l2_select(const loda_geometry* g, const loda_layer* layer, const 
   return shard_stage(g, layer, b, q, scale, sel, status, workspace, stream, 2, 2);
 }
 
+static int g_last_decode_launches = 0;
+int loda_last_decode_launches(void) { return g_last_decode_launches; }
+
 int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
                      const void* k_new, const void* v_new, const int32_t* slots, float scale,
                      const loda_selection* sel, const int32_t* query_to_req, void* out, uint32_t* status,
@@ -406,7 +412,7 @@ int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda
     const AppendArgs ap{(const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, slots, status, 1};
     const cudaError_t e = launch_decode_fused(*g, *layer, *b, q, scale, *sel, status, ap, query_to_req, out,
                                               (cudaStream_t)stream);
-    if (e == cudaSuccess) return LODA_OK;
+    if (e == cudaSuccess) { g_last_decode_launches = 1; return LODA_OK; }
     if (e != cudaErrorNotSupported) {
       cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
       cudaStreamIsCapturing((cudaStream_t)stream, &cap);
@@ -417,6 +423,7 @@ int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda
   }
   LODA_TRY(loda_select_step(g, layer, b, q, k_new, v_new, slots, scale, sel, status, workspace, stream));
   if (b->batch == 0) return LODA_OK;
+  g_last_decode_launches = 1 + g_last_select_launches;
   return gather_attend_impl(g, layer, q, sel->gather, sel->visible_lens, query_to_req, b->batch, g->max_requests,
                             scale, out, nullptr, workspace, /*chained=*/true, stream);
 }
