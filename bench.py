@@ -40,8 +40,8 @@ PKG = "two-level-attention_b200"
 N_LAYERS, HQ, HKV, D, PAGE = 36, 32, 8, 128, 16
 CONTEXT = 131072
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the one-launch decode step on this
-# workload, from one ncu capture (None until captured)
-DECODE_STEP_DRAM_BYTES = None
+# workload, from one ncu capture (profiles/fused_chain_cfg2_128k_batch1.md)
+DECODE_STEP_DRAM_BYTES = 13007616
 SUB = 32
 METRIC = "decode tok/s at 128K ctx, two-level select+attend path over all layers"
 

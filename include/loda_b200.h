@@ -233,6 +233,11 @@ int loda_gather_attend_static(const loda_geometry* g, const loda_layer* layer,
                               float scale, void* out, void* stream);
 
 /* The whole decode step of one layer on one stream: append, L1, L2, attend.
+ * One kernel launch where a thread-block cluster per (request, kv head) row fits
+ * the GPU (batch 1 at long context) and head_dim = head_dim_v = 128: the clusters
+ * that selected the tokens attend over them.  Otherwise the launches of
+ * loda_select_step followed by the attention launch.  Same results either way:
+ * identical lists, attention within the bf16 tolerance of the path.
  * Replaces select_topk_for_layer_batched(decode_write=...) followed by
  * decode_graph_ready (nfa_layer_batch_selector.py:2649-2720,
  * sparse_attn/ops/paged_region_kernels_nfa.py:122-162).  One query per row
