@@ -760,9 +760,6 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
     total += x;
     before += w < warp ? x : 0;
   }
-#ifdef LODA_PHASES
-  if (tid == 0 && blockIdx.y < 8) { g_subphase[32 + blockIdx.y] = total; g_subphase[40 + blockIdx.y] = bound; }
-#endif
   if (total > 2 * NT) return -1;
   LODA_SUB(19);
   {

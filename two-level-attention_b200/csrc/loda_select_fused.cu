@@ -134,11 +134,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   // addresses: a store through the cluster window into the CTA's own shared memory is a remote
   // store that the CTA's next barrier has to wait for (measured: the leader reached the first
   // cluster barrier 2 000 cycles after its peers).
-#ifdef LODA_X_SELFMAP
-  const bool own = false;
-#else
   const bool own = rank == 0;
-#endif
   uint16_t* l_scall = own ? scall : cluster.map_shared_rank(scall, 0);
   int* l_kept = own ? kept : cluster.map_shared_rank(kept, 0);
   int* l_physk = own ? physk : cluster.map_shared_rank(physk, 0);
@@ -260,13 +256,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     for (int i = far_hi + tid; i < ((n_far + 7) & ~7); i += P) scf[i] = 0;
     __syncthreads();
     LODA_PHASE(sel, cta_id, 3);
-#ifdef LODA_X_FAR256
-    constexpr int H = 256;             // the selection runs on the first 256 threads (named barrier 1)
-    constexpr int HB = 1;
-#else
-    constexpr int H = P;
-    constexpr int HB = 0;
-#endif
+    constexpr int H = P, HB = 0;       // the selection runs on all threads of the CTA (barrier 0)
     if (tid < H) {
       int r = 0;
       if ((listed || want_lists) && n_far > far_lo) {
