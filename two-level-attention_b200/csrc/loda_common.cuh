@@ -380,9 +380,11 @@ __device__ __forceinline__ int block_compact_threshold(const uint16_t* sc, int n
 // counters of 16 bits, two per word (bin b in word b >> 1, half b & 1; at most 65535 elements).
 // Thread t covers the words [2048 - (t + 1) W, 2048 - t W), so the running sum over the threads
 // counts from the largest bin down.  *nvalid receives the number of elements; the result is
-// meaningful only when *nvalid > k > 0.  wtot: 64 ints, zero in the columns of absent warps.
+// meaningful only when *nvalid > k > 0; *above (optional) receives the number of elements in the
+// bins above it.  wtot: 64 ints, zero in the columns of absent warps.
 template <int NT, int BAR = 0, int TBASE = 0>
-__device__ __forceinline__ uint32_t block_hist_kth_bin(const uint32_t* hist, int k, int* wtot, int* nvalid) {
+__device__ __forceinline__ uint32_t block_hist_kth_bin(const uint32_t* hist, int k, int* wtot, int* nvalid,
+                                                       int* above = nullptr) {
   static_assert(2048 % NT == 0 && (2048 / NT) % 4 == 0, "whole 16-byte vectors per thread");
   constexpr int NW = NT / 32, WPT = 2048 / NT;
   const int tid = ((int)threadIdx.x - TBASE), lane = tid & 31, warp = tid >> 5;
@@ -414,19 +416,21 @@ __device__ __forceinline__ uint32_t block_hist_kth_bin(const uint32_t* hist, int
   }
   int c = before + incl - own;         // elements in bins above this thread's
   if (c < k && k <= c + own) {         // exactly one thread when tot >= k > 0
-    int bin = 0;
+    int bin = 0, over = 0;               // over: elements in the bins above the chosen one
 #pragma unroll
     for (int i = WPT - 1; i >= 0; --i) {
       const int hi = (int)(w[i] >> 16), lo = (int)(w[i] & 0xFFFFu);
-      if (c < k && k <= c + hi) bin = 2 * (w0 + i) + 1;
+      if (c < k && k <= c + hi) { bin = 2 * (w0 + i) + 1; over = c; }
       c += hi;
-      if (c < k && k <= c + lo) bin = 2 * (w0 + i);
+      if (c < k && k <= c + lo) { bin = 2 * (w0 + i); over = c; }
       c += lo;
     }
     wtot[32] = bin;
+    wtot[33] = over;
   }
   group_sync<NT, BAR>();
   *nvalid = tot;
+  if (above) *above = wtot[33];
   return (uint32_t)wtot[32];
 }
 
@@ -511,8 +515,9 @@ __device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, i
   // scored elements, their maximum, and 0xFFFF - their minimum (so that empty columns, 0, are neutral)
   int nvalid;
   uint32_t smax = 0, smin = 0, hist_bin = 0;
+  int above = 0;         // scores at or above the upper end of the interval the threshold is known to lie in
   if constexpr (HIST) {
-    hist_bin = block_hist_kth_bin<NT, BAR, TBASE>(hist, k, wtot, &nvalid);
+    hist_bin = block_hist_kth_bin<NT, BAR, TBASE>(hist, k, wtot, &nvalid, &above);
   } else {
     int nz = xtra != 0u;
     uint32_t mx = xtra, mi = xtra ? 0xFFFFu - xtra : 0u;
@@ -575,22 +580,24 @@ __device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, i
       first_round = (14 - shift0) >> 1;
       thr = smax & ~((4u << shift0) - 1u);
     }
-    // rounds 0..7 decide two bits each; the closing round counts the scores strictly above the
-    // threshold (one loop body for both: this code runs once per launch, and fetching it costs
-    // as much as executing it)
+    // rounds 0..7 decide two bits each.  `above` follows the count at the upper end of the
+    // threshold's interval (the next candidate above the chosen one), so that after the last
+    // round it is the number of scores strictly above the threshold without a counting round
+    // of its own.  (One rolled loop body: this code runs once per launch, and fetching it costs
+    // as much as executing it.)
 #pragma unroll 1
-    for (int round = first_round; round <= 8; ++round) {
-      const bool closing = round == 8;
-      const int shift = closing ? 0 : 14 - 2 * round;
+    for (int round = first_round; round < 8; ++round) {
+      const int shift = 14 - 2 * round;
       int c1, c2, c3;
-      count3(closing ? thr + 1u : thr | (1u << shift), closing ? 0x10000u : thr | (2u << shift),
-             closing ? 0x10000u : thr | (3u << shift), c1, c2, c3);
+      count3(thr | (1u << shift), thr | (2u << shift), thr | (3u << shift), c1, c2, c3);
       sum3(buf, c1, c2, c3);
       buf ^= 1;
-      if (closing) rem = k - c1;
-      else thr |= (c3 >= k ? 3u : c2 >= k ? 2u : c1 >= k ? 1u : 0u) << shift;   // largest candidate with >= k at or above
+      const uint32_t d = c3 >= k ? 3u : c2 >= k ? 2u : c1 >= k ? 1u : 0u;   // largest candidate with >= k at or above
+      above = d == 3u ? above : d == 2u ? c3 : d == 1u ? c2 : c1;
+      thr |= d << shift;
       LODA_SUB(3 + round);
     }
+    rem = k - above;
   }
   if constexpr (MAXC > 1) {
     if (!in_regs) return block_compact_threshold<NT, BAR, TBASE>(sc, n, k, thr, rem, all, nvalid, out, wtot);
