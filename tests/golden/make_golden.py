@@ -173,7 +173,7 @@ def make_arch(reference):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of a checkout of the reference project")
     a = ap.parse_args()
     ix = tia(a.reference)
     make_quant(ix)
