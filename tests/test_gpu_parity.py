@@ -203,6 +203,40 @@ def test_one_launch_decode_step_matches_oracle_and_the_separate_attention_launch
     assert torch.allclose(out_a.float(), out_b.float(), atol=2e-2, rtol=2e-2)
 
 
+def test_graph_replay_of_the_one_launch_decode_step_equals_eager():
+    """loda_decode_step captured in a CUDA graph (as the decode runner does for all layers) and
+    replayed: same lists and the same attention bits as the eager call."""
+    from helpers import make_setup, mod
+    sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
+    setup = make_setup([12000], seed=6)
+    cache = setup.cache
+    out_eager, launches = _run_decode_step(setup)          # warm-up: builds the index, decides the launch shape
+    assert launches == 1
+    _check_against_oracle(setup, out_eager)
+    g_eager = cache.gather_indices_for_layer(0).clone()
+    l_eager = cache.visible_lens_for_layer(0).clone()
+    slots = cache.slot_mapping_for_layer(0)[:1]
+    static_out = torch.empty_like(out_eager)
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            sel_mod.decode_step_fused(cache, 0, setup.req_ids, setup.q, setup.attention,
+                                      (setup.k_new, setup.v_new, slots), out=static_out)
+    cache.gather_indices_for_layer(0).fill_(-7)
+    cache.visible_lens_for_layer(0).zero_()
+    static_out.zero_()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert cache.read_status() == 0
+    n = int(l_eager.max())
+    assert torch.equal(cache.visible_lens_for_layer(0), l_eager)
+    assert torch.equal(cache.gather_indices_for_layer(0)[..., :n], g_eager[..., :n])
+    assert torch.equal(static_out, out_eager)
+
+
 def test_padding_rows_and_noncontiguous_request_slots():
     from helpers import make_setup, mod
     sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
