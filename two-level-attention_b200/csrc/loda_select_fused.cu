@@ -148,13 +148,13 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   // histogram): zero outside the pool, so cleared before any peer may store
   if (rank == 1 && tid < (L1_NEAR_CAP + 8) / 2) hist2[tid] = 0;
   cluster.barrier_arrive();   // (0) "this CTA runs": waited for just before the first store into a peer
-  pdl_wait();
-  // this thread's first query element is requested before anything that depends on the
-  // request's length, so that the two global round trips overlap
+  // Before the dependency wait: the batch metadata and the page statistics of the two pools.
+  // A launch that lets this one start early is one of this library's (only they release their
+  // dependents before they end), and none of them writes either: the metadata comes from the
+  // host, and the only statistics a selector or append launch writes are those of the newest
+  // token's page, which lies in the sliding window, outside both pools.  Everything else (the
+  // query first of all) is read after the wait.
   const int nq = G * DSUB;
-  float q_first = 0.0f;
-  if (tid < nq)
-    q_first = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + tid / DSUB) * g.head_dim + sub_dim(g, tid % DSUB)]);
   const long long act = B.active_req_ids[b];
   const int len_raw = B.lengths[b];
   const int req = (int)B.valid_req_ids[b];
@@ -190,11 +190,11 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   };
   stage(0);
   stage(1);
+  pdl_wait();
   // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
   for (int i = tid; i < nq; i += P) {
     const int j = i / DSUB, d = i % DSUB;
-    const float qv = i == tid ? q_first
-                              : __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, d)]);
+    const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, d)]);
     const float qh = bf16r(__fmul_rn(qv, scale));
     qhat[i] = qh;
     qlow[i] = fminf(qh, 0.0f);
