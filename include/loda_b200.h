@@ -238,6 +238,12 @@ int loda_gather_attend_static(const loda_geometry* g, const loda_layer* layer,
  * that selected the tokens attend over them.  Otherwise the launches of
  * loda_select_step followed by the attention launch.  Same results either way:
  * identical lists, attention within the bf16 tolerance of the path.
+ * The one-launch kernel reads b->lengths / valid_req_ids / active_req_ids and
+ * the page statistics of pages outside the sliding window before it waits for
+ * the kernel launched before it on the stream; this only ever overlaps with a
+ * kernel of this library (they alone let a dependent start early), and none of
+ * them writes those.  Everything else, the query included, is read after.
+ *
  * Replaces select_topk_for_layer_batched(decode_write=...) followed by
  * decode_graph_ready (nfa_layer_batch_selector.py:2649-2720,
  * sparse_attn/ops/paged_region_kernels_nfa.py:122-162).  One query per row
