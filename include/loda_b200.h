@@ -41,6 +41,7 @@ extern "C" {
 #define LODA_STATUS_BAD_SLOT 1u
 #define LODA_STATUS_BAD_PAGE 2u
 #define LODA_STATUS_TRUNCATED 4u
+#define LODA_STATUS_BAD_REQ 8u   /* an active row's request slot is outside [0, max_requests): treated as a padding row */
 
 /* Static geometry of one attention layer's cache and selector.
  * Mirrors GraphReadyPagedRegionCache.__init__ (sparse_attn/cache/
@@ -71,7 +72,19 @@ typedef struct loda_geometry {
   int32_t pool_near_len;  /* near candidate-pool span in tokens */
   int32_t shard_rank;     /* sequence sharding: this GPU owns the logical pages p with        */
   int32_t shard_count;    /* p % shard_count == shard_rank; 0 or 1 = not sharded              */
+  int32_t near_tokens_p1; /* numeric near-token quota of level 2 (nfa_near_tokens, nfa_layer_batch_selector.py:
+                           * 872-920): 0 = "off" (one quota over the whole middle range, the default); n + 1 =
+                           * n tokens reserved for the near region, the far and near regions then select separately */
+  int32_t far_method;     /* LODA_FAR_*: level-1 score of the far pool (nfa_far_method) */
+  int32_t near_minmax;    /* 0: near pool scored by the page mean (nfa_near_method "avg", the default); 1: by the
+                           * min/max bound */
+  int32_t reserved;
 } loda_geometry;
+
+/* loda_geometry.far_method (nfa_layer_batch_selector.py:290-354, 2412-2427) */
+#define LODA_FAR_MINMAX 0    /* min/max upper bound, mean over the GQA group (default) */
+#define LODA_FAR_AVG 1       /* page mean, mean over the group */
+#define LODA_FAR_AVG_TOP2 2  /* page mean, mean of the two best heads of the group */
 
 /* Per-layer device buffers.
  *   pool_k / pool_v  [num_pages, num_kv_heads, page, head_dim(_v)]   (the
@@ -92,6 +105,11 @@ typedef struct loda_layer {
   uint8_t* tail_code;
   void* tail_sz;
   const int32_t* block_table;
+  /* region skip decisions of this layer per request slot, [max_requests] int32, nonzero = the far /
+   * near region of the request is neither scored nor selected (skip_far_layer_buf / skip_near_layer_buf,
+   * sparse_attn/cache/paged_region_cache.py:293-296, 540-559).  NULL = nothing is skipped. */
+  const int32_t* skip_far;
+  const int32_t* skip_near;
 } loda_layer;
 
 /* Per-step batch metadata (paged_region_cache.py:214-231). */
@@ -124,8 +142,20 @@ typedef struct loda_selection {
   int32_t middle_only;    /* 1: gather / visible_lens receive the level-2 survivors only, without the sink
                            * and window tokens (select_topk_for_layer_batched(middle_only=True),
                            * nfa_layer_batch_selector.py:2649-2671) */
-  int32_t reserved;
+  int32_t flags;          /* LODA_SEL_* bits, 0 by default */
 } loda_selection;
+
+/* loda_selection.flags.
+ * LODA_SEL_CHAINED: the caller guarantees that the kernel launched before this call on the same
+ * stream is a loda_decode_step / loda_select_step of this library on the SAME batch metadata, and
+ * that lengths / valid_req_ids / active_req_ids and the block table were complete before THAT
+ * launch started (the decode of one token through the layers of a model: set it for every layer
+ * but the first).  The one-launch kernel then fetches the batch metadata and stages page
+ * statistics while the previous launch drains.  Without the flag nothing but launch parameters is
+ * read before the launch's dependency wait, and the call is safe behind any kernel (one that
+ * advances lengths on the device, an index build, a foreign kernel that releases its dependents
+ * early). */
+#define LODA_SEL_CHAINED 1
 
 const char* loda_version(void);
 const char* loda_last_error(void);
@@ -238,11 +268,10 @@ int loda_gather_attend_static(const loda_geometry* g, const loda_layer* layer,
  * that selected the tokens attend over them.  Otherwise the launches of
  * loda_select_step followed by the attention launch.  Same results either way:
  * identical lists, attention within the bf16 tolerance of the path.
- * The one-launch kernel reads b->lengths / valid_req_ids / active_req_ids and
- * the page statistics of pages outside the sliding window before it waits for
- * the kernel launched before it on the stream; this only ever overlaps with a
- * kernel of this library (they alone let a dependent start early), and none of
- * them writes those.  Everything else, the query included, is read after.
+ * With sel->flags & LODA_SEL_CHAINED (see there) the one-launch kernel reads
+ * b->lengths / valid_req_ids / active_req_ids and the page statistics of pages
+ * outside the sliding window before it waits for the launch before it; without
+ * the flag every read follows the wait.
  *
  * Replaces select_topk_for_layer_batched(decode_write=...) followed by
  * decode_graph_ready (nfa_layer_batch_selector.py:2649-2720,
@@ -267,8 +296,7 @@ int loda_protected_gather(const loda_geometry* g, const loda_layer* layer, const
                           int32_t* gather, int32_t* visible_lens, uint32_t* status, void* stream);
 
 /* ---- sequence sharding (batch-1 long context over several GPUs) ---------------
- * No counterpart in the reference's code; the mode is described by the task's
- * specification: logical page p belongs to GPU p % shard_count (geometry.shard_rank /
+ * No counterpart in the reference's code (its runs are single-GPU): logical page p belongs to GPU p % shard_count (geometry.shard_rank /
  * shard_count), whose block table holds -1 for the pages of the others.  The selector
  * runs in four stages; between the stages the caller combines the score rows of the
  * GPUs with a bitwise OR (every page / slot is scored by exactly one GPU, the others

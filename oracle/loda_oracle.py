@@ -126,6 +126,10 @@ class SelectorConfig:
     l2_quant: bool = True         # 4-bit tail keys (build) vs raw keys (live reference)
     l2_metric: str = "grouped_logit"   # | 'softmax_prob_mean'
     q_round: bool = True          # bf16-round the scaled query (live selector: always)
+    near_tokens: int = None       # numeric near-token quota (nfa_near_tokens); None = 'off'
+    far_method: str = "minmax"    # | 'avg' | 'avg_top2'  (nfa_far_method)
+    near_method: str = "avg"      # | 'minmax'            (nfa_near_method)
+    geometry_near: int = None     # RegionGeometry.near where it differs from near_len (L1 region bounds)
     dims: np.ndarray = field(default=None, repr=False)
 
     def __post_init__(self):
@@ -140,6 +144,8 @@ class SelectorConfig:
             raise ValueError("near_pages * block_size must be <= near_len")
         if self.level2_topk < self.sink + self.swa:
             raise ValueError("level2_topk must be >= sink + swa")
+        if self.geometry_near is None:
+            self.geometry_near = self.near_len
 
     @property
     def group(self):
@@ -250,15 +256,24 @@ class Regions:
     lower: int
     upper: int
     quota: int
+    skip_far: bool = False
+    skip_near: bool = False
+    far_hi_tok: int = 0       # token bound between the far and the near region of level 2
+    lower0: int = 0           # [lower0, upper0): the middle range before any region is skipped
+    upper0: int = 0
+    base_quota: int = 0
 
 
-def regions(length, cfg: SelectorConfig) -> Regions:
+def regions(length, cfg: SelectorConfig, skip_far=False, skip_near=False) -> Regions:
+    """Region geometry of one request.  skip_far / skip_near: the frozen per-layer decisions of
+    the request (paged_region_cache.py:540-559); a skipped region is neither scored
+    (nfa_layer_batch_selector.py:223-226, 241-267) nor part of the middle range (:1151-1163)."""
     bs, w, spl = cfg.block_size, cfg.swa, cfg.sink_pool_lo
     kt_eff = (length + bs - 1) // bs
     near_blks = max(_cdiv(length - w - cfg.pool_near_len, bs), spl)
     sink_hi = min(cfg.sink, length)
     swa_hi = max(sink_hi, length - w)
-    far_blk = _cdiv(length - w - cfg.near_len, bs)
+    far_blk = _cdiv(length - w - cfg.geometry_near, bs)
     orig_far_hi = min(swa_hi, max(sink_hi, far_blk * bs))
     swa_lo_blk = max(near_blks, kt_eff - max(1, w // bs))
     swa_lo_tok = max(length - w, 0)
@@ -267,13 +282,19 @@ def regions(length, cfg: SelectorConfig) -> Regions:
     sink_byp = cfg.sink % bs != 0
     if sink_byp:
         swa_byp = swa_byp and swa_byp_blk != spl
-    lower = spl * bs
-    upper = max(lower, swa_lo_tok)
-    quota = max(min(length, cfg.level2_topk) - cfg.sink - (length - swa_lo_tok), 0)
-    quota = min(quota, upper - lower)
+    lower0 = spl * bs
+    upper0 = max(lower0, swa_lo_tok)
+    # level-2 region bound (nfa_layer_batch_selector.py:1155-1163)
+    far_hi_tok = min(swa_hi, max(sink_hi, (max(length - w - cfg.geometry_near, 0) // bs) * bs))
+    lower = far_hi_tok if skip_far else lower0
+    upper = far_hi_tok if skip_near else upper0
+    upper = max(lower, upper)
+    base_quota = max(min(length, cfg.level2_topk) - cfg.sink - (length - swa_lo_tok), 0)
+    quota = min(base_quota, upper - lower)
     return Regions(length, kt_eff, near_blks, sink_hi, swa_hi, orig_far_hi,
                    swa_lo_blk, swa_lo_tok, swa_byp_blk, swa_byp, sink_byp,
-                   lower, upper, quota)
+                   lower, upper, quota, bool(skip_far), bool(skip_near), far_hi_tok,
+                   lower0, upper0, base_quota)
 
 
 def _cdiv(a, b):
@@ -287,13 +308,14 @@ def pools(rg: Regions, cfg: SelectorConfig):
     bs, spl = cfg.block_size, cfg.sink_pool_lo
     t = np.arange(rg.kt_eff)
     lo, hi = t * bs, t * bs + bs
+    far_on, near_on = not rg.skip_far, not rg.skip_near
     has_sink = lo < rg.sink_hi
-    has_far = (hi > rg.sink_hi) & (lo < rg.orig_far_hi)
-    has_near = (hi > rg.orig_far_hi) & (lo < rg.swa_hi)
+    has_far = far_on & (hi > rg.sink_hi) & (lo < rg.orig_far_hi)
+    has_near = near_on & (hi > rg.orig_far_hi) & (lo < rg.swa_hi)
     has_swa = (hi > rg.swa_hi) & (lo < rg.length)
     valid = (lo < rg.length) & (has_sink | has_far | has_near | has_swa)
-    far = (t >= spl) & (t < rg.near_blks)
-    near = (t >= rg.near_blks) & (t < rg.swa_lo_blk) & ~((t == rg.swa_byp_blk) & rg.swa_byp)
+    far = (t >= spl) & (t < rg.near_blks) & far_on
+    near = (t >= rg.near_blks) & (t < rg.swa_lo_blk) & ~((t == rg.swa_byp_blk) & rg.swa_byp) & near_on
     if rg.sink_byp:
         far &= t != spl
         near &= t != spl
@@ -303,11 +325,17 @@ def pools(rg: Regions, cfg: SelectorConfig):
 # --------------------------------------------------------------------------
 # query preparation (nfa_layer_batch_selector.py:943-1002)
 # --------------------------------------------------------------------------
+def prepare_q_unrounded(q, cfg: SelectorConfig, scale):
+    """fp32 scaled query on the subspace without the bf16 rounding: what the avg_top2 far score
+    is computed from (nfa_layer_batch_selector.py:2936-2938, 2412-2427)."""
+    qs = act(np.asarray(q, dtype=F32), cfg.mode)[:, cfg.dims]
+    return (qs * F32(scale)).astype(F32)
+
+
 def prepare_q(q, cfg: SelectorConfig, scale):
     """q [Hq, D] -> (q_hat [Hq, d'] bf16-rounded scaled query on the subspace,
     q_fine [Hkv, d'] fp32 sum of q_hat over each GQA group)."""
-    qs = act(np.asarray(q, dtype=F32), cfg.mode)[:, cfg.dims]
-    q_hat = (qs * F32(scale)).astype(F32)
+    q_hat = prepare_q_unrounded(q, cfg, scale)
     if cfg.q_round:
         q_hat = bf16_rn(q_hat)
     g = cfg.group
@@ -347,8 +375,13 @@ def _chain_dot(k, q):
 # --------------------------------------------------------------------------
 # L1 scores (nfa_layer_batch_selector.py:290-354)
 # --------------------------------------------------------------------------
-def l1_scores(vmin, vmax, vsum, q_hat, rg: Regions, cfg: SelectorConfig):
-    """far / near page scores [Hkv, kt_eff]; -inf outside the pools."""
+def l1_scores(vmin, vmax, vsum, q_hat, rg: Regions, cfg: SelectorConfig, q_raw=None):
+    """far / near page scores [Hkv, kt_eff]; -inf outside the pools.
+
+    Each pool is scored by its method: 'minmax' = the min/max upper bound, 'avg' = the page
+    mean, both averaged over the GQA group of per-head bf16 scores; far 'avg_top2' = the mean of
+    the two best per-head page-mean scores of the group, computed from the unrounded scaled
+    query q_raw (nfa_layer_batch_selector.py:2412-2427)."""
     g, hkv, mode = cfg.group, cfg.num_kv_heads, cfg.mode
     far_pool, near_pool = pools(rg, cfg)
     far = np.full((hkv, rg.kt_eff), NEG_INF, dtype=F32)
@@ -358,6 +391,7 @@ def l1_scores(vmin, vmax, vsum, q_hat, rg: Regions, cfg: SelectorConfig):
         for kv in range(hkv):
             mm_acc = np.zeros(rg.kt_eff, dtype=F32)
             av_acc = np.zeros(rg.kt_eff, dtype=F32)
+            per_head = []
             for j in range(g):
                 qh = q_hat[kv * g + j]
                 q_lo, q_hi = np.minimum(qh, F32(0)), np.maximum(qh, F32(0))
@@ -366,8 +400,20 @@ def l1_scores(vmin, vmax, vsum, q_hat, rg: Regions, cfg: SelectorConfig):
                 mm_acc = (mm_acc + act(mm, mode)).astype(F32)
                 av = _chunk_tree_dot(kavg[:, kv], qh)
                 av_acc = (av_acc + act(av, mode)).astype(F32)
-            far[kv] = np.where(far_pool, act((mm_acc / F32(g)).astype(F32), mode), NEG_INF)
-            near[kv] = np.where(near_pool, act((av_acc / F32(g)).astype(F32), mode), NEG_INF)
+                if cfg.far_method == "avg_top2":
+                    per_head.append(act(_chunk_tree_dot(kavg[:, kv], q_raw[kv * g + j]), mode))
+            mm_score = act((mm_acc / F32(g)).astype(F32), mode)
+            av_score = act((av_acc / F32(g)).astype(F32), mode)
+            if cfg.far_method == "minmax":
+                far_score = mm_score
+            elif cfg.far_method == "avg":
+                far_score = av_score
+            else:
+                top = np.sort(np.stack(per_head), axis=0)[::-1]
+                far_score = act(((top[0] + top[1]) / F32(2)).astype(F32), mode)
+            near_score = mm_score if cfg.near_method == "minmax" else av_score
+            far[kv] = np.where(far_pool, far_score, NEG_INF)
+            near[kv] = np.where(near_pool, near_score, NEG_INF)
     return far, near
 
 
@@ -430,13 +476,13 @@ def l2_logits(k_tail, q_fine_kv, mode):
         return bf16_rn(_chain_dot(np.asarray(k_tail, F32), q_fine_kv))
 
 
-def l2_select(tokens, logits, rg: Regions, cfg: SelectorConfig):
-    """Top-quota tokens by (logit descending, lower token first), hole fill,
-    drop ids below the sink, ascending (nfa_layer_batch_selector.py:518-605)."""
-    q = rg.quota
-    if q == 0:
+def filtered_topk(tokens, logits, low, high, q, cfg: SelectorConfig):
+    """Best q candidates of [low, high) by (logit descending, lower token first); missing
+    entries are filled with the first ids of [low, high) not chosen; ids below the sink are
+    dropped; ascending (nfa_layer_batch_selector.py:518-605)."""
+    if q <= 0:
         return np.zeros(0, np.int32)
-    good = ~np.isnan(logits) & (logits != NEG_INF)
+    good = ~np.isnan(logits) & (logits != NEG_INF) & (tokens >= low) & (tokens < high)
     tok, lg = tokens[good], logits[good]
     key = ordered_key(lg, "bf16")
     order = np.lexsort((tok, -key))
@@ -444,11 +490,40 @@ def l2_select(tokens, logits, rg: Regions, cfg: SelectorConfig):
     chosen = np.sort(tok[order[:take]])
     if len(chosen) < q:
         need = q - len(chosen)
-        span = np.arange(rg.lower, min(rg.upper, rg.lower + len(chosen) + need), dtype=np.int64)
+        span = np.arange(low, min(high, low + len(chosen) + need), dtype=np.int64)
         holes = np.setdiff1d(span, chosen, assume_unique=True)[:need]
         chosen = np.sort(np.concatenate((chosen, holes)))
     chosen = chosen[chosen >= cfg.sink]
     return chosen[:cfg.level2_topk].astype(np.int32)
+
+
+def fixed_quota_regions(rg: Regions, cfg: SelectorConfig):
+    """(far_low, far_high, far_quota, near_low, near_high, near_quota) of the numeric
+    near-token quota (nfa_layer_batch_selector.py:872-920): the near region reserves
+    near_tokens of the middle budget; what the far region cannot use goes to the near
+    region, never the other way."""
+    base = rg.base_quota
+    far_quota = max(base - min(int(cfg.near_tokens), base), 0)
+    far_low = rg.far_hi_tok if rg.skip_far else rg.lower0
+    far_high = rg.far_hi_tok
+    far_quota = min(far_quota, max(far_high - far_low, 0))
+    near_quota = max(base - far_quota, 0)
+    near_low = rg.far_hi_tok
+    near_high = rg.far_hi_tok if rg.skip_near else rg.upper0
+    near_quota = min(near_quota, max(near_high - near_low, 0))
+    return far_low, far_high, far_quota, near_low, near_high, near_quota
+
+
+def l2_select(tokens, logits, rg: Regions, cfg: SelectorConfig):
+    """The middle tokens: one quota over [lower, upper) ('off'), or, with a numeric near-token
+    quota, the far and the near region selected separately and concatenated
+    (nfa_layer_batch_selector.py:2274-2332, 922-943)."""
+    if cfg.near_tokens is None:
+        return filtered_topk(tokens, logits, rg.lower, rg.upper, rg.quota, cfg)
+    fl, fh, fq, nl, nh, nq = fixed_quota_regions(rg, cfg)
+    far = filtered_topk(tokens, logits, fl, fh, fq, cfg)
+    near = filtered_topk(tokens, logits, nl, nh, nq, cfg)
+    return np.concatenate((far, near)).astype(np.int32)[:cfg.level2_topk]
 
 
 def l2_select_softmax_prob(tokens, k_tail, q_hat_group, rg, cfg):
@@ -529,7 +604,8 @@ class Selection:
     regions: Regions
 
 
-def select_request(q, k, length, cfg: SelectorConfig, scale, index: RequestIndex = None) -> Selection:
+def select_request(q, k, length, cfg: SelectorConfig, scale, index: RequestIndex = None,
+                   skip_far=False, skip_near=False) -> Selection:
     """Two-level selection for one request and its current query.
 
     q [Hq, D] post-RoPE query of the token being decoded; k [S, Hkv, D] logical
@@ -537,9 +613,10 @@ def select_request(q, k, length, cfg: SelectorConfig, scale, index: RequestIndex
     """
     if index is None:
         index = build_index(k, length, cfg)
-    rg = regions(length, cfg)
+    rg = regions(length, cfg, skip_far, skip_near)
     q_hat, q_fine = prepare_q(q, cfg, scale)
-    far, near = l1_scores(index.vmin, index.vmax, index.vsum, q_hat, rg, cfg)
+    q_raw = prepare_q_unrounded(q, cfg, scale) if cfg.far_method == "avg_top2" else None
+    far, near = l1_scores(index.vmin, index.vmax, index.vsum, q_hat, rg, cfg, q_raw)
     i_f, n_f, i_n, n_n = l1_select(far, near, cfg)
     middle, logical = [], []
     g = cfg.group

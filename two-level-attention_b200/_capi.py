@@ -18,7 +18,9 @@ LODA_OK = 0
 LODA_ERR_ARGUMENT = -1
 LODA_ERR_UNSUPPORTED = -2
 LODA_ERR_LAUNCH = -3
-STATUS_BAD_SLOT, STATUS_BAD_PAGE, STATUS_TRUNCATED = 1, 2, 4
+STATUS_BAD_SLOT, STATUS_BAD_PAGE, STATUS_TRUNCATED, STATUS_BAD_REQ = 1, 2, 4, 8
+SEL_CHAINED = 1
+FAR_MINMAX, FAR_AVG, FAR_AVG_TOP2 = 0, 1, 2
 
 
 class FallbackRequired(Exception):
@@ -31,12 +33,13 @@ class Geometry(C.Structure):
         "dtype", "num_q_heads", "num_kv_heads", "head_dim", "head_dim_v", "sub_dims",
         "sub_lo0", "sub_lo1", "page", "num_pages", "max_blocks", "max_requests",
         "max_query_tokens", "max_visible", "k_far", "k_near", "level2_topk", "sink", "swa",
-        "near_len", "pool_near_len", "shard_rank", "shard_count")]
+        "near_len", "pool_near_len", "shard_rank", "shard_count", "near_tokens_p1", "far_method",
+        "near_minmax", "reserved")]
 
 
 class Layer(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
-        "pool_k", "pool_v", "page_mm", "page_sum", "tail_code", "tail_sz", "block_table")]
+        "pool_k", "pool_v", "page_mm", "page_sum", "tail_code", "tail_sz", "block_table", "skip_far", "skip_near")]
 
 
 class Batch(C.Structure):
@@ -47,7 +50,7 @@ class Batch(C.Structure):
 class Selection(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
         "i_far", "n_far", "i_near", "n_near", "gather", "visible_lens", "middle", "middle_counts")] + [
-        ("middle_only", C.c_int32), ("reserved", C.c_int32)]
+        ("middle_only", C.c_int32), ("flags", C.c_int32)]
 
 
 EXPORTS = ("loda_version", "loda_last_error", "loda_workspace_bytes", "loda_append_decode",
