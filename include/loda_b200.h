@@ -146,15 +146,15 @@ typedef struct loda_selection {
 } loda_selection;
 
 /* loda_selection.flags.
- * LODA_SEL_CHAINED: the caller guarantees that the kernel launched before this call on the same
- * stream is a loda_decode_step / loda_select_step of this library on the SAME batch metadata, and
- * that lengths / valid_req_ids / active_req_ids and the block table were complete before THAT
- * launch started (the decode of one token through the layers of a model: set it for every layer
- * but the first).  The one-launch kernel then fetches the batch metadata and stages page
- * statistics while the previous launch drains.  Without the flag nothing but launch parameters is
- * read before the launch's dependency wait, and the call is safe behind any kernel (one that
- * advances lengths on the device, an index build, a foreign kernel that releases its dependents
- * early). */
+ * LODA_SEL_CHAINED: the caller guarantees that (1) the kernel launched before this call on the same
+ * stream is a loda_decode_step / loda_select_step of this library, and (2) everything this call reads
+ * besides the query — b->lengths / valid_req_ids / active_req_ids, the skip flags and the page
+ * statistics of pages outside the sliding window — was complete before THAT launch started.  This is
+ * the decode of one token through the layers of a model: set the flag for every layer but the first.
+ * The one-launch kernel then fetches the batch metadata and stages page statistics while the previous
+ * launch drains.  Without the flag nothing but launch parameters is read before the launch's
+ * dependency wait, and the call is safe behind any kernel (one that advances lengths on the device, an
+ * index build, a foreign kernel that releases its dependents early). */
 #define LODA_SEL_CHAINED 1
 
 const char* loda_version(void);

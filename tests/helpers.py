@@ -23,7 +23,8 @@ def oracle_config(setup):
         block_size=setup.page, max_blocks=setup.max_blocks, level1_topk=int(a.tia_level1_topk),
         near_pages=int(a.nfa_near_pages), near_len=int(a.nfa_near_len), level2_topk=int(a.tia_level2_topk),
         cmp_ratio=int(a.tia_level2_cmp_ratio), sink=ix.sink_tokens, swa=ix.sliding_window_size,
-        max_visible=setup.max_visible, mode="bf16")
+        max_visible=setup.max_visible, mode="bf16", near_tokens=ix.nt_near_tokens, far_method=ix.far_method,
+        near_method=ix.near_method, geometry_near=c.geometry.near)
 
 
 def make_setup(lengths, **kw):
@@ -34,8 +35,10 @@ def make_setup(lengths, **kw):
 
 def oracle_selection(setup, i):
     case = setup.cases[i]
+    skips = getattr(setup, "skip_states", None)
+    sf, sn = (False, False) if skips is None else skips[i]
     return O.select_request(bf16_to_f32_np(case.q), bf16_to_f32_np(case.k), case.length,
-                            setup.cfg, setup.attention.scaling)
+                            setup.cfg, setup.attention.scaling, skip_far=sf, skip_near=sn)
 
 
 def pools_np(layer):

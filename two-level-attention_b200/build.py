@@ -52,7 +52,7 @@ def needs_build():
 
 
 def build(force=False, verbose=False):
-    if not force and not needs_build():
+    if not force and not verbose and not needs_build():
         return LIB
     os.makedirs(OBJ_DIR, exist_ok=True)
     nvcc, headers = nvcc_path(), _headers()

@@ -135,7 +135,7 @@ cudaError_t launch_write_prefill(const loda_geometry& g, const loda_layer& L, co
                                  const void* v, const int32_t* table, int n_tokens, cudaStream_t st) {
   if (n_tokens <= 0) return cudaSuccess;
   const size_t total = (size_t)g.num_kv_heads * n_tokens * (g.head_dim / 8 + g.head_dim_v / 8);
-  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const int blocks = (int)((total + 255) / 256 < (size_t)device_sm_count() * 16 ? (total + 255) / 256 : (size_t)device_sm_count() * 16);
   write_prefill_kernel<<<blocks, 256, 0, st>>>(g, L, (const bf16*)k, (const bf16*)v, table, n_tokens);
   return cudaGetLastError();
 }

@@ -92,7 +92,12 @@ __device__ __forceinline__ void append_row(
   if (L.page_mm == nullptr || B.active_req_ids[row] < 0) return;
   const int length = B.lengths[row];
   if (length <= 0) return;
-  const int req = (int)B.valid_req_ids[row];
+  const long long req64 = B.valid_req_ids[row];
+  if (req64 < 0 || req64 >= g.max_requests) {          // never address the index with a slot outside the cache
+    if (lane == 0 && status) atomicOr(status, LODA_STATUS_BAD_REQ);
+    return;
+  }
+  const int req = (int)req64;
   const int tok = length - 1;
   const int blk = tok / g.page;
   if (blk >= g.max_blocks) {

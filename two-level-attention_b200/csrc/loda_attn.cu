@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
     loda_geometry g, loda_layer L, const bf16* __restrict__ q, const int32_t* gather,
     const int32_t* visible_lens, const int32_t* query_to_req,
     int n_req_rows, float scale_log2, bf16* __restrict__ out, float* __restrict__ lse, AttnWorkspace ws,
-    int nsplit, int chained) {
+    int nsplit, int chained, int identity) {
   constexpr int KSTR = D + 8, VSTR = DV + 8;   // padded rows: conflict-free ldmatrix
   constexpr int KSTEPS = D / 16, NTV = DV / 8;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -86,7 +86,10 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
   // are read with L2-coherent loads placed after the wait above, through pointers the compiler
   // may not treat as read-only (declared const __restrict__, their loads were hoisted above
   // the wait and saw the lists of the step before).
-  const int req = __ldcg(query_to_req + t);
+  int req = __ldcg(query_to_req + t);
+  // identity: the caller's contract is one query per batch row (query_to_req[t] == t, or < 0 for a row of zeros);
+  // any other value gives a row of zeros here as in the one-launch decode step
+  if (identity && req != t) req = -1;
   int n = 0;
   if (req >= 0 && req < n_req_rows) n = min(max(__ldcg(visible_lens + (size_t)req * g.num_kv_heads + kv), 0), g.max_visible);
   const int c0 = (int)(((long long)split * n) / nsplit);
@@ -339,7 +342,7 @@ size_t attn_smem_bytes(const loda_geometry& g) {
 // 64-token tile per split, at most ATT_MAX_SPLIT (the largest cluster)
 int attn_nsplit(const loda_geometry& g, int n_query) {
   const int pairs = n_query * g.num_kv_heads;
-  const int want = (LODA_ATTN_CTAS_PER_SM * 148 + pairs - 1) / pairs;
+  const int want = (LODA_ATTN_CTAS_PER_SM * device_sm_count() + pairs - 1) / pairs;
   const int by_len = (g.max_visible + ATT_TILE - 1) / ATT_TILE;
   int ns = 1;
   while (ns < want && ns * 2 <= by_len && ns * 2 <= ATT_MAX_SPLIT) ns *= 2;
@@ -351,11 +354,13 @@ static cudaError_t launch_attn_dims(const loda_geometry& g, const loda_layer& L,
                                     const int32_t* gather, const int32_t* visible_lens,
                                     const int32_t* query_to_req, int n_query, int n_req_rows, float scale_log2,
                                     void* out, float* lse, const AttnWorkspace& ws, bool allow_cluster,
-                                    bool chained, cudaStream_t st) {
+                                    bool chained, bool identity, cudaStream_t st) {
   const int nsplit = attn_nsplit(g, n_query);
   const dim3 grid(nsplit, g.num_kv_heads, n_query);
   const size_t smem = attn_smem_bytes(g);
-  static bool cluster_ok = true;     // cleared if this GPU / driver refuses the cluster launch
+  static bool cluster_refused[64] = {};     // per device: set if this GPU / driver refuses the cluster launch
+  const int dev = device_ordinal();
+  const bool cluster_ok = dev >= 0 && dev < 64 && !cluster_refused[dev];
   cudaError_t e;
   if (allow_cluster && cluster_ok && nsplit > 1) {
     auto kernel = attn_kernel<D, DV, true>;
@@ -378,34 +383,34 @@ static cudaError_t launch_attn_dims(const loda_geometry& g, const loda_layer& L,
       cfg.attrs = attr;
       cfg.numAttrs = 2;
       e = cudaLaunchKernelEx(&cfg, kernel, g, L, (const bf16*)q, gather, visible_lens, query_to_req, n_req_rows,
-                             scale_log2, (bf16*)out, lse, ws, nsplit, (int)chained);
+                             scale_log2, (bf16*)out, lse, ws, nsplit, (int)chained, (int)identity);
     }
     if (e == cudaSuccess) return cudaSuccess;
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     cudaStreamIsCapturing(st, &cap);
     if (cap != cudaStreamCaptureStatusNone) return e;   // cannot retry inside a capture
     (void)cudaGetLastError();
-    cluster_ok = false;
+    cluster_refused[dev] = true;
   }
   auto kernel = attn_kernel<D, DV, false>;
   e = set_kernel_smem(kernel, smem);
   if (e != cudaSuccess) return e;
   return launch_pdl(kernel, grid, dim3(ATT_NT), smem, st, g, L, (const bf16*)q, gather, visible_lens, query_to_req,
-                    n_req_rows, scale_log2, (bf16*)out, lse, ws, nsplit, (int)chained);
+                    n_req_rows, scale_log2, (bf16*)out, lse, ws, nsplit, (int)chained, (int)identity);
 }
 
 cudaError_t launch_attn(const loda_geometry& g, const loda_layer& L, const void* q, const int32_t* gather,
                         const int32_t* visible_lens, const int32_t* query_to_req, int n_query,
                         int n_req_rows, float scale, void* out, float* lse, const AttnWorkspace& ws,
-                        bool allow_cluster, bool chained, cudaStream_t st) {
+                        bool allow_cluster, bool chained, bool identity, cudaStream_t st) {
   if (n_query <= 0) return cudaSuccess;
   const float scale_log2 = scale * 1.4426950408889634f;
   if (g.head_dim == 128 && g.head_dim_v == 128)
     return launch_attn_dims<128, 128>(g, L, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale_log2,
-                                      out, lse, ws, allow_cluster, chained, st);
+                                      out, lse, ws, allow_cluster, chained, identity, st);
   if (g.head_dim == 64 && g.head_dim_v == 64)
     return launch_attn_dims<64, 64>(g, L, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale_log2,
-                                    out, lse, ws, allow_cluster, chained, st);
+                                    out, lse, ws, allow_cluster, chained, identity, st);
   return cudaErrorInvalidValue;
 }
 
@@ -487,7 +492,7 @@ extern "C" int loda_gather_attend_static(const loda_geometry* g, const loda_laye
   cudaError_t e = cudaMemsetAsync(ws.ticket, 0, ATT_STATIC_TICKET_BYTES, (cudaStream_t)stream);
   if (e == cudaSuccess)
     e = launch_attn(*g, *layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale, out, nullptr, ws,
-                    /*allow_cluster=*/false, /*chained=*/false, (cudaStream_t)stream);   // this entry point exists for the scratch path
+                    /*allow_cluster=*/false, /*chained=*/false, /*identity=*/false, (cudaStream_t)stream);   // this entry point exists for the scratch path
   if (e != cudaSuccess) {
     char msg[160];
     snprintf(msg, sizeof(msg), "gather_attend_static: %s", cudaGetErrorString(e));

@@ -27,7 +27,7 @@ cudaError_t launch_decode_fused(const loda_geometry&, const loda_layer&, const l
 cudaError_t launch_select_fused(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
                                 const loda_selection&, uint32_t*, const AppendArgs&, cudaStream_t);
 cudaError_t launch_attn(const loda_geometry&, const loda_layer&, const void*, const int32_t*, const int32_t*,
-                        const int32_t*, int, int, float, void*, float*, const AttnWorkspace&, bool, bool, cudaStream_t);
+                        const int32_t*, int, int, float, void*, float*, const AttnWorkspace&, bool, bool, bool, cudaStream_t);
 size_t l1_smem_bytes(const loda_geometry&);
 size_t l2_smem_bytes(const loda_geometry&);
 int attn_nsplit(const loda_geometry&, int);
@@ -48,6 +48,29 @@ static int check_cuda(cudaError_t e, const char* what) {
 }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Properties of the current device, looked up once per device ordinal.
+int device_ordinal() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) { (void)cudaGetLastError(); return -1; }
+  return dev;
+}
+
+int device_sm_count() {
+  constexpr int kMax = 64;
+  static int sms[kMax] = {};
+  const int dev = device_ordinal();
+  if (dev < 0 || dev >= kMax) return 148;
+  if (sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = 148;
+    }
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
 
 constexpr int kAttnMaxSplit = 16;
 
@@ -126,6 +149,14 @@ static int check_geometry(const loda_geometry* g) {
   if (g->pool_near_len / g->page + 8 > 512)
     return fail(LODA_ERR_UNSUPPORTED, "near pool wider than 512 pages");
   if (g->level2_topk < g->sink + g->swa) return fail(LODA_ERR_ARGUMENT, "level2_topk < sink + swa");
+  if (g->far_method < LODA_FAR_MINMAX || g->far_method > LODA_FAR_AVG_TOP2 || g->near_minmax < 0 || g->near_minmax > 1)
+    return fail(LODA_ERR_ARGUMENT, "far_method must be LODA_FAR_*, near_minmax 0 or 1");
+  if (g->near_tokens_p1 < 0 || (g->near_tokens_p1 > 0 && g->near_tokens_p1 - 1 > g->k_near * g->page))
+    return fail(LODA_ERR_ARGUMENT, "near_tokens_p1 must be 0 (off) or 1 + a count of at most k_near * page tokens");
+  if (g->far_method == LODA_FAR_AVG_TOP2 && g->num_q_heads / g->num_kv_heads < 2)
+    return fail(LODA_ERR_ARGUMENT, "far method avg_top2 needs a GQA group of at least two heads");
+  if (g->shard_count > 1 && (g->near_tokens_p1 > 0 || g->far_method != LODA_FAR_MINMAX || g->near_minmax))
+    return fail(LODA_ERR_UNSUPPORTED, "sequence sharding serves the default level-1 methods and quota");
   if (g->max_visible < g->level2_topk) return fail(LODA_ERR_ARGUMENT, "max_visible < level2_topk");
   if (g->sink < 0 || g->near_len < 0 || g->pool_near_len < g->page)
     return fail(LODA_ERR_ARGUMENT, "bad sink / near_len / pool_near_len");
@@ -243,7 +274,8 @@ int loda_select_l1(const loda_geometry* g, const loda_layer* layer, const loda_b
                     "select_l1");
 }
 
-static int g_last_select_launches = 0;     // kernels the latest loda_select_step launched (1 or 2)
+// kernels the latest loda_select_step / loda_decode_step of the calling thread launched
+static thread_local int g_last_select_launches = 0;
 
 int loda_select_step(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
                      const void* k_new, const void* v_new, const int32_t* slots, float scale,
@@ -301,7 +333,7 @@ int loda_select_l2(const loda_geometry* g, const loda_layer* layer, const loda_b
 static int gather_attend_impl(const loda_geometry* g, const loda_layer* layer, const void* q, const int32_t* gather,
                               const int32_t* visible_lens, const int32_t* query_to_req, int32_t n_query,
                               int32_t n_req_rows, float scale, void* out, float* lse, void* workspace,
-                              bool chained, void* stream) {
+                              bool chained, void* stream, bool identity = false) {
   LODA_TRY(check_gather_attend_args(g, layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, out));
   if (n_query == 0) return LODA_OK;
   if (!workspace) return fail(LODA_ERR_ARGUMENT, "gather attention needs a workspace");
@@ -310,7 +342,7 @@ static int gather_attend_impl(const loda_geometry* g, const loda_layer* layer, c
   const AttnWorkspace ws{(int*)(base + w.at_ticket), (float*)(base + w.at_m), (float*)(base + w.at_z),
                          (float*)(base + w.at_o)};
   return check_cuda(launch_attn(*g, *layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale,
-                                out, lse, ws, /*allow_cluster=*/true, chained, (cudaStream_t)stream),
+                                out, lse, ws, /*allow_cluster=*/true, chained, identity, (cudaStream_t)stream),
                     "gather_attend");
 }
 
@@ -394,7 +426,7 @@ int loda_shard_l2_select(const loda_geometry* g, const loda_layer* layer, const 
   return shard_stage(g, layer, b, q, scale, sel, status, workspace, stream, 2, 2);
 }
 
-static int g_last_decode_launches = 0;
+static thread_local int g_last_decode_launches = 0;
 int loda_last_decode_launches(void) { return g_last_decode_launches; }
 
 int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
@@ -424,8 +456,10 @@ int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda
   LODA_TRY(loda_select_step(g, layer, b, q, k_new, v_new, slots, scale, sel, status, workspace, stream));
   if (b->batch == 0) return LODA_OK;
   g_last_decode_launches = 1 + g_last_select_launches;
-  return gather_attend_impl(g, layer, q, sel->gather, sel->visible_lens, query_to_req, b->batch, g->max_requests,
-                            scale, out, nullptr, workspace, /*chained=*/true, stream);
+  // one query per batch row: the gather list has one row per batch row, and a query_to_req entry other
+  // than the row's own index (or < 0) gives a row of zeros, exactly as in the one-launch kernel
+  return gather_attend_impl(g, layer, q, sel->gather, sel->visible_lens, query_to_req, b->batch, b->batch,
+                            scale, out, nullptr, workspace, /*chained=*/true, stream, /*identity=*/true);
 }
 
 }  // extern "C"

@@ -52,20 +52,29 @@ __device__ __forceinline__ int sub_dim(const loda_geometry& g, int d) {
 
 // ---------------------------------------------------------------------------
 // region geometry of one request (nfa_layer_batch_selector.py:209-262,
-// 1136-1163, 1971-1986); no region is skipped
+// 1136-1163, 1971-1986), with the frozen region-skip decisions of the request's
+// layer (:223-226 pools, :1151-1163 middle range) and the numeric near-token
+// quota (:872-920)
 // ---------------------------------------------------------------------------
 struct Regions {
   int length, kt_eff, near_blks, spl;
   int far_lo, far_hi;       // far pool = pages [far_lo, far_hi)
   int swa_lo_blk, swa_lo_tok, swa_byp_blk;
   bool swa_byp, sink_byp;
-  int lower, upper, quota, kt_cap;
+  int lower, upper, quota, kt_cap;   // quota: tokens the middle receives (both regions together under a numeric quota)
   int shard_rank, shard_count;   // sequence sharding: logical page p is scored here iff p % count == rank
+  bool near_on;             // the near pool is scored (its region is not skipped)
+  int near_lo_valid;        // with the far region skipped, near-pool pages below this one are invalid
+  // numeric near-token quota: the far region [fq_lo, fq_hi) receives fq tokens, the near region
+  // [nq_lo, nq_hi) nq; numeric == false: one quota over [lower, upper)
+  bool numeric;
+  int fq_lo, fq_hi, fq, nq_lo, nq_hi, nq;
 };
 
 __device__ __forceinline__ int cdiv_trunc(int a, int b) { return a / b; }  // C division truncates
 
-__device__ __forceinline__ Regions make_regions(const loda_geometry& g, int length) {
+__device__ __forceinline__ Regions make_regions(const loda_geometry& g, int length, bool skip_far = false,
+                                                bool skip_near = false) {
   Regions r;
   const int bs = g.page, w = g.swa;
   r.length = length;
@@ -81,13 +90,56 @@ __device__ __forceinline__ Regions make_regions(const loda_geometry& g, int leng
   r.swa_byp_blk = r.swa_lo_tok / bs;
   r.swa_byp = (r.swa_lo_tok % bs != 0) && (r.swa_byp_blk >= r.spl);
   if (r.sink_byp) r.swa_byp = r.swa_byp && (r.swa_byp_blk != r.spl);
-  r.lower = r.spl * bs;
-  r.upper = max(r.lower, r.swa_lo_tok);
-  int q = max(min(length, g.level2_topk) - g.sink - (length - r.swa_lo_tok), 0);
-  r.quota = min(q, r.upper - r.lower);
+  // token bound between the far and the near region
+  const int sink_hi = min(g.sink, length);
+  const int swa_hi = max(sink_hi, length - w);
+  const int far_hi_tok = min(swa_hi, max(sink_hi, (max(length - w - g.near_len, 0) / bs) * bs));
+  const int lower0 = r.spl * bs;
+  const int upper0 = max(lower0, r.swa_lo_tok);
+  r.lower = skip_far ? far_hi_tok : lower0;
+  r.upper = max(r.lower, skip_near ? far_hi_tok : upper0);
+  const int base_quota = max(min(length, g.level2_topk) - g.sink - (length - r.swa_lo_tok), 0);
+  r.quota = min(base_quota, r.upper - r.lower);
+  // pools of a row with a skipped region: the region's pool is empty, and a page of the other pool
+  // counts only where it reaches into a region that is still on (block_valid of the reference)
+  r.near_on = !skip_near;
+  r.near_lo_valid = skip_far ? far_hi_tok / bs : 0;
+  if (skip_far) r.far_hi = min(r.far_hi, r.far_lo);
+  else if (skip_near) r.far_hi = min(r.far_hi, (far_hi_tok + bs - 1) / bs);
+  r.numeric = g.near_tokens_p1 > 0;
+  r.fq_lo = r.fq_hi = r.fq = r.nq_lo = r.nq_hi = r.nq = 0;
+  if (r.numeric) {
+    const int reserve = min(g.near_tokens_p1 - 1, base_quota);
+    r.fq_lo = skip_far ? far_hi_tok : lower0;
+    r.fq_hi = far_hi_tok;
+    r.fq = min(max(base_quota - reserve, 0), max(r.fq_hi - r.fq_lo, 0));
+    r.nq_lo = far_hi_tok;
+    r.nq_hi = skip_near ? far_hi_tok : upper0;
+    r.nq = min(max(base_quota - r.fq, 0), max(r.nq_hi - r.nq_lo, 0));
+    r.quota = r.fq + r.nq;
+  }
   r.shard_rank = g.shard_rank;
   r.shard_count = g.shard_count;
   return r;
+}
+
+// the skip decisions of request slot `req` in this layer (NULL arrays: nothing skipped)
+__device__ __forceinline__ void load_skip_flags(const loda_layer& L, int req, bool* skip_far, bool* skip_near) {
+  *skip_far = L.skip_far != nullptr && L.skip_far[req] != 0;
+  *skip_near = L.skip_near != nullptr && L.skip_near[req] != 0;
+}
+
+// Request slot of an active batch row, checked: a slot outside [0, max_requests) makes the row a
+// padding row (length 0, slot 0) and raises LODA_STATUS_BAD_REQ instead of addressing memory with it.
+__device__ __forceinline__ int checked_request(const loda_geometry& g, long long act, long long val, int* length,
+                                               uint32_t* status) {
+  if (act < 0) { *length = 0; return (val >= 0 && val < g.max_requests) ? (int)val : 0; }
+  if (val < 0 || val >= g.max_requests) {
+    *length = 0;
+    if (status && threadIdx.x == 0) atomicOr(status, LODA_STATUS_BAD_REQ);
+    return 0;
+  }
+  return (int)val;
 }
 
 __device__ __forceinline__ bool page_owned(const Regions& r, int t) {
@@ -101,6 +153,7 @@ __device__ __forceinline__ bool in_far_pool(const Regions& r, int t) {
 
 __device__ __forceinline__ bool in_near_pool(const Regions& r, int t) {
   if (t < r.near_blks || t >= r.swa_lo_blk || t >= r.kt_eff || t >= r.kt_cap) return false;
+  if (!r.near_on || t < r.near_lo_valid) return false;
   if (r.swa_byp && t == r.swa_byp_blk) return false;
   if (r.sink_byp && t == r.spl) return false;
   return page_owned(r, t);
@@ -864,6 +917,10 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
+
+// host: ordinal (-1 on failure) and multiprocessor count of the current device, looked up once per device
+int device_ordinal();
+int device_sm_count();
 
 // decode append carried by extra CTAs of the L1 launch (enabled == 0: none)
 struct AppendArgs {

@@ -29,7 +29,7 @@ namespace loda {
 
 LODA_PHASE_STORAGE(l1)
 
-template <int DSUB, int P>
+template <int DSUB, int P, bool GENERIC>
 __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, loda_batch B,
                                                 const bf16* __restrict__ q, float scale,
                                                 loda_selection out, SelectWorkspace ws, int nsplit,
@@ -44,9 +44,11 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   const int G = g.num_q_heads / g.num_kv_heads;
   float* qlow = qhat + G * DSUB;
   float* qhigh = qlow + G * DSUB;
-  int* kept = (int*)(qhigh + G * DSUB);                          // k_far + k_near + 2
+  float* qraw = qhigh + G * DSUB;                                // GENERIC: the unrounded scaled query (avg_top2)
+  constexpr int NQ = GENERIC ? 4 : 3;
+  int* kept = (int*)(qhat + NQ * G * DSUB);                      // k_far + k_near + 2
   // (an offset, not pointer arithmetic through an integer: the compiler must keep seeing shared memory)
-  const size_t keys_off = (ROWS_BYTES + (size_t)3 * G * DSUB * 4 + (size_t)(g.k_far + g.k_near + 2) * 4 + 15) & ~(size_t)15;
+  const size_t keys_off = (ROWS_BYTES + (size_t)NQ * G * DSUB * 4 + (size_t)(g.k_far + g.k_near + 2) * 4 + 15) & ~(size_t)15;
   uint32_t* keys = (uint32_t*)(smem + keys_off);                 // 2 P + 8
   int* wtot = (int*)(keys + 2 * P + 8);                          // 8 x 32
   int* sh = wtot + 256;                                          // 8
@@ -74,11 +76,11 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   float q_first = 0.0f;
   if (tid < nq)
     q_first = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + tid / DSUB) * g.head_dim + sub_dim(g, tid % DSUB)]);
-  const long long act = B.active_req_ids[b];
-  const int len_raw = B.lengths[b];
-  const int req = (int)B.valid_req_ids[b];
-  const int length = act >= 0 ? len_raw : 0;
-  const Regions rg = make_regions(g, length);
+  int length = B.lengths[b];
+  const int req = checked_request(g, B.active_req_ids[b], B.valid_req_ids[b], &length, ap.status);
+  bool skip_far, skip_near;
+  load_skip_flags(L, req, &skip_far, &skip_near);
+  const Regions rg = make_regions(g, length, skip_far, skip_near);
   // this CTA's tiles of P pages: split, split + nsplit, ... (interleaved, so that the tiles a
   // short request really has are spread over the CTAs of its row); tiles past the request's
   // last page are neither read nor written, and a CTA without tiles only takes its ticket
@@ -92,15 +94,7 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
     if (p0 >= page_end) break;
     if (it > 0) __syncthreads();                         // the staging rows are reused
     // stage the metadata rows of the tile (issued first: the longest latency)
-    for (int c = tid; c < P * CPR; c += P) {
-      const int pl = c / CPR, cc = c % CPR;
-      const int page = p0 + pl;
-      if (in_far_pool(rg, page)) {
-        cp_async16(rows + (size_t)pl * ROWB + cc * 16, mm_base + (size_t)page * (4 * DSUB) + cc * 16, true);
-      } else if (cc < NC && in_near_pool(rg, page)) {
-        cp_async16(rows + (size_t)pl * ROWB + cc * 16, sum_base + (size_t)page * (2 * DSUB) + cc * 16, true);
-      }
-    }
+    l1_stage_tile<DSUB, P, GENERIC>(g, rg, p0, rows, mm_base, sum_base);
     cp_async_commit();
     if (it == 0) {
       // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
@@ -112,6 +106,7 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
         qhat[i] = qh;
         qlow[i] = fminf(qh, 0.0f);
         qhigh[i] = fmaxf(qh, 0.0f);
+        if (GENERIC) qraw[i] = __fmul_rn(qv, scale);
       }
     }
     LODA_PHASE(l1, cta_id, 2);
@@ -122,7 +117,7 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
     // one page per thread
     const int page = p0 + tid;
     const unsigned char* myrow = rows + (size_t)tid * ROWB;
-    const uint32_t ord = l1_page_score<DSUB>(g, rg, page, myrow, qhat, qlow, qhigh, G);
+    const uint32_t ord = l1_page_score<DSUB, GENERIC>(g, rg, page, myrow, qhat, qlow, qhigh, G, qraw);
     row_scores[page] = (uint16_t)ord;     // the selecting CTA reads pages below page_end (rounded up to 8)
   }
   LODA_PHASE(l1, cta_id, 4);
@@ -213,10 +208,12 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
 // that one CTA's copies overlap the other's arithmetic, for every larger grid.
 constexpr int L1_P_WIDE = 512, L1_P_NARROW = 256;
 
+static bool l1_generic(const loda_geometry& g) { return g.far_method != LODA_FAR_MINMAX || g.near_minmax != 0; }
+
 static size_t l1_smem_bytes_p(const loda_geometry& g, int P) {
   const int G = g.num_q_heads / g.num_kv_heads;
   const size_t rows = (size_t)P * (4 * g.sub_dims + 16);
-  return (rows > L1_TAIL_BYTES ? rows : L1_TAIL_BYTES) + (size_t)3 * G * g.sub_dims * 4 +
+  return (rows > L1_TAIL_BYTES ? rows : L1_TAIL_BYTES) + (size_t)(l1_generic(g) ? 4 : 3) * G * g.sub_dims * 4 +
          (size_t)(g.k_far + g.k_near + 2) * 4 + (size_t)(2 * P + 8) * 4 + (256 + 8) * 4 + 32;
 }
 
@@ -226,20 +223,21 @@ size_t l1_smem_bytes(const loda_geometry& g) { return l1_smem_bytes_p(g, L1_P_WI
 int l1_score_stride(const loda_geometry& g) { return (g.max_blocks + L1_P_WIDE - 1) / L1_P_WIDE * L1_P_WIDE; }
 
 static bool l1_wide(const loda_geometry& g, int rows) {
-  return rows * ((g.max_blocks + L1_P_WIDE - 1) / L1_P_WIDE + 1) <= 148;
+  return rows * ((g.max_blocks + L1_P_WIDE - 1) / L1_P_WIDE + 1) <= device_sm_count();
 }
 
 // CTAs per row: one tile each while the grid is small (batch 1: latency), several
 // interleaved tiles per CTA once rows x tiles exceeds about eight CTAs per SM
 static void l1_split(const loda_geometry& g, int rows, int P, int* ctas_per_row, int* tiles_per_cta) {
   const int ntiles = (g.max_blocks + P - 1) / P;
-  int tpc = (rows * ntiles + 8 * 148 - 1) / (8 * 148);
+  const int sms = device_sm_count();
+  int tpc = (rows * ntiles + 8 * sms - 1) / (8 * sms);
   tpc = tpc < 1 ? 1 : tpc > ntiles ? ntiles : tpc;
   *tiles_per_cta = tpc;
   *ctas_per_row = (ntiles + tpc - 1) / tpc;
 }
 
-template <int DS, int P>
+template <int DS, int P, bool GENERIC>
 static cudaError_t launch_l1_p(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                float scale, const loda_selection& out, const SelectWorkspace& ws,
                                const AppendArgs& ap, int phase, cudaStream_t st) {
@@ -252,9 +250,9 @@ static cudaError_t launch_l1_p(const loda_geometry& g, const loda_layer& L, cons
     tpc = 0;
   }
   const size_t smem = l1_smem_bytes_p(g, P);
-  cudaError_t e = set_kernel_smem(l1_kernel<DS, P>, smem);
+  cudaError_t e = set_kernel_smem(l1_kernel<DS, P, GENERIC>, smem);
   if (e != cudaSuccess) return e;
-  return launch_pdl(l1_kernel<DS, P>, grid, dim3(P), smem, st, g, L, B, (const bf16*)q, scale, out, ws, nsplit, tpc,
+  return launch_pdl(l1_kernel<DS, P, GENERIC>, grid, dim3(P), smem, st, g, L, B, (const bf16*)q, scale, out, ws, nsplit, tpc,
                     ap, phase);
 }
 
@@ -262,9 +260,11 @@ template <int DS>
 static cudaError_t launch_l1_d(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                float scale, const loda_selection& out, const SelectWorkspace& ws,
                                const AppendArgs& ap, int phase, cudaStream_t st) {
+  if (l1_generic(g))      // other level-1 methods than the defaults: one tile shape, methods read at run time
+    return launch_l1_p<DS, L1_P_NARROW, true>(g, L, B, q, scale, out, ws, ap, phase, st);
   return l1_wide(g, B.batch * g.num_kv_heads)
-             ? launch_l1_p<DS, L1_P_WIDE>(g, L, B, q, scale, out, ws, ap, phase, st)
-             : launch_l1_p<DS, L1_P_NARROW>(g, L, B, q, scale, out, ws, ap, phase, st);
+             ? launch_l1_p<DS, L1_P_WIDE, false>(g, L, B, q, scale, out, ws, ap, phase, st)
+             : launch_l1_p<DS, L1_P_NARROW, false>(g, L, B, q, scale, out, ws, ap, phase, st);
 }
 
 // phase 0: scores and selection; 1: scores only; 2: selection only (of the scores in the workspace)

@@ -55,7 +55,10 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
   int* wtot = (int*)(smem + off); off += 192 * 4;
   int* scan = (int*)(smem + off); off += 40 * 4;
   int* sh = (int*)(smem + off); off += 16 * 4;
-  uint8_t* win = (uint8_t*)(smem + off);
+  uint8_t* win = (uint8_t*)(smem + off); off += ((size_t)K2 + 15) & ~(size_t)15;
+  // numeric near-token quota only: one region's scores and the concatenated middle
+  uint16_t* sc2 = (uint16_t*)(smem + off); off += ((size_t)np_max * g.page * 2 + 15) & ~(size_t)15;
+  int* fin = (int*)(smem + off);
 
   const int tid = threadIdx.x;
   const int split = blockIdx.x, row = blockIdx.y;
@@ -63,11 +66,15 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
   LODA_PHASE(l2, cta_id, 0);
   const int b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
   const int G = g.num_q_heads / g.num_kv_heads;
-  const long long act = B.active_req_ids[b];
-  const int len_raw = B.lengths[b];
-  const int req = (int)B.valid_req_ids[b];
-  const int length = act >= 0 ? len_raw : 0;
-  const Regions rg = make_regions(g, length);
+  // A launch chained behind the level-1 launch of the same call (which writes neither) reads the batch
+  // metadata and the query before its dependency wait; a launch that stands alone may follow any
+  // kernel (one that advances the lengths, for instance) and reads nothing before the wait.
+  if (!chained) pdl_wait();
+  int length = B.lengths[b];
+  const int req = checked_request(g, B.active_req_ids[b], B.valid_req_ids[b], &length, status);
+  bool skip_far, skip_near;
+  load_skip_flags(L, req, &skip_far, &skip_near);
+  const Regions rg = make_regions(g, length, skip_far, skip_near);
   const int32_t* table = L.block_table + (size_t)req * g.max_blocks;
 
   // ---- grouped query on the subspace ---------------------------------------
@@ -84,13 +91,12 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
       qf[tid] = acc;
     }
   };
-  if (chained) group_query();
+  group_query();
   LODA_PHASE(l2, cta_id, 1);
-  pdl_wait();
+  if (chained) pdl_wait();
 #if LODA_PDL_TRIGGER == 0
   pdl_launch_dependents();
 #endif
-  if (!chained) group_query();
   __syncthreads();
   LODA_PHASE(l2, cta_id, 2);
 
@@ -134,7 +140,9 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
   pdl_launch_dependents();
 #endif
   LODA_PHASE(l2, cta_id, 5);
-  const L2Shared shm{sc, pages, physs, mid_a, mid_b, wtot, scan, win};
+  L2Shared shm{sc, pages, physs, mid_a, mid_b, wtot, scan, win};
+  shm.sc2 = sc2;
+  shm.fin = fin;
   l2_select_and_write<NT, 0>(g, rg, S, status, table, b, kv, row, length, nitems, shm, ws.l2_ticket + row,
                              LODA_PDL_TRIGGER == 1);
   LODA_PHASE(l2, cta_id, 9);
@@ -148,8 +156,8 @@ __global__ void __launch_bounds__(128) protected_gather_kernel(loda_geometry g, 
                                                                int32_t* __restrict__ visible_lens, uint32_t* status) {
   const int row = blockIdx.x, b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
   pdl_wait();
-  const int length = B.active_req_ids[b] >= 0 ? B.lengths[b] : 0;
-  const int req = (int)B.valid_req_ids[b];
+  int length = B.lengths[b];
+  const int req = checked_request(g, B.active_req_ids[b], B.valid_req_ids[b], &length, status);
   const int32_t* table = L.block_table + (size_t)req * g.max_blocks;
   const int pl2 = 31 - __clz(g.page), pmask = g.page - 1;
   const int cap = g.max_blocks * g.page;
@@ -190,8 +198,9 @@ cudaError_t launch_protected_gather(const loda_geometry& g, const loda_layer& L,
 
 size_t l2_smem_bytes(const loda_geometry& g) {
   const size_t np_max = g.k_far + g.k_near + 2;
-  return ((np_max * g.page * 2 + 15) & ~(size_t)15) + g.sub_dims * 4 + 2 * np_max * 4 +
-         2 * (size_t)g.level2_topk * 4 + 192 * 4 + (40 + 16) * 4 + g.level2_topk + 48;
+  const bool numeric = g.near_tokens_p1 > 0;      // a masked copy of the scores and the concatenated middle
+  return ((np_max * g.page * 2 + 15) & ~(size_t)15) * (numeric ? 2 : 1) + g.sub_dims * 4 + 2 * np_max * 4 +
+         (numeric ? 3 : 2) * (size_t)g.level2_topk * 4 + 192 * 4 + (40 + 16) * 4 + g.level2_topk + 64;
 }
 
 template <int DS>
@@ -201,7 +210,7 @@ static cudaError_t launch_l2_d(const loda_geometry& g, const loda_layer& L, cons
   // scoring CTAs per row: 8 at batch 1 (latency), one once the rows alone give every SM a CTA
   // (every CTA of a row pays the ticket; the row's selection runs in one CTA either way)
   const int rows = B.batch * g.num_kv_heads;
-  int nsplit = (LODA_L2_CTAS_PER_SM * 148 + rows - 1) / rows;
+  int nsplit = (LODA_L2_CTAS_PER_SM * device_sm_count() + rows - 1) / rows;
   nsplit = nsplit < 1 ? 1 : nsplit > L2_SPLIT ? L2_SPLIT : nsplit;
   const dim3 grid(phase == 2 ? 1 : nsplit, rows);      // selection only: one CTA per row
   const size_t smem = l2_smem_bytes(g);

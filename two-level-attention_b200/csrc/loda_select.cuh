@@ -45,16 +45,36 @@ __device__ __forceinline__ float dot_chunks(const float (&k)[DSUB], const float*
   return chunk_tree<NC>(p);
 }
 
+// Which statistic a pool's pages are scored on, and therefore staged: the min/max rows (true) or
+// the sum row (false).  GENERIC == false fixes the default methods at compile time (far pool by
+// the min/max bound, near pool by the page mean); GENERIC == true reads them from the geometry.
+template <bool GENERIC>
+__device__ __forceinline__ bool l1_far_uses_minmax(const loda_geometry& g) {
+  return GENERIC ? g.far_method == LODA_FAR_MINMAX : true;
+}
+template <bool GENERIC>
+__device__ __forceinline__ bool l1_near_uses_minmax(const loda_geometry& g) {
+  return GENERIC ? g.near_minmax != 0 : false;
+}
+
 // Ordered 16-bit score of one logical page from its staged metadata row (min then max, or the
 // sum in the first half); 0 = the page is in neither pool or scores -inf.
-template <int DSUB>
+// Per head the bound (min . min(q, 0) + max . max(q, 0)) or the mean score (mean . q) is rounded to
+// bf16; the page score is the mean over the GQA group, rounded to bf16 — or, for the far method
+// avg_top2, the mean of the two best per-head mean scores computed from the unrounded scaled query
+// qraw (nfa_layer_batch_selector.py:290-354, 2412-2427).
+template <int DSUB, bool GENERIC = false>
 __device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const Regions& rg, int page,
                                                   const unsigned char* myrow, const float* qhat, const float* qlow,
-                                                  const float* qhigh, int G) {
+                                                  const float* qhigh, int G, const float* qraw = nullptr) {
   constexpr int NC = DSUB / 8;
   uint32_t ord = 0;
   const float gf = (float)G;
-  if (in_far_pool(rg, page)) {
+  const bool far = in_far_pool(rg, page);
+  const bool near = !far && in_near_pool(rg, page);
+  if (!far && !near) return 0u;
+  const bool use_mm = far ? l1_far_uses_minmax<GENERIC>(g) : l1_near_uses_minmax<GENERIC>(g);
+  if (use_mm) {
     float kmin[DSUB], kmax[DSUB];
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
@@ -68,7 +88,7 @@ __device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const 
       acc = __fadd_rn(acc, bf16r(mm));
     }
     ord = ord16(bf16r(__fdiv_rn(acc, gf)));
-  } else if (in_near_pool(rg, page)) {
+  } else {
     float kavg[DSUB];
     // mean = sum / page: the page size is a power of two, so the division is an exact scaling and
     // the multiplication by 1 / page gives the same bits at a fraction of the instructions
@@ -77,12 +97,44 @@ __device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const 
     for (int c = 0; c < NC; ++c) unpack8(*(const uint4*)(myrow + c * 16), *(float(*)[8])(kavg + 8 * c));
 #pragma unroll
     for (int i = 0; i < DSUB; ++i) kavg[i] = bf16r(__fmul_rn(kavg[i], inv_bs));
-    float acc = 0.0f;
+    if (GENERIC && far && g.far_method == LODA_FAR_AVG_TOP2) {
+      float t1 = -INFINITY, t2 = -INFINITY;
 #pragma unroll 1
-    for (int j = 0; j < G; ++j) acc = __fadd_rn(acc, bf16r(dot_chunks<DSUB>(kavg, qhat + j * DSUB)));
-    ord = ord16(bf16r(__fdiv_rn(acc, gf)));
+      for (int j = 0; j < G; ++j) {
+        const float v = bf16r(dot_chunks<DSUB>(kavg, qraw + j * DSUB));
+        const float second = v > t1 ? t1 : v;
+        t1 = v > t1 ? v : t1;
+        t2 = second > t2 ? second : t2;
+      }
+      ord = ord16(bf16r(__fdiv_rn(__fadd_rn(t1, t2), 2.0f)));
+    } else {
+      float acc = 0.0f;
+#pragma unroll 1
+      for (int j = 0; j < G; ++j) acc = __fadd_rn(acc, bf16r(dot_chunks<DSUB>(kavg, qhat + j * DSUB)));
+      ord = ord16(bf16r(__fdiv_rn(acc, gf)));
+    }
   }
   return ord == ORD16_NEG_INF ? 0u : ord;   // a -inf score never competes (it equals "not in the pool")
+}
+
+// Stage the metadata rows of the P pages [p0, p0 + P) of one row into dst (rows ROWB bytes apart):
+// for every page of a pool the statistic its score needs, 16 bytes per copy.
+template <int DSUB, int P, bool GENERIC>
+__device__ __forceinline__ void l1_stage_tile(const loda_geometry& g, const Regions& rg, int p0, unsigned char* dst,
+                                              const unsigned char* mm_base, const unsigned char* sum_base) {
+  constexpr int NC = DSUB / 8, CPR = 2 * NC, ROWB = 4 * DSUB + 16;
+  const bool far_mm = l1_far_uses_minmax<GENERIC>(g), near_mm = l1_near_uses_minmax<GENERIC>(g);
+  for (int c = threadIdx.x; c < P * CPR; c += P) {
+    const int pl = c / CPR, cc = c % CPR;
+    const int page = p0 + pl;
+    const bool far = in_far_pool(rg, page);
+    if (!far && !in_near_pool(rg, page)) continue;
+    if (far ? far_mm : near_mm) {
+      cp_async16(dst + (size_t)pl * ROWB + cc * 16, mm_base + (size_t)page * (4 * DSUB) + cc * 16, true);
+    } else if (cc < NC) {
+      cp_async16(dst + (size_t)pl * ROWB + cc * 16, sum_base + (size_t)page * (2 * DSUB) + cc * 16, true);
+    }
+  }
 }
 
 // the selecting CTA reuses the staging area: 40 KB for the far pool's scores (2 bytes per page)
@@ -286,6 +338,9 @@ __device__ __forceinline__ uint32_t l2_slot_score(const loda_geometry& g, const 
 // quota best by bisection, fill holes, drop ids below the sink, and write
 // sink ++ middle ++ window as physical slots.  Runs on the first NT threads of the CTA
 // (BAR as in group_sync).  trigger: release the dependent launch after the selection.
+// With a numeric near-token quota (rg.numeric) the far and the near region select separately on
+// masked copies of the scores and their survivors are concatenated
+// (nfa_layer_batch_selector.py:2274-2332); that needs sm.sc2 and sm.fin.
 struct L2Shared {
   uint16_t* sc;
   int *pages, *physs, *mid_a, *mid_b, *wtot, *scan;
@@ -293,6 +348,8 @@ struct L2Shared {
   const uint32_t* hist = nullptr;    // HIST: 12-bit histogram of the candidate scores (block_hist_kth_bin)
   int* list = nullptr;               // optional copy of the gather list in shared memory (max_visible ints) ...
   int* list_n = nullptr;             // ... and of its length
+  uint16_t* sc2 = nullptr;           // numeric quota: nitems scores of one region
+  int* fin = nullptr;                // numeric quota: level2_topk ints, the concatenated middle
 };
 
 #ifndef LODA_L2TAIL_INLINE
@@ -309,8 +366,132 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
   uint16_t* sc = sm.sc;
   int *pages = sm.pages, *physs = sm.physs, *mid_a = sm.mid_a, *mid_b = sm.mid_b, *wtot = sm.wtot, *scan = sm.scan;
   uint8_t* win = sm.win;
-  const int quota = rg.quota;
   int* slots_sel = mid_b;      // ascending candidate slots kept by the select
+
+  // sink ++ mid[0, count_m) ++ window as physical slots through the block table
+  auto write_union = [&](const int* mid, int count_m) {
+    const int cap = g.max_blocks * g.page;
+    const int sk_all = min(length, g.sink);
+    const int count_s = min(length, g.sink + g.swa) - sk_all;
+    const int s_lo = max(max(length - g.swa, 0), sk_all);
+    const int s_hi = min(length - g.swa + count_s, cap);
+    const int sk = S.middle_only ? 0 : sk_all;                       // middle only: no sink, no window
+    const int n_s = S.middle_only ? 0 : max(s_hi - s_lo, 0);
+    const int total = sk + count_m + n_s;
+    const int n_out = min(total, g.max_visible);
+    int32_t* gout = S.gather + ((size_t)b * g.num_kv_heads + kv) * g.max_visible;
+    for (int i = tid; i < n_out; i += NT) {
+      int id;
+      if (i < sk) id = i;
+      else if (i < sk + count_m) id = mid[i - sk];
+      else id = s_lo + (i - sk - count_m);
+      const int lp = (id >> pl2);
+      int ph = lp < g.max_blocks ? table[lp] : -1;
+      if (ph < 0 || ph >= g.num_pages) {
+        if (rg.shard_count > 1) {
+          ph = -1;              // another GPU's page: skipped by the attention
+        } else {
+          if (status) atomicOr(status, LODA_STATUS_BAD_PAGE);
+          ph = g.num_pages - 1;   // PAD page: zeros, never out of bounds
+        }
+      }
+      const int slot = ph >= 0 ? ph * g.page + (id & pmask) : -1;
+      gout[i] = slot;
+      if (sm.list) sm.list[i] = slot;
+    }
+    if (tid == 0) {
+      if (sm.list_n) *sm.list_n = n_out;
+      S.visible_lens[(size_t)b * g.num_kv_heads + kv] = n_out;
+      if (total > g.max_visible && status) atomicOr(status, LODA_STATUS_TRUNCATED);
+      if (ticket) *ticket = 0;
+    }
+  };
+
+  // Survivors (slots_sel[0, take), ascending slots) of a selection with quota q over [lo, hi) as
+  // ascending token ids: hole fill (nfa_layer_batch_selector.py:545-566), then ids below the sink
+  // dropped (only holes can be there).  Returns the list and its length.
+  auto finish_region = [&](int take, int lo, int q, int* count_out) -> const int* {
+    for (int i = tid; i < take; i += NT) {
+      const int sl = slots_sel[i];
+      mid_a[i] = pages[(sl >> pl2)] * g.page + (sl & pmask);
+    }
+    group_sync<NT, BAR>();
+    int count = take;
+    int* mid = mid_a;
+    if (take < q) {
+      const int need = q - take;
+      // the holes are among the first q ids of [lo, hi) (q <= hi - lo)
+      for (int i = tid; i < q; i += NT) win[i] = 0;
+      group_sync<NT, BAR>();
+      int in_win = 0;
+      for (int i = tid; i < take; i += NT) {
+        const int w = mid_a[i] - lo;
+        if (w < q) { win[w] = 1; ++in_win; }
+      }
+      int cw;
+      block_exclusive_scan<NT, BAR>(in_win, scan, &cw);
+      const int ipt = (q + NT - 1) / NT;
+      const int wlo = min(tid * ipt, q), whi = min(wlo + ipt, q);
+      int zeros = 0;
+      for (int w = wlo; w < whi; ++w) zeros += win[w] == 0;
+      int ztotal;
+      int zrank = block_exclusive_scan<NT, BAR>(zeros, scan, &ztotal);
+      int keep = 0;
+      for (int w = wlo; w < whi; ++w) {
+        if (win[w] == 0) { if (zrank < need) win[w] = 2; ++zrank; }
+        keep += win[w] != 0;
+      }
+      int ktotal;
+      int pos = block_exclusive_scan<NT, BAR>(keep, scan, &ktotal);
+      for (int w = wlo; w < whi; ++w) {
+        if (win[w] != 0) mid_b[pos++] = lo + w;
+      }
+      // chosen tokens beyond the window follow all holes
+      for (int i = cw + tid; i < take; i += NT) mid_b[ktotal + (i - cw)] = mid_a[i];
+      group_sync<NT, BAR>();
+      count = ktotal + (take - cw);
+      mid = mid_b;
+    }
+    int below = 0;
+    for (int i = tid; i < min(count, g.sink); i += NT) below += mid[i] < g.sink;
+    int d0;
+    block_exclusive_scan<NT, BAR>(below, scan, &d0);
+    *count_out = count - d0;
+    return mid + d0;
+  };
+
+  if (rg.numeric) {
+    // ---- numeric near-token quota: far region, then near region, concatenated ----------------
+    int total_m = 0;
+    if (sm.sc2 != nullptr && sm.fin != nullptr) {
+#pragma unroll 1
+      for (int region = 0; region < 2; ++region) {
+        const int lo = region == 0 ? rg.fq_lo : rg.nq_lo, hi = region == 0 ? rg.fq_hi : rg.nq_hi;
+        const int q = region == 0 ? rg.fq : rg.nq;
+        if (q <= 0) continue;
+        for (int i = tid; i < nitems; i += NT) {
+          const int tok = pages[i >> pl2] * g.page + (i & pmask);
+          sm.sc2[i] = (tok >= lo && tok < hi) ? sc[i] : (uint16_t)0;
+        }
+        group_sync<NT, BAR>();
+        const int take = block_bisect_topk<NT, BAR, 0, 4, false>(sm.sc2, nitems, min(q, K2), slots_sel, wtot);
+        int count_m;
+        const int* mid = finish_region(take, lo, q, &count_m);
+        for (int i = tid; i < count_m; i += NT) sm.fin[total_m + i] = mid[i];
+        total_m += count_m;
+        group_sync<NT, BAR>();
+      }
+    }
+    if (trigger) pdl_launch_dependents();
+    if (S.middle != nullptr) {
+      for (int i = tid; i < total_m; i += NT) S.middle[(size_t)row * K2 + i] = sm.fin[i];
+      if (tid == 0) S.middle_counts[row] = total_m;
+    }
+    write_union(sm.fin, total_m);
+    return;
+  }
+
+  const int quota = rg.quota;
   // two instantiations: rows of at most 9 NT slots (one chunk and one single score per thread: the
   // 2 080 slots of the default budgets) run a much shorter instruction stream, and executed once,
   // cold, a selection costs about as much in instruction fetch as in arithmetic
@@ -366,96 +547,14 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
     }
     return;
   }
-  for (int i = tid; i < take; i += NT) {
-    const int sl = slots_sel[i];
-    mid_a[i] = pages[(sl >> pl2)] * g.page + (sl & pmask);
-  }
-  group_sync<NT, BAR>();
-  int count = take;
-  int* mid = mid_a;
-
-  // ---- hole fill (nfa_layer_batch_selector.py:545-566) -------------------------
-  if (take < quota) {
-    const int need = quota - take;
-    // the holes are among the first `quota` ids of [lower, upper)
-    for (int i = tid; i < quota; i += NT) win[i] = 0;
-    group_sync<NT, BAR>();
-    int in_win = 0;
-    for (int i = tid; i < take; i += NT) {
-      const int w = mid_a[i] - rg.lower;
-      if (w < quota) { win[w] = 1; ++in_win; }
-    }
-    int cw;
-    block_exclusive_scan<NT, BAR>(in_win, scan, &cw);
-    const int ipt = (quota + NT - 1) / NT;
-    const int lo = min(tid * ipt, quota), hi = min(lo + ipt, quota);
-    int zeros = 0;
-    for (int w = lo; w < hi; ++w) zeros += win[w] == 0;
-    int ztotal;
-    int zrank = block_exclusive_scan<NT, BAR>(zeros, scan, &ztotal);
-    int keep = 0;
-    for (int w = lo; w < hi; ++w) {
-      if (win[w] == 0) { if (zrank < need) win[w] = 2; ++zrank; }
-      keep += win[w] != 0;
-    }
-    int ktotal;
-    int pos = block_exclusive_scan<NT, BAR>(keep, scan, &ktotal);
-    for (int w = lo; w < hi; ++w) {
-      if (win[w] != 0) mid_b[pos++] = rg.lower + w;
-    }
-    // chosen tokens beyond the window follow all holes
-    for (int i = cw + tid; i < take; i += NT) mid_b[ktotal + (i - cw)] = mid_a[i];
-    group_sync<NT, BAR>();
-    count = ktotal + (take - cw);
-    mid = mid_b;
-  }
-
-  // ---- drop ids below the sink (only holes can be there), ascending already ----
-  int below = 0;
-  for (int i = tid; i < min(count, g.sink); i += NT) below += mid[i] < g.sink;
-  int d0;
-  block_exclusive_scan<NT, BAR>(below, scan, &d0);
-  const int count_m = count - d0;
+  int count_m;
+  const int* mid = finish_region(take, rg.lower, quota, &count_m);
   if (S.middle != nullptr) {
-    for (int i = tid; i < count_m; i += NT) S.middle[(size_t)row * K2 + i] = mid[d0 + i];
+    for (int i = tid; i < count_m; i += NT) S.middle[(size_t)row * K2 + i] = mid[i];
     if (tid == 0) S.middle_counts[row] = count_m;
   }
   // ---- union with sink and window ids (nfa_layer_batch_selector.py:1348-1437) --
-  const int cap = g.max_blocks * g.page;
-  const int sk_all = min(length, g.sink);
-  const int count_s = min(length, g.sink + g.swa) - sk_all;
-  const int s_lo = max(max(length - g.swa, 0), sk_all);
-  const int s_hi = min(length - g.swa + count_s, cap);
-  const int sk = S.middle_only ? 0 : sk_all;                       // middle only: no sink, no window
-  const int n_s = S.middle_only ? 0 : max(s_hi - s_lo, 0);
-  const int total = sk + count_m + n_s;
-  const int n_out = min(total, g.max_visible);
-  int32_t* gout = S.gather + ((size_t)b * g.num_kv_heads + kv) * g.max_visible;
-  for (int i = tid; i < n_out; i += NT) {
-    int id;
-    if (i < sk) id = i;
-    else if (i < sk + count_m) id = mid[d0 + i - sk];
-    else id = s_lo + (i - sk - count_m);
-    const int lp = (id >> pl2);
-    int ph = lp < g.max_blocks ? table[lp] : -1;
-    if (ph < 0 || ph >= g.num_pages) {
-      if (rg.shard_count > 1) {
-        ph = -1;              // another GPU's page: skipped by the attention
-      } else {
-        if (status) atomicOr(status, LODA_STATUS_BAD_PAGE);
-        ph = g.num_pages - 1;   // PAD page: zeros, never out of bounds
-      }
-    }
-    const int slot = ph >= 0 ? ph * g.page + (id & pmask) : -1;
-    gout[i] = slot;
-    if (sm.list) sm.list[i] = slot;
-  }
-  if (tid == 0) {
-    if (sm.list_n) *sm.list_n = n_out;
-    S.visible_lens[(size_t)b * g.num_kv_heads + kv] = n_out;
-    if (total > g.max_visible && status) atomicOr(status, LODA_STATUS_TRUNCATED);
-    if (ticket) *ticket = 0;
-  }
+  write_union(mid, count_m);
 }
 
 }  // namespace loda

@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
                                                             uint32_t* status, AppendArgs ap, int tiles_per_cta,
                                                             FusedAttend at) {
   constexpr int P = SF_P;
-  constexpr int NC = DSUB / 8, CPR = 2 * NC, ROWB = 4 * DSUB + 16;
+  constexpr int ROWB = 4 * DSUB + 16;
   extern __shared__ __align__(16) unsigned char smem[];
   cg::cluster_group cluster = cg::this_cluster();
   const int CS = (int)cluster.num_blocks();
@@ -148,18 +148,20 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   // histogram): zero outside the pool, so cleared before any peer may store
   if (rank == 1 && tid < (L1_NEAR_CAP + 8) / 2) hist2[tid] = 0;
   cluster.barrier_arrive();   // (0) "this CTA runs": waited for just before the first store into a peer
-  // Before the dependency wait: the batch metadata and the page statistics of the two pools.
-  // A launch that lets this one start early is one of this library's (only they release their
-  // dependents before they end), and none of them writes either: the metadata comes from the
-  // host, and the only statistics a selector or append launch writes are those of the newest
-  // token's page, which lies in the sliding window, outside both pools.  Everything else (the
-  // query first of all) is read after the wait.
+  // With LODA_SEL_CHAINED the caller guarantees that the launch before this one is a decode step of
+  // this library on the same batch metadata, complete before that launch began: the metadata and
+  // the page statistics of the two pools are then fetched before the dependency wait, while the
+  // previous launch drains (it writes neither: the only statistics a step writes are those of the
+  // newest token's page, which lies in the sliding window, outside both pools).  Without the flag
+  // nothing is read before the wait.  The query and everything else are always read after it.
+  const bool early = (S.flags & LODA_SEL_CHAINED) != 0;
+  if (!early) pdl_wait();
   const int nq = G * DSUB;
-  const long long act = B.active_req_ids[b];
-  const int len_raw = B.lengths[b];
-  const int req = (int)B.valid_req_ids[b];
-  const int length = act >= 0 ? len_raw : 0;
-  Regions rg = make_regions(g, length);
+  int length = B.lengths[b];
+  const int req = checked_request(g, B.active_req_ids[b], B.valid_req_ids[b], &length, status);
+  bool skip_far, skip_near;
+  load_skip_flags(L, req, &skip_far, &skip_near);
+  Regions rg = make_regions(g, length, skip_far, skip_near);
   rg.shard_rank = 0;          // this launch never serves a sequence-sharded geometry: the ownership
   rg.shard_count = 0;         // tests fold away
   const size_t pg0 = ((size_t)req * g.num_kv_heads + kv) * g.max_blocks;
@@ -175,22 +177,12 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   auto stage = [&](int it) {
     const int p0 = (rank + it * CS) * P;
     unsigned char* dst = rows + (size_t)(it & 1) * lay.rows_bytes;
-    if (it < tiles_per_cta && p0 < page_end) {
-      for (int c = tid; c < P * CPR; c += P) {
-        const int pl = c / CPR, cc = c % CPR;
-        const int page = p0 + pl;
-        if (in_far_pool(rg, page)) {
-          cp_async16(dst + (size_t)pl * ROWB + cc * 16, mm_base + (size_t)page * (4 * DSUB) + cc * 16, true);
-        } else if (cc < NC && in_near_pool(rg, page)) {
-          cp_async16(dst + (size_t)pl * ROWB + cc * 16, sum_base + (size_t)page * (2 * DSUB) + cc * 16, true);
-        }
-      }
-    }
+    if (it < tiles_per_cta && p0 < page_end) l1_stage_tile<DSUB, P, false>(g, rg, p0, dst, mm_base, sum_base);
     cp_async_commit();                                   // one group per tile index, empty when there is no tile
   };
   stage(0);
   stage(1);
-  pdl_wait();
+  if (early) pdl_wait();
   // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
   for (int i = tid; i < nq; i += P) {
     const int j = i / DSUB, d = i % DSUB;
@@ -229,8 +221,9 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
 
   if (rank == 2 && ap.enabled && tid < 32) {
     // The decode append of the row.  It touches only the newest token and its page, which lie
-    // in the sliding window and are read by neither level of this step; the attention kernel
-    // runs after this launch completes.
+    // in the sliding window and are read by neither level of this step.  The attention phase of
+    // this launch (and an attention launch after it) reads the token's K/V from global memory:
+    // the cluster barriers between here and there order these stores before those reads.
     append_row<DSUB>(g, L, B, ap.k_new, ap.v_new, ap.slots, ap.status, b, kv, tid);
   }
   const int32_t* table = L.block_table + (size_t)req * g.max_blocks;
@@ -504,7 +497,10 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   }
 }
 
-static bool g_fused_refused[3] = {false, false, false};    // per sub-space width: a launch failed, stay on the chain
+// Host state of the launch decision, kept per device ordinal: a refusal on one GPU or an occupancy
+// answer from one GPU says nothing about another.  (Host calls are single-threaded per device.)
+constexpr int kMaxDevices = 64;
+static bool g_fused_refused[kMaxDevices][3] = {};    // per sub-space width: a launch failed, stay on the chain
 
 static int fused_slot(int sub_dims) { return sub_dims == 16 ? 0 : sub_dims == 32 ? 1 : 2; }
 
@@ -525,8 +521,11 @@ bool select_fused_applicable(const loda_geometry& g, int rows) {
   const char* path = getenv("LODA_B200_SELECT_PATH");
   if (path && strcmp(path, "split") == 0) return false;
   if (g.sub_dims != 16 && g.sub_dims != 32 && g.sub_dims != 64) return false;
-  if (g_fused_refused[fused_slot(g.sub_dims)]) return false;
-  if (rows < 1 || rows * 8 > 148) return false;                              // one round of clusters of 8 at least
+  const int dev = device_ordinal();
+  if (dev < 0 || dev >= kMaxDevices || g_fused_refused[dev][fused_slot(g.sub_dims)]) return false;
+  if (rows < 1 || rows * 8 > device_sm_count()) return false;                // one round of clusters of 8 at least
+  // other level-1 methods and the numeric near-token quota run on the two-launch chain
+  if (g.far_method != LODA_FAR_MINMAX || g.near_minmax != 0 || g.near_tokens_p1 > 0) return false;
   if ((size_t)g.max_blocks * 2 + 16 > 40 * 1024) return false;
   return fused_shape_ok(g, 16) || fused_shape_ok(g, 8);
 }
@@ -555,7 +554,9 @@ static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, c
   // clusters of 16 CTAs when the GPU holds one for every row at once, else clusters of 8 (two tiles
   // per CTA at 128K tokens); the answers are remembered per shape
   struct Memo { size_t smem; int rows_ok; };
-  static Memo memo[3][2] = {};                           // (per instantiation of this template)
+  static Memo memo[kMaxDevices][3][2] = {};              // (per instantiation of this template)
+  const int dev = device_ordinal();
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorNotSupported;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -569,7 +570,7 @@ static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, c
   cfg.stream = st;
   for (int which = 0; which < 2; ++which) {
     const int cs = which == 0 ? 16 : 8;
-    if (!fused_shape_ok(g, cs) || rows * cs > 148) continue;
+    if (!fused_shape_ok(g, cs) || rows * cs > device_sm_count()) continue;
     if (D > 0 && !fused_attend_ok(g, cs)) continue;
     const int tpc = fused_tiles_per_cta(g, cs);
     const size_t smem = fused_layout(g, tpc, cs).total;
@@ -578,7 +579,7 @@ static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, c
     cfg.gridDim = dim3(cs, rows);
     cfg.dynamicSmemBytes = smem;
     attr[1].val.clusterDim.x = cs;
-    Memo& m = memo[fused_slot(DS)][which];
+    Memo& m = memo[dev][fused_slot(DS)][which];
     if (m.smem != smem) {
       int nclusters = 0;
       if (cudaOccupancyMaxActiveClusters(&nclusters, kernel, &cfg) != cudaSuccess) { (void)cudaGetLastError(); nclusters = 0; }
@@ -591,7 +592,10 @@ static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, c
   return cudaErrorNotSupported;
 }
 
-void select_fused_refuse(int sub_dims) { g_fused_refused[fused_slot(sub_dims)] = true; }
+void select_fused_refuse(int sub_dims) {
+  const int dev = device_ordinal();
+  if (dev >= 0 && dev < kMaxDevices) g_fused_refused[dev][fused_slot(sub_dims)] = true;
+}
 
 // cudaErrorNotSupported = the caller launches the two-kernel chain instead
 cudaError_t launch_select_fused(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,

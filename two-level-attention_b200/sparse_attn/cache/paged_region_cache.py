@@ -38,6 +38,8 @@ class RequestState:
     block_tables: list = field(default_factory=list)
     index_len: list = field(default_factory=list)     # tokens covered by the selector index, per layer
     index_live: list = field(default_factory=list)    # index maintained by the append kernel since built
+    skip_far_by_layer: list = field(default_factory=list)    # frozen per-layer region-skip decisions
+    skip_near_by_layer: list = field(default_factory=list)
     frozen: bool = False
 
 
@@ -118,6 +120,10 @@ class GraphReadyPagedRegionCache:
                                        INVALID_GATHER_IDX, torch.int32)
         self.visible_lens_buf = full((n_layers, max_requests, num_kv_heads), 0, torch.int32)
         self.status_buf = torch.zeros(1, dtype=torch.int32, device=device)
+        # frozen region-skip decisions [layer, request slot], read by the selector kernels on the device
+        # (reference: skip_far_layer_buf / skip_near_layer_buf, paged_region_cache.py:293-296)
+        self.skip_far_layer_buf = torch.zeros((n_layers, max_requests), dtype=torch.int32, device=device)
+        self.skip_near_layer_buf = torch.zeros((n_layers, max_requests), dtype=torch.int32, device=device)
         # pinned staging: one H2D copy per buffer per step
         self._cpu_block_table = torch.full((n_layers, max_requests, max_blocks), pad, dtype=torch.int32).pin_memory()
         self._cpu_slots = torch.full((n_layers, max_query_tokens), PAD_SLOT, dtype=torch.int32).pin_memory()
@@ -162,7 +168,10 @@ class GraphReadyPagedRegionCache:
             raise ValueError(f"request {request_id} already active")
         self.states[request_id] = RequestState(
             block_tables=[[] for _ in range(self.n_layers)],
-            index_len=[0] * self.n_layers, index_live=[False] * self.n_layers)
+            index_len=[0] * self.n_layers, index_live=[False] * self.n_layers,
+            skip_far_by_layer=[False] * self.n_layers, skip_near_by_layer=[False] * self.n_layers)
+        self.skip_far_layer_buf[:, request_id].zero_()
+        self.skip_near_layer_buf[:, request_id].zero_()
         self._cpu_block_table[:, request_id].fill_(self.layers[0].PAD_PAGE_ID)
         self.block_table_buf[:, request_id].fill_(self.layers[0].PAD_PAGE_ID)
         return request_id
@@ -231,22 +240,46 @@ class GraphReadyPagedRegionCache:
         return paged_write_prefill(layer, keys, values, self.block_table_buf[layer_idx, request_id])
 
     def freeze(self, request_id, skip_far_list=None, skip_near_list=None):
-        """End of prefill.  Region skipping is not implemented by the CUDA path:
-        any True entry raises FallbackRequired."""
+        """End of prefill: the per-layer region-skip decisions of the request become fixed
+        (reference: paged_region_cache.py:540-585; the gate policy that takes them is the caller's).
+        A skipped region is neither scored nor selected from by that layer's selector."""
         state = self.states[request_id]
+        skip_far_list = [False] * self.n_layers if skip_far_list is None else list(skip_far_list)
+        skip_near_list = [False] * self.n_layers if skip_near_list is None else list(skip_near_list)
+        if len(skip_far_list) != self.n_layers or len(skip_near_list) != self.n_layers:
+            raise ValueError("freeze expects per-layer skip decisions")
         if state.logical_length == 0:
             raise ValueError("prefill before freeze")
-        for flags in (skip_far_list, skip_near_list):
-            if flags is not None:
-                if len(flags) != self.n_layers:
-                    raise ValueError("freeze expects per-layer skip decisions")
-                if any(bool(x) for x in flags):
-                    raise FallbackRequired("near/far region skipping is not implemented")
         capacity_pages = (state.prompt_length + self.geometry.max_new_tokens
                           + self.geometry.page - 1) // self.geometry.page
         if capacity_pages > self.max_blocks:
             raise ValueError("prompt + max_new_tokens exceeds fixed block-table capacity")
+        state.skip_far_by_layer = [bool(x) for x in skip_far_list]
+        state.skip_near_by_layer = [bool(x) for x in skip_near_list]
+        self.skip_far_layer_buf[:, request_id] = torch.tensor(state.skip_far_by_layer, dtype=torch.int32)
+        self.skip_near_layer_buf[:, request_id] = torch.tensor(state.skip_near_by_layer, dtype=torch.int32)
         state.frozen = True
+
+    # -- region helpers (reference: paged_region_cache.py:589-618) -------------
+    def nfa_skip_signature(self, req_ids):
+        """Per batch row the frozen (skip_far, skip_near) pairs of every layer; None for padding rows."""
+        signature = []
+        for request_id in req_ids:
+            state = self.states.get(request_id) if request_id is not None and request_id >= 0 else None
+            signature.append(None if state is None
+                             else tuple(zip(state.skip_far_by_layer, state.skip_near_by_layer)))
+        return tuple(signature)
+
+    @staticmethod
+    def nfa_region_mode(signature, layer_idx):
+        """0 = mixed or nothing skipped, 1 = every live row skips far, 2 = near, 3 = both."""
+        modes = [item[layer_idx] for item in signature if item is not None]
+        if not modes or any(mode != modes[0] for mode in modes[1:]):
+            return 0
+        skip_far, skip_near = modes[0]
+        if skip_far and skip_near:
+            return 3
+        return 1 if skip_far else 2 if skip_near else 0
 
     # -- per-step planning (reference: plan_common / commit_step) -------------
     def plan_common(self, active_req_ids, query_lengths=None):
@@ -330,7 +363,8 @@ class GraphReadyPagedRegionCache:
         lo0, lo1, dsub = indexer.subspace_ranges()
         key = (lo0, lo1, dsub, int(indexer.args.tia_block_size), int(indexer.args.tia_level1_topk),
                int(indexer.nt_near_pages), int(indexer.args.tia_level2_topk), indexer.sink_tokens,
-               indexer.sliding_window_size, int(indexer.nt_near_len))
+               indexer.sliding_window_size, int(indexer.nt_near_len), indexer.nt_near_tokens,
+               indexer.far_method, indexer.near_method)
         if self._runtime is not None:
             if self._runtime.key != key:
                 raise ValueError("one cache serves one selector configuration")
@@ -365,7 +399,13 @@ class SelectorRuntime:
             max_visible=cache.max_visible_len, k_far=min(max(0, k1 - nb_near), cache.max_blocks),
             k_near=min(nb_near, cache.max_blocks), level2_topk=int(indexer.args.tia_level2_topk),
             sink=indexer.sink_tokens, swa=indexer.sliding_window_size, near_len=cache.geometry.near,
-            pool_near_len=max(page, int(indexer.nt_near_len)))
+            pool_near_len=max(page, int(indexer.nt_near_len)),
+            near_tokens_p1=0 if indexer.nt_near_tokens is None else int(indexer.nt_near_tokens) + 1,
+            far_method={"minmax": _capi.FAR_MINMAX, "avg": _capi.FAR_AVG, "avg_top2": _capi.FAR_AVG_TOP2}[
+                indexer.far_method],
+            near_minmax=1 if indexer.near_method == "minmax" else 0)
+        if indexer.nt_near_tokens is not None and int(indexer.nt_near_len) != cache.geometry.near:
+            raise FallbackRequired("the numeric near-token quota needs nfa_near_len == RegionGeometry.near")
         self.geometry = g
         lib = _capi.lib()
         nbytes = lib.loda_workspace_bytes(C.byref(g))
@@ -393,7 +433,9 @@ class SelectorRuntime:
                 pool_k=layer.kv_pool_k.data_ptr(), pool_v=layer.kv_pool_v.data_ptr(),
                 page_mm=layer.page_mm.data_ptr(), page_sum=layer.page_sum.data_ptr(),
                 tail_code=layer.tail_code.data_ptr(), tail_sz=layer.tail_sz.data_ptr(),
-                block_table=cache.block_table_buf[li].data_ptr()))
+                block_table=cache.block_table_buf[li].data_ptr(),
+                skip_far=cache.skip_far_layer_buf[li].data_ptr(),
+                skip_near=cache.skip_near_layer_buf[li].data_ptr()))
         self.cache = cache
 
     def batch_struct(self, batch):
@@ -402,11 +444,13 @@ class SelectorRuntime:
                            valid_req_ids=c.valid_req_ids_buf.data_ptr(),
                            active_req_ids=c.active_req_ids_buf.data_ptr())
 
-    def selection_struct(self, gather, visible_lens, with_middle=True, with_page_lists=True):
+    def selection_struct(self, gather, visible_lens, with_middle=True, with_page_lists=True, chained=False):
         """`with_page_lists` / `with_middle` add the optional diagnostic outputs
-        (best-first page lists, L2 survivors before the union)."""
+        (best-first page lists, L2 survivors before the union).  `chained`: the call directly follows
+        a decode step of this library on the same batch metadata (LODA_SEL_CHAINED)."""
         pl = with_page_lists
         return _capi.Selection(
+            flags=_capi.SEL_CHAINED if chained else 0,
             i_far=self.i_far.data_ptr() if pl else None, n_far=self.n_far.data_ptr() if pl else None,
             i_near=self.i_near.data_ptr() if pl else None, n_near=self.n_near.data_ptr() if pl else None,
             gather=gather.data_ptr(), visible_lens=visible_lens.data_ptr(),

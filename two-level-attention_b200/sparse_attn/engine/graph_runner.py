@@ -38,8 +38,9 @@ class DecodeGraphRunner:
         cache = self.cache
         for li, attention in enumerate(self.attentions):
             slots = cache.slot_mapping_for_layer(li)[:self.batch]
+            # every layer but the first directly follows the decode step of the layer before it
             decode_step_fused(cache, li, req_ids, self.q[li], attention, (self.k[li], self.v[li], slots),
-                              out=self.out[li])
+                              out=self.out[li], chained=li > 0)
 
     def capture(self, req_ids):
         """One eager step (builds the index of fresh prefills, warms every launch),

@@ -77,10 +77,8 @@ class NFAIndexer:
 
     # -- what the CUDA path implements -------------------------------------
     def require_supported(self):
-        if self.far_method != "minmax" or self.near_method != "avg":
-            raise FallbackRequired("CUDA path implements far=minmax, near=avg")
-        if self.nt_near_tokens is not None:
-            raise FallbackRequired("numeric nfa_near_tokens quota is not implemented (use 'off')")
+        if self.far_method not in ("minmax", "avg", "avg_top2") or self.near_method not in ("avg", "minmax"):
+            raise FallbackRequired("CUDA path implements far in {minmax, avg, avg_top2}, near in {avg, minmax}")
         if not self.enable_subspace or self.l2_subspace != "same":
             raise FallbackRequired("CUDA path scores L1 and L2 on the same proper subspace")
         self.subspace_ranges()

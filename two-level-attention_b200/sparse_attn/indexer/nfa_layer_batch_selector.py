@@ -125,9 +125,11 @@ def last_middle_selection(cache, batch):
     return TokenSelection(rt.middle[:batch], rt.middle_counts[:batch])
 
 
-def decode_step_fused(cache, layer_idx, req_ids, query_states, attention, decode_write, out=None):
+def decode_step_fused(cache, layer_idx, req_ids, query_states, attention, decode_write, out=None, chained=False):
     """append + L1 + L2 + gather attention of one layer through the single
-    C entry point ``loda_decode_step``; returns the attention output [B, HQ, DV]."""
+    C entry point ``loda_decode_step``; returns the attention output [B, HQ, DV].
+    chained=True promises that this call directly follows the same call for another layer of the
+    same step on the same stream (LODA_SEL_CHAINED in include/loda_b200.h)."""
     b = len(req_ids)
     indexer = attention.indexer
     rt = cache.ensure_index(indexer)
@@ -142,7 +144,7 @@ def decode_step_fused(cache, layer_idx, req_ids, query_states, attention, decode
     batch = rt.batch_struct(b)
     diag = bool(getattr(cache, "selector_diagnostics", False))
     sel = rt.selection_struct(cache.gather_indices_for_layer(layer_idx), cache.visible_lens_for_layer(layer_idx),
-                              with_middle=diag, with_page_lists=diag)
+                              with_middle=diag, with_page_lists=diag, chained=chained)
     _capi.check(_capi.lib().loda_decode_step(
         C.byref(rt.geometry), C.byref(rt.layer_structs[layer_idx]), C.byref(batch), _capi.ptr(q),
         _capi.ptr(k), _capi.ptr(v), _capi.ptr(slots), float(attention.scaling), C.byref(sel),

@@ -16,7 +16,7 @@ from .sparse_attn.policies import region_geometry as geo_mod
 
 def make_setup(lengths, *, seed=0, page=16, hq=32, hkv=8, d=128, n_layers=1, max_visible=1024,
                shuffle_pages=True, extra_blocks=4, selector_overrides=None, max_requests=None,
-               device="cuda:0"):
+               device="cuda:0", skip_states=None):
     """Create a cache, prefill every request with `length - 1` synthetic tokens
     (seeded, generated on the CPU), and return the decode inputs of the last
     token of each request."""
@@ -49,7 +49,8 @@ def make_setup(lengths, *, seed=0, page=16, hq=32, hkv=8, d=128, n_layers=1, max
                 kk = case.k[:n_pre].permute(1, 0, 2)[None].to(dev)
                 vv = case.v[:n_pre].permute(1, 0, 2)[None].to(dev)
                 cache.write_prefill(li, rid, kk, vv, physical_pages=pages if li == 0 else None)
-            cache.freeze(rid)
+            sf, sn = (False, False) if skip_states is None else skip_states[i]
+            cache.freeze(rid, [sf] * n_layers, [sn] * n_layers)
         cases.append(case)
         req_ids.append(rid)
     attention = SimpleNamespace(indexer=indexer, scaling=float(d) ** -0.5, layer_idx=0)
@@ -58,4 +59,5 @@ def make_setup(lengths, *, seed=0, page=16, hq=32, hkv=8, d=128, n_layers=1, max
     v_new = torch.stack([c.v[c.length - 1] for c in cases])[:, :, None].to(dev)
     return SimpleNamespace(cache=cache, cases=cases, req_ids=req_ids, attention=attention, q=q,
                            k_new=k_new, v_new=v_new, lengths=list(lengths), dev=dev, indexer=indexer,
-                           args=args, page=page, max_blocks=max_blocks, max_visible=max_visible)
+                           args=args, page=page, max_blocks=max_blocks, max_visible=max_visible,
+                           skip_states=skip_states)
