@@ -171,14 +171,102 @@ def make_arch(reference):
     np.savez_compressed(os.path.join(HERE, "arch_tli.npz"), **out)
 
 
+def make_tls(reference):
+    """Outputs of the PyTorch reference functions the reference ships beside its tls_attn operators
+    (tls_attn/ops: MHAStoreKIndexReference mha_store_k_index.py:188-310, ref_indexer_topk
+    mha_indexer_level1.py:252-276 and mha_indexer_level2.py:293-402, ref_attn sparse_mha.py:199-232),
+    with their inputs.  The two ref_indexer_topk functions are called one batch row (and one KV head)
+    at a time: written for the single-row, single-head shapes of the reference's own checks, they
+    apply row i's sliding mask to every row and the last head's sliding entries only."""
+    sys.path.insert(0, reference)
+    from tls_attn.ops.mha_indexer_level1 import ref_indexer_topk as ref_l1
+    from tls_attn.ops.mha_indexer_level2 import ref_indexer_topk as ref_l2
+    from tls_attn.ops.mha_store_k_index import MHAStoreKIndexReference as RefIndex
+    from tls_attn.ops.sparse_mha import ref_attn
+    out = {}
+    # ---- store K index: prefill, then decode ----
+    g = torch.Generator().manual_seed(1)
+    max_b, max_s, hkv, d, block, cmp, b, s = 4, 256, 2, 128, 16, 4, 3, 200
+    k = torch.randn(b, s, hkv, d, generator=g).bfloat16()
+    offsets = torch.tensor([0, 9, 150], dtype=torch.int32)
+    l1min = torch.zeros(max_b, max_s // block, hkv, d, dtype=torch.bfloat16)
+    l1max = torch.zeros_like(l1min)
+    l2k = torch.zeros(max_b, max_s, hkv, d // cmp, dtype=torch.bfloat16)
+    RefIndex.prefill_forward(k, offsets, l1min, l1max, l2k, block, cmp)
+    out.update(ix_k=bits(k), ix_offsets=offsets.numpy(), ix_l1min=bits(l1min), ix_l1max=bits(l1max), ix_l2k=bits(l2k))
+    kc = torch.randn(max_b, max_s, hkv, d, generator=g).bfloat16()
+    lengths = torch.tensor([208, 37, 51], dtype=torch.int32)
+    RefIndex.decode_forward(kc, lengths, l1min, l1max, l2k, block, cmp)
+    out.update(ix_kc=bits(kc), ix_lengths=lengths.numpy(), ix_l1min_dec=bits(l1min), ix_l1max_dec=bits(l1max),
+               ix_l2k_dec=bits(l2k), ix_shape=np.array([max_b, max_s, hkv, d, block, cmp]))
+    # ---- level 1 ----
+    g = torch.Generator().manual_seed(2)
+    b, hq, hkv, d, topk, sliding, nblk = 3, 8, 2, 128, 16, 3, 160
+    lengths = torch.tensor([150, 12, 90, 4], dtype=torch.int32)
+    q = torch.randn(b, 1, hq, d, generator=g).bfloat16()
+    kmin = (torch.randn(4, nblk, hkv, d, generator=g) - 1).bfloat16()
+    kmax = (torch.randn(4, nblk, hkv, d, generator=g) + 1).bfloat16()
+    scores = torch.full((b, hkv, nblk), float("-inf"))
+    tk = torch.full((b, hkv, topk), -1, dtype=torch.int64)
+    for i in range(b):
+        n = int(lengths[i])
+        sc, _, ti = ref_l1(q[i:i + 1, 0].float(), kmin[i:i + 1, :n].float(), kmax[i:i + 1, :n].float(),
+                           lengths[i:i + 1], min(topk, n), sliding)
+        scores[i, :, :n] = sc[0]
+        valid = torch.isfinite(sc[0].gather(-1, ti[0]))
+        tk[i, :, :ti.shape[-1]] = torch.where(valid, ti[0], -1)
+    out.update(l1_q=bits(q), l1_kmin=bits(kmin), l1_kmax=bits(kmax), l1_lengths=lengths.numpy(),
+               l1_scores=scores.numpy(), l1_topk=tk.numpy().astype(np.int32),
+               l1_shape=np.array([b, hq, hkv, d, topk, sliding, nblk]))
+    # ---- level 2 ----
+    g = torch.Generator().manual_seed(4)
+    b, hq, hkv, dsub, block, k1, k2, sliding, s = 2, 8, 2, 32, 16, 6, 64, 2, 512
+    gs = hq // hkv
+    lengths = torch.tensor([500, 333, 77], dtype=torch.int32)
+    q = torch.randn(b, 1, hq, dsub, generator=g).bfloat16()
+    k = torch.randn(3, s, hkv, dsub, generator=g).bfloat16()
+    bi = torch.tensor([[[3, 0, 7, -1, 12, 20], [1, 2, -1, -1, 9, 4]],
+                       [[5, 6, 0, 2, -1, 10], [-1, -1, -1, -1, -1, -1]]], dtype=torch.int32)
+    width = (k1 + sliding) * block
+    sc_all = torch.full((b, hkv, width), float("-inf"))
+    ix_all = torch.full((b, hkv, width), -1, dtype=torch.int64)
+    tk_all = torch.full((b, hkv, k2), -1, dtype=torch.int64)
+    for i in range(b):
+        for h in range(hkv):
+            sc, ix, ts, ti = ref_l2(q[i:i + 1, 0, h * gs:(h + 1) * gs].float(), k[i:i + 1, :, h:h + 1].float(),
+                                    bi[i:i + 1, h:h + 1], lengths[i:i + 1], block, sliding, k2)
+            sc_all[i, h], ix_all[i, h] = sc[0, 0], ix[0, 0]
+            tk_all[i, h] = torch.where(torch.isinf(ts[0, 0]) & (ts[0, 0] < 0), -1, ti[0, 0])
+    out.update(l2_q=bits(q), l2_k=bits(k), l2_bi=bi.numpy(), l2_lengths=lengths.numpy(), l2_scores=sc_all.numpy(),
+               l2_indices=ix_all.numpy().astype(np.int32), l2_topk=tk_all.numpy().astype(np.int32),
+               l2_shape=np.array([b, hq, hkv, dsub, block, k1, k2, sliding, s]))
+    # ---- sparse attention over chosen tokens ----
+    g = torch.Generator().manual_seed(6)
+    b, s, hq, hkv, d, topk = 2, 300, 8, 2, 128, 96
+    q = torch.randn(b, 1, hq, d, generator=g).bfloat16()
+    k = torch.randn(b, s, hkv, d, generator=g).bfloat16()
+    v = torch.randn(b, s, hkv, d, generator=g).bfloat16()
+    idx = torch.stack([torch.stack([torch.randperm(s, generator=g)[:topk].sort().values for _ in range(hkv)])
+                       for _ in range(b)]).int()
+    idx[0, 1, 10:40] = -1
+    o = ref_attn(q[:, 0].float(), k.float(), v.float(), idx.long())
+    out.update(at_q=bits(q), at_k=bits(k), at_v=bits(v), at_idx=idx.numpy(), at_out=o.numpy())
+    np.savez_compressed(os.path.join(HERE, "tls_ref.npz"), **out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="root of a checkout of the reference project")
+    ap.add_argument("--only", default=None, help="tls: regenerate tls_ref.npz alone")
     a = ap.parse_args()
+    if a.only == "tls":
+        make_tls(a.reference)
+        return
     ix = tia(a.reference)
     make_quant(ix)
     make_tia_index(ix)
     make_paged_ops(a.reference)
+    make_tls(a.reference)
     make_arch(a.reference)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):

@@ -200,3 +200,96 @@ def test_level2_scores_topk_tokens_and_the_chain_into_sparse_attention():
             p = torch.softmax(qf[i, 0, h * gsz:(h + 1) * gsz].double() @ kf[i, t, h].double().T * 128 ** -0.5, dim=-1)
             torch.testing.assert_close(out[i, 0, h * gsz:(h + 1) * gsz].double().cpu(), p @ v[i, t, h].double(),
                                        atol=2e-2, rtol=2e-2)
+
+
+# ---------------------------------------------------------------------------
+# The same operators against outputs of the reference's own PyTorch reference functions
+# (tests/golden/tls_ref.npz, made by tests/golden/make_golden.py from MHAStoreKIndexReference,
+# the two ref_indexer_topk and ref_attn of tls_attn/ops).
+# ---------------------------------------------------------------------------
+def _bf16(g, name):
+    from oracle import loda_oracle as O
+    return torch.from_numpy(O.bits_to_f32(g[name])).bfloat16()
+
+
+def _same_topk_up_to_ties(got, want, score_of, tol):
+    """Two top-k id sets agree except where the scores around the cut differ by less than tol."""
+    got, want = set(int(x) for x in got if x >= 0), set(int(x) for x in want if x >= 0)
+    if got == want:
+        return True
+    if len(got) != len(want):
+        return False
+    cut = min(score_of(t) for t in want)
+    return all(abs(score_of(t) - cut) < tol for t in got ^ want)
+
+
+def test_store_k_index_equals_the_reference_class_outputs():
+    from conftest import golden
+    ops = _ops()
+    g = golden("tls_ref.npz")
+    max_b, max_s, hkv, d, block, cmp = (int(x) for x in g["ix_shape"])
+    ix = ops.MHAStoreKIndexInterface(max_b, max_s, hkv, d, block, cmp)
+    l1min = torch.zeros(max_b, max_s // block, hkv, d, dtype=torch.bfloat16, device=DEV)
+    l1max = torch.zeros_like(l1min)
+    l2k = torch.zeros(max_b, max_s, hkv, d // cmp, dtype=torch.bfloat16, device=DEV)
+    ix.prefill_forward(_bf16(g, "ix_k").to(DEV), torch.from_numpy(g["ix_offsets"]).to(DEV), l1min, l1max, l2k)
+    assert torch.equal(l1min.cpu(), _bf16(g, "ix_l1min")) and torch.equal(l1max.cpu(), _bf16(g, "ix_l1max"))
+    assert torch.equal(l2k.cpu(), _bf16(g, "ix_l2k"))
+    ix.decode_forward(_bf16(g, "ix_kc").to(DEV), torch.from_numpy(g["ix_lengths"]).to(DEV), l1min, l1max, l2k)
+    assert torch.equal(l1min.cpu(), _bf16(g, "ix_l1min_dec")) and torch.equal(l1max.cpu(), _bf16(g, "ix_l1max_dec"))
+    assert torch.equal(l2k.cpu(), _bf16(g, "ix_l2k_dec"))
+
+
+def test_level1_equals_ref_indexer_topk_outputs():
+    from conftest import golden
+    ops = _ops()
+    g = golden("tls_ref.npz")
+    b, hq, hkv, d, topk, sliding, nblk = (int(x) for x in g["l1_shape"])
+    lengths = torch.from_numpy(g["l1_lengths"])
+    l1 = ops.MHAIndexerLevel1Interface(hq, hkv, d, topk, sliding)
+    scores, _, tk_i = l1.forward(_bf16(g, "l1_q").to(DEV), _bf16(g, "l1_kmin").to(DEV), _bf16(g, "l1_kmax").to(DEV),
+                                 lengths.to(DEV))
+    want = torch.from_numpy(g["l1_scores"])[..., :scores.shape[-1]]
+    got = scores[:b].float().cpu()
+    fin = torch.isfinite(want)
+    assert torch.equal(torch.isfinite(got), fin)
+    # the reference function keeps q * scale in fp32, the operator rounds it to bf16 like the reference's kernel
+    torch.testing.assert_close(got[fin], want[fin], atol=5e-2, rtol=5e-3)
+    for i in range(b):
+        for h in range(hkv):
+            assert _same_topk_up_to_ties(tk_i[i, h].cpu().tolist(), g["l1_topk"][i, h].tolist(),
+                                         lambda t: float(want[i, h, t]), 0.1), (i, h)
+
+
+def test_level2_equals_ref_indexer_topk_outputs():
+    from conftest import golden
+    ops = _ops()
+    g = golden("tls_ref.npz")
+    b, hq, hkv, dsub, block, k1, k2, sliding, s = (int(x) for x in g["l2_shape"])
+    l2 = ops.MHAIndexerLevel2Interface(hq, hkv, dsub, k1, k2, block, sliding)
+    scores, indices, _, tk_i = l2.forward(_bf16(g, "l2_q").to(DEV), _bf16(g, "l2_k").to(DEV),
+                                          torch.from_numpy(g["l2_bi"]).to(DEV), torch.from_numpy(g["l2_lengths"]).to(DEV))
+    n = k1 * block
+    want_s, want_i = torch.from_numpy(g["l2_scores"])[..., :n], torch.from_numpy(g["l2_indices"])[..., :n]
+    assert torch.equal(indices[:b].cpu().int(), want_i)
+    got = scores[:b].float().cpu()
+    fin = torch.isfinite(want_s)
+    assert torch.equal(torch.isfinite(got), fin)
+    torch.testing.assert_close(got[fin], want_s[fin], atol=1e-4, rtol=3e-2)
+    full_s, full_i = torch.from_numpy(g["l2_scores"]), torch.from_numpy(g["l2_indices"])
+    for i in range(b):
+        for h in range(hkv):
+            score_of = {int(t): float(sc) for t, sc in zip(full_i[i, h].tolist(), full_s[i, h].tolist()) if t >= 0}
+            assert _same_topk_up_to_ties(tk_i[i, h].cpu().tolist(), g["l2_topk"][i, h].tolist(),
+                                         lambda t: min(score_of.get(t, -1e30), 1e30), 0.05), (i, h)
+
+
+def test_sparse_mha_equals_ref_attn_output():
+    from conftest import golden
+    ops = _ops()
+    g = golden("tls_ref.npz")
+    q, k, v = _bf16(g, "at_q"), _bf16(g, "at_k"), _bf16(g, "at_v")
+    idx = torch.from_numpy(g["at_idx"])
+    att = ops.SparseMHAInterface(q.shape[2], k.shape[2], q.shape[3], v.shape[3], idx.shape[-1])
+    out = att.forward(q.to(DEV), k.to(DEV), v.to(DEV), idx.to(DEV))
+    torch.testing.assert_close(out[:, 0].float().cpu(), torch.from_numpy(g["at_out"]), atol=2e-2, rtol=2e-2)
