@@ -17,8 +17,11 @@ from ..indexer.nfa_layer_batch_selector import decode_step_fused
 
 
 class DecodeGraphRunner:
-    def __init__(self, cache, attentions, batch):
-        """attentions: one object per layer with .indexer, .scaling, .layer_idx."""
+    def __init__(self, cache, attentions, batch, after_layer=None):
+        """attentions: one object per layer with .indexer, .scaling, .layer_idx.
+        after_layer(layer_idx, out): optional work captured behind a layer's attention (the all-gather of the
+        heads' outputs when the KV heads are split over several GPUs)."""
+        self.after_layer = after_layer
         if len(attentions) != cache.n_layers:
             raise ValueError("one attention module per cache layer")
         self.cache, self.attentions, self.batch = cache, attentions, batch
@@ -40,7 +43,9 @@ class DecodeGraphRunner:
             slots = cache.slot_mapping_for_layer(li)[:self.batch]
             # every layer but the first directly follows the decode step of the layer before it
             decode_step_fused(cache, li, req_ids, self.q[li], attention, (self.k[li], self.v[li], slots),
-                              out=self.out[li], chained=li > 0)
+                              out=self.out[li], chained=li > 0 and self.after_layer is None)
+            if self.after_layer is not None:
+                self.after_layer(li, self.out[li])
 
     def capture(self, req_ids):
         """One eager step (builds the index of fresh prefills, warms every launch),
