@@ -361,7 +361,7 @@ def measure_device(torch, capi, lib, wl, W, K, barrier, after_layer=None, kernel
         e1.record(stream)
     stream.synchronize()
     one_ms = max(e0.elapsed_time(e1), 1e-3)
-    replays = max(1, min(2000, int(min_timed_s * 1e3 / one_ms) + 1))
+    replays = max(1, min(2000, int(1.1 * min_timed_s * 1e3 / one_ms) + 2))
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
     barrier()
     with torch.cuda.stream(stream):
@@ -638,7 +638,8 @@ def reference_triton_arm(torch, dev, budget_s=240.0):
                 chain()
             e1.record()
             torch.cuda.synchronize()
-            entry = {"layers": layers, "eager_us_per_layer": e0.elapsed_time(e1) * 1e3 / (5 * layers)}
+            entry = {"layers": layers, "eager_us_per_layer": e0.elapsed_time(e1) * 1e3 / (5 * layers),
+                     "eager_is": "steady state of the reference's eager launch plans (its fast path outside a graph)"}
             try:
                 graph = torch.cuda.CUDAGraph()
                 outs.clear()
@@ -652,6 +653,9 @@ def reference_triton_arm(torch, dev, budget_s=240.0):
                 e1.record()
                 torch.cuda.synchronize()
                 entry["graph_us_per_layer"] = e0.elapsed_time(e1) * 1e3 / (20 * layers)
+                entry["graph_note"] = ("capture of the bare selector call: under capture the reference takes its full "
+                                       "path, whose page-statistics pass covers every block on each replay; its engine "
+                                       "captures the whole model step instead")
             except Exception as exc:      # noqa: BLE001
                 entry["graph_us_per_layer"] = None
                 entry["graph_note"] = f"{type(exc).__name__}: {exc}"[:200]

@@ -42,6 +42,7 @@ extern "C" {
 #define LODA_STATUS_BAD_PAGE 2u
 #define LODA_STATUS_TRUNCATED 4u
 #define LODA_STATUS_BAD_REQ 8u   /* an active row's request slot is outside [0, max_requests): treated as a padding row */
+#define LODA_STATUS_TIMEOUT 16u  /* a bounded wait on an asynchronous copy gave up (the row's result is not valid) */
 
 /* Static geometry of one attention layer's cache and selector.
  * Mirrors GraphReadyPagedRegionCache.__init__ (sparse_attn/cache/
@@ -89,10 +90,16 @@ typedef struct loda_geometry {
 /* Per-layer device buffers.
  *   pool_k / pool_v  [num_pages, num_kv_heads, page, head_dim(_v)]   (the
  *        reference arena [pages+1, 1, Hkv, PAGE, D], paged_region_cache.py:89-98)
- *   page_mm   [max_requests, num_kv_heads, max_blocks, 2, d']  per logical page:
- *        min then max of the subspace keys over the visible tokens
- *   page_sum  [max_requests, num_kv_heads, max_blocks, d']     sum of the same
- *        (replace P_MIN / P_MAX / P_SUM, nfa_layer_batch_selector.py:2103-2118)
+ *   page_mm   per (request slot, kv head) row the min and the max of the subspace keys over the visible
+ *        tokens of every logical page; page_sum: the sum of the same (replace P_MIN / P_MAX / P_SUM,
+ *        nfa_layer_batch_selector.py:2103-2118).  Layout of a row: the logical pages in groups of 32;
+ *        a group stores 16-byte chunk c of its 32 pages, then chunk c + 1, ... — for page_mm the d'/8
+ *        chunks of the min row followed by the d'/8 chunks of the max row (d'/4 chunks, 128 d' bytes per
+ *        group), for page_sum d'/8 chunks (64 d' bytes per group).  Byte offset of chunk c of page p in a
+ *        row: ((p / 32) * CH + c) * 512 + (p % 32) * 16 with CH chunks per page; a row has
+ *        ceil(max_blocks / 32) groups; rows follow each other [max_requests, num_kv_heads].  (32 threads
+ *        reading one chunk of 32 consecutive pages read 512 contiguous bytes, and a run of groups is one
+ *        contiguous block for a bulk copy.)
  *   tail_code [num_pages, num_kv_heads, page, d'/2] bytes: two 4-bit codes per
  *        byte, dim 2i in the low nibble
  *   tail_sz   [num_pages, num_kv_heads, page, 2]: quantisation scale and zero

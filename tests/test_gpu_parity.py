@@ -50,8 +50,10 @@ def _check_against_oracle(setup, out):
     i_far, n_far = rt.i_far.cpu().numpy(), rt.n_far.cpu().numpy()
     i_near, n_near = rt.i_near.cpu().numpy(), rt.n_near.cpu().numpy()
     middle, mcount = rt.middle.cpu().numpy(), rt.middle_counts.cpu().numpy()
-    mm = bf16_to_f32_np(layer.page_mm)
-    psum = bf16_to_f32_np(layer.page_sum)
+    from helpers import mod
+    cache_mod = mod("sparse_attn.cache.paged_region_cache")
+    mm = bf16_to_f32_np(cache_mod.page_minmax_by_page(layer))
+    psum = bf16_to_f32_np(cache_mod.page_sum_by_page(layer))
     code = layer.tail_code.cpu().numpy()
     sz = bf16_to_f32_np(layer.tail_sz)
     for b, rid in enumerate(setup.req_ids):

@@ -64,15 +64,11 @@ __global__ void __launch_bounds__(32 * WARPS) build_index_kernel(
       sz[1] = __float2bfloat16_rn(qo.zero);
     }
   }
-  const size_t pg = ((size_t)req * g.num_kv_heads + kv) * g.max_blocks + blk;
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const int d = lane + 32 * j;
     if (d >= DSUB) continue;
-    bf16* mm = (bf16*)L.page_mm + pg * 2 * DSUB;
-    mm[d] = __float2bfloat16_rn(mn[j]);
-    mm[DSUB + d] = __float2bfloat16_rn(mx[j]);
-    ((bf16*)L.page_sum)[pg * DSUB + d] = __float2bfloat16_rn(sum[j]);
+    store_page_stats<DSUB>(g, L, req, kv, blk, d, mn[j], mx[j], sum[j]);
   }
 }
 

@@ -58,6 +58,22 @@ __device__ __forceinline__ void warp_store_codes(const uint32_t (&code)[(DSUB + 
   }
 }
 
+// Store min / max / sum of subspace dim d of logical page blk of (request slot req, kv head kv)
+// into the interleaved statistics layout (STAT_GROUP in loda_common.cuh): dim d lives in 16-byte
+// chunk d / 8 of the page's min row, chunk d' / 8 + d / 8 of its max row, chunk d / 8 of its sum row.
+template <int DSUB>
+__device__ __forceinline__ void store_page_stats(const loda_geometry& g, const loda_layer& L, int req, int kv, int blk,
+                                                 int d, float mn, float mx, float sum) {
+  constexpr int NC = DSUB / 8, CPR = 2 * NC;
+  const size_t rowi = (size_t)req * g.num_kv_heads + kv;
+  unsigned char* mm_row = (unsigned char*)L.page_mm + rowi * stat_row_bytes(g.max_blocks, CPR);
+  unsigned char* sum_row = (unsigned char*)L.page_sum + rowi * stat_row_bytes(g.max_blocks, NC);
+  const int c = d / 8, e = d % 8;
+  *(bf16*)(mm_row + stat_chunk_offset(blk, c, CPR) + e * 2) = __float2bfloat16_rn(mn);
+  *(bf16*)(mm_row + stat_chunk_offset(blk, NC + c, CPR) + e * 2) = __float2bfloat16_rn(mx);
+  *(bf16*)(sum_row + stat_chunk_offset(blk, c, NC) + e * 2) = __float2bfloat16_rn(sum);
+}
+
 // Append (or refresh) one (row, kv head) with one warp.
 template <int DSUB>
 __device__ __forceinline__ void append_row(
@@ -160,11 +176,7 @@ __device__ __forceinline__ void append_row(
     mn = fminf(mn, x[j]);
     mx = fmaxf(mx, x[j]);
     sum = __fadd_rn(sum, x[j]);
-    const size_t pg = ((size_t)req * g.num_kv_heads + kv) * g.max_blocks + blk;
-    bf16* mm = (bf16*)L.page_mm + pg * 2 * DSUB;
-    mm[d] = __float2bfloat16_rn(mn);
-    mm[DSUB + d] = __float2bfloat16_rn(mx);
-    ((bf16*)L.page_sum)[pg * DSUB + d] = __float2bfloat16_rn(sum);
+    store_page_stats<DSUB>(g, L, req, kv, blk, d, mn, mx, sum);
   }
 }
 

@@ -737,10 +737,10 @@ __device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, i
 
 // (3) large n, small k (k <= 128): a cheap lower bound on the k-th largest score
 // discards almost everything, the survivors are ranked exactly.  The chunks of
-// the row are dealt round-robin to the threads, the threads form 128 groups;
-// the k-th largest of the 128 group maxima is a lower bound of the k-th largest
+// the row are dealt round-robin to the threads, the threads form 256 groups;
+// the k-th largest of the 256 group maxima is a lower bound of the k-th largest
 // score (k groups each hold a score at or above it).  Scores at or above the
-// bound (about 1.5-2 k of them for unclustered scores) are compacted in index
+// bound (about 1.5 k of them for unclustered scores) are compacted in index
 // order and ranked against each other.  Returns -1 without writing anything
 // when more than 2 NT survive (heavily tied or sorted scores): the caller then
 // bisects.  keys: 2 NT + 8 words (16-byte aligned); wtot: 64 ints; sh: 2 ints.
@@ -750,8 +750,11 @@ __device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, i
 template <int NT, int BAR = 0, int TBASE = 0, bool HIST = false>
 __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, int k, int* out, uint32_t* keys,
                                                     int* wtot, int* sh, const uint32_t* hist = nullptr) {
-  static_assert(NT % 128 == 0 && NT / 128 <= 32, "group layout");
-  constexpr int NG = 128;                        // groups
+  static_assert(NT % 256 == 0 && NT / 256 <= 32, "group layout");
+  // 256 groups: the k-th largest of the group maxima is the tighter a bound the more groups there are
+  // (k <= 128 of the best scores fall into ~k (1 - k / 512) distinct groups of 256, so about 1.5 k scores
+  // survive; with 128 groups it was 1.5 k scores for k = 96), and ranking 256 maxima is still cheap
+  constexpr int NG = 256;                        // groups
   constexpr int GS = NT / NG;                    // threads per group
   constexpr int NW = NT / 32;
   const int tid = ((int)threadIdx.x - TBASE), lane = tid & 31, warp = tid >> 5;
@@ -871,8 +874,58 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
 }
 
 // ---------------------------------------------------------------------------
+// Layout of the page statistics (page_mm, page_sum) of one (request, kv head) row: the logical
+// pages are taken in groups of 32; inside a group the 16-byte chunks of the pages are stored chunk
+// by chunk — chunk c of the 32 pages, then chunk c + 1 — so that 32 threads reading chunk c of 32
+// consecutive pages touch one contiguous 512-byte run (coalesced in global memory, conflict-free in
+// shared memory), and any run of whole groups is one contiguous block that a single bulk copy moves.
+// CH = chunks per page: d' / 4 for page_mm (min then max), d' / 8 for page_sum.
+// ---------------------------------------------------------------------------
+constexpr int STAT_GROUP = 32;
+__host__ __device__ __forceinline__ size_t stat_group_bytes(int CH) { return (size_t)STAT_GROUP * CH * 16; }
+__host__ __device__ __forceinline__ size_t stat_row_bytes(int max_blocks, int CH) {
+  return (size_t)((max_blocks + STAT_GROUP - 1) / STAT_GROUP) * stat_group_bytes(CH);
+}
+__host__ __device__ __forceinline__ size_t stat_chunk_offset(int page, int c, int CH) {
+  return ((size_t)(page / STAT_GROUP) * CH + c) * (STAT_GROUP * 16) + (size_t)(page % STAT_GROUP) * 16;
+}
+
+// ---------------------------------------------------------------------------
 // async copy
 // ---------------------------------------------------------------------------
+// Bulk asynchronous copy global -> shared memory of this CTA, completion counted in bytes on an
+// mbarrier (both addresses and the size are multiples of 16 bytes).  Plain copies of this GPU's own
+// memory only: no multicast.
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(arrivals) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
+// Wait for a phase of the barrier, bounded: every try_wait suspends the thread for a while, and
+// after MBAR_WAIT_LIMIT tries the wait gives up and returns false (the caller raises a status bit
+// and carries on with whatever the buffer holds) — a copy that never lands cannot hang the GPU.
+constexpr int MBAR_WAIT_LIMIT = 1 << 22;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+#pragma unroll 1
+  for (int i = 0; i < MBAR_WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  return false;
+}
+
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {
   const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
   const int bytes = valid ? 16 : 0;

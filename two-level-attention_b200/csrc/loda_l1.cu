@@ -29,18 +29,28 @@ namespace loda {
 
 LODA_PHASE_STORAGE(l1)
 
+constexpr int L1_TP = 256;                         // threads per CTA = pages per tile
+
+template <int DSUB>
+struct L1Shape {
+  static constexpr int NSTAGE = DSUB >= 64 ? 2 : 3;          // tiles in flight per CTA
+  static constexpr size_t STAGES_BYTES = (size_t)NSTAGE * L1Tile<DSUB, L1_TP>::STAGE;
+  static constexpr size_t ROWS_BYTES = STAGES_BYTES > L1_TAIL_BYTES ? STAGES_BYTES : L1_TAIL_BYTES;
+};
+
 template <int DSUB, int P, bool GENERIC>
-__global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, loda_batch B,
-                                                const bf16* __restrict__ q, float scale,
-                                                loda_selection out, SelectWorkspace ws, int nsplit,
-                                                int tiles_per_cta, AppendArgs ap, int phase) {
-  constexpr int NC = DSUB / 8;            // 8-dim chunks per statistic
-  constexpr int CPR = 2 * NC;             // 16-byte chunks per min/max row
-  constexpr int ROWB = 4 * DSUB + 16;     // padded row: conflict-free 16-byte reads
-  extern __shared__ __align__(16) unsigned char smem[];
-  constexpr size_t ROWS_BYTES = (size_t)P * ROWB > L1_TAIL_BYTES ? (size_t)P * ROWB : L1_TAIL_BYTES;
-  unsigned char* rows = smem;                                    // staging rows, later scores + histograms
-  float* qhat = (float*)(smem + ROWS_BYTES);                     // [G, DSUB] x3
+__global__ void __launch_bounds__(P, 2) l1_kernel(loda_geometry g, loda_layer L, loda_batch B,
+                                                   const bf16* __restrict__ q, float scale,
+                                                   loda_selection out, SelectWorkspace ws, int nsplit,
+                                                   int tiles_per_cta, AppendArgs ap, int phase) {
+  static_assert(P == L1_TP, "one tile shape");
+  using T = L1Tile<DSUB, P>;
+  constexpr int NSTAGE = L1Shape<DSUB>::NSTAGE;
+  constexpr size_t ROWS_BYTES = L1Shape<DSUB>::ROWS_BYTES;
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* rows = smem;                                    // tile stages, later scores of the row
+  uint64_t* bars = (uint64_t*)(smem + ROWS_BYTES);               // one mbarrier per stage
+  float* qhat = (float*)(smem + ROWS_BYTES + 64);                // [G, DSUB] x3 (x4 GENERIC)
   const int G = g.num_q_heads / g.num_kv_heads;
   float* qlow = qhat + G * DSUB;
   float* qhigh = qlow + G * DSUB;
@@ -48,7 +58,7 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   constexpr int NQ = GENERIC ? 4 : 3;
   int* kept = (int*)(qhat + NQ * G * DSUB);                      // k_far + k_near + 2
   // (an offset, not pointer arithmetic through an integer: the compiler must keep seeing shared memory)
-  const size_t keys_off = (ROWS_BYTES + (size_t)NQ * G * DSUB * 4 + (size_t)(g.k_far + g.k_near + 2) * 4 + 15) & ~(size_t)15;
+  const size_t keys_off = (ROWS_BYTES + 64 + (size_t)NQ * G * DSUB * 4 + (size_t)(g.k_far + g.k_near + 2) * 4 + 15) & ~(size_t)15;
   uint32_t* keys = (uint32_t*)(smem + keys_off);                 // 2 P + 8
   int* wtot = (int*)(keys + 2 * P + 8);                          // 8 x 32
   int* sh = wtot + 256;                                          // 8
@@ -58,6 +68,11 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   const int b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
   const int cta_id = blockIdx.y * gridDim.x + blockIdx.x;
   LODA_PHASE(l1, cta_id, 0);
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < NSTAGE; ++s) mbar_init(bars + s, 1);
+    mbar_init_fence();
+  }
   pdl_wait();
 #if LODA_PDL_TRIGGER == 0
   pdl_launch_dependents();
@@ -84,42 +99,54 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   // this CTA's tiles of P pages: split, split + nsplit, ... (interleaved, so that the tiles a
   // short request really has are spread over the CTAs of its row); tiles past the request's
   // last page are neither read nor written, and a CTA without tiles only takes its ticket
-  const size_t pg0 = ((size_t)req * g.num_kv_heads + kv) * g.max_blocks;
-  const unsigned char* mm_base = (const unsigned char*)L.page_mm + pg0 * (4 * DSUB);
-  const unsigned char* sum_base = (const unsigned char*)L.page_sum + pg0 * (2 * DSUB);
+  const size_t rowi = (size_t)req * g.num_kv_heads + kv;
+  const unsigned char* mm_row = (const unsigned char*)L.page_mm + rowi * stat_row_bytes(g.max_blocks, T::CPR);
+  const unsigned char* sum_row = (const unsigned char*)L.page_sum + rowi * stat_row_bytes(g.max_blocks, T::NC);
   uint16_t* row_scores = ws.l1_scores + (size_t)row * ws.score_stride;
   const int page_end = min(rg.kt_eff, g.max_blocks);
+  __syncthreads();                                       // the barriers are initialised
+  // the first NSTAGE tiles are requested at once (issued first: the longest latency)
+  if (tid < 32) {
+#pragma unroll
+    for (int it = 0; it < NSTAGE; ++it) {
+      const int p0 = (split + it * nsplit) * P;
+      if (it < tiles_per_cta && p0 < page_end)
+        l1_issue_tile<DSUB, P, GENERIC>(g, rg, p0, page_end, rows + (size_t)it * T::STAGE, bars + it, mm_row, sum_row);
+    }
+  }
+  // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
+  for (int i = tid; i < nq; i += P) {
+    const int j = i / DSUB, d = i % DSUB;
+    const float qv = i == tid ? q_first
+                              : __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, d)]);
+    const float qh = bf16r(__fmul_rn(qv, scale));
+    qhat[i] = qh;
+    qlow[i] = fminf(qh, 0.0f);
+    qhigh[i] = fmaxf(qh, 0.0f);
+    if (GENERIC) qraw[i] = __fmul_rn(qv, scale);
+  }
+  __syncthreads();
+  LODA_PHASE(l1, cta_id, 2);
+  bool timed_out = false;
+#pragma unroll 1
   for (int it = 0; it < tiles_per_cta; ++it) {
     const int p0 = (split + it * nsplit) * P;
     if (p0 >= page_end) break;
-    if (it > 0) __syncthreads();                         // the staging rows are reused
-    // stage the metadata rows of the tile (issued first: the longest latency)
-    l1_stage_tile<DSUB, P, GENERIC>(g, rg, p0, rows, mm_base, sum_base);
-    cp_async_commit();
-    if (it == 0) {
-      // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
-      for (int i = tid; i < nq; i += P) {
-        const int j = i / DSUB, d = i % DSUB;
-        const float qv = i == tid ? q_first
-                                  : __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, d)]);
-        const float qh = bf16r(__fmul_rn(qv, scale));
-        qhat[i] = qh;
-        qlow[i] = fminf(qh, 0.0f);
-        qhigh[i] = fmaxf(qh, 0.0f);
-        if (GENERIC) qraw[i] = __fmul_rn(qv, scale);
-      }
-    }
-    LODA_PHASE(l1, cta_id, 2);
-    cp_async_wait<0>();
-    __syncthreads();
-    LODA_PHASE(l1, cta_id, 3);
-
+    const int st = it % NSTAGE;
+    if (!mbar_wait(bars + st, (uint32_t)(it / NSTAGE) & 1u)) timed_out = true;
+    if (it == 0) { LODA_PHASE(l1, cta_id, 3); }
     // one page per thread
-    const int page = p0 + tid;
-    const unsigned char* myrow = rows + (size_t)tid * ROWB;
-    const uint32_t ord = l1_page_score<DSUB, GENERIC>(g, rg, page, myrow, qhat, qlow, qhigh, G, qraw);
-    row_scores[page] = (uint16_t)ord;     // the selecting CTA reads pages below page_end (rounded up to 8)
+    const uint32_t ord = l1_page_score<DSUB, P, GENERIC>(g, rg, p0, page_end, rows + (size_t)st * T::STAGE, qhat, qlow,
+                                                          qhigh, G, qraw);
+    row_scores[p0 + tid] = (uint16_t)ord;     // the selecting CTA reads pages below page_end (rounded up to 8)
+    __syncthreads();                          // every thread has read the stage: refill it
+    if (tid < 32) {
+      const int nxt = it + NSTAGE, pn = (split + nxt * nsplit) * P;
+      if (nxt < tiles_per_cta && pn < page_end)
+        l1_issue_tile<DSUB, P, GENERIC>(g, rg, pn, page_end, rows + (size_t)st * T::STAGE, bars + st, mm_row, sum_row);
+    }
   }
+  if (timed_out && tid == 0 && ap.status) atomicOr(ap.status, LODA_STATUS_TIMEOUT);
   LODA_PHASE(l1, cta_id, 4);
 
   // last CTA of the row selects.  phase 1 = scores only (the caller combines the score rows of
@@ -202,45 +229,39 @@ __global__ void __launch_bounds__(P) l1_kernel(loda_geometry g, loda_layer L, lo
   LODA_PHASE(l1, cta_id, 9);
 }
 
-// Two tile shapes.  512 pages per 512-thread CTA: one CTA per SM (128 registers), the
-// fewest tickets and the shortest path for a grid that fits the GPU in one round (batch 1
-// at 128K tokens: 8 rows x 16 tiles).  256 pages per 256-thread CTA: two CTAs per SM, so
-// that one CTA's copies overlap the other's arithmetic, for every larger grid.
-constexpr int L1_P_WIDE = 512, L1_P_NARROW = 256;
-
 static bool l1_generic(const loda_geometry& g) { return g.far_method != LODA_FAR_MINMAX || g.near_minmax != 0; }
 
-static size_t l1_smem_bytes_p(const loda_geometry& g, int P) {
+template <int DS>
+static size_t l1_smem_bytes_d(const loda_geometry& g) {
   const int G = g.num_q_heads / g.num_kv_heads;
-  const size_t rows = (size_t)P * (4 * g.sub_dims + 16);
-  return (rows > L1_TAIL_BYTES ? rows : L1_TAIL_BYTES) + (size_t)(l1_generic(g) ? 4 : 3) * G * g.sub_dims * 4 +
-         (size_t)(g.k_far + g.k_near + 2) * 4 + (size_t)(2 * P + 8) * 4 + (256 + 8) * 4 + 32;
+  return L1Shape<DS>::ROWS_BYTES + 64 + (size_t)(l1_generic(g) ? 4 : 3) * G * DS * 4 +
+         (size_t)(g.k_far + g.k_near + 2) * 4 + (size_t)(2 * L1_TP + 8) * 4 + (256 + 8) * 4 + 32;
 }
 
-size_t l1_smem_bytes(const loda_geometry& g) { return l1_smem_bytes_p(g, L1_P_WIDE); }
-
-// scores per row in the workspace: whole tiles of either shape
-int l1_score_stride(const loda_geometry& g) { return (g.max_blocks + L1_P_WIDE - 1) / L1_P_WIDE * L1_P_WIDE; }
-
-static bool l1_wide(const loda_geometry& g, int rows) {
-  return rows * ((g.max_blocks + L1_P_WIDE - 1) / L1_P_WIDE + 1) <= device_sm_count();
+size_t l1_smem_bytes(const loda_geometry& g) {
+  return g.sub_dims == 16 ? l1_smem_bytes_d<16>(g) : g.sub_dims == 32 ? l1_smem_bytes_d<32>(g) : l1_smem_bytes_d<64>(g);
 }
 
-// CTAs per row: one tile each while the grid is small (batch 1: latency), several
-// interleaved tiles per CTA once rows x tiles exceeds about eight CTAs per SM
+// scores per row in the workspace: whole tiles
+int l1_score_stride(const loda_geometry& g) { return (g.max_blocks + 511) / 512 * 512; }
+
+// CTAs per row: one tile each while the grid is small (batch 1: latency), several interleaved
+// tiles per CTA (a pipeline of bulk copies inside the CTA) once rows x tiles exceeds about four
+// CTAs per SM
 static void l1_split(const loda_geometry& g, int rows, int P, int* ctas_per_row, int* tiles_per_cta) {
   const int ntiles = (g.max_blocks + P - 1) / P;
   const int sms = device_sm_count();
-  int tpc = (rows * ntiles + 8 * sms - 1) / (8 * sms);
+  int tpc = (rows * ntiles + 4 * sms - 1) / (4 * sms);
   tpc = tpc < 1 ? 1 : tpc > ntiles ? ntiles : tpc;
   *tiles_per_cta = tpc;
   *ctas_per_row = (ntiles + tpc - 1) / tpc;
 }
 
-template <int DS, int P, bool GENERIC>
+template <int DS, bool GENERIC>
 static cudaError_t launch_l1_p(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                float scale, const loda_selection& out, const SelectWorkspace& ws,
                                const AppendArgs& ap, int phase, cudaStream_t st) {
+  constexpr int P = L1_TP;
   const int rows = B.batch * g.num_kv_heads;
   int nsplit, tpc;
   l1_split(g, rows, P, &nsplit, &tpc);
@@ -249,7 +270,7 @@ static cudaError_t launch_l1_p(const loda_geometry& g, const loda_layer& L, cons
     grid = dim3(1, rows);
     tpc = 0;
   }
-  const size_t smem = l1_smem_bytes_p(g, P);
+  const size_t smem = l1_smem_bytes_d<DS>(g);
   cudaError_t e = set_kernel_smem(l1_kernel<DS, P, GENERIC>, smem);
   if (e != cudaSuccess) return e;
   return launch_pdl(l1_kernel<DS, P, GENERIC>, grid, dim3(P), smem, st, g, L, B, (const bf16*)q, scale, out, ws, nsplit, tpc,
@@ -260,11 +281,9 @@ template <int DS>
 static cudaError_t launch_l1_d(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                float scale, const loda_selection& out, const SelectWorkspace& ws,
                                const AppendArgs& ap, int phase, cudaStream_t st) {
-  if (l1_generic(g))      // other level-1 methods than the defaults: one tile shape, methods read at run time
-    return launch_l1_p<DS, L1_P_NARROW, true>(g, L, B, q, scale, out, ws, ap, phase, st);
-  return l1_wide(g, B.batch * g.num_kv_heads)
-             ? launch_l1_p<DS, L1_P_WIDE, false>(g, L, B, q, scale, out, ws, ap, phase, st)
-             : launch_l1_p<DS, L1_P_NARROW, false>(g, L, B, q, scale, out, ws, ap, phase, st);
+  // other level-1 methods than the defaults read them at run time
+  return l1_generic(g) ? launch_l1_p<DS, true>(g, L, B, q, scale, out, ws, ap, phase, st)
+                       : launch_l1_p<DS, false>(g, L, B, q, scale, out, ws, ap, phase, st);
 }
 
 // phase 0: scores and selection; 1: scores only; 2: selection only (of the scores in the workspace)

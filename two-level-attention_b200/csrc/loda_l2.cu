@@ -34,7 +34,7 @@ LODA_SUB_READER(l2)
 constexpr int L2_SPLIT = 8;
 constexpr int L2_NT = 256;
 
-template <int DSUB, int NT>
+template <int DSUB, int NT, bool NUMERIC>
 __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, loda_layer L, loda_batch B,
                                                  const bf16* __restrict__ q, float scale,
                                                  loda_selection S, SelectWorkspace ws, uint32_t* status,
@@ -143,8 +143,8 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
   L2Shared shm{sc, pages, physs, mid_a, mid_b, wtot, scan, win};
   shm.sc2 = sc2;
   shm.fin = fin;
-  l2_select_and_write<NT, 0>(g, rg, S, status, table, b, kv, row, length, nitems, shm, ws.l2_ticket + row,
-                             LODA_PDL_TRIGGER == 1);
+  l2_select_and_write<NT, 0, false, NUMERIC>(g, rg, S, status, table, b, kv, row, length, nitems, shm, ws.l2_ticket + row,
+                                             LODA_PDL_TRIGGER == 1);
   LODA_PHASE(l2, cta_id, 9);
 }
 
@@ -214,9 +214,15 @@ static cudaError_t launch_l2_d(const loda_geometry& g, const loda_layer& L, cons
   nsplit = nsplit < 1 ? 1 : nsplit > L2_SPLIT ? L2_SPLIT : nsplit;
   const dim3 grid(phase == 2 ? 1 : nsplit, rows);      // selection only: one CTA per row
   const size_t smem = l2_smem_bytes(g);
-  cudaError_t e = set_kernel_smem(l2_kernel<DS, L2_NT>, smem);
+  if (g.near_tokens_p1 > 0) {      // numeric near-token quota: the instantiation with the two-region selection
+    cudaError_t e = set_kernel_smem(l2_kernel<DS, L2_NT, true>, smem);
+    if (e != cudaSuccess) return e;
+    return launch_pdl(l2_kernel<DS, L2_NT, true>, grid, dim3(L2_NT), smem, st, g, L, B, (const bf16*)q, scale, S, ws,
+                      status, nsplit, (int)chained, phase);
+  }
+  cudaError_t e = set_kernel_smem(l2_kernel<DS, L2_NT, false>, smem);
   if (e != cudaSuccess) return e;
-  return launch_pdl(l2_kernel<DS, L2_NT>, grid, dim3(L2_NT), smem, st, g, L, B, (const bf16*)q, scale, S, ws, status,
+  return launch_pdl(l2_kernel<DS, L2_NT, false>, grid, dim3(L2_NT), smem, st, g, L, B, (const bf16*)q, scale, S, ws, status,
                     nsplit, (int)chained, phase);
 }
 

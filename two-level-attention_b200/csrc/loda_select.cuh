@@ -57,17 +57,68 @@ __device__ __forceinline__ bool l1_near_uses_minmax(const loda_geometry& g) {
   return GENERIC ? g.near_minmax != 0 : false;
 }
 
-// Ordered 16-bit score of one logical page from its staged metadata row (min then max, or the
-// sum in the first half); 0 = the page is in neither pool or scores -inf.
+// ---------------------------------------------------------------------------
+// Level-1 tiles.  A tile is TP consecutive logical pages of one (request, kv head) row = TP / 32
+// groups of the interleaved statistics layout (STAT_GROUP).  A stage of shared memory holds one
+// tile: a slot of SLOT bytes per group, byte-identical to the group in global memory (the group's
+// min/max rows, or its sum rows in the first half of the slot), plus one spill slot of SUMG bytes
+// for the sums of the one group of a row that holds pages of both pools (the far / near boundary).
+// One bulk asynchronous copy per group and statistic fills it; an mbarrier counts the bytes.
+// ---------------------------------------------------------------------------
+template <int DSUB, int TP>
+struct L1Tile {
+  static constexpr int NC = DSUB / 8, CPR = 2 * NC, GROUPS = TP / STAT_GROUP;
+  static constexpr int SLOT = STAT_GROUP * CPR * 16;      // one group of min/max rows
+  static constexpr int SUMG = STAT_GROUP * NC * 16;       // one group of sum rows
+  static constexpr int STAGE = GROUPS * SLOT + SUMG;      // bytes of one stage
+};
+
+// Does the group of 32 pages starting at page g0 hold pages scored on the min/max rows / on the sums?
+template <bool GENERIC>
+__device__ __forceinline__ void l1_group_needs(const loda_geometry& g, const Regions& rg, int g0, int page_end,
+                                               bool* need_mm, bool* need_sum) {
+  const int lo = g0, hi = min(g0 + STAT_GROUP, page_end);
+  const bool has_far = rg.far_hi > rg.far_lo && lo < rg.far_hi && hi > rg.far_lo;
+  const int nlo = max(rg.near_blks, rg.near_lo_valid), nhi = min(min(rg.swa_lo_blk, rg.kt_eff), rg.kt_cap);
+  const bool has_near = rg.near_on && lo < nhi && hi > nlo && hi > lo;
+  const bool far_mm = l1_far_uses_minmax<GENERIC>(g), near_mm = l1_near_uses_minmax<GENERIC>(g);
+  *need_mm = (has_far && far_mm) || (has_near && near_mm);
+  *need_sum = (has_far && !far_mm) || (has_near && !near_mm);
+}
+
+// Issue the copies of the tile [p0, p0 + TP) into `stage` and arm `bar` with their byte count.
+// Called by all 32 lanes of one warp (lane i handles group i of the tile).
+template <int DSUB, int TP, bool GENERIC>
+__device__ __forceinline__ void l1_issue_tile(const loda_geometry& g, const Regions& rg, int p0, int page_end,
+                                              unsigned char* stage, uint64_t* bar, const unsigned char* mm_row,
+                                              const unsigned char* sum_row) {
+  using T = L1Tile<DSUB, TP>;
+  const int lane = threadIdx.x & 31;
+  bool nm = false, ns = false;
+  if (lane < T::GROUPS) l1_group_needs<GENERIC>(g, rg, p0 + STAT_GROUP * lane, page_end, &nm, &ns);
+  const uint32_t bytes = (nm ? T::SLOT : 0) + (ns ? T::SUMG : 0);
+  const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
+  if (lane == 0) mbar_arrive_expect_tx(bar, total);
+  __syncwarp();
+  const size_t gidx = (size_t)(p0 / STAT_GROUP) + lane;
+  if (nm) bulk_copy_g2s(stage + lane * T::SLOT, mm_row + gidx * T::SLOT, T::SLOT, bar);
+  if (ns) bulk_copy_g2s(nm ? stage + T::GROUPS * T::SLOT : stage + lane * T::SLOT, sum_row + gidx * T::SUMG, T::SUMG, bar);
+}
+
+// Ordered 16-bit score of the logical page p0 + threadIdx.x from the staged tile; 0 = the page is in
+// neither pool or scores -inf.
 // Per head the bound (min . min(q, 0) + max . max(q, 0)) or the mean score (mean . q) is rounded to
 // bf16; the page score is the mean over the GQA group, rounded to bf16 — or, for the far method
 // avg_top2, the mean of the two best per-head mean scores computed from the unrounded scaled query
 // qraw (nfa_layer_batch_selector.py:290-354, 2412-2427).
-template <int DSUB, bool GENERIC = false>
-__device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const Regions& rg, int page,
-                                                  const unsigned char* myrow, const float* qhat, const float* qlow,
+template <int DSUB, int TP, bool GENERIC = false>
+__device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const Regions& rg, int p0, int page_end,
+                                                  const unsigned char* stage, const float* qhat, const float* qlow,
                                                   const float* qhigh, int G, const float* qraw = nullptr) {
-  constexpr int NC = DSUB / 8;
+  using T = L1Tile<DSUB, TP>;
+  constexpr int NC = DSUB / 8, CS = STAT_GROUP * 16;      // CS: bytes between two chunks of a page
+  const int page = p0 + (int)threadIdx.x;
+  const int grp = (int)threadIdx.x / STAT_GROUP, lane = (int)threadIdx.x % STAT_GROUP;
   uint32_t ord = 0;
   const float gf = (float)G;
   const bool far = in_far_pool(rg, page);
@@ -75,11 +126,12 @@ __device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const 
   if (!far && !near) return 0u;
   const bool use_mm = far ? l1_far_uses_minmax<GENERIC>(g) : l1_near_uses_minmax<GENERIC>(g);
   if (use_mm) {
+    const unsigned char* src = stage + grp * T::SLOT + lane * 16;
     float kmin[DSUB], kmax[DSUB];
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
-      unpack8(*(const uint4*)(myrow + c * 16), *(float(*)[8])(kmin + 8 * c));
-      unpack8(*(const uint4*)(myrow + (NC + c) * 16), *(float(*)[8])(kmax + 8 * c));
+      unpack8(*(const uint4*)(src + c * CS), *(float(*)[8])(kmin + 8 * c));
+      unpack8(*(const uint4*)(src + (NC + c) * CS), *(float(*)[8])(kmax + 8 * c));
     }
     float acc = 0.0f;
 #pragma unroll 1
@@ -89,12 +141,16 @@ __device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const 
     }
     ord = ord16(bf16r(__fdiv_rn(acc, gf)));
   } else {
+    // the sums sit in the group's own slot, or in the spill slot when the group also staged min/max rows
+    bool nm, ns;
+    l1_group_needs<GENERIC>(g, rg, p0 + grp * STAT_GROUP, page_end, &nm, &ns);
+    const unsigned char* src = (nm ? stage + T::GROUPS * T::SLOT : stage + grp * T::SLOT) + lane * 16;
     float kavg[DSUB];
     // mean = sum / page: the page size is a power of two, so the division is an exact scaling and
     // the multiplication by 1 / page gives the same bits at a fraction of the instructions
     const float inv_bs = 1.0f / (float)g.page;
 #pragma unroll
-    for (int c = 0; c < NC; ++c) unpack8(*(const uint4*)(myrow + c * 16), *(float(*)[8])(kavg + 8 * c));
+    for (int c = 0; c < NC; ++c) unpack8(*(const uint4*)(src + c * CS), *(float(*)[8])(kavg + 8 * c));
 #pragma unroll
     for (int i = 0; i < DSUB; ++i) kavg[i] = bf16r(__fmul_rn(kavg[i], inv_bs));
     if (GENERIC && far && g.far_method == LODA_FAR_AVG_TOP2) {
@@ -115,26 +171,6 @@ __device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const 
     }
   }
   return ord == ORD16_NEG_INF ? 0u : ord;   // a -inf score never competes (it equals "not in the pool")
-}
-
-// Stage the metadata rows of the P pages [p0, p0 + P) of one row into dst (rows ROWB bytes apart):
-// for every page of a pool the statistic its score needs, 16 bytes per copy.
-template <int DSUB, int P, bool GENERIC>
-__device__ __forceinline__ void l1_stage_tile(const loda_geometry& g, const Regions& rg, int p0, unsigned char* dst,
-                                              const unsigned char* mm_base, const unsigned char* sum_base) {
-  constexpr int NC = DSUB / 8, CPR = 2 * NC, ROWB = 4 * DSUB + 16;
-  const bool far_mm = l1_far_uses_minmax<GENERIC>(g), near_mm = l1_near_uses_minmax<GENERIC>(g);
-  for (int c = threadIdx.x; c < P * CPR; c += P) {
-    const int pl = c / CPR, cc = c % CPR;
-    const int page = p0 + pl;
-    const bool far = in_far_pool(rg, page);
-    if (!far && !in_near_pool(rg, page)) continue;
-    if (far ? far_mm : near_mm) {
-      cp_async16(dst + (size_t)pl * ROWB + cc * 16, mm_base + (size_t)page * (4 * DSUB) + cc * 16, true);
-    } else if (cc < NC) {
-      cp_async16(dst + (size_t)pl * ROWB + cc * 16, sum_base + (size_t)page * (2 * DSUB) + cc * 16, true);
-    }
-  }
 }
 
 // the selecting CTA reuses the staging area: 40 KB for the far pool's scores (2 bytes per page)
@@ -355,7 +391,10 @@ struct L2Shared {
 #ifndef LODA_L2TAIL_INLINE
 #define LODA_L2TAIL_INLINE __forceinline__
 #endif
-template <int NT, int BAR, bool HIST = false>
+// NUMERIC: compile the numeric near-token quota path (a second selection and its hole fill); kernels that only
+// serve the default quota leave it out — this code runs once per launch, cold, and its size is paid in
+// instruction fetch
+template <int NT, int BAR, bool HIST = false, bool NUMERIC = false>
 __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, const Regions& rg, const loda_selection& S,
                                                     uint32_t* status, const int32_t* table, int b, int kv, int row,
                                                     int length, int nitems, const L2Shared& sm, int* ticket,
@@ -460,7 +499,7 @@ __device__ LODA_L2TAIL_INLINE void l2_select_and_write(const loda_geometry& g, c
     return mid + d0;
   };
 
-  if (rg.numeric) {
+  if (NUMERIC && rg.numeric) {
     // ---- numeric near-token quota: far region, then near region, concatenated ----------------
     int total_m = 0;
     if (sm.sc2 != nullptr && sm.fin != nullptr) {

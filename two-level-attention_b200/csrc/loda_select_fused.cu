@@ -43,16 +43,18 @@ constexpr int SF_CLUSTER_MAX = 16; // CTAs per row: 16, or 8 when the GPU cannot
 constexpr int SF_L2_NT = 256;      // threads of the leader that run the level-2 selection
 
 struct FusedLayout {
-  size_t rows_bytes, qv, kept, physk, kept2, physk2, keys, wtot, scan, sh, hist2, list, pfm, pfo, scall, total;
+  size_t rows_bytes, bars, qv, kept, physk, kept2, physk2, keys, wtot, scan, sh, hist2, list, pfm, pfo, scall, total;
 };
 
 __host__ __device__ inline FusedLayout fused_layout(const loda_geometry& g, int tiles_per_cta, int cluster_size) {
   const int G = g.num_q_heads / g.num_kv_heads;
   const int np_max = g.k_far + g.k_near + 2;
   FusedLayout f;
-  const size_t rows = (size_t)SF_P * (4 * g.sub_dims + 16);
+  // one tile stage: 16 groups of min/max rows and the spill slot of sums (L1Tile<d', 512>::STAGE)
+  const size_t rows = (size_t)(SF_P / STAT_GROUP) * 128 * g.sub_dims + 64 * (size_t)g.sub_dims;
   f.rows_bytes = rows > L1_TAIL_BYTES ? rows : L1_TAIL_BYTES;
   size_t off = f.rows_bytes * (tiles_per_cta > 1 ? 2 : 1);      // two staging buffers when a CTA has several tiles
+  f.bars = off; off += 16;                                             // one mbarrier per staging buffer
   f.qv = off; off += (size_t)(3 * G + 1) * g.sub_dims * 4;             // qhat, qlow, qhigh [G][d'], qf [d']
   f.kept = off; off += (size_t)np_max * 4;
   f.physk = off; off += (size_t)np_max * 4;
@@ -102,13 +104,14 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
                                                             uint32_t* status, AppendArgs ap, int tiles_per_cta,
                                                             FusedAttend at) {
   constexpr int P = SF_P;
-  constexpr int ROWB = 4 * DSUB + 16;
-  extern __shared__ __align__(16) unsigned char smem[];
+  using T = L1Tile<DSUB, P>;
+  extern __shared__ __align__(128) unsigned char smem[];
   cg::cluster_group cluster = cg::this_cluster();
   const int CS = (int)cluster.num_blocks();
   const FusedLayout lay = fused_layout(g, tiles_per_cta, CS);
   const int G = g.num_q_heads / g.num_kv_heads;
   unsigned char* rows = smem;
+  uint64_t* bars = (uint64_t*)(smem + lay.bars);
   float* qhat = (float*)(smem + lay.qv);
   float* qlow = qhat + G * DSUB;
   float* qhigh = qlow + G * DSUB;
@@ -143,6 +146,11 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   uint32_t* l_hist2 = own ? hist2 : cluster.map_shared_rank(hist2, 0);
 
   LODA_PHASE(sel, cta_id, 0);
+  if (tid == 0) {
+    mbar_init(bars, 1);
+    mbar_init(bars + 1, 1);
+    mbar_init_fence();
+  }
   if (rank == 0) *(uint4*)(hist2 + 4 * tid) = make_uint4(0, 0, 0, 0);      // 2048 words; counted into after barrier (2)
   // rank 1 collects the near pool's scores in the same place of its own shared memory (it has no
   // histogram): zero outside the pool, so cleared before any peer may store
@@ -164,9 +172,9 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   Regions rg = make_regions(g, length, skip_far, skip_near);
   rg.shard_rank = 0;          // this launch never serves a sequence-sharded geometry: the ownership
   rg.shard_count = 0;         // tests fold away
-  const size_t pg0 = ((size_t)req * g.num_kv_heads + kv) * g.max_blocks;
-  const unsigned char* mm_base = (const unsigned char*)L.page_mm + pg0 * (4 * DSUB);
-  const unsigned char* sum_base = (const unsigned char*)L.page_sum + pg0 * (2 * DSUB);
+  const size_t rowi = (size_t)req * g.num_kv_heads + kv;
+  const unsigned char* mm_row = (const unsigned char*)L.page_mm + rowi * stat_row_bytes(g.max_blocks, T::CPR);
+  const unsigned char* sum_row = (const unsigned char*)L.page_sum + rowi * stat_row_bytes(g.max_blocks, T::NC);
   const int page_end = min(rg.kt_eff, g.max_blocks);
   const int near_hi = min(min(rg.swa_lo_blk, rg.kt_eff), g.max_blocks);
   const int near_lo = rg.near_blks, near_lo8 = near_lo & ~7;
@@ -174,14 +182,18 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   uint16_t* r1_scn = (uint16_t*)(rank == 1 ? hist2 : cluster.map_shared_rank(hist2, 1));   // near row of rank 1
 
   // ---- level 1: score this CTA's tiles (rank, rank + CS, ...), two staging buffers ------------
+  // one bulk copy per group of 32 pages, issued by the lanes of warp 0, counted on the buffer's mbarrier
   auto stage = [&](int it) {
     const int p0 = (rank + it * CS) * P;
-    unsigned char* dst = rows + (size_t)(it & 1) * lay.rows_bytes;
-    if (it < tiles_per_cta && p0 < page_end) l1_stage_tile<DSUB, P, false>(g, rg, p0, dst, mm_base, sum_base);
-    cp_async_commit();                                   // one group per tile index, empty when there is no tile
+    if (it < tiles_per_cta && p0 < page_end)
+      l1_issue_tile<DSUB, P, false>(g, rg, p0, page_end, rows + (size_t)(it & 1) * lay.rows_bytes, bars + (it & 1), mm_row,
+                                    sum_row);
   };
-  stage(0);
-  stage(1);
+  __syncthreads();                                       // the barriers are initialised
+  if (tid < 32) {
+    stage(0);
+    stage(1);
+  }
   if (early) pdl_wait();
   // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
   for (int i = tid; i < nq; i += P) {
@@ -201,20 +213,21 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     for (int j = 0; j < G; ++j) acc = __fadd_rn(acc, qhat[j * DSUB + tid]);
     qf[tid] = acc;
   }
+  bool timed_out = false;
+#pragma unroll 1
   for (int it = 0; it < tiles_per_cta; ++it) {
     const int p0 = (rank + it * CS) * P;
     if (p0 >= page_end) break;
-    cp_async_wait<1>();                                  // tile it has landed (tile it + 1 may be in flight)
-    __syncthreads();
+    if (!mbar_wait(bars + (it & 1), (uint32_t)(it >> 1) & 1u)) timed_out = true;      // tile it has landed
     const int page = p0 + tid;
-    const unsigned char* src = rows + (size_t)(it & 1) * lay.rows_bytes;
-    const uint32_t ord = l1_page_score<DSUB>(g, rg, page, src + (size_t)tid * ROWB, qhat, qlow, qhigh, G);
+    const uint32_t ord = l1_page_score<DSUB, P, false>(g, rg, p0, page_end, rows + (size_t)(it & 1) * lay.rows_bytes, qhat,
+                                                       qlow, qhigh, G);
     l_scall[page] = (uint16_t)ord;                       // into the leader's shared memory
     if (page >= near_lo && page < near_hi && page - near_lo8 < n_near) r1_scn[page - near_lo8] = (uint16_t)ord;
     __syncthreads();                                     // the buffer is free
-    stage(it + 2);
+    if (tid < 32) stage(it + 2);
   }
-  cp_async_wait<0>();
+  if (timed_out && tid == 0 && status) atomicOr(status, LODA_STATUS_TIMEOUT);
   LODA_PHASE(sel, cta_id, 1);
   cluster.sync();                                        // (1) all page scores are in the leader
   LODA_PHASE(sel, cta_id, 2);

@@ -375,6 +375,20 @@ class GraphReadyPagedRegionCache:
         return self._runtime
 
 
+def page_minmax_by_page(layer):
+    """[max_requests, Hkv, pages, 2, d'] view-copy of a layer's page min / max statistics (min then max per
+    logical page) out of the grouped device layout; for checks and diagnostics."""
+    r, h, groups, cpr, gp, e = layer.page_mm.shape
+    t = layer.page_mm.view(r, h, groups, 2, cpr // 2, gp, e).permute(0, 1, 2, 5, 3, 4, 6)
+    return t.reshape(r, h, groups * gp, 2, (cpr // 2) * e)
+
+
+def page_sum_by_page(layer):
+    """[max_requests, Hkv, pages, d'] copy of a layer's page sums out of the grouped device layout."""
+    r, h, groups, nc, gp, e = layer.page_sum.shape
+    return layer.page_sum.permute(0, 1, 2, 4, 3, 5).reshape(r, h, groups * gp, nc * e)
+
+
 class SelectorRuntime:
     """C structs and device buffers shared by every call on one cache."""
 
@@ -423,9 +437,11 @@ class SelectorRuntime:
         self.middle_counts = torch.zeros((mq, hkv), dtype=torch.int32, device=dev)
         self.layer_structs = []
         for li, layer in enumerate(cache.layers):
-            layer.page_mm = torch.zeros((cache.max_requests, hkv, cache.max_blocks, 2, dsub),
+            # statistics in groups of 32 logical pages, chunk-major inside a group (include/loda_b200.h)
+            groups = (cache.max_blocks + 31) // 32
+            layer.page_mm = torch.zeros((cache.max_requests, hkv, groups, dsub // 4, 32, 8),
                                         dtype=cache.dtype, device=dev)
-            layer.page_sum = torch.zeros((cache.max_requests, hkv, cache.max_blocks, dsub),
+            layer.page_sum = torch.zeros((cache.max_requests, hkv, groups, dsub // 8, 32, 8),
                                          dtype=cache.dtype, device=dev)
             layer.tail_code = torch.zeros((g.num_pages, hkv, page, dsub // 2), dtype=torch.uint8, device=dev)
             layer.tail_sz = torch.zeros((g.num_pages, hkv, page, 2), dtype=cache.dtype, device=dev)
