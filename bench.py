@@ -1011,6 +1011,7 @@ def main():
     ms_per_step = ms_total / K
     tok_s = (1.0 if kvhead else world) / (ms_per_step * 1e-3)
     launches_per_layer = int(lib.loda_last_decode_launches()) or 2
+    ctas_per_row = int(lib.loda_last_decode_cluster())
     parity = None
     if not args.skip_parity and rank == 0:
         parity = parity_check(torch, wl, out, lengths.cpu(), W + K - 1)
@@ -1090,6 +1091,7 @@ def main():
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": K * stats["replays"] * N_LAYERS * launches_per_layer, "device_status": status,
             "clocks": clocks, "launches_per_layer_step": launches_per_layer,
+            "ctas_per_row": ctas_per_row if launches_per_layer == 1 else None,
         }
     del wl, runner, cache, out, hq_, hk_, hv_
     torch.cuda.empty_cache()

@@ -294,6 +294,11 @@ int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda
  * selection, then attention) or 3 (L1, L2, attention).  For benchmarks and logs. */
 int loda_last_decode_launches(void);
 
+/* CTAs per (request, kv head) row of the one-launch kernel as the latest call of this thread launched it
+ * (16, 12, 10 or 8: the largest thread-block cluster of which the GPU held one for every row), 0 if the
+ * call ran the separate launches.  For benchmarks and logs. */
+int loda_last_decode_cluster(void);
+
 /* gather / visible_lens = the protected tokens only: sink ++ sliding window as physical
  * slots, per (batch row, kv head).  Replaces build_protected_gather
  * (sparse_attn/ops/paged_region_kernels_nfa.py:84-119).  With loda_selection.middle_only

@@ -59,7 +59,7 @@ EXPORTS = ("loda_version", "loda_last_error", "loda_workspace_bytes", "loda_appe
            "loda_select_step", "loda_tia_quant4", "loda_tia_block_minmax", "loda_tia_scores", "loda_gather_attend_lse",
            "loda_tls_store_kv", "loda_tls_store_k_index", "loda_tls_level1", "loda_tls_level2",
            "loda_shard_workspace_regions", "loda_shard_l1_scores", "loda_shard_l1_select", "loda_shard_l2_scores",
-           "loda_shard_l2_select", "loda_protected_gather", "loda_last_decode_launches")
+           "loda_shard_l2_select", "loda_protected_gather", "loda_last_decode_launches", "loda_last_decode_cluster")
 
 _lib = None
 

@@ -22,6 +22,7 @@ cudaError_t launch_protected_gather(const loda_geometry&, const loda_layer&, con
                                     uint32_t*, cudaStream_t);
 bool select_fused_applicable(const loda_geometry&, int);
 void select_fused_refuse(int);
+int select_fused_last_cluster();
 cudaError_t launch_decode_fused(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
                                 const loda_selection&, uint32_t*, const AppendArgs&, const int32_t*, void*, cudaStream_t);
 cudaError_t launch_select_fused(const loda_geometry&, const loda_layer&, const loda_batch&, const void*, float,
@@ -428,6 +429,7 @@ int loda_shard_l2_select(const loda_geometry* g, const loda_layer* layer, const 
 
 static thread_local int g_last_decode_launches = 0;
 int loda_last_decode_launches(void) { return g_last_decode_launches; }
+int loda_last_decode_cluster(void) { return g_last_decode_launches == 1 || g_last_select_launches == 1 ? select_fused_last_cluster() : 0; }
 
 int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
                      const void* k_new, const void* v_new, const int32_t* slots, float scale,

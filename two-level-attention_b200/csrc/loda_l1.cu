@@ -52,9 +52,8 @@ __global__ void __launch_bounds__(P, 2) l1_kernel(loda_geometry g, loda_layer L,
   uint64_t* bars = (uint64_t*)(smem + ROWS_BYTES);               // one mbarrier per stage
   float* qhat = (float*)(smem + ROWS_BYTES + 64);                // [G, DSUB] x3 (x4 GENERIC)
   const int G = g.num_q_heads / g.num_kv_heads;
-  float* qlow = qhat + G * DSUB;
-  float* qhigh = qlow + G * DSUB;
-  float* qraw = qhigh + G * DSUB;                                // GENERIC: the unrounded scaled query (avg_top2)
+  float* qmm = qhat + G * DSUB;                                  // [G, DSUB, 2]: (min(q, 0), max(q, 0)) interleaved
+  float* qraw = qmm + 2 * G * DSUB;                              // GENERIC: the unrounded scaled query (avg_top2)
   constexpr int NQ = GENERIC ? 4 : 3;
   int* kept = (int*)(qhat + NQ * G * DSUB);                      // k_far + k_near + 2
   // (an offset, not pointer arithmetic through an integer: the compiler must keep seeing shared memory)
@@ -121,8 +120,7 @@ __global__ void __launch_bounds__(P, 2) l1_kernel(loda_geometry g, loda_layer L,
                               : __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, d)]);
     const float qh = bf16r(__fmul_rn(qv, scale));
     qhat[i] = qh;
-    qlow[i] = fminf(qh, 0.0f);
-    qhigh[i] = fmaxf(qh, 0.0f);
+    *(float2*)(qmm + 2 * i) = make_float2(fminf(qh, 0.0f), fmaxf(qh, 0.0f));
     if (GENERIC) qraw[i] = __fmul_rn(qv, scale);
   }
   __syncthreads();
@@ -136,8 +134,8 @@ __global__ void __launch_bounds__(P, 2) l1_kernel(loda_geometry g, loda_layer L,
     if (!mbar_wait(bars + st, (uint32_t)(it / NSTAGE) & 1u)) timed_out = true;
     if (it == 0) { LODA_PHASE(l1, cta_id, 3); }
     // one page per thread
-    const uint32_t ord = l1_page_score<DSUB, P, GENERIC>(g, rg, p0, page_end, rows + (size_t)st * T::STAGE, qhat, qlow,
-                                                          qhigh, G, qraw);
+    const uint32_t ord = l1_page_score<DSUB, P, GENERIC>(g, rg, p0, page_end, rows + (size_t)st * T::STAGE, qhat, qmm, G,
+                                                          qraw);
     row_scores[p0 + tid] = (uint16_t)ord;     // the selecting CTA reads pages below page_end (rounded up to 8)
     __syncthreads();                          // every thread has read the stage: refill it
     if (tid < 32) {

@@ -45,6 +45,53 @@ __device__ __forceinline__ float dot_chunks(const float (&k)[DSUB], const float*
   return chunk_tree<NC>(p);
 }
 
+// Packed fp32 arithmetic (two independent IEEE fp32 operations per instruction, sm_100): the low lane
+// carries the min . min(q, 0) dot of the bound, the high lane the max . max(q, 0) dot, each in the
+// canonical order — the same roundings as two scalar chains at half the instructions.
+__device__ __forceinline__ unsigned long long pack_u32x2(uint32_t lo, uint32_t hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long fadd2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// min/max bound of one head: kp[d] = (min_d, max_d) as packed fp32, qmm = (min(q_d, 0), max(q_d, 0)) interleaved
+// in shared memory.  Chunks of 8 dims summed left to right from 0, chunk sums by the balanced tree, then the
+// two lanes added: bit for bit dot_chunks(min, qlow) + dot_chunks(max, qhigh).
+template <int DSUB>
+__device__ __forceinline__ float bound_pair(const unsigned long long (&kp)[DSUB], const float* qmm) {
+  constexpr int NC = DSUB / 8;
+  unsigned long long p[NC];
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    unsigned long long a = 0ull;                       // (0.0f, 0.0f)
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+      const ulonglong2 q2 = *(const ulonglong2*)(qmm + (8 * c + i) * 2);
+      a = ffma2(kp[8 * c + i], q2.x, a);
+      a = ffma2(kp[8 * c + i + 1], q2.y, a);
+    }
+    p[c] = a;
+  }
+#pragma unroll
+  for (int w = 1; w < NC; w <<= 1) {
+#pragma unroll
+    for (int i = 0; i + w < NC; i += 2 * w) p[i] = fadd2(p[i], p[i + w]);
+  }
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p[0]));
+  return __fadd_rn(lo, hi);
+}
+
 // Which statistic a pool's pages are scored on, and therefore staged: the min/max rows (true) or
 // the sum row (false).  GENERIC == false fixes the default methods at compile time (far pool by
 // the min/max bound, near pool by the page mean); GENERIC == true reads them from the geometry.
@@ -113,8 +160,8 @@ __device__ __forceinline__ void l1_issue_tile(const loda_geometry& g, const Regi
 // qraw (nfa_layer_batch_selector.py:290-354, 2412-2427).
 template <int DSUB, int TP, bool GENERIC = false>
 __device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const Regions& rg, int p0, int page_end,
-                                                  const unsigned char* stage, const float* qhat, const float* qlow,
-                                                  const float* qhigh, int G, const float* qraw = nullptr) {
+                                                  const unsigned char* stage, const float* qhat, const float* qmm,
+                                                  int G, const float* qraw = nullptr) {
   using T = L1Tile<DSUB, TP>;
   constexpr int NC = DSUB / 8, CS = STAT_GROUP * 16;      // CS: bytes between two chunks of a page
   const int page = p0 + (int)threadIdx.x;
@@ -127,18 +174,18 @@ __device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const 
   const bool use_mm = far ? l1_far_uses_minmax<GENERIC>(g) : l1_near_uses_minmax<GENERIC>(g);
   if (use_mm) {
     const unsigned char* src = stage + grp * T::SLOT + lane * 16;
-    float kmin[DSUB], kmax[DSUB];
+    unsigned long long kp[DSUB];                      // (min_d, max_d) as packed fp32
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
-      unpack8(*(const uint4*)(src + c * CS), *(float(*)[8])(kmin + 8 * c));
-      unpack8(*(const uint4*)(src + (NC + c) * CS), *(float(*)[8])(kmax + 8 * c));
+      const uint4 a = *(const uint4*)(src + c * CS), z = *(const uint4*)(src + (NC + c) * CS);
+      kp[8 * c + 0] = pack_u32x2(a.x << 16, z.x << 16); kp[8 * c + 1] = pack_u32x2(a.x & 0xFFFF0000u, z.x & 0xFFFF0000u);
+      kp[8 * c + 2] = pack_u32x2(a.y << 16, z.y << 16); kp[8 * c + 3] = pack_u32x2(a.y & 0xFFFF0000u, z.y & 0xFFFF0000u);
+      kp[8 * c + 4] = pack_u32x2(a.z << 16, z.z << 16); kp[8 * c + 5] = pack_u32x2(a.z & 0xFFFF0000u, z.z & 0xFFFF0000u);
+      kp[8 * c + 6] = pack_u32x2(a.w << 16, z.w << 16); kp[8 * c + 7] = pack_u32x2(a.w & 0xFFFF0000u, z.w & 0xFFFF0000u);
     }
     float acc = 0.0f;
 #pragma unroll 1
-    for (int j = 0; j < G; ++j) {
-      const float mm = __fadd_rn(dot_chunks<DSUB>(kmin, qlow + j * DSUB), dot_chunks<DSUB>(kmax, qhigh + j * DSUB));
-      acc = __fadd_rn(acc, bf16r(mm));
-    }
+    for (int j = 0; j < G; ++j) acc = __fadd_rn(acc, bf16r(bound_pair<DSUB>(kp, qmm + j * 2 * DSUB)));
     ord = ord16(bf16r(__fdiv_rn(acc, gf)));
   } else {
     // the sums sit in the group's own slot, or in the spill slot when the group also staged min/max rows

@@ -39,7 +39,9 @@ LODA_PHASE_STORAGE(sel)
 LODA_SUB_READER(sel)
 
 constexpr int SF_P = 512;          // threads per CTA = pages per tile
-constexpr int SF_CLUSTER_MAX = 16; // CTAs per row: 16, or 8 when the GPU cannot hold a 16-CTA cluster for every row
+constexpr int SF_CLUSTER_MAX = 16; // CTAs per row: the largest of SF_CLUSTER_SIZES the GPU holds for every row at once
+constexpr int SF_NSIZES = 4;
+constexpr int SF_CLUSTER_SIZES[SF_NSIZES] = {16, 12, 10, 8};
 constexpr int SF_L2_NT = 256;      // threads of the leader that run the level-2 selection
 
 struct FusedLayout {
@@ -113,9 +115,8 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   unsigned char* rows = smem;
   uint64_t* bars = (uint64_t*)(smem + lay.bars);
   float* qhat = (float*)(smem + lay.qv);
-  float* qlow = qhat + G * DSUB;
-  float* qhigh = qlow + G * DSUB;
-  float* qf = qhigh + G * DSUB;
+  float* qmm = qhat + G * DSUB;                      // [G, DSUB, 2]: (min(q, 0), max(q, 0)) interleaved
+  float* qf = qmm + 2 * G * DSUB;
   int* kept = (int*)(smem + lay.kept);
   int* physk = (int*)(smem + lay.physk);
   int* kept2 = (int*)(smem + lay.kept2);
@@ -201,8 +202,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, d)]);
     const float qh = bf16r(__fmul_rn(qv, scale));
     qhat[i] = qh;
-    qlow[i] = fminf(qh, 0.0f);
-    qhigh[i] = fmaxf(qh, 0.0f);
+    *(float2*)(qmm + 2 * i) = make_float2(fminf(qh, 0.0f), fmaxf(qh, 0.0f));
   }
   cluster.barrier_wait();     // (0) every CTA of the cluster runs: its shared memory may be addressed from now on
   __syncthreads();            // (and qhat is complete)
@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     if (!mbar_wait(bars + (it & 1), (uint32_t)(it >> 1) & 1u)) timed_out = true;      // tile it has landed
     const int page = p0 + tid;
     const uint32_t ord = l1_page_score<DSUB, P, false>(g, rg, p0, page_end, rows + (size_t)(it & 1) * lay.rows_bytes, qhat,
-                                                       qlow, qhigh, G);
+                                                       qmm, G);
     l_scall[page] = (uint16_t)ord;                       // into the leader's shared memory
     if (page >= near_lo && page < near_hi && page - near_lo8 < n_near) r1_scn[page - near_lo8] = (uint16_t)ord;
     __syncthreads();                                     // the buffer is free
@@ -540,7 +540,9 @@ bool select_fused_applicable(const loda_geometry& g, int rows) {
   // other level-1 methods and the numeric near-token quota run on the two-launch chain
   if (g.far_method != LODA_FAR_MINMAX || g.near_minmax != 0 || g.near_tokens_p1 > 0) return false;
   if ((size_t)g.max_blocks * 2 + 16 > 40 * 1024) return false;
-  return fused_shape_ok(g, 16) || fused_shape_ok(g, 8);
+  for (int i = 0; i < SF_NSIZES; ++i)
+    if (fused_shape_ok(g, SF_CLUSTER_SIZES[i])) return true;
+  return false;
 }
 
 // whether the launch may also run the attention of the step on a cluster of cs CTAs
@@ -564,10 +566,11 @@ static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, c
   auto kernel = select_fused_kernel<DS, D>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   if (e != cudaSuccess) return e;
-  // clusters of 16 CTAs when the GPU holds one for every row at once, else clusters of 8 (two tiles
-  // per CTA at 128K tokens); the answers are remembered per shape
+  // the largest cluster (16, 12, 10 or 8 CTAs per row) of which the GPU holds one for every row at once: the
+  // more CTAs, the fewer tiles each scores and the more SMs stream the row's statistics (a cluster lives
+  // inside one GPC, so the count that fits depends on the GPCs' sizes); the answers are remembered per shape
   struct Memo { size_t smem; int rows_ok; };
-  static Memo memo[kMaxDevices][3][2] = {};              // (per instantiation of this template)
+  static Memo memo[kMaxDevices][3][SF_NSIZES] = {};      // (per instantiation of this template)
   const int dev = device_ordinal();
   if (dev < 0 || dev >= kMaxDevices) return cudaErrorNotSupported;
   cudaLaunchConfig_t cfg = {};
@@ -581,8 +584,11 @@ static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, c
   cfg.numAttrs = 2;
   cfg.blockDim = dim3(SF_P);
   cfg.stream = st;
-  for (int which = 0; which < 2; ++which) {
-    const int cs = which == 0 ? 16 : 8;
+  const char* force = getenv("LODA_B200_CLUSTER");       // A/B measurements: one cluster size only
+  const int forced = force ? atoi(force) : 0;
+  for (int which = 0; which < SF_NSIZES; ++which) {
+    const int cs = SF_CLUSTER_SIZES[which];
+    if (forced && cs != forced) continue;
     if (!fused_shape_ok(g, cs) || rows * cs > device_sm_count()) continue;
     if (D > 0 && !fused_attend_ok(g, cs)) continue;
     const int tpc = fused_tiles_per_cta(g, cs);
@@ -600,10 +606,14 @@ static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, c
       m.rows_ok = nclusters;
     }
     if (rows > m.rows_ok) continue;                      // the clusters of all rows must run at once
+    g_last_cluster_size = cs;
     return cudaLaunchKernelEx(&cfg, kernel, g, L, B, (const bf16*)q, scale, S, status, ap, tpc, at);
   }
   return cudaErrorNotSupported;
 }
+
+static thread_local int g_last_cluster_size = 0;
+int select_fused_last_cluster() { return g_last_cluster_size; }
 
 void select_fused_refuse(int sub_dims) {
   const int dev = device_ordinal();
