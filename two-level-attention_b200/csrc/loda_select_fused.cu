@@ -515,6 +515,9 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
 constexpr int kMaxDevices = 64;
 static bool g_fused_refused[kMaxDevices][3] = {};    // per sub-space width: a launch failed, stay on the chain
 
+static thread_local int g_last_cluster_size = 0;      // CTAs per row of the calling thread's latest one-launch call
+int select_fused_last_cluster() { return g_last_cluster_size; }
+
 static int fused_slot(int sub_dims) { return sub_dims == 16 ? 0 : sub_dims == 32 ? 1 : 2; }
 
 static int fused_tiles_per_cta(const loda_geometry& g, int cs) {
@@ -611,9 +614,6 @@ static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, c
   }
   return cudaErrorNotSupported;
 }
-
-static thread_local int g_last_cluster_size = 0;
-int select_fused_last_cluster() { return g_last_cluster_size; }
 
 void select_fused_refuse(int sub_dims) {
   const int dev = device_ordinal();
