@@ -295,7 +295,7 @@ int loda_decode_step(const loda_geometry* g, const loda_layer* layer, const loda
 int loda_last_decode_launches(void);
 
 /* CTAs per (request, kv head) row of the one-launch kernel as the latest call of this thread launched it
- * (16, 12, 10 or 8: the largest thread-block cluster of which the GPU held one for every row), 0 if the
+ * (16, or 8 where the GPU cannot hold a cluster of 16 for every row), 0 if the
  * call ran the separate launches.  For benchmarks and logs. */
 int loda_last_decode_cluster(void);
 

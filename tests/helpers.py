@@ -17,8 +17,12 @@ def bf16_to_f32_np(t):
 
 
 def oracle_config(setup):
+    import numpy as np
     a, ix, c = setup.args, setup.indexer, setup.cache
+    lo0, lo1, dsub = ix.subspace_ranges()
+    dims = np.concatenate((np.arange(lo0, lo0 + dsub // 2), np.arange(lo1, lo1 + dsub // 2)))
     return O.SelectorConfig(
+        dims=dims,
         head_dim=c.layers[0].head_dim_k, num_q_heads=c.num_query_heads, num_kv_heads=c.num_kv_heads,
         block_size=setup.page, max_blocks=setup.max_blocks, level1_topk=int(a.tia_level1_topk),
         near_pages=int(a.nfa_near_pages), near_len=int(a.nfa_near_len), level2_topk=int(a.tia_level2_topk),

@@ -14,7 +14,7 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-SOURCES = ["loda_append.cu", "loda_l1.cu", "loda_l2.cu", "loda_select_fused.cu", "loda_attn.cu", "loda_tia.cu",
+SOURCES = ["loda_append.cu", "loda_l1.cu", "loda_l2.cu", "loda_select_fused.cu", "loda_attn.cu", "loda_attn_mla.cu", "loda_tia.cu",
            "loda_tls.cu", "loda_shard.cu", "loda_capi.cu"]
 LIB = os.path.join(HERE, "libloda_b200.so")
 OBJ_DIR = os.path.join(HERE, "build")

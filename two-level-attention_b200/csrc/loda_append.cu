@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(256) write_prefill_kernel(
     const size_t src_row = (size_t)kv * n_tokens + n;
     if (c < ck)
       ((uint4*)((bf16*)L.pool_k + dst_row * g.head_dim))[c] = ((const uint4*)(k + src_row * g.head_dim))[c];
-    else
+    else if (L.pool_v != L.pool_k)      // shared-latent layout: no separate value rows
       ((uint4*)((bf16*)L.pool_v + dst_row * g.head_dim_v))[c - ck] =
           ((const uint4*)(v + src_row * g.head_dim_v))[c - ck];
   }

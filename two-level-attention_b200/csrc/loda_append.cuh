@@ -102,7 +102,9 @@ __device__ __forceinline__ void append_row(
     bf16* kdst = (bf16*)L.pool_k + dst_row * g.head_dim;
     bf16* vdst = (bf16*)L.pool_v + dst_row * g.head_dim_v;
     for (int c = lane; c < g.head_dim / 8; c += 32) ((uint4*)kdst)[c] = ((const uint4*)ksrc)[c];
-    for (int c = lane; c < g.head_dim_v / 8; c += 32) ((uint4*)vdst)[c] = ((const uint4*)vsrc)[c];
+    // shared-latent layout (pool_v aliases pool_k): the value is the head of the key row just written
+    if (L.pool_v != L.pool_k)
+      for (int c = lane; c < g.head_dim_v / 8; c += 32) ((uint4*)vdst)[c] = ((const uint4*)vsrc)[c];
     if (pad) return;
   }
   if (L.page_mm == nullptr || B.active_req_ids[row] < 0) return;

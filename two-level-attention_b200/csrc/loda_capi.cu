@@ -29,6 +29,9 @@ cudaError_t launch_select_fused(const loda_geometry&, const loda_layer&, const l
                                 const loda_selection&, uint32_t*, const AppendArgs&, cudaStream_t);
 cudaError_t launch_attn(const loda_geometry&, const loda_layer&, const void*, const int32_t*, const int32_t*,
                         const int32_t*, int, int, float, void*, float*, const AttnWorkspace&, bool, bool, bool, cudaStream_t);
+cudaError_t launch_attn_mla(const loda_geometry&, const loda_layer&, const void*, const int32_t*, const int32_t*,
+                            const int32_t*, int, int, float, void*, float*, const AttnWorkspace&, bool, bool, uint32_t*,
+                            cudaStream_t);
 size_t l1_smem_bytes(const loda_geometry&);
 size_t l2_smem_bytes(const loda_geometry&);
 int attn_nsplit(const loda_geometry&, int);
@@ -198,8 +201,15 @@ int check_gather_attend_args(const loda_geometry* g, const loda_layer* layer, co
     return fail(LODA_ERR_ARGUMENT, "n_query must be in [0, max_query_tokens]");
   if (n_query > 0 && (!q || !gather || !visible_lens || !query_to_req || !out || n_req_rows < 1))
     return fail(LODA_ERR_ARGUMENT, "gather attention needs q, gather, visible_lens, query_to_req and out");
+  if (g->head_dim == 576 && g->head_dim_v == 512) {
+    // shared-latent layout: the value row is the first 512 dims of the key row
+    if (layer->pool_v != layer->pool_k || g->num_kv_heads != 1 || g->num_q_heads > 16)
+      return fail(LODA_ERR_UNSUPPORTED, "head dims 576 / 512 are served for the shared-latent layout only: "
+                                        "pool_v == pool_k, one kv head, at most 16 query heads");
+    return LODA_OK;
+  }
   if (!((g->head_dim == 128 && g->head_dim_v == 128) || (g->head_dim == 64 && g->head_dim_v == 64)))
-    return fail(LODA_ERR_UNSUPPORTED, "gather attention supports head dims 64 and 128");
+    return fail(LODA_ERR_UNSUPPORTED, "gather attention supports head dims 64 and 128, and 576 / 512 with a shared latent");
   return LODA_OK;
 }
 
@@ -342,6 +352,10 @@ static int gather_attend_impl(const loda_geometry* g, const loda_layer* layer, c
   char* base = (char*)workspace;
   const AttnWorkspace ws{(int*)(base + w.at_ticket), (float*)(base + w.at_m), (float*)(base + w.at_z),
                          (float*)(base + w.at_o)};
+  if (g->head_dim == 576)
+    return check_cuda(launch_attn_mla(*g, *layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale, out,
+                                      lse, ws, chained, identity, nullptr, (cudaStream_t)stream),
+                      "gather_attend/latent");
   return check_cuda(launch_attn(*g, *layer, q, gather, visible_lens, query_to_req, n_query, n_req_rows, scale,
                                 out, lse, ws, /*allow_cluster=*/true, chained, identity, (cudaStream_t)stream),
                     "gather_attend");

@@ -39,9 +39,11 @@ LODA_PHASE_STORAGE(sel)
 LODA_SUB_READER(sel)
 
 constexpr int SF_P = 512;          // threads per CTA = pages per tile
-constexpr int SF_CLUSTER_MAX = 16; // CTAs per row: the largest of SF_CLUSTER_SIZES the GPU holds for every row at once
-constexpr int SF_NSIZES = 4;
-constexpr int SF_CLUSTER_SIZES[SF_NSIZES] = {16, 12, 10, 8};
+constexpr int SF_CLUSTER_MAX = 16; // CTAs per row: 16, or 8 when the GPU cannot hold a 16-CTA cluster for every row
+// (clusters of 12 and 10 were measured too: where 16 do not fit, 10 did, and ran the step slower than 8 —
+// 27.0 against 26.6 us per layer-step at 131 072 tokens: every extra CTA lengthens the cluster barriers)
+constexpr int SF_NSIZES = 2;
+constexpr int SF_CLUSTER_SIZES[SF_NSIZES] = {16, 8};
 constexpr int SF_L2_NT = 256;      // threads of the leader that run the level-2 selection
 
 struct FusedLayout {
@@ -55,6 +57,10 @@ __host__ __device__ inline FusedLayout fused_layout(const loda_geometry& g, int 
   // one tile stage: 16 groups of min/max rows and the spill slot of sums (L1Tile<d', 512>::STAGE)
   const size_t rows = (size_t)(SF_P / STAT_GROUP) * 128 * g.sub_dims + 64 * (size_t)g.sub_dims;
   f.rows_bytes = rows > L1_TAIL_BYTES ? rows : L1_TAIL_BYTES;
+  // the attention phase lays a tile of up to 128 tokens (K rows, V rows, slots) and the warps' partial
+  // outputs over the staging area: a single buffer must hold that much
+  const size_t attend = ((size_t)128 * ((size_t)(g.head_dim + 8) * 2 + (size_t)(g.head_dim_v + 8) * 2 + 4) + 127) & ~(size_t)127;
+  if (tiles_per_cta <= 1 && f.rows_bytes < attend && g.head_dim == 128 && g.head_dim_v == 128) f.rows_bytes = attend;
   size_t off = f.rows_bytes * (tiles_per_cta > 1 ? 2 : 1);      // two staging buffers when a CTA has several tiles
   f.bars = off; off += 16;                                             // one mbarrier per staging buffer
   f.qv = off; off += (size_t)(3 * G + 1) * g.sub_dims * 4;             // qhat, qlow, qhigh [G][d'], qf [d']
@@ -569,9 +575,8 @@ static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, c
   auto kernel = select_fused_kernel<DS, D>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   if (e != cudaSuccess) return e;
-  // the largest cluster (16, 12, 10 or 8 CTAs per row) of which the GPU holds one for every row at once: the
-  // more CTAs, the fewer tiles each scores and the more SMs stream the row's statistics (a cluster lives
-  // inside one GPC, so the count that fits depends on the GPCs' sizes); the answers are remembered per shape
+  // clusters of 16 CTAs when the GPU holds one for every row at once (a cluster lives inside one GPC, so the
+  // count that fits depends on the GPCs' sizes), else clusters of 8; the answers are remembered per shape
   struct Memo { size_t smem; int rows_ok; };
   static Memo memo[kMaxDevices][3][SF_NSIZES] = {};      // (per instantiation of this template)
   const int dev = device_ordinal();

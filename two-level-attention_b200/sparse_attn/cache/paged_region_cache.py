@@ -48,7 +48,7 @@ class GraphReadyPagedRegionLayer:
     the all-zero PAD page that invalid block-table entries point to."""
 
     def __init__(self, *, geometry, max_physical_pages, num_kv_heads, num_query_heads=None,
-                 head_dim_k, head_dim_v, dtype, device):
+                 head_dim_k, head_dim_v, dtype, device, shared_latent=False):
         self.geometry = geometry
         self.max_physical_pages = max_physical_pages
         self.PAD_PAGE_ID = max_physical_pages
@@ -60,9 +60,19 @@ class GraphReadyPagedRegionLayer:
         self.device = torch.device(device)
         total, page = max_physical_pages + 1, geometry.page
         self.kv_pool_k = torch.empty((total, 1, num_kv_heads, page, head_dim_k), dtype=dtype, device=device)
-        self.kv_pool_v = torch.empty((total, 1, num_kv_heads, page, head_dim_v), dtype=dtype, device=device)
+        # shared_latent: the value of a token is the first head_dim_v dims of its key row (multi-head latent
+        # attention in its absorbed form: one latent per token serves as key and as value); kv_pool_v is
+        # then a view of kv_pool_k and the kernels read a token's row once
+        self.shared_latent = bool(shared_latent)
+        if self.shared_latent:
+            if head_dim_v > head_dim_k:
+                raise ValueError("a shared latent needs head_dim_v <= head_dim_k")
+            self.kv_pool_v = self.kv_pool_k[..., :head_dim_v]
+        else:
+            self.kv_pool_v = torch.empty((total, 1, num_kv_heads, page, head_dim_v), dtype=dtype, device=device)
         self.kv_pool_k[self.PAD_PAGE_ID].zero_()
-        self.kv_pool_v[self.PAD_PAGE_ID].zero_()
+        if not self.shared_latent:
+            self.kv_pool_v[self.PAD_PAGE_ID].zero_()
         self.free_ids = list(range(max_physical_pages))
         heapq.heapify(self.free_ids)
         # selector index (ensure_index)
@@ -81,7 +91,7 @@ class GraphReadyPagedRegionCache:
 
     def __init__(self, n_layers, geometry, *, max_requests, max_physical_pages, max_blocks,
                  max_visible_len, max_query_tokens, num_kv_heads, num_query_heads=None,
-                 head_dim_k, head_dim_v, dtype, device, visible_buckets=None):
+                 head_dim_k, head_dim_v, dtype, device, visible_buckets=None, shared_latent=False):
         device = torch.device(device)
         if device.type != "cuda":
             raise FallbackRequired("the paged cache of this package lives on a CUDA device")
@@ -100,7 +110,7 @@ class GraphReadyPagedRegionCache:
             GraphReadyPagedRegionLayer(
                 geometry=geometry, max_physical_pages=max_physical_pages, num_kv_heads=num_kv_heads,
                 num_query_heads=self.num_query_heads, head_dim_k=head_dim_k, head_dim_v=head_dim_v,
-                dtype=dtype, device=device)
+                dtype=dtype, device=device, shared_latent=shared_latent)
             for _ in range(n_layers)]
         self.states: dict[int, RequestState] = {}
         self.pending_lengths: dict[int, int] = {}

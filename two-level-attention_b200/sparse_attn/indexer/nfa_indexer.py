@@ -92,6 +92,8 @@ class NFAIndexer:
         if self.subspace == "tail":
             if self.head_dim == 256:       # [NoPE192 | RoPE64]: 16 lowest-frequency dims of each RoPE half
                 return 208, 240, 32
+            if self.head_dim == 576:       # shared latent [compressed 512 | RoPE64]: the same 16 + 16 rotary dims
+                return 528, 560, 32
             half = self.head_dim // 2
             delta = half // self.cmp_ratio
             return half - delta, self.head_dim - delta, 2 * delta
