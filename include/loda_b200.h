@@ -325,9 +325,12 @@ int loda_shard_workspace_regions(const loda_geometry* g, int64_t* out);
 int loda_shard_l1_scores(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
                          const void* q, float scale, const loda_selection* sel, void* workspace,
                          void* stream);
+/* gathered (may be NULL): the score rows of all shard_count GPUs after an all-gather, shard_count blocks of
+ * the size loda_shard_workspace_regions reports for the level, in rank order; the selection ORs them while it
+ * loads the row.  NULL: the caller has already combined the rows inside the workspace. */
 int loda_shard_l1_select(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
-                         const void* q, float scale, const loda_selection* sel, void* workspace,
-                         void* stream);
+                         const void* q, float scale, const loda_selection* sel, const void* gathered,
+                         void* workspace, void* stream);
 /* level 2: logits of the candidate slots on this GPU's pages -> workspace | quota
  * selection, hole fill and union on the combined logits -> gather, visible_lens */
 int loda_shard_l2_scores(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
@@ -335,7 +338,15 @@ int loda_shard_l2_scores(const loda_geometry* g, const loda_layer* layer, const 
                          void* workspace, void* stream);
 int loda_shard_l2_select(const loda_geometry* g, const loda_layer* layer, const loda_batch* b,
                          const void* q, float scale, const loda_selection* sel, uint32_t* status,
-                         void* workspace, void* stream);
+                         const void* gathered, void* workspace, void* stream);
+
+/* Fixed-order log-sum-exp merge of n_parts partial attentions (loda_gather_attend_lse on disjoint token
+ * sets, e.g. the GPUs of a sequence-sharded request after an all-gather): part r lies part_stride_bytes
+ * after part r - 1 and holds out [n_rows, dv] bf16 at byte 0 and lse [n_rows, 2] float at lse_offset_bytes;
+ * out [n_rows, dv] float.  Parts merge in index order, so every GPU that merges the same parts gets the same
+ * bits; a part with sum 0 contributes nothing; all sums 0 give zeros. */
+int loda_lse_merge(const void* parts, int64_t part_stride_bytes, int64_t lse_offset_bytes, int32_t n_parts,
+                   int32_t n_rows, int32_t dv, float* out, void* stream);
 
 /* ---- kernels under the TIA indexer's method surface -------------------------
  * (sparse_attn/indexer/tia_indexer.py; tensors bf16 or fp32, dtype = LODA_DTYPE_*) */

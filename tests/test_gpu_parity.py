@@ -530,3 +530,50 @@ def test_disjoint_protected_and_middle_arms_equal_the_single_list_path():
                 got = torch.cat((pg[bi, kv, :sk], mg[bi, kv, :nm], pg[bi, kv, sk:npr]))
                 assert torch.equal(got, want)
         torch.testing.assert_close(out.float(), ref_out.float(), atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sequence_sharded_stages_on_gathered_rows_and_the_merge_kernel(world):
+    """The same emulation through the buffers the NCCL path uses: the score rows of all views stacked
+    (what all_gather_into_tensor delivers) and ORed by the selecting CTAs while loading, the packed
+    partial attentions stacked and merged by loda_lse_merge."""
+    import ctypes as C
+    from helpers import make_setup, mod
+    sharding = mod("sharding")
+    capi = mod("_capi")
+    setup = make_setup([9000, 300, 20000], seed=12)
+    ref_out = _run_step(setup)
+    cache = setup.cache
+    ref_gather = cache.gather_indices_for_layer(0).clone()
+    ref_lens = cache.visible_lens_for_layer(0).clone()
+    b = len(setup.req_ids)
+    q, scale = setup.q.contiguous(), float(setup.attention.scaling)
+    views = [sharding.SequenceShard(cache, setup.indexer, r, world) for r in range(world)]
+    xs = [v.exchange_buffers(b) for v in views]
+    for v in views:
+        v.l1_scores_stage(0, b, q, scale)
+    l1 = torch.stack([v.l1_scores for v in views])
+    for v in views:
+        v.l1_select_stage(0, b, q, scale, gathered=l1)
+        v.l2_scores_stage(0, b, q, scale)
+    l2 = torch.stack([v.l2_scores for v in views])
+    for v, x in zip(views, xs):
+        v.l2_select_stage(0, b, q, scale, gathered=l2)
+        v.attend_stage(0, b, q, scale, out=x["out"], lse=x["lse"])
+    parts = torch.stack([x["part"] for x in xs])
+    x = xs[0]
+    hq, dv = x["out"].shape[1], x["out"].shape[2]
+    capi.check(capi.lib().loda_lse_merge(capi.ptr(parts), x["part_bytes"], x["lse_off"], world, b * hq, dv,
+                                         capi.ptr(x["merged"]), capi.current_stream()))
+    torch.cuda.synchronize()
+    assert cache.read_status() == 0
+    for v in views:
+        assert torch.equal(v.visible_lens[:b], ref_lens[:b])
+    n = int(ref_lens[:b].max())
+    stacked = torch.stack([v.gather[:b, :, :n] for v in views])
+    valid = torch.arange(n, device=stacked.device)[None, None, :] < ref_lens[:b, :, None]
+    assert torch.equal(stacked.clamp_min(-1).max(0).values[valid], ref_gather[:b, :, :n][valid])
+    torch.testing.assert_close(x["merged"], ref_out.float(), atol=ATOL, rtol=RTOL)
+    want = sharding.lse_merge(torch.stack([y["out"].float() for y in xs]), torch.stack([y["lse"][..., 0] for y in xs]),
+                              torch.stack([y["lse"][..., 1] for y in xs]))
+    torch.testing.assert_close(x["merged"], want, atol=1e-5, rtol=1e-5)

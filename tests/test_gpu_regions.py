@@ -125,3 +125,14 @@ def test_token_selection_type_matches_the_reference_contract():
                                           width=indices.shape[-1])
     assert torch.equal(again.counts, counts)
     assert torch.equal(again.indices * again.valid(), indices * picked.valid())
+
+
+@pytest.mark.parametrize("nreq", [10, 12, 18])
+def test_batches_whose_attention_splits_in_two(nreq):
+    """Between 74 and 147 (request, kv head) pairs the attention splits every list over two CTAs, each of
+    which merges more output elements than it has threads."""
+    from helpers import make_setup
+    lengths = [3000 + 517 * i for i in range(nreq)]
+    setup = make_setup(lengths, seed=65)
+    out = _run_step(setup)
+    _check_against_oracle(setup, out)

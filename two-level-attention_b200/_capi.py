@@ -59,7 +59,7 @@ EXPORTS = ("loda_version", "loda_last_error", "loda_workspace_bytes", "loda_appe
            "loda_select_step", "loda_tia_quant4", "loda_tia_block_minmax", "loda_tia_scores", "loda_gather_attend_lse",
            "loda_tls_store_kv", "loda_tls_store_k_index", "loda_tls_level1", "loda_tls_level2",
            "loda_shard_workspace_regions", "loda_shard_l1_scores", "loda_shard_l1_select", "loda_shard_l2_scores",
-           "loda_shard_l2_select", "loda_protected_gather", "loda_last_decode_launches", "loda_last_decode_cluster")
+           "loda_shard_l2_select", "loda_protected_gather", "loda_last_decode_launches", "loda_last_decode_cluster", "loda_lse_merge")
 
 _lib = None
 
@@ -101,9 +101,10 @@ def lib():
     L.loda_protected_gather.argtypes = [G, LY, B, P, P, P, V]
     L.loda_shard_workspace_regions.argtypes = [G, P]
     L.loda_shard_l1_scores.argtypes = [G, LY, B, P, F, S, P, V]
-    L.loda_shard_l1_select.argtypes = [G, LY, B, P, F, S, P, V]
+    L.loda_shard_l1_select.argtypes = [G, LY, B, P, F, S, P, P, V]
     L.loda_shard_l2_scores.argtypes = [G, LY, B, P, F, S, P, P, V]
-    L.loda_shard_l2_select.argtypes = [G, LY, B, P, F, S, P, P, V]
+    L.loda_shard_l2_select.argtypes = [G, LY, B, P, F, S, P, P, P, V]
+    L.loda_lse_merge.argtypes = [P, C.c_int64, C.c_int64, I, I, I, P, V]
     for name in EXPORTS[3:]:
         getattr(L, name).restype = C.c_int
     _lib = L

@@ -231,8 +231,9 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
     cluster.sync();
     LODA_PHASE(attn, cta_id, 7);
     const int per = (G * DV + nsplit - 1) / nsplit;
-    const int e = split * per + tid;
-    if (tid < per && e < G * DV) {
+    const int e_end = min((split + 1) * per, G * DV);
+#pragma unroll 1
+    for (int e = split * per + tid; e < e_end; e += ATT_NT) {      // a slice may hold more elements than the CTA has threads
       const int gi = e / DV, dv = e % DV;
       float pm[ATT_MAX_SPLIT], pz[ATT_MAX_SPLIT], po[ATT_MAX_SPLIT];
 #pragma unroll

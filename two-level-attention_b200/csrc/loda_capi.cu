@@ -404,7 +404,7 @@ int loda_shard_workspace_regions(const loda_geometry* g, int64_t* out) {
 
 static int shard_stage(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q, float scale,
                        const loda_selection* sel, uint32_t* status, void* workspace, void* stream, int level,
-                       int phase) {
+                       int phase, const void* gathered = nullptr) {
   LODA_TRY(check_geometry(g));
   LODA_TRY(check_layer(layer));
   LODA_TRY(check_batch(g, b));
@@ -413,7 +413,13 @@ static int shard_stage(const loda_geometry* g, const loda_layer* layer, const lo
   if (!q || !sel || !workspace) return fail(LODA_ERR_ARGUMENT, "staged selector needs q, a selection struct and a workspace");
   if (level == 2 && phase == 2 && (!sel->gather || !sel->visible_lens))
     return fail(LODA_ERR_ARGUMENT, "the level-2 selection needs gather and visible_lens");
-  const SelectWorkspace ws = select_ws(*g, workspace);
+  SelectWorkspace ws = select_ws(*g, workspace);
+  if (gathered != nullptr) {      // the score rows of all GPUs, stacked: ORed by the selecting CTA while loading
+    const size_t rows = (size_t)g->max_query_tokens * g->num_kv_heads;
+    ws.gathered = (const uint16_t*)gathered;
+    ws.n_gathered = g->shard_count;
+    ws.gathered_stride = level == 1 ? rows * (size_t)l1_score_stride(*g) : rows * (size_t)(g->k_far + g->k_near + 2) * g->page;
+  }
   if (level == 1) {
     const AppendArgs none{nullptr, nullptr, nullptr, nullptr, 0};
     loda_selection no_lists = *sel;
@@ -429,16 +435,17 @@ int loda_shard_l1_scores(const loda_geometry* g, const loda_layer* layer, const 
   return shard_stage(g, layer, b, q, scale, sel, nullptr, workspace, stream, 1, 1);
 }
 int loda_shard_l1_select(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
-                         float scale, const loda_selection* sel, void* workspace, void* stream) {
-  return shard_stage(g, layer, b, q, scale, sel, nullptr, workspace, stream, 1, 2);
+                         float scale, const loda_selection* sel, const void* gathered, void* workspace, void* stream) {
+  return shard_stage(g, layer, b, q, scale, sel, nullptr, workspace, stream, 1, 2, gathered);
 }
 int loda_shard_l2_scores(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
                          float scale, const loda_selection* sel, uint32_t* status, void* workspace, void* stream) {
   return shard_stage(g, layer, b, q, scale, sel, status, workspace, stream, 2, 1);
 }
 int loda_shard_l2_select(const loda_geometry* g, const loda_layer* layer, const loda_batch* b, const void* q,
-                         float scale, const loda_selection* sel, uint32_t* status, void* workspace, void* stream) {
-  return shard_stage(g, layer, b, q, scale, sel, status, workspace, stream, 2, 2);
+                         float scale, const loda_selection* sel, uint32_t* status, const void* gathered, void* workspace,
+                         void* stream) {
+  return shard_stage(g, layer, b, q, scale, sel, status, workspace, stream, 2, 2, gathered);
 }
 
 static thread_local int g_last_decode_launches = 0;

@@ -1044,6 +1044,13 @@ struct SelectWorkspace {
   int* phys;             // [rows, k_far + k_near + 2]: their physical page ids (-1 = invalid)
   int* np;               // [rows]
   uint16_t* l2_scores;   // [rows, (k_far + k_near + 2) * page]: ordered bf16 logit per candidate slot
+  // sequence sharding, selection phases: the score rows of all GPUs after an all-gather, [n_gathered] blocks
+  // of the same shape as l1_scores (level 1) or l2_scores (level 2), gathered_stride elements apart; the
+  // selecting CTA ORs them while loading (every page / slot is scored by exactly one GPU, the others hold 0).
+  // NULL: the rows in l1_scores / l2_scores are already combined.
+  const uint16_t* gathered = nullptr;
+  int n_gathered = 0;
+  size_t gathered_stride = 0;
 };
 struct AttnWorkspace {
   int* ticket;    // [n_query * Hkv], zero between launches

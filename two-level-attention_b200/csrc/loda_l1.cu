@@ -172,15 +172,25 @@ __global__ void __launch_bounds__(P, 2) l1_kernel(loda_geometry g, loda_layer L,
   {
     // all the loads of a batch are issued before the first is used (one round trip, not one per load)
     const uint4* src = (const uint4*)row_scores;         // 8 scores per load; unscored pages hold 0
+    // sequence sharding: the rows of all GPUs, ORed while loading
+    auto ldrow = [&](int c) {
+      if (ws.gathered == nullptr) return __ldcg(src + c);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      for (int s = 0; s < ws.n_gathered; ++s) {
+        const uint4 u = __ldcg((const uint4*)(ws.gathered + s * ws.gathered_stride + (size_t)row * ws.score_stride) + c);
+        v.x |= u.x; v.y |= u.y; v.z |= u.z; v.w |= u.w;
+      }
+      return v;
+    };
     const int nc_far = (n_far + 7) / 8, nc_near = (n_near + 7) / 8;          // nc_near <= L1_NEAR_CAP / 8 <= P
     uint4 nreg = make_uint4(0u, 0u, 0u, 0u);
-    if (tid < nc_near) nreg = __ldcg(src + near_lo8 / 8 + tid);
+    if (tid < nc_near) nreg = ldrow(near_lo8 / 8 + tid);
     for (int c0 = 0; c0 < nc_far; c0 += 4 * P) {
       uint4 f[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const int c = c0 + k * P + tid;
-        f[k] = c < nc_far ? __ldcg(src + c) : make_uint4(0u, 0u, 0u, 0u);
+        f[k] = c < nc_far ? ldrow(c) : make_uint4(0u, 0u, 0u, 0u);
       }
 #pragma unroll
       for (int k = 0; k < 4; ++k) {

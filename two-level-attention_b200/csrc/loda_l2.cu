@@ -103,16 +103,56 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
   const int np = min(__ldcg(ws.np + row), np_max);
   const int nitems = np * g.page;
   uint16_t* row_scores = ws.l2_scores + (size_t)row * np_max * g.page;
+  // the row's page list (at most k_far + k_near + 2 entries) in shared memory: the scoring loop and the
+  // selection both index it
+  for (int i = tid; i < np; i += NT) {
+    pages[i] = __ldcg(ws.pages + (size_t)row * np_max + i);
+    physs[i] = __ldcg(ws.phys + (size_t)row * np_max + i);
+  }
+  __syncthreads();
   // ---- score this CTA's share of the candidate slots ---------------------------
+  // U slots per thread and round: first every slot's codes and (scale, zero) are requested, then the
+  // logits are formed — one round trip to memory per round instead of one per slot
   {
+    constexpr int U = 4, WORDS = DSUB / 8;
+    const int pl2 = 31 - __clz(g.page), pmask = g.page - 1;         // page is a power of two
     const int per = ((nitems + nsplit - 1) / nsplit + 7) & ~7;         // multiple of 8 slots
     const int lo = min(split * per, nitems), hi = phase == 2 ? lo : min(lo + per, nitems);
-    for (int idx = lo + tid; idx < hi; idx += NT) {
-      const int i = idx >> (31 - __clz(g.page)), o = idx & (g.page - 1);      // page is a power of two
-      const int pg = __ldcg(ws.pages + (size_t)row * np_max + i);
-      const int ph = __ldcg(ws.phys + (size_t)row * np_max + i);
-      const uint32_t ord = l2_slot_score<DSUB>(g, L, rg, length, kv, pg, ph, o, qf, status);
-      row_scores[idx] = (uint16_t)ord;
+#pragma unroll 1
+    for (int base = lo + tid; base < hi; base += U * NT) {
+      uint32_t w[U][WORDS];
+      __nv_bfloat162 sz[U];
+      bool ok[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = base + u * NT;
+        ok[u] = false;
+        if (idx < hi) {
+          const int i = idx >> pl2, o = idx & pmask;
+          const int pg = pages[i], ph = physs[i];
+          const int tok = pg * g.page + o;
+          if (ph >= 0 && tok >= g.sink && tok < rg.swa_lo_tok && tok < length && tok >= rg.lower && tok < rg.upper) {
+            const size_t trow = ((size_t)ph * g.num_kv_heads + kv) * g.page + o;
+            sz[u] = *(const __nv_bfloat162*)((const bf16*)L.tail_sz + trow * 2);
+            l2_load_codes<DSUB>((const uint8_t*)L.tail_code + trow * (DSUB / 2), w[u]);
+            ok[u] = true;
+          } else if (ph < 0 && status && rg.shard_count <= 1) {      // under sequence sharding a missing page is another GPU's
+            atomicOr(status, LODA_STATUS_BAD_PAGE);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = base + u * NT;
+        if (idx < hi) {
+          uint32_t ord = 0;
+          if (ok[u]) {
+            const float lg = l2_logit_words<DSUB>(w[u], __low2float(sz[u]), __high2float(sz[u]), qf);
+            if (lg == lg && lg != -INFINITY) ord = ord16(lg);
+          }
+          row_scores[idx] = (uint16_t)ord;
+        }
+      }
     }
   }
   LODA_PHASE(l2, cta_id, 3);
@@ -130,10 +170,18 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
     if (!sh[0]) return;
     __threadfence();
   }
-  for (int i = tid; i < (nitems + 7) / 8; i += NT) ((uint4*)sc)[i] = __ldcg((const uint4*)row_scores + i);
-  for (int i = tid; i < np; i += NT) {
-    pages[i] = __ldcg(ws.pages + (size_t)row * np_max + i);
-    physs[i] = __ldcg(ws.phys + (size_t)row * np_max + i);
+  for (int i = tid; i < (nitems + 7) / 8; i += NT) {
+    uint4 v;
+    if (ws.gathered == nullptr) {
+      v = __ldcg((const uint4*)row_scores + i);
+    } else {                                               // sequence sharding: the rows of all GPUs, ORed while loading
+      v = make_uint4(0u, 0u, 0u, 0u);
+      for (int s = 0; s < ws.n_gathered; ++s) {
+        const uint4 u = __ldcg((const uint4*)(ws.gathered + s * ws.gathered_stride + (size_t)row * np_max * g.page) + i);
+        v.x |= u.x; v.y |= u.y; v.z |= u.z; v.w |= u.w;
+      }
+    }
+    ((uint4*)sc)[i] = v;
   }
   __syncthreads();
 #if LODA_PDL_TRIGGER == 3

@@ -349,26 +349,15 @@ __device__ __forceinline__ int l1_select_pages(const loda_geometry& g, const Reg
   return np;
 }
 
+// Logit of one token from its packed 4-bit codes (WORDS 32-bit words, dim 2i in the low nibble of byte i):
+// de-quantised key bf16(bf16(code * scale) - zero), one left-to-right fp32 chain of separate multiplies
+// and adds over the d' dims, rounded to bf16.
 // ROLLED: one loop body per word of codes, for a caller that scores a single slot per thread (the
 // straight-line form costs more in instruction fetch there than its arithmetic)
 template <int DSUB, bool ROLLED = false>
-__device__ __forceinline__ float l2_logit(const uint8_t* __restrict__ codes, float scale, float zero,
-                                          const float* __restrict__ qf) {
+__device__ __forceinline__ float l2_logit_words(uint32_t (&w)[DSUB / 8], float scale, float zero,
+                                                const float* __restrict__ qf) {
   constexpr int WORDS = DSUB / 8;   // 32-bit words of packed codes
-  uint32_t w[WORDS];
-  if constexpr (WORDS == 4) {
-    const uint4 u = *(const uint4*)codes;
-    w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
-  } else if constexpr (WORDS == 2) {
-    const uint2 u = *(const uint2*)codes;
-    w[0] = u.x; w[1] = u.y;
-  } else {
-#pragma unroll
-    for (int i = 0; i < WORDS; i += 4) {
-      const uint4 u = *(const uint4*)(codes + 4 * i);
-      w[i] = u.x; w[i + 1] = u.y; w[i + 2] = u.z; w[i + 3] = u.w;
-    }
-  }
   float acc = 0.0f;
   if constexpr (ROLLED) {
 #pragma unroll 1
@@ -395,6 +384,32 @@ __device__ __forceinline__ float l2_logit(const uint8_t* __restrict__ codes, flo
     }
   }
   return bf16r(acc);
+}
+
+template <int DSUB>
+__device__ __forceinline__ void l2_load_codes(const uint8_t* __restrict__ codes, uint32_t (&w)[DSUB / 8]) {
+  constexpr int WORDS = DSUB / 8;
+  if constexpr (WORDS == 4) {
+    const uint4 u = *(const uint4*)codes;
+    w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
+  } else if constexpr (WORDS == 2) {
+    const uint2 u = *(const uint2*)codes;
+    w[0] = u.x; w[1] = u.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < WORDS; i += 4) {
+      const uint4 u = *(const uint4*)(codes + 4 * i);
+      w[i] = u.x; w[i + 1] = u.y; w[i + 2] = u.z; w[i + 3] = u.w;
+    }
+  }
+}
+
+template <int DSUB, bool ROLLED = false>
+__device__ __forceinline__ float l2_logit(const uint8_t* __restrict__ codes, float scale, float zero,
+                                          const float* __restrict__ qf) {
+  uint32_t w[DSUB / 8];
+  l2_load_codes<DSUB>(codes, w);
+  return l2_logit_words<DSUB, ROLLED>(w, scale, zero, qf);
 }
 
 // Ordered 16-bit logit of candidate slot (logical page pg, physical page ph, offset o); 0 = the

@@ -595,8 +595,11 @@ static cudaError_t launch_fused_d(const loda_geometry& g, const loda_layer& L, c
   const char* force = getenv("LODA_B200_CLUSTER");       // A/B measurements: one cluster size only
   const int forced = force ? atoi(force) : 0;
   for (int which = 0; which < SF_NSIZES; ++which) {
-    const int cs = SF_CLUSTER_SIZES[which];
-    if (forced && cs != forced) continue;
+    int cs = SF_CLUSTER_SIZES[which];
+    if (forced >= 3 && forced <= SF_CLUSTER_MAX) {         // a forced size need not be one of the defaults
+      if (which > 0) break;
+      cs = forced;
+    }
     if (!fused_shape_ok(g, cs) || rows * cs > device_sm_count()) continue;
     if (D > 0 && !fused_attend_ok(g, cs)) continue;
     const int tpc = fused_tiles_per_cta(g, cs);

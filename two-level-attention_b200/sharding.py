@@ -161,7 +161,7 @@ class SequenceShard:
     def owns_token(self, position):
         return (position // self.cache.geometry.page) % self.world == self.rank
 
-    def _call(self, fn, layer_idx, batch, q, scale, with_status):
+    def _call(self, fn, layer_idx, batch, q, scale, with_status, gathered=False):
         import ctypes as C
 
         from . import _capi
@@ -171,6 +171,8 @@ class SequenceShard:
                 _capi.ptr(q), float(scale), C.byref(sel)]
         if with_status:
             args.append(C.c_void_p(cache.status_buf.data_ptr()))
+        if gathered is not False:                      # the selection stages take the stacked rows of all ranks (or NULL)
+            args.append(_capi.ptr(gathered))
         args += [_capi.ptr(self.workspace), _capi.current_stream()]
         _capi.check(fn(*args))
 
@@ -178,27 +180,51 @@ class SequenceShard:
         from . import _capi
         self._call(_capi.lib().loda_shard_l1_scores, layer_idx, batch, q, scale, False)
 
-    def l1_select_stage(self, layer_idx, batch, q, scale):
+    def l1_select_stage(self, layer_idx, batch, q, scale, gathered=None):
         from . import _capi
-        self._call(_capi.lib().loda_shard_l1_select, layer_idx, batch, q, scale, False)
+        self._call(_capi.lib().loda_shard_l1_select, layer_idx, batch, q, scale, False, gathered)
 
     def l2_scores_stage(self, layer_idx, batch, q, scale):
         from . import _capi
         self._call(_capi.lib().loda_shard_l2_scores, layer_idx, batch, q, scale, True)
 
-    def l2_select_stage(self, layer_idx, batch, q, scale):
+    def l2_select_stage(self, layer_idx, batch, q, scale, gathered=None):
         from . import _capi
-        self._call(_capi.lib().loda_shard_l2_select, layer_idx, batch, q, scale, True)
+        self._call(_capi.lib().loda_shard_l2_select, layer_idx, batch, q, scale, True, gathered)
 
-    def attend_stage(self, layer_idx, batch, q, scale):
+    def exchange_buffers(self, batch):
+        """Fixed-address buffers of the collective exchanges (allocated once per batch size): the stacked
+        score rows of all ranks for both levels, this rank's packed partial attention (out bf16, then the
+        (max, sum) pairs) and the stacked partials of all ranks."""
+        store = self.__dict__.setdefault("_exchange", {})
+        buf = store.get(batch)
+        if buf is None:
+            cache, dev, world = self.cache, self.cache.device, self.world
+            hq, dv = cache.num_query_heads, cache.layers[0].head_dim_v
+            out_bytes = batch * hq * dv * 2
+            lse_off = (out_bytes + 15) // 16 * 16
+            part_bytes = (lse_off + batch * hq * 2 * 4 + 15) // 16 * 16
+            part = torch.zeros(part_bytes, dtype=torch.uint8, device=dev)
+            buf = dict(
+                l1=torch.zeros((world,) + tuple(self.l1_scores.shape), dtype=torch.int16, device=dev),
+                l2=torch.zeros((world,) + tuple(self.l2_scores.shape), dtype=torch.int16, device=dev),
+                part=part, parts=torch.zeros((world, part_bytes), dtype=torch.uint8, device=dev),
+                out=part[:out_bytes].view(torch.bfloat16).view(batch, hq, dv),
+                lse=part[lse_off:lse_off + batch * hq * 8].view(torch.float32).view(batch, hq, 2),
+                lse_off=lse_off, part_bytes=part_bytes,
+                merged=torch.zeros((batch, hq, dv), dtype=torch.float32, device=dev))
+            store[batch] = buf
+        return buf
+
+    def attend_stage(self, layer_idx, batch, q, scale, out=None, lse=None):
         """Attention over this rank's tokens of the selection: (out [B, Hq, Dv] bf16, lse [B, Hq, 2])."""
         import ctypes as C
 
         from . import _capi
         cache = self.cache
         hq, dv = cache.num_query_heads, cache.layers[layer_idx].head_dim_v
-        out = q.new_empty((batch, hq, dv))
-        lse = torch.empty((batch, hq, 2), dtype=torch.float32, device=q.device)
+        out = q.new_empty((batch, hq, dv)) if out is None else out
+        lse = torch.empty((batch, hq, 2), dtype=torch.float32, device=q.device) if lse is None else lse
         _capi.check(_capi.lib().loda_gather_attend_lse(
             C.byref(self.geometry), C.byref(self.layers[layer_idx]), _capi.ptr(q), _capi.ptr(self.gather),
             _capi.ptr(self.visible_lens), _capi.ptr(cache.query_to_req_buf), batch, cache.max_requests, float(scale),
@@ -211,24 +237,29 @@ def sequence_sharded_decode_step(shard, layer_idx, req_ids, query_states, attent
     ranks: level-1 scores of the own pages, all-gather + OR, page selection (identical on every
     rank); level-2 logits of the own pages' candidates, all-gather + OR, token selection
     (identical); attention over the own tokens; all-gather of (out, max, sum) and a fixed-order
-    log-sum-exp merge.  Returns (out [B, Hq, Dv] fp32, gather, visible_lens); the index lists are
+    log-sum-exp merge.  Three collectives (one all_gather_into_tensor each, into fixed buffers) and seven
+    kernels per layer: the selecting CTAs OR the gathered rows while they load them, one kernel merges.  Returns (out [B, Hq, Dv] fp32, gather, visible_lens); the index lists are
     those of the single-GPU path with -1 at the other ranks' tokens.  The cache must have been
     planned for the step (plan_common) and hold the step's token (the owner of its page appends)."""
+    import ctypes as C
+
+    from . import _capi
     b = len(req_ids)
     q = query_states.contiguous()
     scale = float(attention.scaling)
+    x = shard.exchange_buffers(b)
+    # level 1: own pages' scores -> one all-gather of the rows -> selection on the OR of the ranks' rows
     shard.l1_scores_stage(layer_idx, b, q, scale)
-    shard.l1_scores.copy_(combine_disjoint_scores(shard.l1_scores, group))
-    shard.l1_select_stage(layer_idx, b, q, scale)
+    dist.all_gather_into_tensor(x["l1"], shard.l1_scores, group=group)
+    shard.l1_select_stage(layer_idx, b, q, scale, gathered=x["l1"])
+    # level 2: own candidates' logits -> all-gather -> quota selection, hole fill and union
     shard.l2_scores_stage(layer_idx, b, q, scale)
-    shard.l2_scores.copy_(combine_disjoint_scores(shard.l2_scores, group))
-    shard.l2_select_stage(layer_idx, b, q, scale)
-    out, lse = shard.attend_stage(layer_idx, b, q, scale)
-    dv = out.shape[-1]
-    world = dist.get_world_size(group)
-    packed = torch.cat((out.float(), lse), dim=-1).contiguous()            # [B, Hq, Dv + 2]
-    parts = [torch.empty_like(packed) for _ in range(world)]
-    dist.all_gather(parts, packed, group=group)
-    allp = torch.stack(parts)                                              # rank order = merge order
-    merged = lse_merge(allp[..., :dv], allp[..., dv], allp[..., dv + 1])
-    return merged, shard.gather, shard.visible_lens
+    dist.all_gather_into_tensor(x["l2"], shard.l2_scores, group=group)
+    shard.l2_select_stage(layer_idx, b, q, scale, gathered=x["l2"])
+    # attention over the own tokens -> all-gather of (out, max, sum) -> fixed-order merge (one kernel)
+    shard.attend_stage(layer_idx, b, q, scale, out=x["out"], lse=x["lse"])
+    dist.all_gather_into_tensor(x["parts"], x["part"], group=group)
+    hq, dv = x["out"].shape[1], x["out"].shape[2]
+    _capi.check(_capi.lib().loda_lse_merge(_capi.ptr(x["parts"]), x["part_bytes"], x["lse_off"], shard.world, b * hq, dv,
+                                           _capi.ptr(x["merged"]), _capi.current_stream()))
+    return x["merged"], shard.gather, shard.visible_lens
