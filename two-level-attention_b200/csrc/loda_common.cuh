@@ -13,10 +13,12 @@
 #ifdef LODA_PHASES
 static __device__ long long g_subphase[64];
 #define LODA_SUB(i) do { if (threadIdx.x == 0 && blockIdx.y == 0) g_subphase[(i)] = clock64(); } while (0)
+#define LODA_SUB0(i) do { if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x == 0) g_subphase[(i)] = clock64(); } while (0)
 #define LODA_SUB_READER(name) extern "C" int loda_phase_read_sub_##name(long long* host) { \
     return (int)cudaMemcpyFromSymbol(host, g_subphase, sizeof(long long) * 64); }
 #else
 #define LODA_SUB(i)
+#define LODA_SUB0(i)
 #define LODA_SUB_READER(name)
 #endif
 
@@ -736,7 +738,7 @@ __device__ LODA_BISECT_INLINE int block_bisect_topk(const uint16_t* sc, int n, i
 }
 
 // (3) large n, small k (k <= 128): a cheap lower bound on the k-th largest score
-// discards almost everything, the survivors are ranked exactly.  The chunks of
+// discards almost everything, the survivors are ranked exactly.  The scores of
 // the row are dealt round-robin to the threads, the threads form 256 groups;
 // the k-th largest of the 256 group maxima is a lower bound of the k-th largest
 // score (k groups each hold a score at or above it).  Scores at or above the
@@ -767,14 +769,15 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
     const uint32_t bin = block_hist_kth_bin<NT, BAR, TBASE>(hist, k, wtot, &nvalid);
     bound = nvalid > k ? max(bin << 4, 1u) : 1u;
   } else {
-    // thread maximum (two independent chains)
+    // thread maximum over the scores tid, tid + NT, ...: a thread's scores lie NT positions apart, so a run of
+    // neighbouring high scores (page scores vary slowly with position) spreads over as many groups as it is
+    // long and the bound stays tight; dealt in chunks of 8 neighbours, such a run fed few groups and left
+    // ten times as many survivors (two independent chains)
     uint32_t m0 = 0, m1 = 0;
 #pragma unroll 1                                 // (the loops of this routine run once per launch: fetching an
-    for (int ch = tid; ch < nchunks; ch += NT) { //  unrolled copy costs more than the loop overhead it saves)
-      uint32_t v[8];
-      unpack_u16x8(((const uint4*)sc)[ch], v);
-      m0 = max(max(m0, max(v[0], v[1])), max(v[2], v[3]));
-      m1 = max(max(m1, max(v[4], v[5])), max(v[6], v[7]));
+    for (int i = tid; i < n; i += 2 * NT) {      //  unrolled copy costs more than the loop overhead it saves)
+      m0 = max(m0, (uint32_t)sc[i]);
+      if (i + NT < n) m1 = max(m1, (uint32_t)sc[i + NT]);
     }
     uint32_t m = max(m0, m1);
 #pragma unroll

@@ -254,12 +254,13 @@ size_t l1_smem_bytes(const loda_geometry& g) {
 int l1_score_stride(const loda_geometry& g) { return (g.max_blocks + 511) / 512 * 512; }
 
 // CTAs per row: one tile each while the grid is small (batch 1: latency), several interleaved
-// tiles per CTA (a pipeline of bulk copies inside the CTA) once rows x tiles exceeds about four
-// CTAs per SM
+// tiles per CTA (a pipeline of bulk copies inside the CTA) once rows x tiles exceeds about eight
+// CTAs per SM (fewer, longer CTAs lengthen the tail: the last CTAs to start score and then select while
+// the GPU drains)
 static void l1_split(const loda_geometry& g, int rows, int P, int* ctas_per_row, int* tiles_per_cta) {
   const int ntiles = (g.max_blocks + P - 1) / P;
   const int sms = device_sm_count();
-  int tpc = (rows * ntiles + 4 * sms - 1) / (4 * sms);
+  int tpc = (rows * ntiles + 8 * sms - 1) / (8 * sms);
   tpc = tpc < 1 ? 1 : tpc > ntiles ? ntiles : tpc;
   *tiles_per_cta = tpc;
   *ctas_per_row = (ntiles + tpc - 1) / tpc;

@@ -170,7 +170,9 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   // newest token's page, which lies in the sliding window, outside both pools).  Without the flag
   // nothing is read before the wait.  The query and everything else are always read after it.
   const bool early = (S.flags & LODA_SEL_CHAINED) != 0;
+  LODA_SUB0(48);
   if (!early) pdl_wait();
+  LODA_SUB0(49);
   const int nq = G * DSUB;
   int length = B.lengths[b];
   const int req = checked_request(g, B.active_req_ids[b], B.valid_req_ids[b], &length, status);
@@ -196,11 +198,13 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
       l1_issue_tile<DSUB, P, false>(g, rg, p0, page_end, rows + (size_t)(it & 1) * lay.rows_bytes, bars + (it & 1), mm_row,
                                     sum_row);
   };
+  LODA_SUB0(50);
   __syncthreads();                                       // the barriers are initialised
   if (tid < 32) {
     stage(0);
     stage(1);
   }
+  LODA_SUB0(51);
   if (early) pdl_wait();
   // scaled, bf16-rounded query on the subspace (nfa_layer_batch_selector.py:943-963)
   for (int i = tid; i < nq; i += P) {
@@ -210,8 +214,10 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     qhat[i] = qh;
     *(float2*)(qmm + 2 * i) = make_float2(fminf(qh, 0.0f), fmaxf(qh, 0.0f));
   }
+  LODA_SUB0(52);
   cluster.barrier_wait();     // (0) every CTA of the cluster runs: its shared memory may be addressed from now on
   __syncthreads();            // (and qhat is complete)
+  LODA_SUB0(53);
   // grouped query of level 2: the fp32 sum over the group, in head order, of the bf16-rounded scaled
   // query elements — exactly the values just stored in qhat (the barrier above orders them)
   if (tid < DSUB) {
@@ -225,12 +231,14 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
     const int p0 = (rank + it * CS) * P;
     if (p0 >= page_end) break;
     if (!mbar_wait(bars + (it & 1), (uint32_t)(it >> 1) & 1u)) timed_out = true;      // tile it has landed
+    LODA_SUB0(54 + 2 * it);
     const int page = p0 + tid;
     const uint32_t ord = l1_page_score<DSUB, P, false>(g, rg, p0, page_end, rows + (size_t)(it & 1) * lay.rows_bytes, qhat,
                                                        qmm, G);
     l_scall[page] = (uint16_t)ord;                       // into the leader's shared memory
     if (page >= near_lo && page < near_hi && page - near_lo8 < n_near) r1_scn[page - near_lo8] = (uint16_t)ord;
     __syncthreads();                                     // the buffer is free
+    LODA_SUB0(55 + 2 * it);
     if (tid < 32) stage(it + 2);
   }
   if (timed_out && tid == 0 && status) atomicOr(status, LODA_STATUS_TIMEOUT);
