@@ -136,3 +136,33 @@ def test_batches_whose_attention_splits_in_two(nreq):
     setup = make_setup(lengths, seed=65)
     out = _run_step(setup)
     _check_against_oracle(setup, out)
+
+
+@pytest.mark.parametrize("path", ["grid", "stream"])
+def test_level1_grid_and_streaming_kernels(path, monkeypatch):
+    """The two forms of the batched level-1 launch (a CTA per item; a resident grid that streams its
+    items' tiles and then selects rows from a queue) on a batch with empty, short and long rows and
+    all region-skip states; twice on the same cache, so that the queue and the tickets are rearmed."""
+    from helpers import make_setup
+    monkeypatch.setenv("LODA_B200_L1_PATH", path)
+    lengths = [9000, 131, 20000, 4400, 70000, 6000, 300, 12289, 33000, 5, 4241, 65537]
+    skips = [NS, NS, NEAR, BOTH, NS, FAR, NS, FAR, NS, NS, NEAR, NS]
+    setup = make_setup(lengths, seed=67, skip_states=skips)
+    out = _run_step(setup)
+    _check_against_oracle(setup, out)
+    again = _run_step(setup)
+    assert torch.equal(out, again)
+
+
+@pytest.mark.parametrize("overrides,page", [
+    ({"nfa_far_method": "avg_top2", "nfa_near_method": "minmax"}, 16),
+    ({"tia_level2_cmp_ratio": 2}, 16),
+    ({"tia_level2_cmp_ratio": 8}, 64),
+], ids=["other_methods", "sub64", "sub16_page64"])
+def test_level1_streaming_kernel_other_shapes(overrides, page, monkeypatch):
+    from helpers import make_setup
+    monkeypatch.setenv("LODA_B200_L1_PATH", "stream")
+    setup = make_setup([9000, 20000, 700, 40000, 2500], seed=69, page=page, selector_overrides=overrides,
+                       skip_states=[NS, NS, NS, FAR, NEAR])
+    out = _run_step(setup)
+    _check_against_oracle(setup, out)

@@ -61,7 +61,6 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
   int* sh = (int*)(wz + ATT_WARPS * 16);           // 4
   float* fm = (float*)(sh + 4);                    // [16] merged max of this CTA
   float* fz = fm + 16;                             // [16] merged sum of this CTA
-  uint64_t* bars = (uint64_t*)(fz + 16);           // [STAGES] one mbarrier per stage (two arrivals: the issuing warps)
   float* wo = (float*)Vs;                          // [WARPS][G][DV], after the last tile (V stages consumed)
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -76,13 +75,7 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
   // read before the wait; a launch that stands alone reads it after.
   uint32_t qa[KSTEPS][4];
   auto load_q = [&]() { attn_load_q<D>(qa, q + ((size_t)t * g.num_q_heads + kv * G) * D, G, lane); };
-  if (tid == 0) {
-#pragma unroll
-    for (int s = 0; s < ATT_STAGES; ++s) mbar_init(bars + s, 2);
-    mbar_init_fence();
-  }
   if (chained) load_q();
-  __syncthreads();                                   // the barriers are initialised
   pdl_wait();
 #if LODA_PDL_TRIGGER == 0
   pdl_launch_dependents();
@@ -109,53 +102,60 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
   for (int i = 0; i < NTV; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.0f; }
   float m_run[2] = {-INFINITY, -INFINITY}, z_run[2] = {0.0f, 0.0f};   // rows lane/4 and lane/4 + 8
 
-  // Staging: a token's K row and V row are contiguous in the pool, so each is ONE bulk asynchronous copy
-  // (D * 2 and DV * 2 bytes) into its padded row of the tile.  Thread r < 64 owns row r of every tile: it
-  // reads the row's list entry and issues the two copies, an mbarrier per stage counts the bytes (one
-  // arrival with the expected bytes per issuing warp); a skipped slot, and the rows that pad the last
-  // tile to a multiple of 16, are zero-filled with plain stores.  ATT_STAGES tiles are in flight.
-  static_assert(ATT_TILE == 64 && ATT_NT >= 64, "rows of a tile are owned by the first two warps");
+  // Staging: 16-byte chunk (row kr + k * RPI, column kc) of every tile belongs to this
+  // thread, so it reads the gather-list entries of its own rows into registers and needs
+  // no shared slot table to issue the copies.  ATT_STAGES tiles are in flight: all the
+  // lists of the first tiles are fetched in one round of loads, then all their copies are
+  // issued; after the math of tile i its stage is refilled with tile i + ATT_STAGES, whose
+  // list entries were fetched one iteration earlier.
+  constexpr int KCH = D / 8, VCH = DV / 8;
+  static_assert(KCH == VCH, "K and V rows are staged by the same threads");
+  constexpr int RPI = ATT_NT / KCH, NIT = ATT_TILE / RPI;
+  static_assert(ATT_NT % KCH == 0 && ATT_TILE % RPI == 0, "tile shape");
+  const int kr = tid / KCH, kc = tid % KCH;
   const int slot_end = g.num_pages * g.page;
   const int ntiles = (c1 - c0 + ATT_TILE - 1) / ATT_TILE;
-  auto issue = [&](int stage, int tile) {
-    if (warp >= 2) return;
-    bf16* Kb = Ks + stage * ATT_TILE * KSTR;
-    bf16* Vb = Vs + stage * ATT_TILE * VSTR;
-    const int ntok = min(ATT_TILE, c1 - c0 - tile * ATT_TILE);
-    const int nrow = (ntok + 15) & ~15;
-    const int r = tid;
-    int s = -1;
-    if (tile < ntiles && r < ntok) {
-      s = __ldcg(list + c0 + tile * ATT_TILE + r);
-      if (s >= slot_end) s = -1;
-    }
-    if (tile < ntiles) slot_s[stage * ATT_TILE + r] = s;
-    const uint32_t total = __reduce_add_sync(0xffffffffu, s >= 0 ? (uint32_t)(D + DV) * 2u : 0u);
-    if (tile < ntiles && s < 0 && r < nrow) {
-#pragma unroll 1
-      for (int c = 0; c < D / 8; ++c) *(uint4*)(Kb + r * KSTR + c * 8) = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll 1
-      for (int c = 0; c < DV / 8; ++c) *(uint4*)(Vb + r * VSTR + c * 8) = make_uint4(0u, 0u, 0u, 0u);
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier plain accesses to the stage, then async writes
-    if (lane == 0) mbar_arrive_expect_tx(bars + stage, total);
-    __syncwarp();
-    if (s >= 0) {
-      // page is a power of two: slot -> pool row without a division
-      const long long off = ((long long)(s >> page_log2) * g.num_kv_heads + kv) * g.page + (s & (g.page - 1));
-      bulk_copy_g2s(Kb + r * KSTR, (const bf16*)L.pool_k + off * D, D * 2, bars + stage);
-      bulk_copy_g2s(Vb + r * VSTR, (const bf16*)L.pool_v + off * DV, DV * 2, bars + stage);
+  auto fetch_slots = [&](int (&sl)[NIT], int tile) {
+    const int base = c0 + tile * ATT_TILE;
+#pragma unroll
+    for (int k = 0; k < NIT; ++k) {
+      const int idx = base + kr + k * RPI;
+      const int s = (tile < ntiles && idx < c1) ? __ldcg(list + idx) : -1;
+      sl[k] = s >= slot_end ? -1 : s;
     }
   };
+  auto issue = [&](int stage, const int (&sl)[NIT], int tile) {
+    if (tile < ntiles) {
+      bf16* Kb = Ks + stage * ATT_TILE * KSTR;
+      bf16* Vb = Vs + stage * ATT_TILE * VSTR;
+      int* sb = slot_s + stage * ATT_TILE;
 #pragma unroll
-  for (int s = 0; s < ATT_STAGES; ++s) issue(s, s);
+      for (int k = 0; k < NIT; ++k) {
+        const int r = kr + k * RPI, s = sl[k];
+        // page is a power of two: slot -> pool row without a division
+        const long long off = s >= 0 ? ((long long)(s >> page_log2) * g.num_kv_heads + kv) * g.page + (s & (g.page - 1)) : 0;
+        cp_async16(Kb + r * KSTR + kc * 8, (const bf16*)L.pool_k + off * D + kc * 8, s >= 0);
+        cp_async16(Vb + r * VSTR + kc * 8, (const bf16*)L.pool_v + off * DV + kc * 8, s >= 0);
+        if (kc == 0) sb[r] = s;
+      }
+    }
+    cp_async_commit();     // one group per tile index, empty past the last tile
+  };
+  int nxt[NIT];
+  {
+    int sl[ATT_STAGES][NIT];
+#pragma unroll
+    for (int s = 0; s < ATT_STAGES; ++s) fetch_slots(sl[s], s);
+#pragma unroll
+    for (int s = 0; s < ATT_STAGES; ++s) issue(s, sl[s], s);
+  }
+  fetch_slots(nxt, ATT_STAGES);
   LODA_PHASE(attn, cta_id, 3);
   int stage = 0;
-  bool timed_out = false;
   for (int it = 0; it < ntiles; ++it) {
     const int ntok = min(ATT_TILE, c1 - c0 - it * ATT_TILE);
-    if (!mbar_wait(bars + stage, (uint32_t)(it / ATT_STAGES) & 1u)) timed_out = true;
-    __syncthreads();                                 // zero-filled rows and the slot table are visible
+    cp_async_wait<ATT_STAGES - 1>();
+    __syncthreads();
     if (it == 0) { LODA_PHASE(attn, cta_id, 4); }
     const bf16* Kt = Ks + stage * ATT_TILE * KSTR;
     const bf16* Vt = Vs + stage * ATT_TILE * VSTR;
@@ -166,10 +166,11 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
       attn_warp_step<D, DV>(Kt, Vt, slot_t, tok0, ntok, qa, scale_log2, oacc, m_run, z_run);
     }
     __syncthreads();   // the stage is free: refill it
-    issue(stage, it + ATT_STAGES);
+    issue(stage, nxt, it + ATT_STAGES);
+    fetch_slots(nxt, it + ATT_STAGES + 1);
     stage = stage + 1 == ATT_STAGES ? 0 : stage + 1;
   }
-  (void)timed_out;     // a wait that gave up leaves the row's result invalid; the selector kernels report the bit
+  cp_async_wait<0>();
 
   // ---- merge the warps of this CTA (fixed order) -------------------------------
 #if LODA_PDL_TRIGGER == 1 || LODA_PDL_TRIGGER == 3
@@ -334,7 +335,7 @@ __global__ void __launch_bounds__(ATT_NT) attn_kernel(
 size_t attn_smem_bytes(const loda_geometry& g) {
   // the per-warp partial outputs [WARPS][G][DV] fp32 reuse the V stages (G <= 16 fits)
   return ATT_STAGES * ((size_t)ATT_TILE * (g.head_dim + 8) * 2 + (size_t)ATT_TILE * (g.head_dim_v + 8) * 2 + ATT_TILE * 4) +
-         2 * ATT_WARPS * 16 * 4 + 16 + 2 * 16 * 4 + ATT_STAGES * 8 + 8;
+         2 * ATT_WARPS * 16 * 4 + 16 + 2 * 16 * 4;
 }
 
 // power-of-two split count: no more splits than it takes to give every SM a CTA (a split

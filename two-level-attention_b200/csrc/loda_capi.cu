@@ -90,7 +90,7 @@ static WsLayout ws_layout(const loda_geometry& g) {
   const size_t G = g.num_q_heads / g.num_kv_heads;
   const size_t np_max = g.k_far + g.k_near + 2;
   size_t off = 0;
-  w.l1_ticket = off; off = align_up(off + rows * 4, 256);
+  w.l1_ticket = off; off = align_up(off + (rows + 2) * 4, 256);
   w.l2_ticket = off; off = align_up(off + rows * 4, 256);
   w.at_ticket = off; off = align_up(off + pairs * 4, 256);
   w.np = off; off = align_up(off + rows * 4, 256);
@@ -110,6 +110,7 @@ static SelectWorkspace select_ws(const loda_geometry& g, void* workspace) {
   char* base = (char*)workspace;
   SelectWorkspace ws;
   ws.l1_ticket = (int*)(base + w.l1_ticket);
+  ws.ticket_rows = g.max_query_tokens * g.num_kv_heads;
   ws.l2_ticket = (int*)(base + w.l2_ticket);
   ws.l1_scores = (uint16_t*)(base + w.l1_scores);
   ws.score_stride = l1_score_stride(g);

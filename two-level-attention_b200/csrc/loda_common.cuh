@@ -161,6 +161,14 @@ __device__ __forceinline__ bool in_near_pool(const Regions& r, int t) {
   return page_owned(r, t);
 }
 
+// First page behind both level-1 pools: tiles from there on hold no page that is scored (the sliding
+// window's pages), so they are neither staged nor written.
+__device__ __forceinline__ int pools_end(const Regions& r) {
+  const int far_end = r.far_hi > r.far_lo ? r.far_hi : 0;
+  const int near_end = r.near_on ? min(min(r.swa_lo_blk, r.kt_eff), r.kt_cap) : 0;
+  return max(far_end, near_end);
+}
+
 #ifndef LODA_BISECT_INLINE
 #define LODA_BISECT_INLINE __forceinline__
 #endif
@@ -788,7 +796,20 @@ __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, i
     LODA_SUB(17);
     int is_kth = 0;
     uint32_t gkey = 0;
-    if (tid < NG) {
+    if constexpr (GS >= 2) {
+      // two threads per maximum (tid and tid + NG, in different warps), each against half of the maxima;
+      // the counts meet behind the maxima in `keys`
+      const int part = tid / NG;
+      gkey = keys[tid % NG];
+      int cnt = 0;
+      if (part < 2 && gkey != 0) cnt = count_greater(keys + part * (NG / 2), NG / 8, gkey);
+      if (part < 2) keys[NG + tid] = (uint32_t)cnt;
+      group_sync<NT, BAR>();
+      if (tid < NG) {
+        is_kth = gkey != 0 && (int)(keys[NG + tid] + keys[2 * NG + tid]) == k - 1;
+        if (is_kth) sh[0] = (int)(gkey >> 16);
+      }
+    } else if (tid < NG) {
       gkey = keys[tid];
       is_kth = gkey != 0 && count_greater(keys, NG / 4, gkey) == k - 1;
       if (is_kth) sh[0] = (int)(gkey >> 16);
@@ -906,6 +927,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, int arrivals) {
 __device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("{\n.reg .b64 t;\nmbarrier.arrive.shared::cta.b64 t, [%0];\n}" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -1039,7 +1063,9 @@ inline cudaError_t set_kernel_smem(K kernel, size_t smem) {
 
 // scratch views handed to the kernels (carved out of the caller's workspace)
 struct SelectWorkspace {
-  int* l1_ticket;        // [rows], zero between launches
+  int* l1_ticket;        // [ticket_rows + 2], zero between launches: a ticket per row, then the row queue
+                         // and the exit count of the streaming level-1 kernel
+  int ticket_rows;
   int* l2_ticket;        // [rows], zero between launches
   uint16_t* l1_scores;   // [rows, score_stride]: ordered bf16 score of every logical page (0 = not in a pool)
   int score_stride;

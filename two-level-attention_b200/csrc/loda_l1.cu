@@ -28,6 +28,7 @@
 namespace loda {
 
 LODA_PHASE_STORAGE(l1)
+LODA_SUB_READER(l1)
 
 constexpr int L1_TP = 256;                         // threads per CTA = pages per tile
 
@@ -37,6 +38,91 @@ struct L1Shape {
   static constexpr size_t STAGES_BYTES = (size_t)NSTAGE * L1Tile<DSUB, L1_TP>::STAGE;
   static constexpr size_t ROWS_BYTES = STAGES_BYTES > L1_TAIL_BYTES ? STAGES_BYTES : L1_TAIL_BYTES;
 };
+
+// The selecting CTA's work on one row once all its page scores are in the workspace: the scores are
+// copied into two rows of shared memory, one per pool, each holding 0 outside its pool (`rows`: the
+// consumed tile stages), the pages are selected, and the ascending page list with its physical
+// pages is handed to the level-2 launch.  All P threads of the CTA.
+template <int DSUB, int P, bool GENERIC>
+__device__ __forceinline__ void l1_finish_row(const loda_geometry& g, const loda_layer& L, const Regions& rg,
+                                              const loda_selection& out, const SelectWorkspace& ws, int row, int req,
+                                              unsigned char* rows, int* kept, uint32_t* keys, int* wtot, int* sh,
+                                              int cta_id, bool trigger) {
+  const int tid = threadIdx.x;
+  const uint16_t* row_scores = ws.l1_scores + (size_t)row * ws.score_stride;
+  // the staging rows are consumed: the row's scores are copied into two rows of
+  // shared memory, one per pool, each holding 0 outside its pool
+  const int near_hi = min(min(rg.swa_lo_blk, rg.kt_eff), g.max_blocks);
+  const int far_lo = rg.far_lo, far_hi = max(rg.far_hi, rg.far_lo);
+  const int near_lo = rg.near_blks, near_lo8 = near_lo & ~7;
+  const int n_far = far_hi;                                                   // far row: pages [0, far_hi)
+  static_assert(2 * P >= L1_NEAR_CAP, "the near row is ranked with at most two scores per thread");
+  const int n_near = near_hi > near_lo ? min(near_hi - near_lo8, L1_NEAR_CAP) : 0;   // near row: pages [near_lo8, ...)
+  uint16_t* scf = (uint16_t*)rows;                       // up to 40 KB
+  uint16_t* scn = (uint16_t*)(rows + 40 * 1024);         // L1_NEAR_CAP scores
+  {
+    // all the loads of a batch are issued before the first is used (one round trip, not one per load)
+    const uint4* src = (const uint4*)row_scores;         // 8 scores per load; unscored pages hold 0
+    // sequence sharding: the rows of all GPUs, ORed while loading
+    auto ldrow = [&](int c) {
+      if (ws.gathered == nullptr) return __ldcg(src + c);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      for (int s = 0; s < ws.n_gathered; ++s) {
+        const uint4 u = __ldcg((const uint4*)(ws.gathered + s * ws.gathered_stride + (size_t)row * ws.score_stride) + c);
+        v.x |= u.x; v.y |= u.y; v.z |= u.z; v.w |= u.w;
+      }
+      return v;
+    };
+    const int nc_far = (n_far + 7) / 8, nc_near = (n_near + 7) / 8;          // nc_near <= L1_NEAR_CAP / 8 <= P
+    uint4 nreg = make_uint4(0u, 0u, 0u, 0u);
+    if (tid < nc_near) nreg = ldrow(near_lo8 / 8 + tid);
+    for (int c0 = 0; c0 < nc_far; c0 += 4 * P) {
+      uint4 f[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = c0 + k * P + tid;
+        f[k] = c < nc_far ? ldrow(c) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = c0 + k * P + tid;
+        if (c < nc_far) {
+          uint32_t v[8];
+          unpack_u16x8(f[k], v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { const int i = c * 8 + j; v[j] = (i >= far_lo && i < far_hi) ? v[j] : 0u; }
+          ((uint4*)scf)[c] = make_uint4(v[0] | v[1] << 16, v[2] | v[3] << 16, v[4] | v[5] << 16, v[6] | v[7] << 16);
+        }
+      }
+    }
+    if (tid < nc_near) {
+      uint32_t v[8];
+      unpack_u16x8(nreg, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const int i = near_lo8 + tid * 8 + j; v[j] = (i >= near_lo && i < near_hi) ? v[j] : 0u; }
+      ((uint4*)scn)[tid] = make_uint4(v[0] | v[1] << 16, v[2] | v[3] << 16, v[4] | v[5] << 16, v[6] | v[7] << 16);
+    }
+  }
+  __syncthreads();
+  LODA_PHASE(l1, cta_id, 6);
+  const int np = l1_select_pages<P>(g, rg, out, row, scf, scn, n_far, far_lo, n_near, near_lo, near_lo8, near_hi, kept,
+                                    keys, wtot, sh, trigger);
+  LODA_PHASE(l1, cta_id, 8);
+  // hand the ascending page list and its physical pages to the L2 launch
+  const int np_max = g.k_far + g.k_near + 2;
+  const int32_t* table = L.block_table + (size_t)req * g.max_blocks;
+  for (int i = tid; i < np; i += P) {
+    const int pg = kept[i];
+    int ph = (pg >= 0 && pg < g.max_blocks) ? table[pg] : -1;
+    if (ph < 0 || ph >= g.num_pages) ph = -1;
+    ws.pages[(size_t)row * np_max + i] = pg;
+    ws.phys[(size_t)row * np_max + i] = ph;
+  }
+  if (tid == 0) {
+    ws.np[row] = np;
+    ws.l1_ticket[row] = 0;
+  }
+}
 
 template <int DSUB, int P, bool GENERIC>
 __global__ void __launch_bounds__(P, 2) l1_kernel(loda_geometry g, loda_layer L, loda_batch B,
@@ -103,13 +189,14 @@ __global__ void __launch_bounds__(P, 2) l1_kernel(loda_geometry g, loda_layer L,
   const unsigned char* sum_row = (const unsigned char*)L.page_sum + rowi * stat_row_bytes(g.max_blocks, T::NC);
   uint16_t* row_scores = ws.l1_scores + (size_t)row * ws.score_stride;
   const int page_end = min(rg.kt_eff, g.max_blocks);
+  const int tile_end = min(page_end, pools_end(rg));     // tiles behind the pools are skipped
   __syncthreads();                                       // the barriers are initialised
   // the first NSTAGE tiles are requested at once (issued first: the longest latency)
   if (tid < 32) {
 #pragma unroll
     for (int it = 0; it < NSTAGE; ++it) {
       const int p0 = (split + it * nsplit) * P;
-      if (it < tiles_per_cta && p0 < page_end)
+      if (it < tiles_per_cta && p0 < tile_end)
         l1_issue_tile<DSUB, P, GENERIC>(g, rg, p0, page_end, rows + (size_t)it * T::STAGE, bars + it, mm_row, sum_row);
     }
   }
@@ -129,18 +216,18 @@ __global__ void __launch_bounds__(P, 2) l1_kernel(loda_geometry g, loda_layer L,
 #pragma unroll 1
   for (int it = 0; it < tiles_per_cta; ++it) {
     const int p0 = (split + it * nsplit) * P;
-    if (p0 >= page_end) break;
+    if (p0 >= tile_end) break;
     const int st = it % NSTAGE;
     if (!mbar_wait(bars + st, (uint32_t)(it / NSTAGE) & 1u)) timed_out = true;
     if (it == 0) { LODA_PHASE(l1, cta_id, 3); }
     // one page per thread
     const uint32_t ord = l1_page_score<DSUB, P, GENERIC>(g, rg, p0, page_end, rows + (size_t)st * T::STAGE, qhat, qmm, G,
                                                           qraw);
-    row_scores[p0 + tid] = (uint16_t)ord;     // the selecting CTA reads pages below page_end (rounded up to 8)
+    row_scores[p0 + tid] = (uint16_t)ord;     // the selecting CTA masks what lies outside the pools
     __syncthreads();                          // every thread has read the stage: refill it
     if (tid < 32) {
       const int nxt = it + NSTAGE, pn = (split + nxt * nsplit) * P;
-      if (nxt < tiles_per_cta && pn < page_end)
+      if (nxt < tiles_per_cta && pn < tile_end)
         l1_issue_tile<DSUB, P, GENERIC>(g, rg, pn, page_end, rows + (size_t)st * T::STAGE, bars + st, mm_row, sum_row);
     }
   }
@@ -159,82 +246,217 @@ __global__ void __launch_bounds__(P, 2) l1_kernel(loda_geometry g, loda_layer L,
     if (!sh[0]) return;
     __threadfence();
   }
-  // the staging rows are consumed: the row's scores are copied into two rows of
-  // shared memory, one per pool, each holding 0 outside its pool
-  const int near_hi = min(min(rg.swa_lo_blk, rg.kt_eff), g.max_blocks);
-  const int far_lo = rg.far_lo, far_hi = max(rg.far_hi, rg.far_lo);
-  const int near_lo = rg.near_blks, near_lo8 = near_lo & ~7;
-  const int n_far = far_hi;                                                   // far row: pages [0, far_hi)
-  static_assert(2 * P >= L1_NEAR_CAP, "the near row is ranked with at most two scores per thread");
-  const int n_near = near_hi > near_lo ? min(near_hi - near_lo8, L1_NEAR_CAP) : 0;   // near row: pages [near_lo8, ...)
-  uint16_t* scf = (uint16_t*)rows;                       // up to 40 KB
-  uint16_t* scn = (uint16_t*)(rows + 40 * 1024);         // L1_NEAR_CAP scores
-  {
-    // all the loads of a batch are issued before the first is used (one round trip, not one per load)
-    const uint4* src = (const uint4*)row_scores;         // 8 scores per load; unscored pages hold 0
-    // sequence sharding: the rows of all GPUs, ORed while loading
-    auto ldrow = [&](int c) {
-      if (ws.gathered == nullptr) return __ldcg(src + c);
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      for (int s = 0; s < ws.n_gathered; ++s) {
-        const uint4 u = __ldcg((const uint4*)(ws.gathered + s * ws.gathered_stride + (size_t)row * ws.score_stride) + c);
-        v.x |= u.x; v.y |= u.y; v.z |= u.z; v.w |= u.w;
+  l1_finish_row<DSUB, P, GENERIC>(g, L, rg, out, ws, row, req, rows, kept, keys, wtot, sh, cta_id, LODA_PDL_TRIGGER == 1);
+  LODA_PHASE(l1, cta_id, 9);
+}
+
+// ---------------------------------------------------------------------------
+// Level 1 for large batches: a grid that fills the GPU once (two CTAs per SM) and stays.  The rows'
+// tiles are cut into items (row, split) as above; CTA c takes the items c, c + gridDim.x, ...; it reads
+// the metadata of all its items in one round trip at the start, and its tiles then flow through the
+// stages as one stream across the items: warp 0 refills a stage as soon as all eight warps have
+// released it (an `empty` mbarrier per stage, one arrival per warp) with the next tile of the stream,
+// whichever item that belongs to, so no item pays for its own first copy and no barrier of the CTA
+// sits between two tiles.  The query of an item is staged into a ring of four slots when its first
+// tile is issued.  After an item's last tile its threads fence and one of them adds the row's ticket.
+// When a CTA's items are done it turns to selection: it claims the next row from a queue (rows in
+// order, which is roughly the order in which they complete), waits — bounded — for the row's ticket
+// to show all its items, and selects as the last CTA of a row does above.  Every CTA of the grid is
+// resident (the host sizes the grid by the occupancy the runtime reports), so a CTA that waits for a
+// row waits for CTAs that are running.
+// ---------------------------------------------------------------------------
+constexpr int L1S_MAX_ITEMS = 16;      // items per CTA
+constexpr int L1S_QRING = 4;           // query slots: tiles of at most NSTAGE + 1 <= 4 items are in flight
+constexpr int L1S_POLL_LIMIT = 1 << 18;
+
+template <int DSUB, bool GENERIC>
+__global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, loda_layer L, loda_batch B,
+                                                             const bf16* __restrict__ q, float scale,
+                                                             loda_selection out, SelectWorkspace ws, int nsplit,
+                                                             int tiles_per_cta, AppendArgs ap, int n_rows) {
+  constexpr int P = L1_TP;
+  using T = L1Tile<DSUB, P>;
+  constexpr int NSTAGE = L1Shape<DSUB>::NSTAGE;
+  constexpr size_t ROWS_BYTES = L1Shape<DSUB>::ROWS_BYTES;
+  constexpr int NQ = GENERIC ? 4 : 3;
+  static_assert(NSTAGE + 1 <= L1S_QRING, "query ring");
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* rows = smem;
+  uint64_t* full = (uint64_t*)(smem + ROWS_BYTES);               // [NSTAGE] bytes of a tile have landed
+  uint64_t* empty = full + 4;                                    // [NSTAGE] all warps have read the tile
+  int4* desc = (int4*)(smem + ROWS_BYTES + 64);                  // [MAX_ITEMS] (length, request slot, skip bits, tiles)
+  const int G = g.num_q_heads / g.num_kv_heads;
+  const int nq = G * DSUB;
+  float* qring = (float*)(desc + L1S_MAX_ITEMS);                 // [QRING][NQ * G * DSUB]
+  int* kept = (int*)(qring + (size_t)L1S_QRING * NQ * nq);       // k_far + k_near + 2
+  const size_t keys_off = (ROWS_BYTES + 64 + L1S_MAX_ITEMS * 16 + (size_t)L1S_QRING * NQ * nq * 4 +
+                           (size_t)(g.k_far + g.k_near + 2) * 4 + 15) & ~(size_t)15;
+  uint32_t* keys = (uint32_t*)(smem + keys_off);                 // 2 P + 8
+  int* wtot = (int*)(keys + 2 * P + 8);                          // 8 x 32
+  int* sh = wtot + 256;                                          // 8
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int cta = blockIdx.x, ncta = gridDim.x;
+  const int W = n_rows * nsplit;
+  const int n_items = cta < W ? min((W - cta + ncta - 1) / ncta, L1S_MAX_ITEMS) : 0;
+  const int cta_id = cta;
+  LODA_PHASE(l1, cta_id, 0);
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < NSTAGE; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, P / 32); }
+    mbar_init_fence();
+  }
+  pdl_wait();
+  LODA_PHASE(l1, cta_id, 1);
+  // the decode append of the rows cta, cta + ncta, ...: the newest token and its page lie in the
+  // sliding window and are read by neither level of this step
+  if (ap.enabled && warp == 1) {
+    for (int r = cta; r < n_rows; r += ncta) append_row<DSUB>(g, L, B, ap.k_new, ap.v_new, ap.slots, ap.status, r / g.num_kv_heads, r % g.num_kv_heads, lane);
+  }
+  // metadata of this CTA's items, one item per thread: a single round of dependent loads per CTA
+  auto item_row = [&](int k) { return (cta + k * ncta) / nsplit; };
+  auto item_split = [&](int k) { return (cta + k * ncta) % nsplit; };
+  auto item_regions = [&](const int4& d) { return make_regions(g, d.x, (d.z & 1) != 0, (d.z & 2) != 0); };
+  if (tid < n_items) {
+    const int row = item_row(tid), b = row / g.num_kv_heads;
+    int length = B.lengths[b];
+    const long long act = B.active_req_ids[b], val = B.valid_req_ids[b];
+    int req = 0;
+    if (act < 0) { length = 0; req = (val >= 0 && val < g.max_requests) ? (int)val : 0; }
+    else if (val < 0 || val >= g.max_requests) { length = 0; if (ap.status) atomicOr(ap.status, LODA_STATUS_BAD_REQ); }
+    else req = (int)val;
+    bool skip_far, skip_near;
+    load_skip_flags(L, req, &skip_far, &skip_near);
+    const Regions rg = make_regions(g, length, skip_far, skip_near);
+    const int tile_end = min(min(rg.kt_eff, g.max_blocks), pools_end(rg));
+    const int first = item_split(tid) * P, step = nsplit * P;
+    int nt = tile_end > first ? (tile_end - first + step - 1) / step : 0;
+    nt = min(nt, tiles_per_cta);
+    desc[tid] = make_int4(length, req, (skip_far ? 1 : 0) | (skip_near ? 2 : 0), nt);
+  }
+  __syncthreads();                                       // barriers and descriptors are ready
+  LODA_PHASE(l1, cta_id, 2);
+
+  // ---- producer (warp 0): the tile stream ---------------------------------------------------
+  int pk = 0, pit = 0, pseq = 0, pslot = -1;             // item, tile of the item, position in the stream, query slot
+  bool dead = false;                                     // a wait gave up: no further waiting
+  auto issue_next = [&]() {
+    while (pk < n_items && pit >= desc[pk].w) { ++pk; pit = 0; }
+    if (pk >= n_items) return;
+    const int st = pseq % NSTAGE;
+    if (pseq >= NSTAGE && !dead && !mbar_wait(empty + st, (uint32_t)(pseq / NSTAGE - 1) & 1u)) dead = true;
+    const int4 d = desc[pk];
+    const int row = item_row(pk), b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
+    if (pit == 0) {
+      // scaled, bf16-rounded query of the item's row on the subspace (nfa_layer_batch_selector.py:943-963);
+      // the slots go round over the items that have tiles
+      ++pslot;
+      float* qhat = qring + (size_t)(pslot % L1S_QRING) * NQ * nq;
+      float* qmm = qhat + nq;
+      float* qraw = qmm + 2 * nq;
+      for (int i = lane; i < nq; i += 32) {
+        const int j = i / DSUB, dd = i % DSUB;
+        const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, dd)]);
+        const float qh = bf16r(__fmul_rn(qv, scale));
+        qhat[i] = qh;
+        *(float2*)(qmm + 2 * i) = make_float2(fminf(qh, 0.0f), fmaxf(qh, 0.0f));
+        if (GENERIC) qraw[i] = __fmul_rn(qv, scale);
       }
-      return v;
-    };
-    const int nc_far = (n_far + 7) / 8, nc_near = (n_near + 7) / 8;          // nc_near <= L1_NEAR_CAP / 8 <= P
-    uint4 nreg = make_uint4(0u, 0u, 0u, 0u);
-    if (tid < nc_near) nreg = ldrow(near_lo8 / 8 + tid);
-    for (int c0 = 0; c0 < nc_far; c0 += 4 * P) {
-      uint4 f[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int c = c0 + k * P + tid;
-        f[k] = c < nc_far ? ldrow(c) : make_uint4(0u, 0u, 0u, 0u);
+      __syncwarp();                                      // ordered before the arrival on `full` below
+    }
+    const Regions rg = item_regions(d);
+    const size_t rowi = (size_t)d.y * g.num_kv_heads + kv;
+    const unsigned char* mm_row = (const unsigned char*)L.page_mm + rowi * stat_row_bytes(g.max_blocks, T::CPR);
+    const unsigned char* sum_row = (const unsigned char*)L.page_sum + rowi * stat_row_bytes(g.max_blocks, T::NC);
+    const int p0 = (item_split(pk) + pit * nsplit) * P;
+    l1_issue_tile<DSUB, P, GENERIC>(g, rg, p0, min(rg.kt_eff, g.max_blocks), rows + (size_t)st * T::STAGE, full + st, mm_row,
+                                    sum_row);
+    ++pit;
+    ++pseq;
+  };
+  if (warp == 0) {
+#pragma unroll 1
+    for (int s = 0; s < NSTAGE; ++s) issue_next();
+  }
+
+  // ---- consumers (all warps): item by item ----------------------------------------------------
+  int cseq = 0, cslot = -1;
+#pragma unroll 1
+  for (int k = 0; k < n_items; ++k) {
+    const int4 d = desc[k];
+    const int row = item_row(k);
+    if (d.w > 0) {
+      const Regions rg = item_regions(d);
+      const int page_end = min(rg.kt_eff, g.max_blocks);
+      ++cslot;
+      const float* qhat = qring + (size_t)(cslot % L1S_QRING) * NQ * nq;
+      uint16_t* row_scores = ws.l1_scores + (size_t)row * ws.score_stride;
+#pragma unroll 1
+      for (int it = 0; it < d.w; ++it) {
+        const int st = cseq % NSTAGE;
+        if (cseq < 10) { LODA_SUB0(32 + 3 * cseq); }
+        if (!dead && !mbar_wait(full + st, (uint32_t)(cseq / NSTAGE) & 1u)) dead = true;
+        if (cseq < 10) { LODA_SUB0(33 + 3 * cseq); }
+        const int p0 = (item_split(k) + it * nsplit) * P;
+        const uint32_t ord = l1_page_score<DSUB, P, GENERIC>(g, rg, p0, page_end, rows + (size_t)st * T::STAGE, qhat,
+                                                              qhat + nq, G, qhat + 3 * nq);
+        row_scores[p0 + tid] = (uint16_t)ord;            // the selecting CTA masks what lies outside the pools
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + st);          // this warp has read the stage
+        if (cseq < 10) { LODA_SUB0(34 + 3 * cseq); }
+        ++cseq;
+        if (warp == 0) issue_next();
       }
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int c = c0 + k * P + tid;
-        if (c < nc_far) {
-          uint32_t v[8];
-          unpack_u16x8(f[k], v);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) { const int i = c * 8 + j; v[j] = (i >= far_lo && i < far_hi) ? v[j] : 0u; }
-          ((uint4*)scf)[c] = make_uint4(v[0] | v[1] << 16, v[2] | v[3] << 16, v[4] | v[5] << 16, v[6] | v[7] << 16);
+    }
+    // the item is done (an item without tiles too): publish the scores, count the row's ticket
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) atomicAdd(ws.l1_ticket + row, 1);
+  }
+  if (dead && lane == 0 && ap.status) atomicOr(ap.status, LODA_STATUS_TIMEOUT);
+  LODA_PHASE(l1, cta_id, 4);
+  pdl_launch_dependents();
+
+  // ---- selection: rows from the queue -------------------------------------------------------------
+  int* queue = ws.l1_ticket + ws.ticket_rows;            // [0] next row to select, [1] CTAs that have left
+#pragma unroll 1
+  for (;;) {
+    __syncthreads();                                     // sh and the selection buffers of the row before are consumed
+    if (tid == 0) {
+      const int r = atomicAdd(queue, 1);
+      int ok = 1;
+      if (r < n_rows) {
+        int tries = 0;
+        while (*(volatile int*)(ws.l1_ticket + r) < nsplit) {
+          if (++tries > L1S_POLL_LIMIT) { ok = 0; break; }
+          __nanosleep(64);
         }
       }
+      sh[4] = r;
+      sh[5] = ok;
     }
-    if (tid < nc_near) {
-      uint32_t v[8];
-      unpack_u16x8(nreg, v);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) { const int i = near_lo8 + tid * 8 + j; v[j] = (i >= near_lo && i < near_hi) ? v[j] : 0u; }
-      ((uint4*)scn)[tid] = make_uint4(v[0] | v[1] << 16, v[2] | v[3] << 16, v[4] | v[5] << 16, v[6] | v[7] << 16);
+    __syncthreads();
+    const int r = sh[4];
+    if (r >= n_rows) break;
+    if (!sh[5]) {                                        // the row never completed: report, leave its outputs alone
+      if (tid == 0 && ap.status) atomicOr(ap.status, LODA_STATUS_TIMEOUT);
+      continue;
     }
+    __threadfence();                                     // the scores of the row's items, published before their tickets
+    const int b = r / g.num_kv_heads;
+    int length = B.lengths[b];
+    const int req = checked_request(g, B.active_req_ids[b], B.valid_req_ids[b], &length, nullptr);
+    bool skip_far, skip_near;
+    load_skip_flags(L, req, &skip_far, &skip_near);
+    const Regions rg = make_regions(g, length, skip_far, skip_near);
+    LODA_PHASE(l1, cta_id, 5);
+    l1_finish_row<DSUB, P, GENERIC>(g, L, rg, out, ws, r, req, rows, kept, keys, wtot, sh, cta_id, false);
+    LODA_PHASE(l1, cta_id, 9);
   }
-  __syncthreads();
-#if LODA_PDL_TRIGGER == 3
-  pdl_launch_dependents();
-#endif
-  LODA_PHASE(l1, cta_id, 6);
-  const int np = l1_select_pages<P>(g, rg, out, row, scf, scn, n_far, far_lo, n_near, near_lo, near_lo8, near_hi, kept,
-                                    keys, wtot, sh, LODA_PDL_TRIGGER == 1);
-  LODA_PHASE(l1, cta_id, 8);
-  // hand the ascending page list and its physical pages to the L2 launch
-  const int np_max = g.k_far + g.k_near + 2;
-  const int32_t* table = L.block_table + (size_t)req * g.max_blocks;
-  for (int i = tid; i < np; i += P) {
-    const int pg = kept[i];
-    int ph = (pg >= 0 && pg < g.max_blocks) ? table[pg] : -1;
-    if (ph < 0 || ph >= g.num_pages) ph = -1;
-    ws.pages[(size_t)row * np_max + i] = pg;
-    ws.phys[(size_t)row * np_max + i] = ph;
+  if (tid == 0 && atomicAdd(queue + 1, 1) == ncta - 1) {   // the last CTA to leave rearms the queue
+    queue[0] = 0;
+    queue[1] = 0;
   }
-  if (tid == 0) {
-    ws.np[row] = np;
-    ws.l1_ticket[row] = 0;
-  }
-  LODA_PHASE(l1, cta_id, 9);
 }
 
 static bool l1_generic(const loda_geometry& g) { return g.far_method != LODA_FAR_MINMAX || g.near_minmax != 0; }
@@ -266,12 +488,57 @@ static void l1_split(const loda_geometry& g, int rows, int P, int* ctas_per_row,
   *ctas_per_row = (ntiles + tpc - 1) / tpc;
 }
 
+template <int DS>
+static size_t l1_stream_smem_bytes_d(const loda_geometry& g) {
+  const int G = g.num_q_heads / g.num_kv_heads;
+  return L1Shape<DS>::ROWS_BYTES + 64 + L1S_MAX_ITEMS * 16 + (size_t)L1S_QRING * (l1_generic(g) ? 4 : 3) * G * DS * 4 +
+         (size_t)(g.k_far + g.k_near + 2) * 4 + (size_t)(2 * L1_TP + 8) * 4 + (256 + 8) * 4 + 32;
+}
+
+// Grid of the streaming kernel: every CTA resident at once (what the runtime reports for this kernel
+// and its shared memory, per device), or 0 when the kernel cannot be used.
+template <int DS, bool GENERIC>
+static int l1_stream_grid(size_t smem) {
+  static int per_sm[64] = {};                    // per device ordinal; -1 = refused
+  const int dev = device_ordinal();
+  if (dev < 0 || dev >= 64) return 0;
+  if (per_sm[dev] == 0) {
+    int n = 0;
+    if (set_kernel_smem(l1_stream_kernel<DS, GENERIC>, smem) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, l1_stream_kernel<DS, GENERIC>, L1_TP, smem) != cudaSuccess || n < 1) {
+      (void)cudaGetLastError();
+      n = -1;
+    }
+    per_sm[dev] = n > 2 ? 2 : n;
+  }
+  return per_sm[dev] > 0 ? per_sm[dev] * device_sm_count() : 0;
+}
+
 template <int DS, bool GENERIC>
 static cudaError_t launch_l1_p(const loda_geometry& g, const loda_layer& L, const loda_batch& B, const void* q,
                                float scale, const loda_selection& out, const SelectWorkspace& ws,
                                const AppendArgs& ap, int phase, cudaStream_t st) {
   constexpr int P = L1_TP;
   const int rows = B.batch * g.num_kv_heads;
+  // large batches: the streaming kernel (LODA_B200_L1_PATH=grid keeps the grid of one CTA per item,
+  // =stream takes the streaming kernel for small batches too)
+  if (phase == 0 && ws.gathered == nullptr) {
+    const char* e = getenv("LODA_B200_L1_PATH");
+    const bool never = e && strcmp(e, "grid") == 0, always = e && strcmp(e, "stream") == 0;
+    const size_t smem = l1_stream_smem_bytes_d<DS>(g);
+    const int ntiles = (g.max_blocks + P - 1) / P;
+    const int ncta = never ? 0 : l1_stream_grid<DS, GENERIC>(smem);
+    if (ncta > 0 && (always || (long long)rows * ntiles >= 4LL * ncta)) {
+      // about four items per CTA; an item = the tiles split, split + nsplit, ... of a row
+      int nsplit = (4 * ncta + rows - 1) / rows;
+      nsplit = nsplit < 1 ? 1 : nsplit > ntiles ? ntiles : nsplit;
+      const int tpc = (ntiles + nsplit - 1) / nsplit;
+      nsplit = (ntiles + tpc - 1) / tpc;
+      if (((long long)rows * nsplit + ncta - 1) / ncta <= L1S_MAX_ITEMS)
+        return launch_pdl(l1_stream_kernel<DS, GENERIC>, dim3(ncta), dim3(P), smem, st, g, L, B, (const bf16*)q, scale, out,
+                          ws, nsplit, tpc, ap, rows);
+    }
+  }
   int nsplit, tpc;
   l1_split(g, rows, P, &nsplit, &tpc);
   dim3 grid(nsplit + (ap.enabled ? 1 : 0), rows);

@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
 #pragma unroll 1
     for (int base = lo + tid; base < hi; base += U * NT) {
       uint32_t w[U][WORDS];
-      __nv_bfloat162 sz[U];
+      uint32_t sz[U];
       bool ok[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
           const int tok = pg * g.page + o;
           if (ph >= 0 && tok >= g.sink && tok < rg.swa_lo_tok && tok < length && tok >= rg.lower && tok < rg.upper) {
             const size_t trow = ((size_t)ph * g.num_kv_heads + kv) * g.page + o;
-            sz[u] = *(const __nv_bfloat162*)((const bf16*)L.tail_sz + trow * 2);
+            sz[u] = *(const uint32_t*)((const bf16*)L.tail_sz + trow * 2);
             l2_load_codes<DSUB>((const uint8_t*)L.tail_code + trow * (DSUB / 2), w[u]);
             ok[u] = true;
           } else if (ph < 0 && status && rg.shard_count <= 1) {      // under sequence sharding a missing page is another GPU's
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
         if (idx < hi) {
           uint32_t ord = 0;
           if (ok[u]) {
-            const float lg = l2_logit_words<DSUB>(w[u], __low2float(sz[u]), __high2float(sz[u]), qf);
+            const float lg = l2_logit_words<DSUB>(w[u], sz[u], qf);
             if (lg == lg && lg != -INFINITY) ord = ord16(lg);
           }
           row_scores[idx] = (uint16_t)ord;

@@ -134,7 +134,11 @@ __device__ __forceinline__ void l1_group_needs(const loda_geometry& g, const Reg
 }
 
 // Issue the copies of the tile [p0, p0 + TP) into `stage` and arm `bar` with their byte count.
-// Called by all 32 lanes of one warp (lane i handles group i of the tile).
+// Called by all 32 lanes of one warp (lane i handles group i of the tile).  The groups of a row are
+// contiguous in global memory and their slots contiguous in the stage, so the min/max rows of a run of
+// neighbouring groups travel as ONE bulk copy (the usual tile lies inside the far pool: one copy of
+// GROUPS * SLOT bytes instead of one per group, whose issue by the lanes of a warp is serialised);
+// the sums (a handful of groups per row) and any second run go group by group.
 template <int DSUB, int TP, bool GENERIC>
 __device__ __forceinline__ void l1_issue_tile(const loda_geometry& g, const Regions& rg, int p0, int page_end,
                                               unsigned char* stage, uint64_t* bar, const unsigned char* mm_row,
@@ -145,10 +149,17 @@ __device__ __forceinline__ void l1_issue_tile(const loda_geometry& g, const Regi
   if (lane < T::GROUPS) l1_group_needs<GENERIC>(g, rg, p0 + STAT_GROUP * lane, page_end, &nm, &ns);
   const uint32_t bytes = (nm ? T::SLOT : 0) + (ns ? T::SUMG : 0);
   const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
+  const uint32_t mmask = __ballot_sync(0xffffffffu, nm);
+  const int first = __ffs(mmask) - 1, count = __popc(mmask);
+  const bool one_run = mmask != 0u && ((mmask >> first) + 1u & (mmask >> first)) == 0u;   // the set bits are neighbours
   if (lane == 0) mbar_arrive_expect_tx(bar, total);
   __syncwarp();
   const size_t gidx = (size_t)(p0 / STAT_GROUP) + lane;
-  if (nm) bulk_copy_g2s(stage + lane * T::SLOT, mm_row + gidx * T::SLOT, T::SLOT, bar);
+  if (one_run) {
+    if (lane == first) bulk_copy_g2s(stage + lane * T::SLOT, mm_row + gidx * T::SLOT, (uint32_t)count * T::SLOT, bar);
+  } else if (nm) {
+    bulk_copy_g2s(stage + lane * T::SLOT, mm_row + gidx * T::SLOT, T::SLOT, bar);
+  }
   if (ns) bulk_copy_g2s(nm ? stage + T::GROUPS * T::SLOT : stage + lane * T::SLOT, sum_row + gidx * T::SUMG, T::SUMG, bar);
 }
 
@@ -352,12 +363,45 @@ __device__ __forceinline__ int l1_select_pages(const loda_geometry& g, const Reg
 // Logit of one token from its packed 4-bit codes (WORDS 32-bit words, dim 2i in the low nibble of byte i):
 // de-quantised key bf16(bf16(code * scale) - zero), one left-to-right fp32 chain of separate multiplies
 // and adds over the d' dims, rounded to bf16.
+// The de-quantisation runs two dims at a time in packed bf16 arithmetic, which gives the same bits as
+// the fp32 form with its two roundings to bf16 and keeps the conversion unit (a quarter of the fp32
+// rate, and three conversions per dim in the fp32 form) out of the loop:
+//   code -> bf16: 0x4300 | code is the bf16 number 128 + code; minus 128 is exact;
+//   bf16(code * scale): the product of an integer below 16 and a bf16 number is exact in fp32, so the
+//     fp32 form rounds once, as mul.rn.bf16x2 does;
+//   bf16(t - zero): the difference of two bf16 numbers is exact in fp32 when their exponents differ by
+//     15 or less; beyond that the smaller one is less than 2^-6 of half a bf16 unit of the larger, and
+//     both forms return the larger: one rounding either way.
+// sz: the token's (scale, zero) pair as stored, scale in the low half.
 // ROLLED: one loop body per word of codes, for a caller that scores a single slot per thread (the
 // straight-line form costs more in instruction fetch there than its arithmetic)
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// the eight de-quantised keys of one word of codes, as fp32
+__device__ __forceinline__ void l2_dequant_word(uint32_t w, uint32_t scale2, uint32_t zero2, float (&x)[8]) {
+#pragma unroll
+  for (int n = 0; n < 4; ++n) {
+    // nibble n into the low half, nibble n + 4 into the high half, each as the bf16 number 128 + code
+    const uint32_t c = bf16x2_sub(((w >> (4 * n)) & 0x000F000Fu) | 0x43004300u, 0x43004300u);
+    const uint32_t k = bf16x2_sub(bf16x2_mul(c, scale2), zero2);
+    x[n] = __uint_as_float(k << 16);
+    x[n + 4] = __uint_as_float(k & 0xFFFF0000u);
+  }
+}
+
 template <int DSUB, bool ROLLED = false>
-__device__ __forceinline__ float l2_logit_words(uint32_t (&w)[DSUB / 8], float scale, float zero,
-                                                const float* __restrict__ qf) {
+__device__ __forceinline__ float l2_logit_words(uint32_t (&w)[DSUB / 8], uint32_t sz, const float* __restrict__ qf) {
   constexpr int WORDS = DSUB / 8;   // 32-bit words of packed codes
+  const uint32_t scale2 = __byte_perm(sz, 0u, 0x1010), zero2 = __byte_perm(sz, 0u, 0x3232);
   float acc = 0.0f;
   if constexpr (ROLLED) {
 #pragma unroll 1
@@ -365,22 +409,18 @@ __device__ __forceinline__ float l2_logit_words(uint32_t (&w)[DSUB / 8], float s
       const uint32_t wi = w[0];
 #pragma unroll
       for (int r = 0; r + 1 < WORDS; ++r) w[r] = w[r + 1];       // the registers rotate
+      float x[8];
+      l2_dequant_word(wi, scale2, zero2, x);
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        const float c = (float)((wi >> (4 * n)) & 15u);
-        const float x = bf16r(__fsub_rn(bf16r(__fmul_rn(c, scale)), zero));
-        acc = __fadd_rn(acc, __fmul_rn(x, qf[8 * i + n]));
-      }
+      for (int n = 0; n < 8; ++n) acc = __fadd_rn(acc, __fmul_rn(x[n], qf[8 * i + n]));
     }
   } else {
 #pragma unroll
     for (int i = 0; i < WORDS; ++i) {
+      float x[8];
+      l2_dequant_word(w[i], scale2, zero2, x);
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        const float c = (float)((w[i] >> (4 * n)) & 15u);
-        const float x = bf16r(__fsub_rn(bf16r(__fmul_rn(c, scale)), zero));
-        acc = __fadd_rn(acc, __fmul_rn(x, qf[8 * i + n]));
-      }
+      for (int n = 0; n < 8; ++n) acc = __fadd_rn(acc, __fmul_rn(x[n], qf[8 * i + n]));
     }
   }
   return bf16r(acc);
@@ -405,11 +445,10 @@ __device__ __forceinline__ void l2_load_codes(const uint8_t* __restrict__ codes,
 }
 
 template <int DSUB, bool ROLLED = false>
-__device__ __forceinline__ float l2_logit(const uint8_t* __restrict__ codes, float scale, float zero,
-                                          const float* __restrict__ qf) {
+__device__ __forceinline__ float l2_logit(const uint8_t* __restrict__ codes, uint32_t sz, const float* __restrict__ qf) {
   uint32_t w[DSUB / 8];
   l2_load_codes<DSUB>(codes, w);
-  return l2_logit_words<DSUB, ROLLED>(w, scale, zero, qf);
+  return l2_logit_words<DSUB, ROLLED>(w, sz, qf);
 }
 
 // Ordered 16-bit logit of candidate slot (logical page pg, physical page ph, offset o); 0 = the
@@ -422,8 +461,8 @@ __device__ __forceinline__ uint32_t l2_slot_score(const loda_geometry& g, const 
   uint32_t ord = 0;
   if (ph >= 0 && tok >= g.sink && tok < rg.swa_lo_tok && tok < length && tok >= rg.lower && tok < rg.upper) {
     const size_t trow = ((size_t)ph * g.num_kv_heads + kv) * g.page + o;
-    const __nv_bfloat162 sz = *(const __nv_bfloat162*)((const bf16*)L.tail_sz + trow * 2);
-    const float lg = l2_logit<DSUB, ROLLED>((const uint8_t*)L.tail_code + trow * (DSUB / 2), __low2float(sz), __high2float(sz), qf);
+    const uint32_t sz = *(const uint32_t*)((const bf16*)L.tail_sz + trow * 2);
+    const float lg = l2_logit<DSUB, ROLLED>((const uint8_t*)L.tail_code + trow * (DSUB / 2), sz, qf);
     if (lg == lg && lg != -INFINITY) ord = ord16(lg);
   } else if (ph < 0 && status && rg.shard_count <= 1) {     // under sequence sharding a missing page is another GPU's
     atomicOr(status, LODA_STATUS_BAD_PAGE);

@@ -139,7 +139,12 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   const int rank = (int)cluster.block_rank();        // = blockIdx.x: the cluster spans the grid's x
   const int row = blockIdx.y;
   const int b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
+#ifdef LODA_PHASES
+  // debug timeline: launches that carry the chained flag record behind the others
+  const int cta_id = blockIdx.y * gridDim.x + blockIdx.x + ((S.flags & LODA_SEL_CHAINED) ? gridDim.x * gridDim.y : 0);
+#else
   const int cta_id = blockIdx.y * gridDim.x + blockIdx.x;
+#endif
   // The leader's copies of what the cluster shares.  The leader itself uses its plain shared
   // addresses: a store through the cluster window into the CTA's own shared memory is a remote
   // store that the CTA's next barrier has to wait for (measured: the leader reached the first
@@ -185,6 +190,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   const unsigned char* mm_row = (const unsigned char*)L.page_mm + rowi * stat_row_bytes(g.max_blocks, T::CPR);
   const unsigned char* sum_row = (const unsigned char*)L.page_sum + rowi * stat_row_bytes(g.max_blocks, T::NC);
   const int page_end = min(rg.kt_eff, g.max_blocks);
+  const int tile_end = min(page_end, pools_end(rg));     // tiles behind the pools are skipped
   const int near_hi = min(min(rg.swa_lo_blk, rg.kt_eff), g.max_blocks);
   const int near_lo = rg.near_blks, near_lo8 = near_lo & ~7;
   const int n_near = near_hi > near_lo ? min(near_hi - near_lo8, L1_NEAR_CAP) : 0;
@@ -194,7 +200,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
   // one bulk copy per group of 32 pages, issued by the lanes of warp 0, counted on the buffer's mbarrier
   auto stage = [&](int it) {
     const int p0 = (rank + it * CS) * P;
-    if (it < tiles_per_cta && p0 < page_end)
+    if (it < tiles_per_cta && p0 < tile_end)
       l1_issue_tile<DSUB, P, false>(g, rg, p0, page_end, rows + (size_t)(it & 1) * lay.rows_bytes, bars + (it & 1), mm_row,
                                     sum_row);
   };
@@ -229,7 +235,7 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
 #pragma unroll 1
   for (int it = 0; it < tiles_per_cta; ++it) {
     const int p0 = (rank + it * CS) * P;
-    if (p0 >= page_end) break;
+    if (p0 >= tile_end) break;
     if (!mbar_wait(bars + (it & 1), (uint32_t)(it >> 1) & 1u)) timed_out = true;      // tile it has landed
     LODA_SUB0(54 + 2 * it);
     const int page = p0 + tid;
@@ -450,6 +456,10 @@ __global__ void __launch_bounds__(SF_P) select_fused_kernel(loda_geometry g, lod
       __syncthreads();
       if (warp * 16 < ntok) attn_warp_step<D, DV>(Ks, Vs, slot_t, warp * 16, ntok, qa, at.scale_log2, oacc, m_run, z_run);
     }
+    // The dependent launch is released here: the next layer's launch then runs its prologue (metadata,
+    // first statistics tiles) while this one merges.  Releasing earlier gains nothing (measured at the
+    // kernel's start, after level 1 and before the attention: the same step time): the prologue is
+    // already hidden, and the dependent's wait ends when this grid has completed, wherever it was released.
     pdl_launch_dependents();
     LODA_PHASE(sel, cta_id, 10);
     // merge the warps of this CTA (fixed order) and hand the CTA's partial to the leader
