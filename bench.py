@@ -469,7 +469,8 @@ def batched_arm(torch, capi, lib, dev, seed, barrier):
             "kernel_us_per_launch": per_kernel, "device_status": status, "parity_checked": parity,
             "l1_roofline": {"bound": "hbm", "achieved": l1_bytes / (per_kernel["l1"] * 1e-6) / 1e9, "peak": peak,
                             "unit": "GB/s", "frac": l1_bytes / (per_kernel["l1"] * 1e-6) / 1e9 / peak,
-                            "peak_kind": f"of {kind}", "algorithmic_bytes": l1_bytes},
+                            "peak_kind": f"of {kind}", "algorithmic_bytes": l1_bytes,
+                            "traffic": measured_traffic("l1_stream_kernel", "cfg3-32req")},
             "chain_hbm_frac_of_8TBs": tot_bytes / (us_layer * 1e-6) / 8e12}
 
 

@@ -252,44 +252,51 @@ __global__ void __launch_bounds__(P, 2) l1_kernel(loda_geometry g, loda_layer L,
 
 // ---------------------------------------------------------------------------
 // Level 1 for large batches: a grid that fills the GPU once (two CTAs per SM) and stays.  The rows'
-// tiles are cut into items (row, split) as above; CTA c takes the items c, c + gridDim.x, ...; it reads
-// the metadata of all its items in one round trip at the start, and its tiles then flow through the
-// stages as one stream across the items: warp 0 refills a stage as soon as all eight warps have
-// released it (an `empty` mbarrier per stage, one arrival per warp) with the next tile of the stream,
-// whichever item that belongs to, so no item pays for its own first copy and no barrier of the CTA
-// sits between two tiles.  The query of an item is staged into a ring of four slots when its first
-// tile is issued.  After an item's last tile its threads fence and one of them adds the row's ticket.
-// When a CTA's items are done it turns to selection: it claims the next row from a queue (rows in
-// order, which is roughly the order in which they complete), waits — bounded — for the row's ticket
-// to show all its items, and selects as the last CTA of a row does above.  Every CTA of the grid is
-// resident (the host sizes the grid by the occupancy the runtime reports), so a CTA that waits for a
-// row waits for CTAs that are running.
+// tiles are cut into items (row, split) as above; CTA c takes the items c, c + gridDim.x, ...  It reads
+// the metadata and the queries of all its items in one round trip at the start.  Then every WARP runs
+// a pipeline of its own over the CTA's tiles: a warp scores the 32 pages of one group of each tile,
+// and a group is one contiguous block of the statistics, so the warp fetches its group of the tiles
+// ahead itself (one bulk copy of a group's min/max rows, or of its sum rows, on the warp's own
+// mbarrier per stage) and never waits for another warp: no barrier of the CTA and no shared stage
+// between two tiles, across items as within them.  (The one group of a row that holds pages of both
+// pools stages its min/max rows and reads its sums from global memory.)  A warp that has finished its
+// part of an item publishes its scores and adds one to the row's ticket.  When its warps are done the
+// CTA turns to selection: it claims the next row from a queue (rows in order, roughly the order in
+// which they complete), waits — bounded — for the row's ticket to show all warps of all its items, and
+// selects as the last CTA of a row does above.  Every CTA of the grid is resident
+// (the host sizes the grid by the occupancy the runtime reports), so a CTA that waits for a row waits
+// for CTAs that are running.
 // ---------------------------------------------------------------------------
-constexpr int L1S_MAX_ITEMS = 16;      // items per CTA
-constexpr int L1S_QRING = 4;           // query slots: tiles of at most NSTAGE + 1 <= 4 items are in flight
+constexpr int L1S_MAX_ITEMS = 8;       // items per CTA (their queries stay in shared memory)
+constexpr int L1S_STAGES = 3;          // groups in flight per warp
 constexpr int L1S_POLL_LIMIT = 1 << 18;
+
+template <int DSUB>
+struct L1Stream {
+  using T = L1Tile<DSUB, L1_TP>;
+  static constexpr size_t STAGES_BYTES = (size_t)L1S_STAGES * (L1_TP / 32) * T::SLOT;     // [stage][warp] slots
+  static constexpr size_t ROWS_BYTES = STAGES_BYTES > L1_TAIL_BYTES ? STAGES_BYTES : L1_TAIL_BYTES;
+};
 
 template <int DSUB, bool GENERIC>
 __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, loda_layer L, loda_batch B,
                                                              const bf16* __restrict__ q, float scale,
                                                              loda_selection out, SelectWorkspace ws, int nsplit,
                                                              int tiles_per_cta, AppendArgs ap, int n_rows) {
-  constexpr int P = L1_TP;
+  constexpr int P = L1_TP, NWARP = P / 32, NSTAGE = L1S_STAGES;
   using T = L1Tile<DSUB, P>;
-  constexpr int NSTAGE = L1Shape<DSUB>::NSTAGE;
-  constexpr size_t ROWS_BYTES = L1Shape<DSUB>::ROWS_BYTES;
+  constexpr size_t ROWS_BYTES = L1Stream<DSUB>::ROWS_BYTES;
   constexpr int NQ = GENERIC ? 4 : 3;
-  static_assert(NSTAGE + 1 <= L1S_QRING, "query ring");
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* rows = smem;
-  uint64_t* full = (uint64_t*)(smem + ROWS_BYTES);               // [NSTAGE] bytes of a tile have landed
-  uint64_t* empty = full + 4;                                    // [NSTAGE] all warps have read the tile
-  int4* desc = (int4*)(smem + ROWS_BYTES + 64);                  // [MAX_ITEMS] (length, request slot, skip bits, tiles)
+  unsigned char* rows = smem;                                    // [NSTAGE][NWARP] group slots, later the row's scores
+  uint64_t* full = (uint64_t*)(smem + ROWS_BYTES);               // [NWARP][NSTAGE]
+  int4* desc = (int4*)(smem + ROWS_BYTES + NWARP * NSTAGE * 8);  // [MAX_ITEMS] (length, request slot, skip bits, tiles)
+  Regions* regs = (Regions*)(desc + L1S_MAX_ITEMS);              // [MAX_ITEMS] the items' region geometry
   const int G = g.num_q_heads / g.num_kv_heads;
   const int nq = G * DSUB;
-  float* qring = (float*)(desc + L1S_MAX_ITEMS);                 // [QRING][NQ * G * DSUB]
-  int* kept = (int*)(qring + (size_t)L1S_QRING * NQ * nq);       // k_far + k_near + 2
-  const size_t keys_off = (ROWS_BYTES + 64 + L1S_MAX_ITEMS * 16 + (size_t)L1S_QRING * NQ * nq * 4 +
+  float* qall = (float*)(regs + L1S_MAX_ITEMS);                  // [MAX_ITEMS][NQ * G * DSUB]
+  int* kept = (int*)(qall + (size_t)L1S_MAX_ITEMS * NQ * nq);    // k_far + k_near + 2
+  const size_t keys_off = (ROWS_BYTES + NWARP * NSTAGE * 8 + L1S_MAX_ITEMS * (16 + sizeof(Regions)) + (size_t)L1S_MAX_ITEMS * NQ * nq * 4 +
                            (size_t)(g.k_far + g.k_near + 2) * 4 + 15) & ~(size_t)15;
   uint32_t* keys = (uint32_t*)(smem + keys_off);                 // 2 P + 8
   int* wtot = (int*)(keys + 2 * P + 8);                          // 8 x 32
@@ -301,22 +308,22 @@ __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, lo
   const int n_items = cta < W ? min((W - cta + ncta - 1) / ncta, L1S_MAX_ITEMS) : 0;
   const int cta_id = cta;
   LODA_PHASE(l1, cta_id, 0);
-  if (tid == 0) {
+  if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < NSTAGE; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, P / 32); }
+    for (int s = 0; s < NSTAGE; ++s) mbar_init(full + warp * NSTAGE + s, 1);
     mbar_init_fence();
   }
   pdl_wait();
   LODA_PHASE(l1, cta_id, 1);
   // the decode append of the rows cta, cta + ncta, ...: the newest token and its page lie in the
   // sliding window and are read by neither level of this step
-  if (ap.enabled && warp == 1) {
-    for (int r = cta; r < n_rows; r += ncta) append_row<DSUB>(g, L, B, ap.k_new, ap.v_new, ap.slots, ap.status, r / g.num_kv_heads, r % g.num_kv_heads, lane);
+  if (ap.enabled && warp == NWARP - 1) {
+    for (int r = cta; r < n_rows; r += ncta)
+      append_row<DSUB>(g, L, B, ap.k_new, ap.v_new, ap.slots, ap.status, r / g.num_kv_heads, r % g.num_kv_heads, lane);
   }
-  // metadata of this CTA's items, one item per thread: a single round of dependent loads per CTA
   auto item_row = [&](int k) { return (cta + k * ncta) / nsplit; };
   auto item_split = [&](int k) { return (cta + k * ncta) % nsplit; };
-  auto item_regions = [&](const int4& d) { return make_regions(g, d.x, (d.z & 1) != 0, (d.z & 2) != 0); };
+  // metadata of this CTA's items, one item per thread: a single round of dependent loads per CTA
   if (tid < n_items) {
     const int row = item_row(tid), b = row / g.num_kv_heads;
     int length = B.lengths[b];
@@ -333,87 +340,98 @@ __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, lo
     int nt = tile_end > first ? (tile_end - first + step - 1) / step : 0;
     nt = min(nt, tiles_per_cta);
     desc[tid] = make_int4(length, req, (skip_far ? 1 : 0) | (skip_near ? 2 : 0), nt);
+    regs[tid] = rg;
   }
-  __syncthreads();                                       // barriers and descriptors are ready
+  // scaled, bf16-rounded queries of the items' rows on the subspace (nfa_layer_batch_selector.py:943-963)
+  for (int i = tid; i < n_items * nq; i += P) {
+    const int k = i / nq, e = i % nq, j = e / DSUB, dd = e % DSUB;
+    const int row = item_row(k), b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
+    const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, dd)]);
+    const float qh = bf16r(__fmul_rn(qv, scale));
+    float* qhat = qall + (size_t)k * NQ * nq;
+    qhat[e] = qh;
+    *(float2*)(qhat + nq + 2 * e) = make_float2(fminf(qh, 0.0f), fmaxf(qh, 0.0f));
+    if (GENERIC) qhat[3 * nq + e] = __fmul_rn(qv, scale);
+  }
+  __syncthreads();                                       // barriers, descriptors and queries are ready
   LODA_PHASE(l1, cta_id, 2);
 
-  // ---- producer (warp 0): the tile stream ---------------------------------------------------
-  int pk = 0, pit = 0, pseq = 0, pslot = -1;             // item, tile of the item, position in the stream, query slot
-  bool dead = false;                                     // a wait gave up: no further waiting
-  auto issue_next = [&]() {
-    while (pk < n_items && pit >= desc[pk].w) { ++pk; pit = 0; }
-    if (pk >= n_items) return;
-    const int st = pseq % NSTAGE;
-    if (pseq >= NSTAGE && !dead && !mbar_wait(empty + st, (uint32_t)(pseq / NSTAGE - 1) & 1u)) dead = true;
-    const int4 d = desc[pk];
-    const int row = item_row(pk), b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
-    if (pit == 0) {
-      // scaled, bf16-rounded query of the item's row on the subspace (nfa_layer_batch_selector.py:943-963);
-      // the slots go round over the items that have tiles
-      ++pslot;
-      float* qhat = qring + (size_t)(pslot % L1S_QRING) * NQ * nq;
-      float* qmm = qhat + nq;
-      float* qraw = qmm + 2 * nq;
-      for (int i = lane; i < nq; i += 32) {
-        const int j = i / DSUB, dd = i % DSUB;
-        const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, dd)]);
-        const float qh = bf16r(__fmul_rn(qv, scale));
-        qhat[i] = qh;
-        *(float2*)(qmm + 2 * i) = make_float2(fminf(qh, 0.0f), fmaxf(qh, 0.0f));
-        if (GENERIC) qraw[i] = __fmul_rn(qv, scale);
+  // ---- every warp: its group of every tile of the CTA's items ---------------------------------------
+  {
+    uint64_t* wfull = full + warp * NSTAGE;
+    auto slot_of = [&](int st) { return rows + ((size_t)st * NWARP + warp) * T::SLOT; };
+    int pk = 0, pit = 0, pseq = 0;                       // producer side: item, tile of the item, place in the stream
+    bool dead = false;                                   // a wait gave up: no further waiting
+    // the group's statistics of the next tile of the stream into the stage that is free
+    auto issue_next = [&]() {
+      while (pk < n_items && pit >= desc[pk].w) { ++pk; pit = 0; }
+      if (pk >= n_items) return;
+      const int4 d = desc[pk];
+      const Regions& rg = regs[pk];
+      const int row = item_row(pk), kv = row % g.num_kv_heads;
+      const int g0 = (item_split(pk) + pit * nsplit) * P + warp * STAT_GROUP;      // first page of the warp's group
+      bool nm, ns;
+      l1_group_needs<GENERIC>(g, rg, g0, min(rg.kt_eff, g.max_blocks), &nm, &ns);
+      if (lane == 0) {
+        const int st = pseq % NSTAGE;
+        const size_t rowi = (size_t)d.y * g.num_kv_heads + kv;
+        const size_t gidx = (size_t)(g0 / STAT_GROUP);
+        const uint32_t bytes = nm ? (uint32_t)T::SLOT : ns ? (uint32_t)T::SUMG : 0u;
+        mbar_arrive_expect_tx(wfull + st, bytes);         // no bytes: the phase completes at once
+        if (nm)
+          bulk_copy_g2s(slot_of(st), (const unsigned char*)L.page_mm + rowi * stat_row_bytes(g.max_blocks, T::CPR) + gidx * T::SLOT,
+                        T::SLOT, wfull + st);
+        else if (ns)
+          bulk_copy_g2s(slot_of(st), (const unsigned char*)L.page_sum + rowi * stat_row_bytes(g.max_blocks, T::NC) + gidx * T::SUMG,
+                        T::SUMG, wfull + st);
       }
-      __syncwarp();                                      // ordered before the arrival on `full` below
-    }
-    const Regions rg = item_regions(d);
-    const size_t rowi = (size_t)d.y * g.num_kv_heads + kv;
-    const unsigned char* mm_row = (const unsigned char*)L.page_mm + rowi * stat_row_bytes(g.max_blocks, T::CPR);
-    const unsigned char* sum_row = (const unsigned char*)L.page_sum + rowi * stat_row_bytes(g.max_blocks, T::NC);
-    const int p0 = (item_split(pk) + pit * nsplit) * P;
-    l1_issue_tile<DSUB, P, GENERIC>(g, rg, p0, min(rg.kt_eff, g.max_blocks), rows + (size_t)st * T::STAGE, full + st, mm_row,
-                                    sum_row);
-    ++pit;
-    ++pseq;
-  };
-  if (warp == 0) {
+      ++pit;
+      ++pseq;
+    };
 #pragma unroll 1
     for (int s = 0; s < NSTAGE; ++s) issue_next();
-  }
-
-  // ---- consumers (all warps): item by item ----------------------------------------------------
-  int cseq = 0, cslot = -1;
+    int cseq = 0;
 #pragma unroll 1
-  for (int k = 0; k < n_items; ++k) {
-    const int4 d = desc[k];
-    const int row = item_row(k);
-    if (d.w > 0) {
-      const Regions rg = item_regions(d);
+    for (int k = 0; k < n_items; ++k) {
+      const int4 d = desc[k];
+      const int row = item_row(k), kv = row % g.num_kv_heads;
+      if (d.w == 0) {                                    // an item without tiles still counts for its row
+        if (lane == 0) atomicAdd(ws.l1_ticket + row, 1);
+        continue;
+      }
+      const Regions rg = regs[k];
       const int page_end = min(rg.kt_eff, g.max_blocks);
-      ++cslot;
-      const float* qhat = qring + (size_t)(cslot % L1S_QRING) * NQ * nq;
+      const float* qhat = qall + (size_t)k * NQ * nq;
       uint16_t* row_scores = ws.l1_scores + (size_t)row * ws.score_stride;
+      const size_t rowi = (size_t)d.y * g.num_kv_heads + kv;
+      const unsigned char* sum_row = (const unsigned char*)L.page_sum + rowi * stat_row_bytes(g.max_blocks, T::NC);
 #pragma unroll 1
       for (int it = 0; it < d.w; ++it) {
         const int st = cseq % NSTAGE;
         if (cseq < 10) { LODA_SUB0(32 + 3 * cseq); }
-        if (!dead && !mbar_wait(full + st, (uint32_t)(cseq / NSTAGE) & 1u)) dead = true;
+        if (!dead && !mbar_wait(wfull + st, (uint32_t)(cseq / NSTAGE) & 1u)) dead = true;
         if (cseq < 10) { LODA_SUB0(33 + 3 * cseq); }
-        const int p0 = (item_split(k) + it * nsplit) * P;
-        const uint32_t ord = l1_page_score<DSUB, P, GENERIC>(g, rg, p0, page_end, rows + (size_t)st * T::STAGE, qhat,
-                                                              qhat + nq, G, qhat + 3 * nq);
-        row_scores[p0 + tid] = (uint16_t)ord;            // the selecting CTA masks what lies outside the pools
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty + st);          // this warp has read the stage
+        const int g0 = (item_split(k) + it * nsplit) * P + warp * STAT_GROUP;
+        bool nm, ns;
+        l1_group_needs<GENERIC>(g, rg, g0, page_end, &nm, &ns);
+        const unsigned char* slot = slot_of(st) + lane * 16;
+        // a group with pages of both pools staged its min/max rows: its sums come from global memory
+        const unsigned char* sum_src = nm ? sum_row + (size_t)(g0 / STAT_GROUP) * T::SUMG + lane * 16 : slot;
+        const uint32_t ord = l1_page_score_src<DSUB, GENERIC>(g, rg, g0 + lane, slot, sum_src, qhat, qhat + nq, G, qhat + 3 * nq);
+        row_scores[g0 + lane] = (uint16_t)ord;           // the selecting CTA masks what lies outside the pools
+        __syncwarp();                                    // every lane has read the slot
         if (cseq < 10) { LODA_SUB0(34 + 3 * cseq); }
         ++cseq;
-        if (warp == 0) issue_next();
+        issue_next();
       }
+      // this warp's part of the item is done: publish its scores, then count it on the row's ticket (a row
+      // is complete at nsplit x NWARP; its selection may start while this CTA still scores other items)
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) atomicAdd(ws.l1_ticket + row, 1);
     }
-    // the item is done (an item without tiles too): publish the scores, count the row's ticket
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) atomicAdd(ws.l1_ticket + row, 1);
+    if (dead && lane == 0 && ap.status) atomicOr(ap.status, LODA_STATUS_TIMEOUT);
   }
-  if (dead && lane == 0 && ap.status) atomicOr(ap.status, LODA_STATUS_TIMEOUT);
   LODA_PHASE(l1, cta_id, 4);
   pdl_launch_dependents();
 
@@ -427,7 +445,7 @@ __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, lo
       int ok = 1;
       if (r < n_rows) {
         int tries = 0;
-        while (*(volatile int*)(ws.l1_ticket + r) < nsplit) {
+        while (*(volatile int*)(ws.l1_ticket + r) < nsplit * NWARP) {
           if (++tries > L1S_POLL_LIMIT) { ok = 0; break; }
           __nanosleep(64);
         }
@@ -491,8 +509,9 @@ static void l1_split(const loda_geometry& g, int rows, int P, int* ctas_per_row,
 template <int DS>
 static size_t l1_stream_smem_bytes_d(const loda_geometry& g) {
   const int G = g.num_q_heads / g.num_kv_heads;
-  return L1Shape<DS>::ROWS_BYTES + 64 + L1S_MAX_ITEMS * 16 + (size_t)L1S_QRING * (l1_generic(g) ? 4 : 3) * G * DS * 4 +
-         (size_t)(g.k_far + g.k_near + 2) * 4 + (size_t)(2 * L1_TP + 8) * 4 + (256 + 8) * 4 + 32;
+  return L1Stream<DS>::ROWS_BYTES + (L1_TP / 32) * L1S_STAGES * 8 + L1S_MAX_ITEMS * (16 + sizeof(Regions)) +
+         (size_t)L1S_MAX_ITEMS * (l1_generic(g) ? 4 : 3) * G * DS * 4 + (size_t)(g.k_far + g.k_near + 2) * 4 +
+         (size_t)(2 * L1_TP + 8) * 4 + (256 + 8) * 4 + 32;
 }
 
 // Grid of the streaming kernel: every CTA resident at once (what the runtime reports for this kernel
@@ -509,7 +528,7 @@ static int l1_stream_grid(size_t smem) {
       (void)cudaGetLastError();
       n = -1;
     }
-    per_sm[dev] = n > 2 ? 2 : n;
+    per_sm[dev] = n >= 2 ? 2 : -1;                // one CTA per SM would leave the warps' latencies uncovered
   }
   return per_sm[dev] > 0 ? per_sm[dev] * device_sm_count() : 0;
 }

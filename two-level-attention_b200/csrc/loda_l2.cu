@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
   int* scan = (int*)(smem + off); off += 40 * 4;
   int* sh = (int*)(smem + off); off += 16 * 4;
   uint8_t* win = (uint8_t*)(smem + off); off += ((size_t)K2 + 15) & ~(size_t)15;
+  uint32_t* hist = (uint32_t*)(smem + off); off += 2048 * 4;      // the row's scores by their top 12 bits (selecting CTA)
   // numeric near-token quota only: one region's scores and the concatenated middle
   uint16_t* sc2 = (uint16_t*)(smem + off); off += ((size_t)np_max * g.page * 2 + 15) & ~(size_t)15;
   int* fin = (int*)(smem + off);
@@ -170,6 +171,10 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
     if (!sh[0]) return;
     __threadfence();
   }
+  // the row's scores into shared memory, counted on the way into a histogram by their top 12 bits (two
+  // 16-bit counters per word): the selection starts from the bin of the quota-th best score
+  for (int i = tid; i < 2048 / 4; i += NT) ((uint4*)hist)[i] = make_uint4(0u, 0u, 0u, 0u);
+  __syncthreads();
   for (int i = tid; i < (nitems + 7) / 8; i += NT) {
     uint4 v;
     if (ws.gathered == nullptr) {
@@ -182,6 +187,12 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
       }
     }
     ((uint4*)sc)[i] = v;
+    uint32_t o[8];
+    unpack_u16x8(v, o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (o[j] != 0u && i * 8 + j < nitems) atomicAdd(hist + (o[j] >> 5), 1u << ((o[j] >> 4 & 1u) * 16));
+    }
   }
   __syncthreads();
 #if LODA_PDL_TRIGGER == 3
@@ -191,7 +202,8 @@ __global__ void __launch_bounds__(NT, LODA_L2_MINB) l2_kernel(loda_geometry g, l
   L2Shared shm{sc, pages, physs, mid_a, mid_b, wtot, scan, win};
   shm.sc2 = sc2;
   shm.fin = fin;
-  l2_select_and_write<NT, 0, false, NUMERIC>(g, rg, S, status, table, b, kv, row, length, nitems, shm, ws.l2_ticket + row,
+  shm.hist = hist;
+  l2_select_and_write<NT, 0, true, NUMERIC>(g, rg, S, status, table, b, kv, row, length, nitems, shm, ws.l2_ticket + row,
                                              LODA_PDL_TRIGGER == 1);
   LODA_PHASE(l2, cta_id, 9);
 }
@@ -248,7 +260,7 @@ size_t l2_smem_bytes(const loda_geometry& g) {
   const size_t np_max = g.k_far + g.k_near + 2;
   const bool numeric = g.near_tokens_p1 > 0;      // a masked copy of the scores and the concatenated middle
   return ((np_max * g.page * 2 + 15) & ~(size_t)15) * (numeric ? 2 : 1) + g.sub_dims * 4 + 2 * np_max * 4 +
-         (numeric ? 3 : 2) * (size_t)g.level2_topk * 4 + 192 * 4 + (40 + 16) * 4 + g.level2_topk + 64;
+         (numeric ? 3 : 2) * (size_t)g.level2_topk * 4 + 192 * 4 + (40 + 16) * 4 + g.level2_topk + 64 + 2048 * 4;
 }
 
 template <int DS>

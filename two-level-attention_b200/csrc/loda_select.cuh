@@ -163,20 +163,20 @@ __device__ __forceinline__ void l1_issue_tile(const loda_geometry& g, const Regi
   if (ns) bulk_copy_g2s(nm ? stage + T::GROUPS * T::SLOT : stage + lane * T::SLOT, sum_row + gidx * T::SUMG, T::SUMG, bar);
 }
 
-// Ordered 16-bit score of the logical page p0 + threadIdx.x from the staged tile; 0 = the page is in
-// neither pool or scores -inf.
+// Ordered 16-bit score of one logical page; 0 = the page is in neither pool or scores -inf.
+// mm_src / sum_src: chunk 0 of the page's min/max rows / sum rows in the group layout (the chunks of a page
+// lie STAT_GROUP * 16 bytes apart), in shared or global memory; only the one the page's pool is scored on
+// is read.
 // Per head the bound (min . min(q, 0) + max . max(q, 0)) or the mean score (mean . q) is rounded to
 // bf16; the page score is the mean over the GQA group, rounded to bf16 — or, for the far method
 // avg_top2, the mean of the two best per-head mean scores computed from the unrounded scaled query
 // qraw (nfa_layer_batch_selector.py:290-354, 2412-2427).
-template <int DSUB, int TP, bool GENERIC = false>
-__device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const Regions& rg, int p0, int page_end,
-                                                  const unsigned char* stage, const float* qhat, const float* qmm,
-                                                  int G, const float* qraw = nullptr) {
-  using T = L1Tile<DSUB, TP>;
+template <int DSUB, bool GENERIC = false>
+__device__ __forceinline__ uint32_t l1_page_score_src(const loda_geometry& g, const Regions& rg, int page,
+                                                      const unsigned char* mm_src, const unsigned char* sum_src,
+                                                      const float* qhat, const float* qmm, int G,
+                                                      const float* qraw = nullptr) {
   constexpr int NC = DSUB / 8, CS = STAT_GROUP * 16;      // CS: bytes between two chunks of a page
-  const int page = p0 + (int)threadIdx.x;
-  const int grp = (int)threadIdx.x / STAT_GROUP, lane = (int)threadIdx.x % STAT_GROUP;
   uint32_t ord = 0;
   const float gf = (float)G;
   const bool far = in_far_pool(rg, page);
@@ -184,7 +184,7 @@ __device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const 
   if (!far && !near) return 0u;
   const bool use_mm = far ? l1_far_uses_minmax<GENERIC>(g) : l1_near_uses_minmax<GENERIC>(g);
   if (use_mm) {
-    const unsigned char* src = stage + grp * T::SLOT + lane * 16;
+    const unsigned char* src = mm_src;
     unsigned long long kp[DSUB];                      // (min_d, max_d) as packed fp32
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
@@ -199,10 +199,7 @@ __device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const 
     for (int j = 0; j < G; ++j) acc = __fadd_rn(acc, bf16r(bound_pair<DSUB>(kp, qmm + j * 2 * DSUB)));
     ord = ord16(bf16r(__fdiv_rn(acc, gf)));
   } else {
-    // the sums sit in the group's own slot, or in the spill slot when the group also staged min/max rows
-    bool nm, ns;
-    l1_group_needs<GENERIC>(g, rg, p0 + grp * STAT_GROUP, page_end, &nm, &ns);
-    const unsigned char* src = (nm ? stage + T::GROUPS * T::SLOT : stage + grp * T::SLOT) + lane * 16;
+    const unsigned char* src = sum_src;
     float kavg[DSUB];
     // mean = sum / page: the page size is a power of two, so the division is an exact scaling and
     // the multiplication by 1 / page gives the same bits at a fraction of the instructions
@@ -229,6 +226,21 @@ __device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const 
     }
   }
   return ord == ORD16_NEG_INF ? 0u : ord;   // a -inf score never competes (it equals "not in the pool")
+}
+
+// The same for the logical page p0 + threadIdx.x of a tile staged by l1_issue_tile: the sums sit in the
+// group's own slot, or in the spill slot when the group also staged min/max rows.
+template <int DSUB, int TP, bool GENERIC = false>
+__device__ __forceinline__ uint32_t l1_page_score(const loda_geometry& g, const Regions& rg, int p0, int page_end,
+                                                  const unsigned char* stage, const float* qhat, const float* qmm,
+                                                  int G, const float* qraw = nullptr) {
+  using T = L1Tile<DSUB, TP>;
+  const int grp = (int)threadIdx.x / STAT_GROUP, lane = (int)threadIdx.x % STAT_GROUP;
+  bool nm, ns;
+  l1_group_needs<GENERIC>(g, rg, p0 + grp * STAT_GROUP, page_end, &nm, &ns);
+  const unsigned char* mm_src = stage + grp * T::SLOT + lane * 16;
+  const unsigned char* sum_src = (nm ? stage + T::GROUPS * T::SLOT : stage + grp * T::SLOT) + lane * 16;
+  return l1_page_score_src<DSUB, GENERIC>(g, rg, p0 + (int)threadIdx.x, mm_src, sum_src, qhat, qmm, G, qraw);
 }
 
 // the selecting CTA reuses the staging area: 40 KB for the far pool's scores (2 bytes per page)
