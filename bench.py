@@ -933,6 +933,8 @@ def main():
     ap.add_argument("--skip-dense", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-batched", action="store_true")
+    ap.add_argument("--only-batched", action="store_true",
+                    help="run only the 32-request arm and print its object (small captures of its kernels under a profiler)")
     ap.add_argument("--skip-tls", action="store_true")
     ap.add_argument("--skip-cfg4", action="store_true")
     ap.add_argument("--skip-reference-triton", action="store_true")
@@ -978,6 +980,10 @@ def main():
         torch.cuda.synchronize()
 
     K, W = args.steps, args.warmup
+    if args.only_batched:
+        if rank == 0:
+            print(json.dumps({"batched": batched_arm(torch, capi, lib, dev, 5, lambda: torch.cuda.synchronize())}), flush=True)
+        return
     if args.shard == "sequence" and world > 1:
         run_sequence_sharded(torch, dist, capi, lib, dev, local, rank, world, K, W, barrier)
         dist.barrier()

@@ -42,7 +42,7 @@ extern "C" {
 #define LODA_STATUS_BAD_PAGE 2u
 #define LODA_STATUS_TRUNCATED 4u
 #define LODA_STATUS_BAD_REQ 8u   /* an active row's request slot is outside [0, max_requests): treated as a padding row */
-#define LODA_STATUS_TIMEOUT 16u  /* a bounded wait on an asynchronous copy gave up (the row's result is not valid) */
+#define LODA_STATUS_TIMEOUT 16u  /* a bounded wait (on an asynchronous copy, or on a row's scores in the level-1 launch of a large batch) gave up: the row's result is not valid */
 
 /* Static geometry of one attention layer's cache and selector.
  * Mirrors GraphReadyPagedRegionCache.__init__ (sparse_attn/cache/

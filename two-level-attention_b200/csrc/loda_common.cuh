@@ -919,7 +919,7 @@ __host__ __device__ __forceinline__ size_t stat_chunk_offset(int page, int c, in
 // ---------------------------------------------------------------------------
 // Bulk asynchronous copy global -> shared memory of this CTA, completion counted in bytes on an
 // mbarrier (both addresses and the size are multiples of 16 bytes).  Plain copies of this GPU's own
-// memory only: no multicast.
+// memory into the issuing CTA's shared memory only.
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int arrivals) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(arrivals) : "memory");
