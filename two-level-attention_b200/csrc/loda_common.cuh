@@ -761,10 +761,12 @@ template <int NT, int BAR = 0, int TBASE = 0, bool HIST = false>
 __device__ __forceinline__ int block_prefilter_topk(const uint16_t* sc, int n, int k, int* out, uint32_t* keys,
                                                     int* wtot, int* sh, const uint32_t* hist = nullptr) {
   static_assert(NT % 256 == 0 && NT / 256 <= 32, "group layout");
-  // 256 groups: the k-th largest of the group maxima is the tighter a bound the more groups there are
-  // (k <= 128 of the best scores fall into ~k (1 - k / 512) distinct groups of 256, so about 1.5 k scores
-  // survive; with 128 groups it was 1.5 k scores for k = 96), and ranking 256 maxima is still cheap
-  constexpr int NG = 256;                        // groups
+  // The k-th largest of the group maxima is the tighter a bound the more groups there are: the g-th
+  // largest group maximum is about the score of rank -NG ln(1 - g / NG), so k = 96 leaves ~120 survivors
+  // with 256 groups and ~180 with 128 (whatever the row's length) — but ranking the maxima costs NG / 4
+  // vector compares per thread.  Two threads share a maximum's ranking, so a CTA of 512 threads takes 256
+  // groups and one of 256 threads 128: 16 + 45 compare rounds there instead of 64 + 30.
+  constexpr int NG = NT >= 512 ? 256 : 128;      // groups
   constexpr int GS = NT / NG;                    // threads per group
   constexpr int NW = NT / 32;
   const int tid = ((int)threadIdx.x - TBASE), lane = tid & 31, warp = tid >> 5;

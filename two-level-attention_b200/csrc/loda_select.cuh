@@ -337,9 +337,13 @@ __device__ __forceinline__ int l1_select_pages(const loda_geometry& g, const Reg
         }
       }
       if (n_near > 0) {
-        n_n = n_near <= P ? block_rank_topk_small<P>(scn, n_near, g.k_near, kept_near, keys, wtot)
-                          : block_rank_topk_pair<P>(scn, n_near, g.k_near, kept_near, keys, wtot);
-        for (int i = tid; i < n_n; i += P) kept_near[i] += near_lo8;
+        // the near row starts at a multiple of 8 pages; ranked from the pool's first page on, the usual
+        // pool of P pages takes the one-score-per-thread routine (half the compares of the pair routine)
+        const int lead = near_lo - near_lo8, nn = n_near - lead;
+        if (nn > 0)
+          n_n = nn <= P ? block_rank_topk_small<P>(scn + lead, nn, g.k_near, kept_near, keys, wtot)
+                        : block_rank_topk_pair<P>(scn + lead, nn, g.k_near, kept_near, keys, wtot);
+        for (int i = tid; i < n_n; i += P) kept_near[i] += near_lo;
         __syncthreads();
       }
     }

@@ -250,11 +250,12 @@ def sequence_sharded_decode_step(shard, layer_idx, req_ids, query_states, attent
     x = shard.exchange_buffers(b)
     # level 1: own pages' scores -> one all-gather of the rows -> selection on the OR of the ranks' rows
     shard.l1_scores_stage(layer_idx, b, q, scale)
-    dist.all_gather_into_tensor(x["l1"], shard.l1_scores, group=group)
+    # (16-bit integers are not a collective dtype of the NCCL process group: the rows travel as bytes)
+    dist.all_gather_into_tensor(x["l1"].view(torch.uint8), shard.l1_scores.view(torch.uint8), group=group)
     shard.l1_select_stage(layer_idx, b, q, scale, gathered=x["l1"])
     # level 2: own candidates' logits -> all-gather -> quota selection, hole fill and union
     shard.l2_scores_stage(layer_idx, b, q, scale)
-    dist.all_gather_into_tensor(x["l2"], shard.l2_scores, group=group)
+    dist.all_gather_into_tensor(x["l2"].view(torch.uint8), shard.l2_scores.view(torch.uint8), group=group)
     shard.l2_select_stage(layer_idx, b, q, scale, gathered=x["l2"])
     # attention over the own tokens -> all-gather of (out, max, sum) -> fixed-order merge (one kernel)
     shard.attend_stage(layer_idx, b, q, scale, out=x["out"], lse=x["lse"])

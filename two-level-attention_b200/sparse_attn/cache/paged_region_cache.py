@@ -121,11 +121,30 @@ class GraphReadyPagedRegionCache:
             return torch.full(shape, value, dtype=dtype, device=device)
 
         self.block_table_buf = full((n_layers, max_requests, max_blocks), pad, torch.int32)
-        self.slot_mapping_buf = full((n_layers, max_query_tokens), PAD_SLOT, torch.int32)
-        self.query_to_req_buf = full((max_query_tokens,), -1, torch.int32)
-        self.active_req_ids_buf = full((max_query_tokens,), self.INVALID_REQ_ID, torch.int64)
-        self.valid_req_ids_buf = full((max_query_tokens,), 0, torch.int64)
-        self.planned_lengths_buf = full((max_query_tokens,), 0, torch.int32)
+        # The per-step metadata (slots, query -> request row, lengths, request ids) is one block on the
+        # device and one block of pinned host memory with the same layout, moved by ONE copy per step;
+        # the buffers below are views of the device block.
+        q_cap = max_query_tokens
+        n32 = (n_layers + 2) * q_cap
+        n32 += n32 & 1                                   # the 64-bit ids start on an 8-byte boundary
+        self._meta_dev = torch.zeros(n32 + 4 * q_cap, dtype=torch.int32, device=device)
+        self._meta_cpu = torch.zeros(n32 + 4 * q_cap, dtype=torch.int32).pin_memory()
+
+        def carve(block):
+            slots = block[:n_layers * q_cap].view(n_layers, q_cap)
+            q2r = block[n_layers * q_cap:(n_layers + 1) * q_cap]
+            lens = block[(n_layers + 1) * q_cap:(n_layers + 2) * q_cap]
+            act = block[n32:n32 + 2 * q_cap].view(torch.int64)
+            val = block[n32 + 2 * q_cap:n32 + 4 * q_cap].view(torch.int64)
+            return slots, q2r, lens, act, val
+
+        (self.slot_mapping_buf, self.query_to_req_buf, self.planned_lengths_buf, self.active_req_ids_buf,
+         self.valid_req_ids_buf) = carve(self._meta_dev)
+        self._cpu_slots, cpu_q2r, cpu_lens, cpu_act, cpu_val = carve(self._meta_cpu)
+        self._cpu_slots.fill_(PAD_SLOT)
+        cpu_q2r.fill_(-1)
+        cpu_act.fill_(self.INVALID_REQ_ID)
+        self._meta_dev.copy_(self._meta_cpu)
         self.gather_indices_buf = full((n_layers, max_requests, num_kv_heads, max_visible_len),
                                        INVALID_GATHER_IDX, torch.int32)
         self.visible_lens_buf = full((n_layers, max_requests, num_kv_heads), 0, torch.int32)
@@ -136,13 +155,10 @@ class GraphReadyPagedRegionCache:
         self.skip_near_layer_buf = torch.zeros((n_layers, max_requests), dtype=torch.int32, device=device)
         # pinned staging: one H2D copy per buffer per step
         self._cpu_block_table = torch.full((n_layers, max_requests, max_blocks), pad, dtype=torch.int32).pin_memory()
-        self._cpu_slots = torch.full((n_layers, max_query_tokens), PAD_SLOT, dtype=torch.int32).pin_memory()
-        self._cpu_meta64 = torch.zeros((2, max_query_tokens), dtype=torch.int64).pin_memory()
-        self._cpu_meta32 = torch.zeros((2, max_query_tokens), dtype=torch.int32).pin_memory()
         # numpy views of the same pinned memory: scalar writes without tensor dispatch
         self._np_slots = self._cpu_slots.numpy()
-        self._np_meta64 = self._cpu_meta64.numpy()
-        self._np_meta32 = self._cpu_meta32.numpy()
+        self._np_meta64 = (cpu_act.numpy(), cpu_val.numpy())
+        self._np_meta32 = (cpu_lens.numpy(), cpu_q2r.numpy())
         self._runtime = None
         self._nfa_selector_workspace = {}
         # True: selector calls also write the best-first page lists and the L2
@@ -332,13 +348,7 @@ class GraphReadyPagedRegionCache:
             lens[b] = planned
             q2r[b] = b
             self.pending_lengths[request_id] = planned
-        act, val = self._cpu_meta64[0], self._cpu_meta64[1]
-        lens, q2r = self._cpu_meta32[0], self._cpu_meta32[1]
-        self.slot_mapping_buf[:, :batch].copy_(self._cpu_slots[:, :batch], non_blocking=True)
-        self.active_req_ids_buf[:batch].copy_(act[:batch], non_blocking=True)
-        self.valid_req_ids_buf[:batch].copy_(val[:batch], non_blocking=True)
-        self.planned_lengths_buf[:batch].copy_(lens[:batch], non_blocking=True)
-        self.query_to_req_buf.copy_(q2r, non_blocking=True)
+        self._meta_dev.copy_(self._meta_cpu, non_blocking=True)      # one copy: slots, rows, lengths, ids
 
     def commit_step(self):
         for request_id, planned in self.pending_lengths.items():
