@@ -327,6 +327,16 @@ def dense_decode_us(torch, dev):
     return arms
 
 
+def agree_max(torch, value):
+    """The largest of the ranks' values (every rank must replay a graph that holds collectives equally often)."""
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return int(value)
+    t = torch.tensor([int(value)], device="cuda", dtype=torch.int64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return int(t.item())
+
+
 def measure_device(torch, capi, lib, wl, W, K, barrier, after_layer=None, kernels=True, min_timed_s=MIN_TIMED_S,
                    out=None):
     """Device-resident timing of a workload: W eager warm-up steps, K steps captured in one CUDA graph
@@ -362,6 +372,7 @@ def measure_device(torch, capi, lib, wl, W, K, barrier, after_layer=None, kernel
     stream.synchronize()
     one_ms = max(e0.elapsed_time(e1), 1e-3)
     replays = max(1, min(2000, int(1.1 * min_timed_s * 1e3 / one_ms) + 2))
+    replays = agree_max(torch, replays)      # the same count on every rank: the graph may hold collectives
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
     barrier()
     with torch.cuda.stream(stream):

@@ -157,6 +157,7 @@ class GraphReadyPagedRegionCache:
         self._cpu_block_table = torch.full((n_layers, max_requests, max_blocks), pad, dtype=torch.int32).pin_memory()
         # numpy views of the same pinned memory: scalar writes without tensor dispatch
         self._np_slots = self._cpu_slots.numpy()
+        self._np_block_table = self._cpu_block_table.numpy()
         self._np_meta64 = (cpu_act.numpy(), cpu_val.numpy())
         self._np_meta32 = (cpu_lens.numpy(), cpu_q2r.numpy())
         self._runtime = None
@@ -336,13 +337,14 @@ class GraphReadyPagedRegionCache:
             planned = state.logical_length + 1
             pos = planned - 1
             lp, off = divmod(pos, page)
-            for layer_idx in range(self.n_layers):
-                table = state.block_tables[layer_idx]
-                if len(table) <= lp:
-                    self._grow_table(state, request_id, layer_idx, lp + 1)
-                    self.block_table_buf[layer_idx, request_id, lp:lp + 1].copy_(
-                        self._cpu_block_table[layer_idx, request_id, lp:lp + 1], non_blocking=True)
-                slots_np[layer_idx, b] = table[lp] * page + off
+            if min(map(len, state.block_tables)) <= lp:      # the token opens a page in some layer
+                for layer_idx in range(self.n_layers):
+                    if len(state.block_tables[layer_idx]) <= lp:
+                        self._grow_table(state, request_id, layer_idx, lp + 1)
+                        self.block_table_buf[layer_idx, request_id, lp:lp + 1].copy_(
+                            self._cpu_block_table[layer_idx, request_id, lp:lp + 1], non_blocking=True)
+            # the slot of the token in every layer at once (the pinned table mirrors the per-layer lists)
+            slots_np[:, b] = self._np_block_table[:, request_id, lp] * page + off
             act[b] = request_id
             val[b] = request_id
             lens[b] = planned
