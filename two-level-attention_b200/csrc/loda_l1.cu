@@ -267,8 +267,19 @@ __global__ void __launch_bounds__(P, 2) l1_kernel(loda_geometry g, loda_layer L,
 // (the host sizes the grid by the occupancy the runtime reports), so a CTA that waits for a row waits
 // for CTAs that are running.
 // ---------------------------------------------------------------------------
-constexpr int L1S_MAX_ITEMS = 8;       // items per CTA (their queries stay in shared memory)
-constexpr int L1S_STAGES = 3;          // groups in flight per warp
+// (build-time knobs; measured on the 32-request batch: 2 stages and 4 items 48.7 us, 3 and 4 48.8, 3 and 6 49.0,
+// 2 and 8 51.5 — the launch is bound by the scoring arithmetic, not by the depth or the item size)
+#ifndef LODA_L1S_MAX_ITEMS
+#define LODA_L1S_MAX_ITEMS 8
+#endif
+#ifndef LODA_L1S_STAGES
+#define LODA_L1S_STAGES 3
+#endif
+#ifndef LODA_L1S_TARGET_ITEMS
+#define LODA_L1S_TARGET_ITEMS 4
+#endif
+constexpr int L1S_MAX_ITEMS = LODA_L1S_MAX_ITEMS;       // items per CTA (their queries stay in shared memory)
+constexpr int L1S_STAGES = LODA_L1S_STAGES;             // groups in flight per warp
 constexpr int L1S_POLL_LIMIT = 1 << 18;
 
 template <int DSUB>
@@ -549,7 +560,7 @@ static cudaError_t launch_l1_p(const loda_geometry& g, const loda_layer& L, cons
     const int ncta = never ? 0 : l1_stream_grid<DS, GENERIC>(smem);
     if (ncta > 0 && (always || (long long)rows * ntiles >= 4LL * ncta)) {
       // about four items per CTA; an item = the tiles split, split + nsplit, ... of a row
-      int nsplit = (4 * ncta + rows - 1) / rows;
+      int nsplit = (LODA_L1S_TARGET_ITEMS * ncta + rows - 1) / rows;
       nsplit = nsplit < 1 ? 1 : nsplit > ntiles ? ntiles : nsplit;
       const int tpc = (ntiles + nsplit - 1) / nsplit;
       nsplit = (ntiles + tpc - 1) / tpc;
