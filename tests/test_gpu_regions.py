@@ -166,3 +166,40 @@ def test_level1_streaming_kernel_other_shapes(overrides, page, monkeypatch):
                        skip_states=[NS, NS, NS, FAR, NEAR])
     out = _run_step(setup)
     _check_against_oracle(setup, out)
+
+
+def test_streaming_kernel_gives_up_on_a_row_that_never_completes(monkeypatch):
+    """The streaming level-1 kernel waits for a row's ticket before it selects the row.  The wait is bounded:
+    with the ticket of one row made unreachable (a count that its items can never bring up to the full
+    number) the launch returns after the poll limit, raises LODA_STATUS_TIMEOUT, leaves that row alone and
+    serves the others; with the scratch zeroed again the next step is exact."""
+    from helpers import make_setup, mod
+    sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
+    capi = mod("_capi")
+    monkeypatch.setenv("LODA_B200_L1_PATH", "stream")
+    lengths = [9000, 20000, 700]
+    setup = make_setup(lengths, seed=71)
+    cache = setup.cache
+    out_ok = _run_step(setup)                                  # a normal step (builds the index)
+    _check_against_oracle(setup, out_ok)
+    lens_ok = cache.visible_lens_for_layer(0).clone()
+    rt = cache._runtime
+    rows = len(lengths) * cache.num_kv_heads
+    tickets = rt.workspace[:4 * (rows + 2)].view(torch.int32)  # the tickets lead the scratch; then queue, exit count
+    stuck = 1 * cache.num_kv_heads + 3                         # request 1, kv head 3
+    tickets[stuck] = -(1 << 24)
+    cache.plan_common(setup.req_ids)
+    slots = cache.slot_mapping_for_layer(0)[:len(lengths)]
+    out = sel_mod.decode_step_fused(cache, 0, setup.req_ids, setup.q, setup.attention,
+                                    (setup.k_new, setup.v_new, slots))
+    torch.cuda.synchronize()
+    status = cache.read_status()
+    assert status & capi.STATUS_TIMEOUT
+    assert int(tickets[rows]) == 0 and int(tickets[rows + 1]) == 0      # queue and exit count rearmed
+    heads = [h for h in range(out.shape[1]) if h // (cache.num_query_heads // cache.num_kv_heads) != 3]
+    assert torch.equal(out[0], out_ok[0]) and torch.equal(out[2], out_ok[2])
+    assert torch.equal(out[1][heads], out_ok[1][heads])
+    assert torch.equal(cache.visible_lens_for_layer(0), lens_ok)        # the stuck row kept its list of the step before
+    tickets.zero_()
+    again = _run_step(setup)
+    assert torch.equal(again, out_ok)

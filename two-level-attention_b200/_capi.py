@@ -18,7 +18,7 @@ LODA_OK = 0
 LODA_ERR_ARGUMENT = -1
 LODA_ERR_UNSUPPORTED = -2
 LODA_ERR_LAUNCH = -3
-STATUS_BAD_SLOT, STATUS_BAD_PAGE, STATUS_TRUNCATED, STATUS_BAD_REQ = 1, 2, 4, 8
+STATUS_BAD_SLOT, STATUS_BAD_PAGE, STATUS_TRUNCATED, STATUS_BAD_REQ, STATUS_TIMEOUT = 1, 2, 4, 8, 16
 SEL_CHAINED = 1
 FAR_MINMAX, FAR_AVG, FAR_AVG_TOP2 = 0, 1, 2
 
