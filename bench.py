@@ -145,7 +145,7 @@ class ClockSampler:
 
 
 def build_workload(torch, dev, total_steps, seed, lengths=None, n_layers=None, hq=None, hkv=None,
-                   theta=1e6, llama3=False):
+                   theta=1e6, llama3=False, page=None, d=None, dv=None, shared_latent=False):
     """Cache with `n_layers` layers holding one request per entry of `lengths` (tokens already in
     the cache), index buffers allocated, plus device-resident inputs for `total_steps` steps."""
     cache_mod = mod("sparse_attn.cache.paged_region_cache")
@@ -159,15 +159,19 @@ def build_workload(torch, dev, total_steps, seed, lengths=None, n_layers=None, h
     hq = HQ if hq is None else hq
     hkv = HKV if hkv is None else hkv
     nb = len(lengths)
-    args = nfa.nfa_args("tail", tia_block_size=PAGE)
+    page = PAGE if page is None else page
+    d = D if d is None else d
+    dv = d if dv is None else dv
+    args = nfa.nfa_args("tail", tia_block_size=page, **({} if d == 128 else {"head_dim": d}))
     indexer = idx_mod.NFAIndexer(args)
-    geometry = geo_mod.RegionGeometry(sink=4, near=4096, window=128, page=PAGE, max_new_tokens=4096)
-    max_blocks = (max(lengths) + 1 + 4096 + PAGE - 1) // PAGE
-    pages = sum((n + 4096 + PAGE - 1) // PAGE for n in lengths) + 8
+    geometry = geo_mod.RegionGeometry(sink=4, near=4096, window=128, page=page, max_new_tokens=4096)
+    max_blocks = (max(lengths) + 1 + 4096 + page - 1) // page
+    pages = sum((n + 4096 + page - 1) // page for n in lengths) + 8
     cache = cache_mod.GraphReadyPagedRegionCache(
         n_layers, geometry, max_requests=nb, max_physical_pages=pages, max_blocks=max_blocks,
         max_visible_len=1024, max_query_tokens=nb, num_kv_heads=hkv, num_query_heads=hq,
-        head_dim_k=D, head_dim_v=D, dtype=torch.bfloat16, device=dev)
+        head_dim_k=d, head_dim_v=dv, dtype=torch.bfloat16, device=dev,
+        **({"shared_latent": True} if shared_latent else {}))
     g = torch.Generator(device=dev)
     g.manual_seed(seed)
     rids = [cache.add_request() for _ in lengths]
@@ -175,23 +179,26 @@ def build_workload(torch, dev, total_steps, seed, lengths=None, n_layers=None, h
         perm = torch.randperm(pages, generator=g, device=dev).tolist()     # shuffled free list of this layer
         used = 0
         for r, n_pre in enumerate(lengths):
-            need = (n_pre + PAGE - 1) // PAGE
-            case = synth.make_decode_case(n_pre, num_q_heads=hq, num_kv_heads=hkv, head_dim=D,
+            need = (n_pre + page - 1) // page
+            case = synth.make_decode_case(n_pre, num_q_heads=hq, num_kv_heads=hkv, head_dim=d,
                                           seed=seed * 1000 + li * 97 + r, dtype=torch.bfloat16, device=dev,
                                           theta=theta, llama3_scaling=llama3)
-            cache.write_prefill(li, rids[r], case.k.permute(1, 0, 2)[None], case.v.permute(1, 0, 2)[None],
+            vals = case.k[..., :dv] if shared_latent else case.v[..., :dv]
+            cache.write_prefill(li, rids[r], case.k.permute(1, 0, 2)[None], vals.permute(1, 0, 2)[None],
                                 physical_pages=perm[used:used + need])
             used += need
-            del case
+            del case, vals
     for rid in rids:
         cache.freeze(rid)
-    attention = SimpleNamespace(indexer=indexer, scaling=float(D) ** -0.5, layer_idx=0)
+    attention = SimpleNamespace(indexer=indexer, scaling=float(d) ** -0.5, layer_idx=0)
     rt = cache.ensure_index(indexer)
-    q = torch.randn(total_steps, n_layers, nb, hq, D, generator=g, device=dev).to(torch.bfloat16)
-    k = torch.randn(total_steps, n_layers, nb, hkv, 1, D, generator=g, device=dev).to(torch.bfloat16)
-    v = torch.randn(total_steps, n_layers, nb, hkv, 1, D, generator=g, device=dev).to(torch.bfloat16)
+    q = torch.randn(total_steps, n_layers, nb, hq, d, generator=g, device=dev).to(torch.bfloat16)
+    k = torch.randn(total_steps, n_layers, nb, hkv, 1, d, generator=g, device=dev).to(torch.bfloat16)
+    v = k[..., :dv] if shared_latent else torch.randn(total_steps, n_layers, nb, hkv, 1, dv, generator=g,
+                                                      device=dev).to(torch.bfloat16)
     return SimpleNamespace(cache=cache, rid=rids[0], rids=rids, attention=attention, rt=rt, q=q, k=k, v=v,
-                           indexer=indexer, lengths=lengths, n_layers=n_layers, batch=nb, hq=hq, hkv=hkv)
+                           indexer=indexer, lengths=lengths, n_layers=n_layers, batch=nb, hq=hq, hkv=hkv,
+                           page=page, d=d, dv=dv)
 
 
 def preplan(torch, wl, n_steps):
@@ -205,11 +212,11 @@ def preplan(torch, wl, n_steps):
         first_len = state.logical_length
         for s in range(n_steps):
             planned = first_len + s + 1
-            lp, off = divmod(planned - 1, PAGE)
+            lp, off = divmod(planned - 1, wl.page)
             lengths[s, r] = planned
             for li in range(nl):
                 cache._grow_table(state, rid, li, lp + 1)
-                slots[s, li, r] = state.block_tables[li][lp] * PAGE + off
+                slots[s, li, r] = state.block_tables[li][lp] * wl.page + off
         cache.block_table_buf[:, rid].copy_(cache._cpu_block_table[:, rid])
     ids = torch.tensor(wl.rids, dtype=torch.int64)
     cache.active_req_ids_buf[:nb] = ids.to(cache.device)
@@ -347,7 +354,7 @@ def measure_device(torch, capi, lib, wl, W, K, barrier, after_layer=None, kernel
     sel_mod = mod("sparse_attn.indexer.nfa_layer_batch_selector")
     lengths, slots = preplan(torch, wl, W + K)
     if out is None:
-        out = torch.zeros(wl.n_layers, wl.batch, wl.hq, D, dtype=torch.bfloat16, device=cache.device)
+        out = torch.zeros(wl.n_layers, wl.batch, wl.hq, wl.dv, dtype=torch.bfloat16, device=cache.device)
     # the index of the prefilled pages is built by one bulk pass before the first step
     for li in range(wl.n_layers):
         sel_mod._ensure_index_built(cache, wl.rt, li, wl.rids, has_current_token_in_pool=True)
@@ -512,6 +519,31 @@ def cfg4_arm(torch, dist, capi, lib, dev, rank, world, barrier, layers=8):
            "tok_s_32_layers": 8 / (us_layer * 1e-6 * 32), "timing": stats, "device_status": status,
            "launches_per_layer_step": int(lib.loda_last_decode_launches())}
     del wl, out
+    torch.cuda.empty_cache()
+    return res
+
+
+def cfg5_arm(torch, capi, lib, dev, layers=6):
+    """Config 5 shape: MLA attention on the shared latent (16 query heads on one 576-dim latent row per token
+    that is key and, in its first 512 dims, value), 64-token pages, 16 requests of 131 072 tokens, `layers`
+    layers (16 x 131 072 x 1 152 B = 2.4 GB per layer; a step touches ~26 MB per layer, so six layers exceed L2)."""
+    wl = build_workload(torch, dev, 3 + 4 + 2, seed=31, lengths=[CONTEXT - 1] * 16, n_layers=layers, hq=16, hkv=1,
+                        page=64, d=576, dv=512, shared_latent=True)
+    ms, stats, _, status, _, _, _ = measure_device(torch, capi, lib, wl, 3, 4, lambda: torch.cuda.synchronize(),
+                                                   kernels=False, min_timed_s=0.3)
+    us_layer = ms * 1e3 / (4 * layers)
+    n_pages = (CONTEXT + 63) // 64
+    # per request: min/max rows of the far pool's pages (d' = 32: 128 B per page), the candidates' codes
+    # ((96 + 32 + 2) pages x 64 tokens x 20 B), the latent rows of the 1 024 visible tokens (1 152 B each)
+    alg = 16 * (n_pages * 128 + 130 * 64 * 20 + 1024 * 1152)
+    peak, kind = peaks()
+    res = {"workload": f"cfg5: MLA shared latent 576/512, 16 query heads, 16 requests x {CONTEXT} tokens, 64-token pages, "
+                       f"{layers} layers", "us_per_decode_step_per_layer": us_layer,
+           "tok_s_27_layers": 16 / (us_layer * 1e-6 * 27), "timing": stats, "device_status": status,
+           "launches_per_layer_step": int(lib.loda_last_decode_launches()),
+           "algorithmic_bytes_per_layer_step": alg,
+           "hbm_frac": alg / (us_layer * 1e-6) / 1e9 / peak, "peak_kind": f"of {kind}"}
+    del wl
     torch.cuda.empty_cache()
     return res
 
@@ -948,6 +980,8 @@ def main():
                     help="run only the 32-request arm and print its object (small captures of its kernels under a profiler)")
     ap.add_argument("--skip-tls", action="store_true")
     ap.add_argument("--skip-cfg4", action="store_true")
+    ap.add_argument("--skip-cfg5", action="store_true")
+    ap.add_argument("--only-cfg5", action="store_true", help="run only the latent-attention arm and print its object")
     ap.add_argument("--skip-reference-triton", action="store_true")
     ap.add_argument("--skip-parity", action="store_true")
     ap.add_argument("--skip-reference-code", action="store_true",
@@ -991,6 +1025,10 @@ def main():
         torch.cuda.synchronize()
 
     K, W = args.steps, args.warmup
+    if args.only_cfg5:
+        if rank == 0:
+            print(json.dumps({"cfg5": cfg5_arm(torch, capi, lib, dev)}), flush=True)
+        return
     if args.only_batched:
         if rank == 0:
             print(json.dumps({"batched": batched_arm(torch, capi, lib, dev, 5, lambda: torch.cuda.synchronize())}), flush=True)
@@ -1121,6 +1159,9 @@ def main():
         if rank == 0:
             line["cfg4"] = res
     if rank == 0:
+        if not args.skip_cfg5 and world == 1:
+            torch.cuda.empty_cache()
+            line["cfg5"] = cfg5_arm(torch, capi, lib, dev)
         if not args.skip_tls and world == 1:
             torch.cuda.empty_cache()
             line["tls_chain"] = tls_chain_arm(torch, dev)
