@@ -10,7 +10,7 @@ Triton kernels, so its outputs have to be produced on a GPU.  Two steps:
         baseline/_ref with pip (the project itself declares no package, so a three-line setup.py
         is written next to a temporary copy); baseline/_ref is not tracked by git.
 
-    python tests/golden/make_golden_gpu.py --out gpurun_out/ref_selector.npz        (on a GPU)
+    python tests/golden/make_golden_gpu.py --out <dir>/ref_selector.npz             (on a GPU)
         imports the reference from baseline/_ref, builds its GraphReadyPagedRegionCache, runs the
         selector and the gather attention on seeded inputs and stores inputs (as seeds and
         parameters) and outputs.  The resulting file is committed as tests/golden/ref_selector.npz.
@@ -181,11 +181,13 @@ def run_case(torch, mods, name, kind, page, lengths, skips, cfg, log):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--install", action="store_true")
-    ap.add_argument("--reference", default="/root/reference")
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "ref_selector.npz"))
+    ap.add_argument("--reference", default=None, help="checkout of the reference project (with --install)")
+    ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden", "ref_selector.new.npz"))
     ap.add_argument("--only", default=None, help="comma-separated case names")
     a = ap.parse_args()
     if a.install:
+        if not a.reference:
+            ap.error("--install needs --reference <checkout>")
         sys.exit(install(a.reference))
     os.makedirs(os.path.dirname(a.out), exist_ok=True)
     logf = open(os.path.splitext(a.out)[0] + ".log", "w")
