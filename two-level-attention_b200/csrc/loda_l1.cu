@@ -529,10 +529,13 @@ static size_t l1_stream_smem_bytes_d(const loda_geometry& g) {
 // and its shared memory, per device), or 0 when the kernel cannot be used.
 template <int DS, bool GENERIC>
 static int l1_stream_grid(size_t smem) {
-  static int per_sm[64] = {};                    // per device ordinal; -1 = refused
+  // per device ordinal, remembered for the shared-memory size it was asked for (the size follows the
+  // geometry: another GQA group or page budget may change how many CTAs an SM holds)
+  static int per_sm[64] = {};                    // -1 = refused
+  static size_t asked[64] = {};
   const int dev = device_ordinal();
   if (dev < 0 || dev >= 64) return 0;
-  if (per_sm[dev] == 0) {
+  if (per_sm[dev] == 0 || asked[dev] != smem) {
     int n = 0;
     if (set_kernel_smem(l1_stream_kernel<DS, GENERIC>, smem) != cudaSuccess ||
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, l1_stream_kernel<DS, GENERIC>, L1_TP, smem) != cudaSuccess || n < 1) {
@@ -540,6 +543,7 @@ static int l1_stream_grid(size_t smem) {
       n = -1;
     }
     per_sm[dev] = n >= 2 ? 2 : -1;                // one CTA per SM would leave the warps' latencies uncovered
+    asked[dev] = smem;
   }
   return per_sm[dev] > 0 ? per_sm[dev] * device_sm_count() : 0;
 }
