@@ -251,35 +251,32 @@ __global__ void __launch_bounds__(P, 2) l1_kernel(loda_geometry g, loda_layer L,
 }
 
 // ---------------------------------------------------------------------------
-// Level 1 for large batches: a grid that fills the GPU once (two CTAs per SM) and stays.  The rows'
-// tiles are cut into items (row, split) as above; CTA c takes the items c, c + gridDim.x, ...  It reads
-// the metadata and the queries of all its items in one round trip at the start.  Then every WARP runs
-// a pipeline of its own over the CTA's tiles: a warp scores the 32 pages of one group of each tile,
-// and a group is one contiguous block of the statistics, so the warp fetches its group of the tiles
-// ahead itself (one bulk copy of a group's min/max rows, or of its sum rows, on the warp's own
-// mbarrier per stage) and never waits for another warp: no barrier of the CTA and no shared stage
-// between two tiles, across items as within them.  (The one group of a row that holds pages of both
-// pools stages its min/max rows and reads its sums from global memory.)  A warp that has finished its
-// part of an item publishes its scores and adds one to the row's ticket.  When its warps are done the
-// CTA turns to selection: it claims the next row from a queue (rows in order, roughly the order in
-// which they complete), waits — bounded — for the row's ticket to show all warps of all its items, and
-// selects as the last CTA of a row does above.  Every CTA of the grid is resident
-// (the host sizes the grid by the occupancy the runtime reports), so a CTA that waits for a row waits
-// for CTAs that are running.
+// Level 1 for large batches: a grid that fills the GPU once (two CTAs per SM) and stays.  Every CTA
+// first counts the tiles of P pages that each row of the batch really has (its pools' extent, from the
+// row's length and skip flags) and forms their prefix sums, so all CTAs agree on one flat sequence of
+// (row, tile) pairs, row by row; CTA c takes the c-th of gridDim.x equal slices of that sequence — the
+// same number of tiles (one more or less) for every CTA, whatever the rows' lengths.  A slice touches a
+// few consecutive rows: their metadata, region geometry and scaled queries are staged once (eight rows
+// at a time).  Then every WARP runs a pipeline of its own over the slice: a warp scores the 32 pages of
+// one group of each tile, and a group is one contiguous block of the statistics, so the warp fetches
+// its group of the tiles ahead itself (one bulk copy of a group's min/max rows, or of its sum rows, on
+// the warp's own mbarrier per stage) and never waits for another warp: no barrier of the CTA and no
+// shared stage between two tiles, across rows as within them.  (The one group of a row that holds pages
+// of both pools stages its min/max rows and reads its sums from global memory.)  A warp that has
+// finished its tiles of a row publishes its scores and adds their number to the row's ticket.  When
+// its warps are done the CTA turns to selection: it claims the next row from a queue (rows in order,
+// the order in which they complete), waits — bounded — until the row's ticket shows all warps of all
+// its tiles, and selects as the last CTA of a row does above.  Every CTA of the grid is resident (the
+// host sizes the grid by the occupancy the runtime reports), so a CTA that waits for a row waits for
+// CTAs that are running.
 // ---------------------------------------------------------------------------
-// (build-time knobs; measured on the 32-request batch: 2 stages and 4 items 48.7 us, 3 and 4 48.8, 3 and 6 49.0,
-// 2 and 8 51.5 — the launch is bound by the scoring arithmetic, not by the depth or the item size)
-#ifndef LODA_L1S_MAX_ITEMS
-#define LODA_L1S_MAX_ITEMS 8
-#endif
+// (build-time knobs; measured on the 32-request batch with the earlier item scheme: 2 stages 48.7 us, 3 stages 48.8)
 #ifndef LODA_L1S_STAGES
-#define LODA_L1S_STAGES 3
+#define LODA_L1S_STAGES 2
 #endif
-#ifndef LODA_L1S_TARGET_ITEMS
-#define LODA_L1S_TARGET_ITEMS 4
-#endif
-constexpr int L1S_MAX_ITEMS = LODA_L1S_MAX_ITEMS;       // items per CTA (their queries stay in shared memory)
+constexpr int L1S_BATCH = 8;            // rows whose queries are staged at a time
 constexpr int L1S_STAGES = LODA_L1S_STAGES;             // groups in flight per warp
+constexpr int L1S_MAX_ROWS = 512;       // rows of a batch (the tile counts' prefix sums stay in shared memory)
 constexpr int L1S_POLL_LIMIT = 1 << 18;
 
 template <int DSUB>
@@ -287,13 +284,15 @@ struct L1Stream {
   using T = L1Tile<DSUB, L1_TP>;
   static constexpr size_t STAGES_BYTES = (size_t)L1S_STAGES * (L1_TP / 32) * T::SLOT;     // [stage][warp] slots
   static constexpr size_t ROWS_BYTES = STAGES_BYTES > L1_TAIL_BYTES ? STAGES_BYTES : L1_TAIL_BYTES;
+  static constexpr size_t FIXED_BYTES = ROWS_BYTES + (L1_TP / 32) * L1S_STAGES * 8 + (L1S_MAX_ROWS + 4) * 4 +
+                                        L1S_BATCH * (16 + sizeof(Regions));
 };
 
 template <int DSUB, bool GENERIC>
 __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, loda_layer L, loda_batch B,
                                                              const bf16* __restrict__ q, float scale,
-                                                             loda_selection out, SelectWorkspace ws, int nsplit,
-                                                             int tiles_per_cta, AppendArgs ap, int n_rows) {
+                                                             loda_selection out, SelectWorkspace ws, AppendArgs ap,
+                                                             int n_rows) {
   constexpr int P = L1_TP, NWARP = P / 32, NSTAGE = L1S_STAGES;
   using T = L1Tile<DSUB, P>;
   constexpr size_t ROWS_BYTES = L1Stream<DSUB>::ROWS_BYTES;
@@ -301,13 +300,14 @@ __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, lo
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* rows = smem;                                    // [NSTAGE][NWARP] group slots, later the row's scores
   uint64_t* full = (uint64_t*)(smem + ROWS_BYTES);               // [NWARP][NSTAGE]
-  int4* desc = (int4*)(smem + ROWS_BYTES + NWARP * NSTAGE * 8);  // [MAX_ITEMS] (length, request slot, skip bits, tiles)
-  Regions* regs = (Regions*)(desc + L1S_MAX_ITEMS);              // [MAX_ITEMS] the items' region geometry
+  int* prefix = (int*)(full + NWARP * NSTAGE);                   // [n_rows + 1] tiles before each row
+  int4* desc = (int4*)(prefix + L1S_MAX_ROWS + 4);               // [BATCH] (length, request slot, first tile, end tile)
+  Regions* regs = (Regions*)(desc + L1S_BATCH);                  // [BATCH] the rows' region geometry
   const int G = g.num_q_heads / g.num_kv_heads;
   const int nq = G * DSUB;
-  float* qall = (float*)(regs + L1S_MAX_ITEMS);                  // [MAX_ITEMS][NQ * G * DSUB]
-  int* kept = (int*)(qall + (size_t)L1S_MAX_ITEMS * NQ * nq);    // k_far + k_near + 2
-  const size_t keys_off = (ROWS_BYTES + NWARP * NSTAGE * 8 + L1S_MAX_ITEMS * (16 + sizeof(Regions)) + (size_t)L1S_MAX_ITEMS * NQ * nq * 4 +
+  float* qall = (float*)(regs + L1S_BATCH);                      // [BATCH][NQ * G * DSUB]
+  int* kept = (int*)(qall + (size_t)L1S_BATCH * NQ * nq);        // k_far + k_near + 2
+  const size_t keys_off = (L1Stream<DSUB>::FIXED_BYTES + (size_t)L1S_BATCH * NQ * nq * 4 +
                            (size_t)(g.k_far + g.k_near + 2) * 4 + 15) & ~(size_t)15;
   uint32_t* keys = (uint32_t*)(smem + keys_off);                 // 2 P + 8
   int* wtot = (int*)(keys + 2 * P + 8);                          // 8 x 32
@@ -315,8 +315,6 @@ __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, lo
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int cta = blockIdx.x, ncta = gridDim.x;
-  const int W = n_rows * nsplit;
-  const int n_items = cta < W ? min((W - cta + ncta - 1) / ncta, L1S_MAX_ITEMS) : 0;
   const int cta_id = cta;
   LODA_PHASE(l1, cta_id, 0);
   if (lane == 0) {
@@ -332,114 +330,155 @@ __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, lo
     for (int r = cta; r < n_rows; r += ncta)
       append_row<DSUB>(g, L, B, ap.k_new, ap.v_new, ap.slots, ap.status, r / g.num_kv_heads, r % g.num_kv_heads, lane);
   }
-  auto item_row = [&](int k) { return (cta + k * ncta) / nsplit; };
-  auto item_split = [&](int k) { return (cta + k * ncta) % nsplit; };
-  // metadata of this CTA's items, one item per thread: a single round of dependent loads per CTA
-  if (tid < n_items) {
-    const int row = item_row(tid), b = row / g.num_kv_heads;
-    int length = B.lengths[b];
+  // metadata of one row, checked like checked_request (every CTA reads every row: only CTA 0 reports)
+  auto row_meta = [&](int row, int* length, int* req, bool* skip_far, bool* skip_near) {
+    const int b = row / g.num_kv_heads;
+    *length = B.lengths[b];
     const long long act = B.active_req_ids[b], val = B.valid_req_ids[b];
-    int req = 0;
-    if (act < 0) { length = 0; req = (val >= 0 && val < g.max_requests) ? (int)val : 0; }
-    else if (val < 0 || val >= g.max_requests) { length = 0; if (ap.status) atomicOr(ap.status, LODA_STATUS_BAD_REQ); }
-    else req = (int)val;
-    bool skip_far, skip_near;
-    load_skip_flags(L, req, &skip_far, &skip_near);
-    const Regions rg = make_regions(g, length, skip_far, skip_near);
+    *req = 0;
+    if (act < 0) { *length = 0; *req = (val >= 0 && val < g.max_requests) ? (int)val : 0; }
+    else if (val < 0 || val >= g.max_requests) { *length = 0; if (ap.status && cta == 0) atomicOr(ap.status, LODA_STATUS_BAD_REQ); }
+    else *req = (int)val;
+    load_skip_flags(L, *req, skip_far, skip_near);
+  };
+  auto row_tiles = [&](const Regions& rg) {
     const int tile_end = min(min(rg.kt_eff, g.max_blocks), pools_end(rg));
-    const int first = item_split(tid) * P, step = nsplit * P;
-    int nt = tile_end > first ? (tile_end - first + step - 1) / step : 0;
-    nt = min(nt, tiles_per_cta);
-    desc[tid] = make_int4(length, req, (skip_far ? 1 : 0) | (skip_near ? 2 : 0), nt);
-    regs[tid] = rg;
+    return (tile_end + P - 1) / P;
+  };
+  // tiles of every row, prefix sums (the same in every CTA)
+  {
+    int base = 0;
+    for (int r0 = 0; r0 < n_rows; r0 += P) {
+      const int row = r0 + tid;
+      int nt = 0;
+      if (row < n_rows) {
+        int length, req;
+        bool sf, sn;
+        row_meta(row, &length, &req, &sf, &sn);
+        nt = row_tiles(make_regions(g, length, sf, sn));
+      }
+      int total;
+      const int before = block_exclusive_scan<P>(nt, wtot, &total);
+      if (row < n_rows) prefix[row] = base + before;
+      base += total;
+      __syncthreads();                                   // the scan's scratch is reused by the next round
+    }
+    if (tid == 0) prefix[n_rows] = base;
   }
-  // scaled, bf16-rounded queries of the items' rows on the subspace (nfa_layer_batch_selector.py:943-963)
-  for (int i = tid; i < n_items * nq; i += P) {
-    const int k = i / nq, e = i % nq, j = e / DSUB, dd = e % DSUB;
-    const int row = item_row(k), b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
-    const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, dd)]);
-    const float qh = bf16r(__fmul_rn(qv, scale));
-    float* qhat = qall + (size_t)k * NQ * nq;
-    qhat[e] = qh;
-    *(float2*)(qhat + nq + 2 * e) = make_float2(fminf(qh, 0.0f), fmaxf(qh, 0.0f));
-    if (GENERIC) qhat[3 * nq + e] = __fmul_rn(qv, scale);
-  }
-  __syncthreads();                                       // barriers, descriptors and queries are ready
+  __syncthreads();                                       // barriers and prefix sums are ready
+  const int total_tiles = prefix[n_rows];
+  const int lo = (int)((long long)cta * total_tiles / ncta), hi = (int)((long long)(cta + 1) * total_tiles / ncta);
   LODA_PHASE(l1, cta_id, 2);
 
-  // ---- every warp: its group of every tile of the CTA's items ---------------------------------------
-  {
+  // ---- this CTA's slice [lo, hi) of the tile sequence, eight rows at a time ---------------------------
+  if (lo < hi) {
+    // the row that holds tile lo: the last row whose prefix is <= lo among rows that have tiles
+    int rb = 0;
+    {
+      int a = 0, b2 = n_rows;                            // prefix[a] <= lo < prefix[b2]
+      while (b2 - a > 1) {
+        const int m = (a + b2) >> 1;
+        if (prefix[m] <= lo) a = m; else b2 = m;
+      }
+      rb = a;
+    }
     uint64_t* wfull = full + warp * NSTAGE;
     auto slot_of = [&](int st) { return rows + ((size_t)st * NWARP + warp) * T::SLOT; };
-    int pk = 0, pit = 0, pseq = 0;                       // producer side: item, tile of the item, place in the stream
+    int pseq = 0, cseq = 0;                              // places in the warp's stream (kept across the row batches)
     bool dead = false;                                   // a wait gave up: no further waiting
-    // the group's statistics of the next tile of the stream into the stage that is free
-    auto issue_next = [&]() {
-      while (pk < n_items && pit >= desc[pk].w) { ++pk; pit = 0; }
-      if (pk >= n_items) return;
-      const int4 d = desc[pk];
-      const Regions& rg = regs[pk];
-      const int row = item_row(pk), kv = row % g.num_kv_heads;
-      const int g0 = (item_split(pk) + pit * nsplit) * P + warp * STAT_GROUP;      // first page of the warp's group
-      bool nm, ns;
-      l1_group_needs<GENERIC>(g, rg, g0, min(rg.kt_eff, g.max_blocks), &nm, &ns);
-      if (lane == 0) {
-        const int st = pseq % NSTAGE;
-        const size_t rowi = (size_t)d.y * g.num_kv_heads + kv;
-        const size_t gidx = (size_t)(g0 / STAT_GROUP);
-        const uint32_t bytes = nm ? (uint32_t)T::SLOT : ns ? (uint32_t)T::SUMG : 0u;
-        mbar_arrive_expect_tx(wfull + st, bytes);         // no bytes: the phase completes at once
-        if (nm)
-          bulk_copy_g2s(slot_of(st), (const unsigned char*)L.page_mm + rowi * stat_row_bytes(g.max_blocks, T::CPR) + gidx * T::SLOT,
-                        T::SLOT, wfull + st);
-        else if (ns)
-          bulk_copy_g2s(slot_of(st), (const unsigned char*)L.page_sum + rowi * stat_row_bytes(g.max_blocks, T::NC) + gidx * T::SUMG,
-                        T::SUMG, wfull + st);
+#pragma unroll 1
+    while (rb < n_rows && prefix[rb] < hi) {
+      int nr = 0;
+      while (nr < L1S_BATCH && rb + nr < n_rows && prefix[rb + nr] < hi) ++nr;
+      __syncthreads();                                   // the warps are done with the rows staged before
+      if (tid < nr) {
+        const int row = rb + tid;
+        int length, req;
+        bool sf, sn;
+        row_meta(row, &length, &req, &sf, &sn);
+        regs[tid] = make_regions(g, length, sf, sn);
+        const int t0 = max(lo, prefix[row]) - prefix[row], t1 = min(hi, prefix[row + 1]) - prefix[row];
+        desc[tid] = make_int4(length, req, t0, max(t1, t0));
       }
-      ++pit;
-      ++pseq;
-    };
-#pragma unroll 1
-    for (int s = 0; s < NSTAGE; ++s) issue_next();
-    int cseq = 0;
-#pragma unroll 1
-    for (int k = 0; k < n_items; ++k) {
-      const int4 d = desc[k];
-      const int row = item_row(k), kv = row % g.num_kv_heads;
-      if (d.w == 0) {                                    // an item without tiles still counts for its row
-        if (lane == 0) atomicAdd(ws.l1_ticket + row, 1);
-        continue;
+      // scaled, bf16-rounded queries of the rows on the subspace (nfa_layer_batch_selector.py:943-963)
+      for (int i = tid; i < nr * nq; i += P) {
+        const int k = i / nq, e = i % nq, j = e / DSUB, dd = e % DSUB;
+        const int row = rb + k, b = row / g.num_kv_heads, kv = row % g.num_kv_heads;
+        const float qv = __bfloat162float(q[((size_t)b * g.num_q_heads + kv * G + j) * g.head_dim + sub_dim(g, dd)]);
+        const float qh = bf16r(__fmul_rn(qv, scale));
+        float* qhat = qall + (size_t)k * NQ * nq;
+        qhat[e] = qh;
+        *(float2*)(qhat + nq + 2 * e) = make_float2(fminf(qh, 0.0f), fmaxf(qh, 0.0f));
+        if (GENERIC) qhat[3 * nq + e] = __fmul_rn(qv, scale);
       }
-      const Regions rg = regs[k];
-      const int page_end = min(rg.kt_eff, g.max_blocks);
-      const float* qhat = qall + (size_t)k * NQ * nq;
-      uint16_t* row_scores = ws.l1_scores + (size_t)row * ws.score_stride;
-      const size_t rowi = (size_t)d.y * g.num_kv_heads + kv;
-      const unsigned char* sum_row = (const unsigned char*)L.page_sum + rowi * stat_row_bytes(g.max_blocks, T::NC);
-#pragma unroll 1
-      for (int it = 0; it < d.w; ++it) {
-        const int st = cseq % NSTAGE;
-        if (cseq < 10) { LODA_SUB0(32 + 3 * cseq); }
-        if (!dead && !mbar_wait(wfull + st, (uint32_t)(cseq / NSTAGE) & 1u)) dead = true;
-        if (cseq < 10) { LODA_SUB0(33 + 3 * cseq); }
-        const int g0 = (item_split(k) + it * nsplit) * P + warp * STAT_GROUP;
+      __syncthreads();
+      // every warp: its group of every tile of the staged rows
+      int pk = 0, pit = 0;                               // producer side: row of the batch, tile of its range
+      auto issue_next = [&]() {
+        while (pk < nr && desc[pk].z + pit >= desc[pk].w) { ++pk; pit = 0; }
+        if (pk >= nr) return;
+        const int4 d = desc[pk];
+        const Regions& rg = regs[pk];
+        const int row = rb + pk, kv = row % g.num_kv_heads;
+        const int g0 = (d.z + pit) * P + warp * STAT_GROUP;          // first page of the warp's group
         bool nm, ns;
-        l1_group_needs<GENERIC>(g, rg, g0, page_end, &nm, &ns);
-        const unsigned char* slot = slot_of(st) + lane * 16;
-        // a group with pages of both pools staged its min/max rows: its sums come from global memory
-        const unsigned char* sum_src = nm ? sum_row + (size_t)(g0 / STAT_GROUP) * T::SUMG + lane * 16 : slot;
-        const uint32_t ord = l1_page_score_src<DSUB, GENERIC>(g, rg, g0 + lane, slot, sum_src, qhat, qhat + nq, G, qhat + 3 * nq);
-        row_scores[g0 + lane] = (uint16_t)ord;           // the selecting CTA masks what lies outside the pools
-        __syncwarp();                                    // every lane has read the slot
-        if (cseq < 10) { LODA_SUB0(34 + 3 * cseq); }
-        ++cseq;
-        issue_next();
+        l1_group_needs<GENERIC>(g, rg, g0, min(rg.kt_eff, g.max_blocks), &nm, &ns);
+        if (lane == 0) {
+          const int st = pseq % NSTAGE;
+          const size_t rowi = (size_t)d.y * g.num_kv_heads + kv;
+          const size_t gidx = (size_t)(g0 / STAT_GROUP);
+          const uint32_t bytes = nm ? (uint32_t)T::SLOT : ns ? (uint32_t)T::SUMG : 0u;
+          mbar_arrive_expect_tx(wfull + st, bytes);       // no bytes: the phase completes at once
+          if (nm)
+            bulk_copy_g2s(slot_of(st), (const unsigned char*)L.page_mm + rowi * stat_row_bytes(g.max_blocks, T::CPR) + gidx * T::SLOT,
+                          T::SLOT, wfull + st);
+          else if (ns)
+            bulk_copy_g2s(slot_of(st), (const unsigned char*)L.page_sum + rowi * stat_row_bytes(g.max_blocks, T::NC) + gidx * T::SUMG,
+                          T::SUMG, wfull + st);
+        }
+        ++pit;
+        ++pseq;
+      };
+#pragma unroll 1
+      for (int s = 0; s < NSTAGE; ++s) issue_next();
+#pragma unroll 1
+      for (int k = 0; k < nr; ++k) {
+        const int4 d = desc[k];
+        const int row = rb + k, kv = row % g.num_kv_heads;
+        const int nt = d.w - d.z;
+        if (nt <= 0) continue;
+        const Regions rg = regs[k];
+        const int page_end = min(rg.kt_eff, g.max_blocks);
+        const float* qhat = qall + (size_t)k * NQ * nq;
+        uint16_t* row_scores = ws.l1_scores + (size_t)row * ws.score_stride;
+        const size_t rowi = (size_t)d.y * g.num_kv_heads + kv;
+        const unsigned char* sum_row = (const unsigned char*)L.page_sum + rowi * stat_row_bytes(g.max_blocks, T::NC);
+#pragma unroll 1
+        for (int it = 0; it < nt; ++it) {
+          const int st = cseq % NSTAGE;
+          if (cseq < 10) { LODA_SUB0(32 + 3 * cseq); }
+          if (!dead && !mbar_wait(wfull + st, (uint32_t)(cseq / NSTAGE) & 1u)) dead = true;
+          if (cseq < 10) { LODA_SUB0(33 + 3 * cseq); }
+          const int g0 = (d.z + it) * P + warp * STAT_GROUP;
+          bool nm, ns;
+          l1_group_needs<GENERIC>(g, rg, g0, page_end, &nm, &ns);
+          const unsigned char* slot = slot_of(st) + lane * 16;
+          // a group with pages of both pools staged its min/max rows: its sums come from global memory
+          const unsigned char* sum_src = nm ? sum_row + (size_t)(g0 / STAT_GROUP) * T::SUMG + lane * 16 : slot;
+          const uint32_t ord = l1_page_score_src<DSUB, GENERIC>(g, rg, g0 + lane, slot, sum_src, qhat, qhat + nq, G, qhat + 3 * nq);
+          row_scores[g0 + lane] = (uint16_t)ord;         // the selecting CTA masks what lies outside the pools
+          __syncwarp();                                  // every lane has read the slot
+          if (cseq < 10) { LODA_SUB0(34 + 3 * cseq); }
+          ++cseq;
+          issue_next();
+        }
+        // this warp's tiles of the row are done: publish its scores, then count them on the row's ticket (a
+        // row is complete at NWARP x its tiles; its selection may start while this CTA still scores)
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(ws.l1_ticket + row, nt);
       }
-      // this warp's part of the item is done: publish its scores, then count it on the row's ticket (a row
-      // is complete at nsplit x NWARP; its selection may start while this CTA still scores other items)
-      __threadfence();
-      __syncwarp();
-      if (lane == 0) atomicAdd(ws.l1_ticket + row, 1);
+      rb += nr;
     }
     if (dead && lane == 0 && ap.status) atomicOr(ap.status, LODA_STATUS_TIMEOUT);
   }
@@ -455,8 +494,9 @@ __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, lo
       const int r = atomicAdd(queue, 1);
       int ok = 1;
       if (r < n_rows) {
+        const int want = (prefix[r + 1] - prefix[r]) * NWARP;
         int tries = 0;
-        while (*(volatile int*)(ws.l1_ticket + r) < nsplit * NWARP) {
+        while (*(volatile int*)(ws.l1_ticket + r) < want) {
           if (++tries > L1S_POLL_LIMIT) { ok = 0; break; }
           __nanosleep(64);
         }
@@ -471,12 +511,10 @@ __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, lo
       if (tid == 0 && ap.status) atomicOr(ap.status, LODA_STATUS_TIMEOUT);
       continue;
     }
-    __threadfence();                                     // the scores of the row's items, published before their tickets
-    const int b = r / g.num_kv_heads;
-    int length = B.lengths[b];
-    const int req = checked_request(g, B.active_req_ids[b], B.valid_req_ids[b], &length, nullptr);
+    __threadfence();                                     // the scores of the row's tiles, published before their tickets
+    int length, req;
     bool skip_far, skip_near;
-    load_skip_flags(L, req, &skip_far, &skip_near);
+    row_meta(r, &length, &req, &skip_far, &skip_near);
     const Regions rg = make_regions(g, length, skip_far, skip_near);
     LODA_PHASE(l1, cta_id, 5);
     l1_finish_row<DSUB, P, GENERIC>(g, L, rg, out, ws, r, req, rows, kept, keys, wtot, sh, cta_id, false);
@@ -520,9 +558,8 @@ static void l1_split(const loda_geometry& g, int rows, int P, int* ctas_per_row,
 template <int DS>
 static size_t l1_stream_smem_bytes_d(const loda_geometry& g) {
   const int G = g.num_q_heads / g.num_kv_heads;
-  return L1Stream<DS>::ROWS_BYTES + (L1_TP / 32) * L1S_STAGES * 8 + L1S_MAX_ITEMS * (16 + sizeof(Regions)) +
-         (size_t)L1S_MAX_ITEMS * (l1_generic(g) ? 4 : 3) * G * DS * 4 + (size_t)(g.k_far + g.k_near + 2) * 4 +
-         (size_t)(2 * L1_TP + 8) * 4 + (256 + 8) * 4 + 32;
+  return L1Stream<DS>::FIXED_BYTES + (size_t)L1S_BATCH * (l1_generic(g) ? 4 : 3) * G * DS * 4 +
+         (size_t)(g.k_far + g.k_near + 2) * 4 + (size_t)(2 * L1_TP + 8) * 4 + (256 + 8) * 4 + 32;
 }
 
 // Grid of the streaming kernel: every CTA resident at once (what the runtime reports for this kernel
@@ -562,16 +599,9 @@ static cudaError_t launch_l1_p(const loda_geometry& g, const loda_layer& L, cons
     const size_t smem = l1_stream_smem_bytes_d<DS>(g);
     const int ntiles = (g.max_blocks + P - 1) / P;
     const int ncta = never ? 0 : l1_stream_grid<DS, GENERIC>(smem);
-    if (ncta > 0 && (always || (long long)rows * ntiles >= 4LL * ncta)) {
-      // about four items per CTA; an item = the tiles split, split + nsplit, ... of a row
-      int nsplit = (LODA_L1S_TARGET_ITEMS * ncta + rows - 1) / rows;
-      nsplit = nsplit < 1 ? 1 : nsplit > ntiles ? ntiles : nsplit;
-      const int tpc = (ntiles + nsplit - 1) / nsplit;
-      nsplit = (ntiles + tpc - 1) / tpc;
-      if (((long long)rows * nsplit + ncta - 1) / ncta <= L1S_MAX_ITEMS)
-        return launch_pdl(l1_stream_kernel<DS, GENERIC>, dim3(ncta), dim3(P), smem, st, g, L, B, (const bf16*)q, scale, out,
-                          ws, nsplit, tpc, ap, rows);
-    }
+    if (ncta > 0 && rows <= L1S_MAX_ROWS && (always || (long long)rows * ntiles >= 4LL * ncta))
+      return launch_pdl(l1_stream_kernel<DS, GENERIC>, dim3(ncta), dim3(P), smem, st, g, L, B, (const bf16*)q, scale, out,
+                        ws, ap, rows);
   }
   int nsplit, tpc;
   l1_split(g, rows, P, &nsplit, &tpc);
