@@ -25,7 +25,12 @@ captured graph and the timed region): strong scaling of one decode stream.  `--s
 runs one independent request per GPU instead (weak scaling, no collective), `--shard sequence`
 deals the pages of the one request over the GPUs.  The `cfg4` object repeats the measurement on
 the batched shape of the Llama-3.1-8B configuration (8 requests of 131 072 tokens, RoPE theta 5e5
-with llama3 scaling, a stated number of its 32 layers) with the same KV-head partition.
+with llama3 scaling, a stated number of its 32 layers) with the same KV-head partition.  On one GPU
+the line also carries `batched` (32 requests of 8 192..65 536 tokens: the three-launch chain and the
+level-1 kernel's bandwidth; `--only-batched` runs it alone), `cfg5` (the MLA shared-latent shape: 16
+requests of 131 072 tokens on one 576-dim latent row per token; `--only-cfg5`), the `tls_attn` chain,
+the reference's own Triton selector on the same GPU (when its packages are installed under
+baseline/_ref) and the CPU baseline.
 """
 from __future__ import annotations
 
