@@ -12,7 +12,11 @@
 // thread 0 of the CTAs with blockIdx.y == 0 records clock64() at numbered points
 #ifdef LODA_PHASES
 static __device__ long long g_subphase[64];
+#ifdef LODA_SUB_X0      // one-dimensional grids: the first CTA only
+#define LODA_SUB(i) do { if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x == 0) g_subphase[(i)] = clock64(); } while (0)
+#else
 #define LODA_SUB(i) do { if (threadIdx.x == 0 && blockIdx.y == 0) g_subphase[(i)] = clock64(); } while (0)
+#endif
 #define LODA_SUB0(i) do { if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x == 0) g_subphase[(i)] = clock64(); } while (0)
 #define LODA_SUB_READER(name) extern "C" int loda_phase_read_sub_##name(long long* host) { \
     return (int)cudaMemcpyFromSymbol(host, g_subphase, sizeof(long long) * 64); }

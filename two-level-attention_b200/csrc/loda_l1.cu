@@ -285,7 +285,7 @@ struct L1Stream {
   static constexpr size_t STAGES_BYTES = (size_t)L1S_STAGES * (L1_TP / 32) * T::SLOT;     // [stage][warp] slots
   static constexpr size_t ROWS_BYTES = STAGES_BYTES > L1_TAIL_BYTES ? STAGES_BYTES : L1_TAIL_BYTES;
   static constexpr size_t FIXED_BYTES = ROWS_BYTES + (L1_TP / 32) * L1S_STAGES * 8 + (L1S_MAX_ROWS + 4) * 4 +
-                                        L1S_BATCH * (16 + sizeof(Regions));
+                                        L1S_MAX_ROWS * 8 + L1S_BATCH * (16 + sizeof(Regions));
 };
 
 template <int DSUB, bool GENERIC>
@@ -301,7 +301,8 @@ __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, lo
   unsigned char* rows = smem;                                    // [NSTAGE][NWARP] group slots, later the row's scores
   uint64_t* full = (uint64_t*)(smem + ROWS_BYTES);               // [NWARP][NSTAGE]
   int* prefix = (int*)(full + NWARP * NSTAGE);                   // [n_rows + 1] tiles before each row
-  int4* desc = (int4*)(prefix + L1S_MAX_ROWS + 4);               // [BATCH] (length, request slot, first tile, end tile)
+  int2* rowmeta = (int2*)(prefix + L1S_MAX_ROWS + 4);            // [n_rows] (length, request slot | skip bits << 28)
+  int4* desc = (int4*)(rowmeta + L1S_MAX_ROWS);                  // [BATCH] (length, request slot, first tile, end tile)
   Regions* regs = (Regions*)(desc + L1S_BATCH);                  // [BATCH] the rows' region geometry
   const int G = g.num_q_heads / g.num_kv_heads;
   const int nq = G * DSUB;
@@ -356,6 +357,7 @@ __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, lo
         bool sf, sn;
         row_meta(row, &length, &req, &sf, &sn);
         nt = row_tiles(make_regions(g, length, sf, sn));
+        rowmeta[row] = make_int2(length, req | (sf ? 1 << 28 : 0) | (sn ? 1 << 29 : 0));     // (max_requests < 2^28)
       }
       int total;
       const int before = block_exclusive_scan<P>(nt, wtot, &total);
@@ -393,12 +395,10 @@ __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, lo
       __syncthreads();                                   // the warps are done with the rows staged before
       if (tid < nr) {
         const int row = rb + tid;
-        int length, req;
-        bool sf, sn;
-        row_meta(row, &length, &req, &sf, &sn);
-        regs[tid] = make_regions(g, length, sf, sn);
+        const int2 m = rowmeta[row];
+        regs[tid] = make_regions(g, m.x, (m.y >> 28 & 1) != 0, (m.y >> 29 & 1) != 0);
         const int t0 = max(lo, prefix[row]) - prefix[row], t1 = min(hi, prefix[row + 1]) - prefix[row];
-        desc[tid] = make_int4(length, req, t0, max(t1, t0));
+        desc[tid] = make_int4(m.x, m.y & 0x0FFFFFFF, t0, max(t1, t0));
       }
       // scaled, bf16-rounded queries of the rows on the subspace (nfa_layer_batch_selector.py:943-963)
       for (int i = tid; i < nr * nq; i += P) {
@@ -512,10 +512,9 @@ __global__ void __launch_bounds__(L1_TP, 2) l1_stream_kernel(loda_geometry g, lo
       continue;
     }
     __threadfence();                                     // the scores of the row's tiles, published before their tickets
-    int length, req;
-    bool skip_far, skip_near;
-    row_meta(r, &length, &req, &skip_far, &skip_near);
-    const Regions rg = make_regions(g, length, skip_far, skip_near);
+    const int2 m = rowmeta[r];
+    const int req = m.y & 0x0FFFFFFF;
+    const Regions rg = make_regions(g, m.x, (m.y >> 28 & 1) != 0, (m.y >> 29 & 1) != 0);
     LODA_PHASE(l1, cta_id, 5);
     l1_finish_row<DSUB, P, GENERIC>(g, L, rg, out, ws, r, req, rows, kept, keys, wtot, sh, cta_id, false);
     LODA_PHASE(l1, cta_id, 9);
@@ -601,7 +600,7 @@ static cudaError_t launch_l1_p(const loda_geometry& g, const loda_layer& L, cons
     const int ncta = never ? 0 : l1_stream_grid<DS, GENERIC>(smem);
     // (measured on 131 072-token rows: 32 rows = 1 056 tiles 30.7 us against 33.4 us on the item grid, 16 rows =
     // 528 tiles 25.5 against 20.9: the resident grid pays once a CTA has about three tiles)
-    if (ncta > 0 && rows <= L1S_MAX_ROWS && (always || (long long)rows * ntiles >= 3LL * ncta))
+    if (ncta > 0 && rows <= L1S_MAX_ROWS && g.max_requests < (1 << 28) && (always || (long long)rows * ntiles >= 3LL * ncta))
       return launch_pdl(l1_stream_kernel<DS, GENERIC>, dim3(ncta), dim3(P), smem, st, g, L, B, (const bf16*)q, scale, out,
                         ws, ap, rows);
   }
