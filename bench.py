@@ -957,8 +957,8 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tok/s", "n_gpus": world,
         "steps": k, "warmup": 1, "ms_per_step": base["us_per_step_per_layer"] * 1e-3,
         "step_is": "one layer-step (1 of 36 layers); value = 1 / (36 x mean step time)",
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
+        "higher_is_better": True, "scaling": "strong" if args.shard == "kvhead" else "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
         "config": workload_config(world, args.shard),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -1131,7 +1131,9 @@ def main():
         fastest = min(dense_times) if dense_times else None
         line = {
             "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if kvhead else "weak",
+            "ms_per_step": ms_per_step, "higher_is_better": True,
+            # the default series (KV heads over the ranks) keeps the total work fixed as N grows, N = 1 included
+            "scaling": "strong" if args.shard == "kvhead" else "weak",
             "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world, args.shard),
