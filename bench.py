@@ -344,7 +344,7 @@ def agree_max(torch, value):
     import torch.distributed as dist
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
         return int(value)
-    t = torch.tensor([int(value)], device="cuda", dtype=torch.int64)
+    t = torch.tensor([int(value)], device="cuda" if dist.get_backend() == "nccl" else "cpu", dtype=torch.int64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return int(t.item())
 

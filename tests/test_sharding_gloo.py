@@ -114,3 +114,32 @@ def test_score_rows_of_disjoint_owners_combine_to_the_full_row_world2():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert all(r[1] and r[2] and r[3] == (4, 1000) for r in res)
+
+
+def _agree_worker(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        q.put((rank, bench.agree_max(torch, 140 + 3 * rank)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ranks_agree_on_the_replay_count_world2():
+    """A CUDA graph that holds collectives must be replayed equally often on every rank; the count each
+    rank derives from its own timing is replaced by the largest."""
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29650 + os.getpid() % 200
+    procs = [ctx.Process(target=_agree_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == {0: 143, 1: 143}
